@@ -1,0 +1,48 @@
+import json
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+GOLDEN = os.path.join(ROOT, "tests", "golden")
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run on the B200 box)")
+
+
+def pytest_collection_modifyitems(config, items):
+    if torch.cuda.is_available():
+        return
+    skip = pytest.mark.skip(reason="no CUDA device")
+    for item in items:
+        if "gpu" in item.keywords:
+            item.add_marker(skip)
+
+
+@pytest.fixture(scope="session")
+def golden_meta():
+    with open(os.path.join(GOLDEN, "meta.json")) as f:
+        return json.load(f)
+
+
+@pytest.fixture(scope="session")
+def golden():
+    def load(name):
+        return {k: v for k, v in np.load(os.path.join(GOLDEN, name + ".npz")).items()}
+
+    return load
+
+
+def rel_err(a: torch.Tensor, ref: torch.Tensor) -> float:
+    """max|a - ref| / rms(ref): the parity metric of the hot path."""
+    ref = ref.double()
+    rms = ref.pow(2).mean().sqrt().item()
+    if rms == 0.0:
+        rms = 1.0
+    return (a.double() - ref).abs().max().item() / rms
