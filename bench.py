@@ -1,0 +1,389 @@
+"""Throughput of the e3nn message-passing hot path on B200, one JSON line on stdout.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference]
+
+Workloads (synthetic, seeded; shapes and distributions of the BASELINE configurations):
+  conv_l2_15   fused gather -> SH(lmax 2) -> 'uvu' (15 paths, 64 channels) -> per-destination sum;
+               65,536 nodes, 2,097,152 edges, in-degree 32, uniform random sources, per-edge weights.
+  conv_l2_11   same graph, the 11-path layout (outputs restricted to the node irreps).
+  conv_l3_23   the 'uvu' l<=3 layout (23 paths, 64x0e+64x1o+64x2e+64x3o), same graph shape.
+  sh_l3        spherical harmonics lmax 3 on 4,194,304 edge vectors.
+
+A "step" is one pass of the hot path over the whole graph.  `value` is timed with CUDA events on the
+launching stream with every input resident in HBM (inputs are far larger than L2, nothing is cached
+between steps); `e2e` runs the same step through the public Python API from pinned host buffers,
+copies included.  With --gpus N (launched by torchrun) destination rows are split into N contiguous
+ranges, each rank owns the features of its own rows and all-gathers the source features every step
+(strong scaling; NCCL).  `--impl reference` times the CPU oracle (a restatement of e3nn's own
+arithmetic with torch CPU operators, all host threads) on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+WORKLOADS = {
+    # name: (layout, nodes, in-degree)
+    "conv_l2_15": ("cfg3_15", 65536, 32),
+    "conv_l2_11": ("cfg3_11", 65536, 32),
+    "conv_l3_23": ("cfg5_23", 65536, 32),
+}
+DEFAULT_WORKLOAD = "conv_l2_15"
+# DRAM bytes (read + write) of one conv launch measured with ncu on a 1/8-size graph and scaled
+# linearly in the edge count (profiles/); None until a capture exists for the layout.
+NCU_TRAFFIC_BYTES = {}
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx = float(parts[1])
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------- workload
+def make_graph(layout: str, nodes: int, degree: int, rank: int, world: int, device):
+    """This rank's shard: destination rows [n0, n1), their edges (already sorted by destination)."""
+    from e3nn_b200 import layouts
+
+    tp = layouts.bench_conv_tp(layout)
+    n0, n1 = nodes * rank // world, nodes * (rank + 1) // world
+    n_local = n1 - n0
+    e_local = n_local * degree
+    gen = torch.Generator(device=device).manual_seed(1234 + rank)
+    data = {
+        "tp": tp, "nodes": nodes, "n0": n0, "n_local": n_local, "e_local": e_local, "degree": degree,
+        "node_x_local": torch.randn(n_local, tp.irreps_in1.dim, device=device, generator=gen),
+        "vec": torch.nn.functional.normalize(torch.randn(e_local, 3, device=device, generator=gen), dim=-1),
+        "src": torch.randint(0, nodes, (e_local,), device=device, generator=gen),
+        "rowptr": torch.arange(0, e_local + 1, degree, device=device, dtype=torch.int64),
+        "w": torch.randn(e_local, tp.weight_numel, device=device, generator=gen),
+    }
+    return data
+
+
+def conv_step(d, node_x_full, world):
+    import e3nn_b200
+
+    if world > 1:
+        torch.distributed.all_gather_into_tensor(node_x_full, d["node_x_local"])
+    return e3nn_b200.conv_uvu(d["tp"], node_x_full, d["vec"], d["src"], d["rowptr"], d["w"],
+                              scale=d["degree"] ** -0.5, edge_attr_is_vector=True)
+
+
+def algorithmic_bytes_per_edge(tp, nodes, edges):
+    """Unique bytes the fused step must move: per edge weights + vector + int64 src/dst,
+    per node one read of its features and one write of its output row."""
+    per_edge = 4 * tp.weight_numel + 12 + 16
+    per_node = 4 * tp.irreps_in1.dim + 4 * tp.irreps_out.dim
+    return per_edge + per_node * nodes / edges
+
+
+def run_ours(args):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("bench.py --gpus N>1 must be launched with torch.distributed.run (one rank per GPU)")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        torch.distributed.init_process_group("nccl", device_id=device)
+
+    if args.workload == "sh_l3":
+        return run_sh(args, rank, world, device)
+    layout, nodes, degree = WORKLOADS[args.workload]
+    d = make_graph(layout, nodes, degree, rank, world, device)
+    tp = d["tp"]
+    node_x_full = torch.empty(nodes, tp.irreps_in1.dim, device=device) if world > 1 else d["node_x_local"]
+    edges_total = nodes * degree
+
+    def barrier():
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        out = conv_step(d, node_x_full, world)
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    kernel_ms = []
+    k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    start.record()
+    for _ in range(args.steps):
+        out = conv_step(d, node_x_full, world)
+    stop.record()
+    barrier()
+    ms_total = start.elapsed_time(stop)
+    clocks = sampler.stop() if rank == 0 else None
+    # dominant kernel alone (same launch, events directly around it), for the roofline
+    for _ in range(max(3, min(args.steps, 10))):
+        k0.record()
+        out = conv_step(d, node_x_full, 1)
+        k1.record()
+        torch.cuda.synchronize()
+        kernel_ms.append(k0.elapsed_time(k1))
+    t = torch.tensor([ms_total], device=device)
+    if world > 1:
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+    ms_step = t.item() / args.steps
+
+    # ---- end to end from pinned host memory through the public API
+    e2e_steps = max(1, min(args.steps, 3))
+    host = {k: d[k].cpu().pin_memory() for k in ("node_x_local", "vec", "src", "rowptr", "w")}
+    out_host = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+    h2d = sum(v.numel() * v.element_size() for v in host.values())
+    d2h = out_host.numel() * out_host.element_size()
+
+    def e2e_step():
+        import e3nn_b200
+
+        dev = {k: v.to(device, non_blocking=True) for k, v in host.items()}
+        nx = dev["node_x_local"]
+        if world > 1:
+            torch.distributed.all_gather_into_tensor(node_x_full, nx)
+            nx = node_x_full
+        o = e3nn_b200.conv_uvu(tp, nx, dev["vec"], dev["src"], dev["rowptr"], dev["w"], scale=degree ** -0.5,
+                               edge_attr_is_vector=True)
+        out_host.copy_(o, non_blocking=True)
+
+    del d["w"], d["vec"], d["src"]
+    torch.cuda.empty_cache()
+    e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    start.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    stop.record()
+    barrier()
+    t = torch.tensor([start.elapsed_time(stop)], device=device)
+    if world > 1:
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+    e2e_ms = t.item() / e2e_steps
+
+    if rank != 0:
+        if world > 1:
+            torch.distributed.destroy_process_group()
+        return
+    peak, peak_kind = measured_peaks()
+    kernel_ms.sort()
+    k_ms = kernel_ms[len(kernel_ms) // 2]
+    bytes_per_launch = algorithmic_bytes_per_edge(tp, nodes, edges_total) * d["e_local"]
+    achieved = bytes_per_launch / (k_ms * 1e-3) / 1e9
+    traffic = NCU_TRAFFIC_BYTES.get(args.workload)
+    line = {
+        "metric": "TP edges/sec (fused SH + uvu + scatter, fp32)",
+        "value": edges_total / (ms_step * 1e-3),
+        "unit": "edges/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {
+            "workload": args.workload, "layout": f"{tp.irreps_in1} x {tp.irreps_in2} -> {len(tp.instructions)} uvu paths",
+            "nodes": nodes, "edges": edges_total, "in_degree": degree, "weight_numel": tp.weight_numel,
+            "out_dim": tp.irreps_out.dim, "l2": "inputs (%.1f GB/step) far larger than the 126 MB L2" % (bytes_per_launch / 1e9),
+            "parallelism": f"dst-range x{world}" + (" + allgather(node features)" if world > 1 else ""),
+        },
+        "roofline": {
+            "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+            "traffic": traffic, "peak_kind": f"of {peak_kind}", "kernel": "conv_fwd_kernel<1>",
+            "kernel_ms": k_ms, "algorithmic_bytes_per_edge": algorithmic_bytes_per_edge(tp, nodes, edges_total),
+        },
+        "e2e": {"value": edges_total / (e2e_ms * 1e-3), "unit": "edges/s", "h2d_bytes_per_step": h2d * world,
+                "d2h_bytes_per_step": d2h * world, "steps": e2e_steps},
+        "gpu_launches": args.steps * 1,
+        "clocks": clocks,
+    }
+    if world == 1:
+        line["cpu_baseline"] = cpu_baseline(args.workload, budget_s=12.0)
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        torch.distributed.destroy_process_group()
+
+
+def run_sh(args, rank, world, device):
+    from e3nn_b200 import o3
+
+    n_total = 4_194_304
+    n = n_total // world
+    gen = torch.Generator(device=device).manual_seed(rank)
+    vec = torch.randn(n, 3, device=device, generator=gen)
+    sh = o3.SphericalHarmonics("0e+1o+2e+3o", True, "component")
+    for _ in range(args.warmup):
+        out = sh(vec)
+    torch.cuda.synchronize()
+    flush = torch.empty(64 * 1024 * 1024, device=device)  # 256 MB > L2
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    times = []
+    for _ in range(args.steps):
+        flush.zero_()
+        start.record()
+        out = sh(vec)
+        stop.record()
+        torch.cuda.synchronize()
+        times.append(start.elapsed_time(stop))
+    times.sort()
+    ms = times[len(times) // 2]
+    if rank != 0:
+        return
+    peak, peak_kind = measured_peaks()
+    achieved = 76.0 * n / (ms * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": "SH edges/sec (lmax 3, fp32)", "value": n_total / (ms * 1e-3), "unit": "edges/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "sh_l3", "edges": n_total, "l2": "256 MB buffer written between timed launches"},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": None, "peak_kind": f"of {peak_kind}", "kernel": "sh_fwd_kernel<3>"},
+        "gpu_launches": args.steps,
+    }), flush=True)
+
+
+# ------------------------------------------------------------------------------------------- CPU arm
+def cpu_conv_sample(workload: str, sample_edges: int, threads: int):
+    """One pass of the oracle over a sample of the workload: returns seconds."""
+    from oracle import e3nn_oracle as orc
+
+    layout, nodes, degree = WORKLOADS[workload]
+    from e3nn_b200 import layouts
+
+    node, edge, keep = layouts.BENCH_CONV_LAYOUTS[layout]
+    keep_lp = [(l, p) for _, l, p in orc.parse_irreps(keep)]
+    mid, ins = orc.conv_uvu_layout(node, edge, keep_lp)
+    lmax = max(l for _, l, _ in orc.parse_irreps(edge))
+    torch.set_num_threads(threads)
+    gen = torch.Generator().manual_seed(0)
+    n_dst = sample_edges // degree
+    node_x = torch.randn(nodes, orc.irreps_dim(orc.parse_irreps(node)), generator=gen)
+    vec = torch.randn(sample_edges, 3, generator=gen)
+    src = torch.randint(0, nodes, (sample_edges,), generator=gen)
+    dst = torch.arange(sample_edges) // degree
+    wn = sum(m for m, _, _ in orc.parse_irreps(mid))
+    w = torch.randn(sample_edges, wn, generator=gen)
+    t0 = time.perf_counter()
+    orc.conv_uvu(node, edge, mid, ins, node_x, vec, src, dst, w, n_dst, list(range(lmax + 1)), scale=degree ** -0.5,
+                 chunk=16384)
+    return time.perf_counter() - t0
+
+
+def cpu_baseline(workload: str, budget_s: float):
+    threads = os.cpu_count() or 1
+    sample = 16384
+    t = cpu_conv_sample(workload, sample, threads)  # warm-up and rate estimate
+    sample = int(min(1 << 20, max(16384, sample * budget_s / max(t, 1e-3)))) // 16384 * 16384
+    t = cpu_conv_sample(workload, sample, threads)
+    return {"value": sample / t, "unit": "edges/s", "cores": threads, "kind": "port",
+            "sample": f"{sample} edges of the same graph (fp32 torch-CPU oracle, chunks of 16384 edges), {t:.1f} s"}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    workload = args.workload if args.workload in WORKLOADS else DEFAULT_WORKLOAD
+    layout, nodes, degree = WORKLOADS[workload]
+    threads = os.cpu_count() or 1
+    sample = 65536
+    for _ in range(min(args.warmup, 1)):
+        cpu_conv_sample(workload, 16384, threads)
+    times = [cpu_conv_sample(workload, sample, threads) for _ in range(max(1, min(args.steps, 5)))]
+    t = sum(times) / len(times)
+    value = sample / t
+    print(json.dumps({
+        "impl": "reference", "metric": "TP edges/sec (fused SH + uvu + scatter, fp32)", "value": value,
+        "unit": "edges/s", "n_gpus": args.gpus, "steps": len(times), "warmup": min(args.warmup, 1),
+        "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": workload, "nodes": nodes, "edges": nodes * degree, "in_degree": degree},
+        "cpu_baseline": {"value": value, "unit": "edges/s", "cores": threads, "kind": "port",
+                         "sample": f"{sample} edges per step of the same graph (fp32 torch-CPU oracle)"},
+        "e2e": {"value": value, "unit": "edges/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS) + ["sh_l3"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,219 @@
+// fp32 CUDA-core evaluation of weight-shared contractions: 'uvw' tensor-product paths and the
+// per-irrep Linear.  Table driven (no per-layout code): the host describes the contraction as a
+// "dense plan" and this kernel evaluates, per output irrep ("group"),
+//
+//     out[z, w, k] = sum_K  A[z, k, K] * W[wbase(K) + w * wstride]
+//     A[z, k, K]   = sum_{(i,j,c) in cg(path(K), k)}  c * x1[z, x1off(K) + i] * x2[z, x2off(K) + j]
+//
+// where K runs over the (path, u, v) triples feeding that output irrep.  A block stages the A
+// rows of a tile of z in shared memory (phase 1) and then runs a register-tiled FFMA product
+// against W, which stays L2-resident (phase 2).  This is the fp32-accurate mode (<= 1e-5 x RMS);
+// the tensor-core mode lives in uvw_tc.cu.
+//
+// Plan layout (int32 words, floats bit-cast), built by e3nn_b200/o3/_dense_plan.py:
+//   [0] magic 0x65336250  [1] d1  [2] d2  [3] dout  [4] n_groups  [5] n_paths  [6] total words
+//   [7] off_groups [8] off_kent [9] off_pathk [10] off_cg   [11] max K over groups
+//   groups  : n_groups x 6 : out_off, mul_out, dim3, K, kent_start, w_stride
+//   kent    : sum K   x 4 : path, x1off, x2off (-1: factor 1), wbase
+//   pathk   : per path, per k (path base in word [off_pathk + path]) -> (cg_start, cg_count) pairs
+//   cg      : triples (i, j, coef)
+#include "common.cuh"
+
+namespace e3b {
+
+constexpr int kDenseMagic = 0x65336250;
+constexpr int kDenseThreads = 256;
+constexpr int kTM = 8;   // rows per thread
+constexpr int kTN = 4;   // output channels per thread
+constexpr int kRowsPerPass = (kDenseThreads / 32) * kTM;  // 64
+constexpr int kColsPerPass = 32 * kTN;                    // 128
+
+struct DenseGroup { int out_off, mul_out, dim3, K, kent_start, w_stride; };
+
+template <bool VEC4>
+__global__ void __launch_bounds__(kDenseThreads) dense_fwd_kernel(const int32_t* __restrict__ plan,
+        const float* __restrict__ x1, const float* __restrict__ x2, const float* __restrict__ W,
+        float* __restrict__ out, int64_t Z, int group, int rows_z /* z per tile */, int accumulate,
+        int64_t w_row_stride /* 0: shared weights, else floats between the weight rows of consecutive z */) {
+    extern __shared__ float smem[];
+    const int d1 = plan[1], d2 = plan[2], dout = plan[3];
+    const int32_t* gp = plan + plan[7] + 6 * group;
+    const DenseGroup g{gp[0], gp[1], gp[2], gp[3], gp[4], gp[5]};
+    const int32_t* kent = plan + plan[8] + 4 * g.kent_start;
+    const int32_t* pathk_dir = plan + plan[9];
+    const int32_t* cg = plan + plan[10];
+
+    const int RT = rows_z * g.dim3;                 // rows of the A tile (<= kRowsPerPass)
+    float* sA = smem;                               // [K][kRowsPerPass]
+    int* sW = reinterpret_cast<int*>(smem + static_cast<size_t>(g.K) * kRowsPerPass);  // [K] wbase
+
+    const int tid = threadIdx.x;
+    for (int kk = tid; kk < g.K; kk += kDenseThreads) sW[kk] = kent[4 * kk + 3];
+
+    const int64_t tiles = (Z + rows_z - 1) / rows_z;
+    for (int64_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+        const int64_t z0 = tile * rows_z;
+        __syncthreads();
+        // ---- phase 1: A tile.  element index = kk * RT + r, r = zl * dim3 + k
+        const int total = g.K * RT;
+        for (int idx = tid; idx < total; idx += kDenseThreads) {
+            const int kk = idx / RT, r = idx - kk * RT;
+            const int zl = r / g.dim3, k = r - zl * g.dim3;
+            const int64_t z = z0 + zl;
+            float a = 0.0f;
+            if (z < Z) {
+                const int path = kent[4 * kk], x1off = kent[4 * kk + 1], x2off = kent[4 * kk + 2];
+                const int32_t* pk = plan + pathk_dir[path] + 2 * k;
+                const int cstart = pk[0], ccount = pk[1];
+                const float* xr = x1 + z * d1 + x1off;
+                const float* yr = x2off >= 0 ? x2 + z * d2 + x2off : nullptr;
+                for (int c = 0; c < ccount; ++c) {
+                    const int32_t* t = cg + 3 * (cstart + c);
+                    const float coef = __int_as_float(t[2]);
+                    a = fmaf(coef * xr[t[0]], yr ? yr[t[1]] : 1.0f, a);
+                }
+            }
+            sA[kk * kRowsPerPass + r] = a;
+        }
+        // rows RT..kRowsPerPass of the tile are never read by live outputs
+        __syncthreads();
+        // ---- phase 2: out rows x channels, passes of 64 rows (one pass: RT <= 64) x 128 channels
+        const int tx = tid & 31, ty = tid >> 5;
+        const int r0 = ty * kTM;
+        for (int c0 = 0; c0 < g.mul_out; c0 += kColsPerPass) {
+            const int w0 = c0 + tx * kTN;
+            float acc[kTM][kTN];
+#pragma unroll
+            for (int i = 0; i < kTM; ++i)
+#pragma unroll
+                for (int j = 0; j < kTN; ++j) acc[i][j] = 0.0f;
+            if (r0 < RT && w0 < g.mul_out && w_row_stride != 0) {
+                // per-row weights: every row of the tile reads its own weight vector
+                int64_t wrow[kTM];
+#pragma unroll
+                for (int i = 0; i < kTM; ++i) {
+                    const int64_t z = z0 + (r0 + i) / g.dim3;
+                    wrow[i] = (z < Z ? z : 0) * w_row_stride;
+                }
+                for (int kk = 0; kk < g.K; ++kk) {
+                    const float4 a0 = *reinterpret_cast<const float4*>(sA + kk * kRowsPerPass + r0);
+                    const float4 a1 = *reinterpret_cast<const float4*>(sA + kk * kRowsPerPass + r0 + 4);
+                    const float a[kTM] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+#pragma unroll
+                    for (int i = 0; i < kTM; ++i) {
+                        if (r0 + i >= RT) continue;
+                        const float* wp = W + wrow[i] + sW[kk];
+#pragma unroll
+                        for (int j = 0; j < kTN; ++j)
+                            if (w0 + j < g.mul_out)
+                                acc[i][j] = fmaf(a[i], __ldg(wp + static_cast<int64_t>(w0 + j) * g.w_stride), acc[i][j]);
+                    }
+                }
+            } else if (r0 < RT && w0 < g.mul_out) {
+                for (int kk = 0; kk < g.K; ++kk) {
+                    const float4 a0 = *reinterpret_cast<const float4*>(sA + kk * kRowsPerPass + r0);
+                    const float4 a1 = *reinterpret_cast<const float4*>(sA + kk * kRowsPerPass + r0 + 4);
+                    const float a[kTM] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+                    float wv[kTN];
+                    const float* wp = W + sW[kk];
+                    if (VEC4) {
+                        const float4 t = __ldg(reinterpret_cast<const float4*>(wp + w0));
+                        wv[0] = t.x; wv[1] = t.y; wv[2] = t.z; wv[3] = t.w;
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < kTN; ++j)
+                            wv[j] = (w0 + j < g.mul_out) ? __ldg(wp + static_cast<int64_t>(w0 + j) * g.w_stride) : 0.0f;
+                    }
+#pragma unroll
+                    for (int i = 0; i < kTM; ++i)
+#pragma unroll
+                        for (int j = 0; j < kTN; ++j) acc[i][j] = fmaf(a[i], wv[j], acc[i][j]);
+                }
+            }
+            if (r0 < RT && w0 < g.mul_out) {
+#pragma unroll
+                for (int i = 0; i < kTM; ++i) {
+                    const int r = r0 + i;
+                    if (r >= RT) continue;
+                    const int zl = r / g.dim3, k = r - zl * g.dim3;
+                    const int64_t z = z0 + zl;
+                    if (z >= Z) continue;
+                    float* orow = out + z * dout + g.out_off;
+#pragma unroll
+                    for (int j = 0; j < kTN; ++j) {
+                        if (w0 + j < g.mul_out) {
+                            float* p = orow + (w0 + j) * g.dim3 + k;
+                            *p = accumulate ? *p + acc[i][j] : acc[i][j];
+                        }
+                    }
+                }
+            }
+        }
+    }
+}
+
+// out[z, c] (+)= bias[c] over listed column ranges / zero fill of untouched columns.
+__global__ void dense_fill_kernel(float* __restrict__ out, int64_t Z, int dout, int col0, int ncol,
+                                  const float* __restrict__ bias /* may be null: zero fill */, int add) {
+    const int64_t total = Z * ncol;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const int64_t z = i / ncol;
+        const int c = static_cast<int>(i - z * ncol);
+        float* p = out + z * dout + col0 + c;
+        const float v = bias ? bias[c] : 0.0f;
+        *p = add ? *p + v : v;
+    }
+}
+
+}  // namespace e3b
+
+extern "C" int e3b_dense_fwd(const int32_t* plan_host, const int32_t* plan_dev, const float* x1, const float* x2,
+                             const float* weight, int64_t weight_row_stride, float* out, int64_t num_rows,
+                             int accumulate, void* stream) {
+    using namespace e3b;
+    if (!plan_host || plan_host[0] != kDenseMagic) return fail(E3B_ERR_ARG, "dense_fwd: bad plan");
+    if (num_rows < 0) return fail(E3B_ERR_ARG, "dense_fwd: negative row count");
+    if (num_rows == 0) return E3B_OK;
+    if (!plan_dev || !x1 || !out || !weight) return fail(E3B_ERR_ARG, "dense_fwd: null pointer");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int n_groups = plan_host[4];
+    const int32_t* groups = plan_host + plan_host[7];
+    const int32_t* kent_all = plan_host + plan_host[8];
+    for (int g = 0; g < n_groups; ++g) {
+        const int mul_out = groups[6 * g + 1], dim3 = groups[6 * g + 2], K = groups[6 * g + 3];
+        const int kent_start = groups[6 * g + 4], w_stride = groups[6 * g + 5];
+        if (K == 0 || mul_out == 0) continue;
+        if (dim3 > kRowsPerPass) return fail(E3B_ERR_UNSUPPORTED, "dense_fwd: irrep dimension %d too large", dim3);
+        const int rows_z = kRowsPerPass / dim3;
+        const size_t smem = sizeof(float) * static_cast<size_t>(K) * kRowsPerPass + sizeof(int) * static_cast<size_t>(K);
+        if (smem > 200 * 1024) return fail(E3B_ERR_UNSUPPORTED, "dense_fwd: contraction length %d too large", K);
+        bool vec4 = (weight_row_stride == 0) && (w_stride == 1) && (mul_out % 4 == 0) && (reinterpret_cast<uintptr_t>(weight) % 16 == 0);
+        if (vec4)
+            for (int kk = 0; kk < K && vec4; ++kk) vec4 = (kent_all[4 * (kent_start + kk) + 3] % 4) == 0;
+        const int64_t tiles = ceil_div(num_rows, rows_z);
+        const unsigned grid = static_cast<unsigned>(std::min<int64_t>(tiles, kNumSMs * 4));
+        if (vec4) {
+            E3B_CUDA_TRY(cudaFuncSetAttribute(dense_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            dense_fwd_kernel<true><<<grid, kDenseThreads, smem, s>>>(plan_dev, x1, x2, weight, out, num_rows, g, rows_z, accumulate, weight_row_stride);
+        } else {
+            E3B_CUDA_TRY(cudaFuncSetAttribute(dense_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            dense_fwd_kernel<false><<<grid, kDenseThreads, smem, s>>>(plan_dev, x1, x2, weight, out, num_rows, g, rows_z, accumulate, weight_row_stride);
+        }
+        int rc = check_launch("e3b_dense_fwd");
+        if (rc != E3B_OK) return rc;
+    }
+    return E3B_OK;
+}
+
+extern "C" int e3b_fill_columns(float* out, int64_t num_rows, int row_stride, int col0, int ncol, const float* bias,
+                                int add, void* stream) {
+    using namespace e3b;
+    if (num_rows < 0 || ncol < 0 || col0 < 0 || col0 + ncol > row_stride) return fail(E3B_ERR_ARG, "fill_columns: bad range");
+    if (num_rows == 0 || ncol == 0) return E3B_OK;
+    if (!out) return fail(E3B_ERR_ARG, "fill_columns: null pointer");
+    const int64_t total = num_rows * ncol;
+    const unsigned grid = static_cast<unsigned>(std::min<int64_t>(ceil_div(total, 256), kNumSMs * 16));
+    dense_fill_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(out, num_rows, row_stride, col0, ncol, bias, add);
+    return check_launch("e3b_fill_columns");
+}

@@ -1,0 +1,205 @@
+"""Drop-in ``Linear``: per-irrep channel mixing (``e3nn/o3/_linear.py:28-345``).
+
+Same constructor, attributes (``weight``, ``bias``, ``weight_numel``, ``bias_numel``,
+``output_mask``, ``instructions``), weight layout and error types as the reference.  The
+contraction runs in ``e3b_dense_fwd`` (fp32); the gradient w.r.t. the features reuses the same
+kernel with a transposed plan.  ``f_in`` / ``f_out`` and per-row weights are not implemented.
+"""
+from __future__ import annotations
+
+from math import prod
+from typing import List, NamedTuple, Optional, Tuple, Union
+
+import torch
+
+from .. import _lib
+from ._dense_plan import linear_plan
+from ._irreps import Irreps
+from ._spec import LinearInstruction, normalize_linear_instructions
+
+
+class LinearSlices(NamedTuple):
+    slice: slice
+    shape: Tuple[int, int]
+
+
+class _LinearFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, bias, lin):
+        Z = x.shape[0]
+        dev = x.device
+        out = torch.empty(Z, lin.irreps_out.dim, dtype=torch.float32, device=dev)
+        core = _lib.core()
+        with torch.cuda.device(dev):
+            s = _lib.stream_ptr()
+            for off, n in lin._unwritten:
+                _lib.check(core.e3b_fill_columns(_lib._ptr(out), Z, out.shape[1], off, n, None, 0, s), "e3b_fill_columns")
+            if lin.weight_numel > 0:
+                plan_dev = lin._plan_on(dev, False)
+                rc = core.e3b_dense_fwd(lin._plan_host.ctypes.data, _lib._ptr(plan_dev), _lib._ptr(x), None,
+                                        _lib._ptr(w), 0, _lib._ptr(out), Z, 0, s)
+                _lib.check(rc, "e3b_dense_fwd")
+            boff = 0
+            for off, n, written in lin._bias_ranges:
+                rc = core.e3b_fill_columns(_lib._ptr(out), Z, out.shape[1], off, n,
+                                           bias.data_ptr() + 4 * boff, int(written), s)
+                _lib.check(rc, "e3b_fill_columns")
+                boff += n
+        ctx.save_for_backward(w)
+        ctx.lin = lin
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        (w,) = ctx.saved_tensors
+        lin = ctx.lin
+        if ctx.needs_input_grad[1] or ctx.needs_input_grad[2]:
+            raise NotImplementedError("gradients w.r.t. Linear weights / biases are not implemented in e3nn_b200")
+        grad_out = grad_out.contiguous()
+        Z, dev = grad_out.shape[0], grad_out.device
+        gx = torch.zeros(Z, lin.irreps_in.dim, dtype=torch.float32, device=dev)
+        if lin.weight_numel > 0:
+            with torch.cuda.device(dev):
+                rc = _lib.core().e3b_dense_fwd(lin._plan_t_host.ctypes.data, _lib._ptr(lin._plan_on(dev, True)),
+                                               _lib._ptr(grad_out), None, _lib._ptr(w), 0, _lib._ptr(gx), Z, 0,
+                                               _lib.stream_ptr())
+            _lib.check(rc, "e3b_dense_fwd (transposed)")
+        return gx, None, None, None
+
+
+class Linear(torch.nn.Module):
+    def __init__(
+        self,
+        irreps_in,
+        irreps_out,
+        *,
+        f_in: Optional[int] = None,
+        f_out: Optional[int] = None,
+        internal_weights: Optional[bool] = None,
+        shared_weights: Optional[bool] = None,
+        instructions: Optional[List[Tuple[int, int]]] = None,
+        biases: Union[bool, List[bool]] = False,
+        path_normalization: str = "element",
+        _optimize_einsums: Optional[bool] = None,
+    ) -> None:
+        super().__init__()
+        if f_in is not None or f_out is not None:
+            raise NotImplementedError("Linear(f_in=..., f_out=...) is not implemented by e3nn_b200")
+        irreps_in, irreps_out = Irreps(irreps_in), Irreps(irreps_out)
+        self.instructions = normalize_linear_instructions(irreps_in, irreps_out, instructions, biases, None,
+                                                          path_normalization)
+        if shared_weights is False and internal_weights is None:
+            internal_weights = False
+        if shared_weights is None:
+            shared_weights = True
+        if internal_weights is None:
+            internal_weights = True
+        assert shared_weights or not internal_weights
+        if not shared_weights:
+            raise NotImplementedError("Linear with per-row weights is not implemented by e3nn_b200")
+        self.internal_weights, self.shared_weights = internal_weights, shared_weights
+        self.irreps_in, self.irreps_out = irreps_in, irreps_out
+
+        live = [ins for ins in self.instructions if 0 not in ins.path_shape]
+        self.weight_numel = sum(prod(ins.path_shape) for ins in live if ins.i_in != -1)
+        self.bias_numel = sum(prod(ins.path_shape) for ins in live if ins.i_in == -1)
+        # the flat weight vector skips empty instructions, exactly as the reference's code generator does
+        packed = [ins if 0 not in ins.path_shape else ins._replace(path_shape=(0, 0)) for ins in self.instructions]
+        self._plan_host, written = linear_plan(irreps_in, irreps_out, packed, transpose=False)
+        try:
+            self._plan_t_host, _ = linear_plan(irreps_in, irreps_out, packed, transpose=True)
+        except NotImplementedError:
+            self._plan_t_host = None
+        self._plan_dev = {}
+        offs = irreps_out.offsets()
+        bias_out = [ins.i_out for ins in self.instructions if ins.i_in == -1 and 0 not in ins.path_shape]
+        self._unwritten = [
+            (offs[i], mul * ir.dim) for i, (mul, ir) in enumerate(irreps_out)
+            if i not in written and i not in bias_out and mul * ir.dim > 0
+        ]
+        self._bias_ranges = [(offs[i], irreps_out[i].dim, i in written) for i in bias_out]
+
+        if internal_weights and self.weight_numel > 0:
+            self.weight = torch.nn.Parameter(torch.randn(self.weight_numel))
+        else:
+            self.register_buffer("weight", torch.Tensor())
+        if internal_weights and self.bias_numel > 0:
+            self.bias = torch.nn.Parameter(torch.zeros(self.bias_numel))
+        else:
+            self.register_buffer("bias", torch.Tensor())
+
+        if irreps_out.dim > 0:
+            output_mask = torch.cat(
+                [
+                    torch.ones(mul_ir.dim)
+                    if any((ins.i_out == i_out) and (0 not in ins.path_shape) for ins in self.instructions)
+                    else torch.zeros(mul_ir.dim)
+                    for i_out, mul_ir in enumerate(irreps_out)
+                ]
+            )
+        else:
+            output_mask = torch.ones(0)
+        self.register_buffer("output_mask", output_mask)
+
+        self.weight_index_slices = []
+        for i, ins in enumerate(self.instructions):
+            offset = sum(prod(p.path_shape) for p in self.instructions[:i])
+            self.weight_index_slices.append(LinearSlices(slice(offset, offset + prod(ins.path_shape), None), ins.path_shape))
+
+    def __repr__(self) -> str:
+        return f"{self.__class__.__name__}({self.irreps_in} -> {self.irreps_out} | {self.weight_numel} weights)"
+
+    def _plan_on(self, device, transposed: bool) -> torch.Tensor:
+        key = (str(device), transposed)
+        if key not in self._plan_dev:
+            host = self._plan_t_host if transposed else self._plan_host
+            if host is None:
+                raise NotImplementedError("gradient of this Linear layout w.r.t. its input is not implemented")
+            self._plan_dev[key] = torch.from_numpy(host).to(device)
+        return self._plan_dev[key]
+
+    def forward(self, features, weight: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None):
+        if weight is None:
+            if self.weight_numel > 0 and not self.internal_weights:
+                raise RuntimeError("Weights must be provided when internal_weights = False")
+            weight = self.weight
+        if bias is None:
+            if self.bias_numel > 0 and not self.internal_weights:
+                raise RuntimeError("Biases must be provided when internal_weights = False")
+            bias = self.bias
+        _lib.require_cuda(features)
+        if features.dtype != torch.float32:
+            raise TypeError(f"e3nn_b200 Linear is fp32 only, got {features.dtype}")
+        torch._assert(features.shape[-1] == self.irreps_in.dim, "Incorrect last dimension for features")
+        lead = features.shape[:-1]
+        x = features.reshape(-1, self.irreps_in.dim).contiguous()
+        if x.shape[0] == 0 or self.irreps_out.dim == 0:
+            return features.new_zeros(*lead, self.irreps_out.dim)
+        w = weight.reshape(-1).contiguous() if weight.numel() > 0 else x.new_zeros(1)
+        b = bias.reshape(-1).contiguous() if bias.numel() > 0 else x.new_zeros(1)
+        out = _LinearFunction.apply(x, w, b, self)
+        return out.reshape(*lead, self.irreps_out.dim)
+
+    def weight_view_for_instruction(self, instruction: int, weight: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if weight is None:
+            assert self.internal_weights, "Weights must be provided when internal_weights = False"
+            weight = self.weight
+        batchshape = weight.shape[:-1]
+        offset = sum(prod(ins.path_shape) for ins in self.instructions[:instruction])
+        ins = self.instructions[instruction]
+        return weight.narrow(-1, offset, prod(ins.path_shape)).view(batchshape + ins.path_shape)
+
+    def weight_views(self, weight: Optional[torch.Tensor] = None, yield_instruction: bool = False):
+        if weight is None:
+            assert self.internal_weights, "Weights must be provided when internal_weights = False"
+            weight = self.weight
+        batchshape = weight.shape[:-1]
+        offset = 0
+        for ins_i, ins in enumerate(self.instructions):
+            flatsize = prod(ins.path_shape)
+            this_weight = weight.narrow(-1, offset, flatsize).view(batchshape + ins.path_shape)
+            offset += flatsize
+            if yield_instruction:
+                yield ins_i, ins, this_weight
+            else:
+                yield this_weight

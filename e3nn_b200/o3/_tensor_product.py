@@ -1,0 +1,322 @@
+"""Drop-in ``TensorProduct`` / ``FullyConnectedTensorProduct`` for the 'uvu' and 'uvw' modes.
+
+Constructor arguments, attributes (``irreps_in1/2/out``, ``instructions``, ``weight_numel``,
+``internal_weights``, ``shared_weights``, ``weight``, ``output_mask``), weight layout, weight views,
+broadcasting rules and error types follow ``e3nn/o3/_tensor_product/_tensor_product.py:23-609``
+and ``_sub.py:10-68``.  The arithmetic runs in CUDA kernels only:
+
+* 'uvu' paths: a per-layout generated module (``e3nn_b200/codegen/uvu.py``);
+* 'uvw' paths: ``e3b_dense_fwd`` (fp32) or the tcgen05 tensor-core kernel (``math_mode='tf32'``).
+
+Connection modes other than 'uvu' and 'uvw' raise ``NotImplementedError``.
+"""
+from __future__ import annotations
+
+from math import prod
+from typing import Iterator, List, Optional, Union
+
+import numpy as np
+import torch
+
+from .. import _lib
+from ._dense_plan import uvw_plan
+from ._irreps import Irreps
+from ._spec import SUPPORTED_MODES, Instruction, TPSpec, normalize_tp_instructions
+
+
+class _UvuFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x1, x2, w, mod, w_shared: bool):
+        Z = x1.shape[0]
+        out = torch.empty(Z, mod.dout, dtype=torch.float32, device=x1.device)
+        with torch.cuda.device(x1.device):
+            rc = mod.lib.e3b_uvu_fwd(_lib._ptr(x1), _lib._ptr(x2), _lib._ptr(w), _lib._ptr(out), Z, int(w_shared),
+                                     _lib.stream_ptr())
+        mod.check(rc, "e3b_uvu_fwd")
+        ctx.save_for_backward(x1, x2, w)
+        ctx.mod, ctx.w_shared = mod, w_shared
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        x1, x2, w = ctx.saved_tensors
+        mod = ctx.mod
+        grad_out = grad_out.contiguous()
+        g1, g2, gw = torch.empty_like(x1), torch.empty_like(x2), torch.empty_like(w)
+        with torch.cuda.device(x1.device):
+            rc = mod.lib.e3b_uvu_bwd(_lib._ptr(x1), _lib._ptr(x2), _lib._ptr(w), _lib._ptr(grad_out), _lib._ptr(g1),
+                                     _lib._ptr(g2), _lib._ptr(gw), x1.shape[0], int(ctx.w_shared), _lib.stream_ptr())
+        mod.check(rc, "e3b_uvu_bwd")
+        return g1, g2, gw, None, None
+
+
+class _DenseFunction(torch.autograd.Function):
+    """Forward of the weight-shared 'uvw' paths (no gradient kernels yet)."""
+
+    @staticmethod
+    def forward(ctx, x1, x2, w, plan_host, plan_dev, out, accumulate: bool):
+        w_row_stride = w.shape[1] if w.dim() == 2 else 0
+        with torch.cuda.device(x1.device):
+            rc = _lib.core().e3b_dense_fwd(plan_host.ctypes.data, _lib._ptr(plan_dev), _lib._ptr(x1), _lib._ptr(x2),
+                                           _lib._ptr(w), w_row_stride, _lib._ptr(out), x1.shape[0], int(accumulate),
+                                           _lib.stream_ptr())
+        _lib.check(rc, "e3b_dense_fwd")
+        ctx.mark_dirty(out)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        raise NotImplementedError("gradients of 'uvw' tensor products are not implemented in e3nn_b200")
+
+
+class TensorProduct(torch.nn.Module):
+    """Tensor product with parametrised paths ('uvu' and 'uvw' connection modes)."""
+
+    def __init__(
+        self,
+        irreps_in1,
+        irreps_in2,
+        irreps_out,
+        instructions: List[tuple],
+        in1_var=None,
+        in2_var=None,
+        out_var=None,
+        irrep_normalization: str = None,
+        path_normalization: str = None,
+        internal_weights: Optional[bool] = None,
+        shared_weights: Optional[bool] = None,
+        compile_left_right: bool = True,
+        compile_right: bool = False,
+        normalization=None,
+        _specialized_code: Optional[bool] = None,
+        _optimize_einsums: Optional[bool] = None,
+        math_mode: str = "fp32",
+    ) -> None:
+        super().__init__()
+        if normalization is not None:
+            irrep_normalization = normalization
+        if irrep_normalization is None:
+            irrep_normalization = "component"
+        if path_normalization is None:
+            path_normalization = "element"
+        if compile_right:
+            raise NotImplementedError("TensorProduct.right() is not part of the accelerated path")
+        assert math_mode in ("fp32", "tf32")
+        self.math_mode = math_mode
+
+        self.irreps_in1 = Irreps(irreps_in1)
+        self.irreps_in2 = Irreps(irreps_in2)
+        self.irreps_out = Irreps(irreps_out)
+        self.instructions = normalize_tp_instructions(
+            self.irreps_in1, self.irreps_in2, self.irreps_out, instructions, in1_var, in2_var, out_var,
+            irrep_normalization, path_normalization,
+        )
+        for ins in self.instructions:
+            if ins.connection_mode not in SUPPORTED_MODES:
+                raise NotImplementedError(
+                    f"connection mode '{ins.connection_mode}' is not implemented by e3nn_b200 (only 'uvu' and 'uvw')"
+                )
+            if ins.connection_mode == "uvu":
+                assert self.irreps_in1[ins.i_in1].mul == self.irreps_out[ins.i_out].mul
+            if ins.connection_mode == "uvw":
+                assert ins.has_weight
+
+        self._in1_dim, self._in2_dim = self.irreps_in1.dim, self.irreps_in2.dim
+
+        if shared_weights is False and internal_weights is None:
+            internal_weights = False
+        if shared_weights is None:
+            shared_weights = True
+        if internal_weights is None:
+            internal_weights = shared_weights and any(i.has_weight for i in self.instructions)
+        assert shared_weights or not internal_weights
+        self.internal_weights = internal_weights
+        self.shared_weights = shared_weights
+
+        self.weight_numel = sum(prod(ins.path_shape) for ins in self.instructions if ins.has_weight)
+        if internal_weights and self.weight_numel > 0:
+            assert self.shared_weights, "Having internal weights impose shared weights"
+            self.weight = torch.nn.Parameter(torch.randn(self.weight_numel))
+        else:
+            self.register_buffer("weight", torch.Tensor())
+
+        if self.irreps_out.dim > 0:
+            output_mask = torch.cat(
+                [
+                    torch.ones(mul * ir.dim)
+                    if any(
+                        (ins.i_out == i_out) and (ins.path_weight != 0) and (0 not in ins.path_shape)
+                        for ins in self.instructions
+                    )
+                    else torch.zeros(mul * ir.dim)
+                    for i_out, (mul, ir) in enumerate(self.irreps_out)
+                ]
+            )
+        else:
+            output_mask = torch.ones(0)
+        self.register_buffer("output_mask", output_mask)
+
+        self._spec = TPSpec(self.irreps_in1, self.irreps_in2, self.irreps_out, tuple(self.instructions), shared_weights)
+        self._uvw_ids = [n for n, ins in self._spec.live_instructions() if ins.connection_mode == "uvw"]
+        self._has_uvu = any(ins.connection_mode == "uvu" for _, ins in self._spec.live_instructions())
+        self._plan_host = None
+        self._plan_dev = {}
+        if self._uvw_ids:
+            self._plan_host, self._uvw_written = uvw_plan(self._spec)
+
+    def __repr__(self) -> str:
+        npath = sum(prod(i.path_shape) for i in self.instructions)
+        return (
+            f"{self.__class__.__name__}"
+            f"({self.irreps_in1.simplify()} x {self.irreps_in2.simplify()} "
+            f"-> {self.irreps_out.simplify()} | {npath} paths | {self.weight_numel} weights)"
+        )
+
+    # ---- weights (e3nn/o3/_tensor_product/_tensor_product.py:441-468) ------------------------
+    def _prep_weights_python(self, weight):
+        if isinstance(weight, list):
+            weight_shapes = [ins.path_shape for ins in self.instructions if ins.has_weight]
+            if not self.shared_weights:
+                weight = [w.reshape(-1, prod(shape)) for w, shape in zip(weight, weight_shapes)]
+            else:
+                weight = [w.reshape(prod(shape)) for w, shape in zip(weight, weight_shapes)]
+            return torch.cat(weight, dim=-1)
+        return weight
+
+    def _get_weights(self, weight) -> torch.Tensor:
+        weight = self._prep_weights_python(weight)
+        if weight is None:
+            if self.weight_numel > 0 and not self.internal_weights:
+                raise RuntimeError("Weights must be provided when the TensorProduct does not have `internal_weights`")
+            return self.weight
+        if self.shared_weights:
+            torch._assert(weight.shape == (self.weight_numel,), "Invalid weight shape")
+        else:
+            torch._assert(weight.shape[-1] == self.weight_numel, "Invalid weight shape")
+            torch._assert(weight.ndim > 1, "When shared weights is false, weights must have batch dimension")
+        return weight
+
+    def weight_view_for_instruction(self, instruction: int, weight: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if not self.instructions[instruction].has_weight:
+            raise ValueError(f"Instruction {instruction} has no weights.")
+        offset = sum(prod(ins.path_shape) for ins in self.instructions[:instruction] if ins.has_weight)
+        ins = self.instructions[instruction]
+        weight = self._get_weights(weight)
+        batchshape = weight.shape[:-1]
+        return weight.narrow(-1, offset, prod(ins.path_shape)).view(batchshape + ins.path_shape)
+
+    def weight_views(self, weight: Optional[torch.Tensor] = None, yield_instruction: bool = False):
+        weight = self._get_weights(weight)
+        batchshape = weight.shape[:-1]
+        offset = 0
+        for ins_i, ins in enumerate(self.instructions):
+            if ins.has_weight:
+                flatsize = prod(ins.path_shape)
+                this_weight = weight.narrow(-1, offset, flatsize).view(batchshape + ins.path_shape)
+                offset += flatsize
+                if yield_instruction:
+                    yield ins_i, ins, this_weight
+                else:
+                    yield this_weight
+
+    # ---- forward --------------------------------------------------------------------------
+    def _uvu_module(self):
+        return _lib.uvu_layout_module(self._uvu_only_spec())
+
+    def _uvu_only_spec(self) -> TPSpec:
+        if not hasattr(self, "_uvu_only"):
+            # 'uvw' instructions are replaced by dead place-holders (zero path weight is not enough: the
+            # generator skips them by mode), keeping the flat weight offsets of the 'uvu' paths.
+            self._uvu_only = _UvuView(self._spec)
+        return self._uvu_only
+
+    def _plan_on(self, device) -> torch.Tensor:
+        key = str(device)
+        if key not in self._plan_dev:
+            self._plan_dev[key] = torch.from_numpy(self._plan_host).to(device)
+        return self._plan_dev[key]
+
+    def forward(self, x, y, weight: Optional[torch.Tensor] = None):
+        torch._assert(x.shape[-1] == self._in1_dim, "Incorrect last dimension for x")
+        torch._assert(y.shape[-1] == self._in2_dim, "Incorrect last dimension for y")
+        w = self._get_weights(weight)
+        _lib.require_cuda(x, y, w if w.numel() > 0 else None)
+        for t in (x, y, w):
+            if t.numel() > 0 and t.dtype != torch.float32:
+                raise TypeError(f"e3nn_b200 tensor products are fp32 only, got {t.dtype}")
+
+        # broadcast the leading dims (e3nn/o3/_tensor_product/_codegen.py:43-71)
+        lead_shapes = [x.shape[:-1], y.shape[:-1]]
+        if not self.shared_weights:
+            lead_shapes.append(w.shape[:-1])
+        lead = torch.broadcast_shapes(*lead_shapes)
+        Z = int(np.prod(lead)) if len(lead) > 0 else 1
+        out_dim = self.irreps_out.dim
+        if Z == 0 or out_dim == 0:
+            return x.new_zeros(*lead, out_dim)
+        x2d = x.expand(*lead, self._in1_dim).reshape(Z, self._in1_dim).contiguous()
+        y2d = y.expand(*lead, self._in2_dim).reshape(Z, self._in2_dim).contiguous()
+        if self.shared_weights:
+            w2d = w.contiguous()
+        else:
+            w2d = w.expand(*lead, self.weight_numel).reshape(Z, self.weight_numel).contiguous()
+        if w2d.numel() == 0:
+            w2d = x2d.new_zeros(1)
+
+        if self._has_uvu:
+            out = _UvuFunction.apply(x2d, y2d, w2d, self._uvu_module(), self.shared_weights)
+        elif self._uvw_ids:
+            out = torch.empty(Z, out_dim, dtype=torch.float32, device=x.device)
+            self._zero_unwritten(out)
+        else:
+            out = x2d.new_zeros(Z, out_dim)
+        if self._uvw_ids:
+            out = self._uvw_forward(x2d, y2d, w2d, out, accumulate=self._has_uvu)
+        return out.reshape(*lead, out_dim)
+
+    def _zero_unwritten(self, out: torch.Tensor) -> None:
+        offs = self.irreps_out.offsets()
+        for i_out, (mul, ir) in enumerate(self.irreps_out):
+            if i_out not in self._uvw_written and mul * ir.dim > 0:
+                with torch.cuda.device(out.device):
+                    rc = _lib.core().e3b_fill_columns(_lib._ptr(out), out.shape[0], out.shape[1], offs[i_out],
+                                                      mul * ir.dim, None, 0, _lib.stream_ptr())
+                _lib.check(rc, "e3b_fill_columns")
+
+    def _uvw_forward(self, x2d, y2d, w, out, accumulate: bool):
+        if self.math_mode == "tf32":
+            from ._uvw_tc import uvw_tc_forward
+
+            return uvw_tc_forward(self, x2d, y2d, w, out, accumulate)
+        return _DenseFunction.apply(x2d, y2d, w, self._plan_host, self._plan_on(x2d.device), out, accumulate)
+
+
+class _UvuView(TPSpec):
+    """A `TPSpec` whose generator-visible paths are the 'uvu' ones of another spec."""
+
+    def __init__(self, spec: TPSpec):
+        object.__setattr__(self, "irreps_in1", spec.irreps_in1)
+        object.__setattr__(self, "irreps_in2", spec.irreps_in2)
+        object.__setattr__(self, "irreps_out", spec.irreps_out)
+        object.__setattr__(self, "instructions", spec.instructions)
+        object.__setattr__(self, "shared_weights", spec.shared_weights)
+
+    def live_instructions(self):
+        return [(n, ins) for n, ins in TPSpec.live_instructions(self) if ins.connection_mode == "uvu"]
+
+
+class FullyConnectedTensorProduct(TensorProduct):
+    """All allowed 'uvw' paths between the three layouts (``_sub.py:10-68``)."""
+
+    def __init__(self, irreps_in1, irreps_in2, irreps_out, irrep_normalization: str = None,
+                 path_normalization: str = None, **kwargs) -> None:
+        irreps_in1, irreps_in2, irreps_out = Irreps(irreps_in1), Irreps(irreps_in2), Irreps(irreps_out)
+        instr = [
+            (i_1, i_2, i_out, "uvw", True, 1.0)
+            for i_1, (_, ir_1) in enumerate(irreps_in1)
+            for i_2, (_, ir_2) in enumerate(irreps_in2)
+            for i_out, (_, ir_out) in enumerate(irreps_out)
+            if ir_out in ir_1 * ir_2
+        ]
+        super().__init__(irreps_in1, irreps_in2, irreps_out, instr, irrep_normalization=irrep_normalization,
+                         path_normalization=path_normalization, **kwargs)

