@@ -159,6 +159,8 @@ def run_ours(args):
     if args.workload == "sh_l3":
         return run_sh(args, rank, world, device)
     layout, nodes, degree = WORKLOADS[args.workload]
+    if args.nodes > 0:
+        nodes = args.nodes
     d = make_graph(layout, nodes, degree, rank, world, device)
     tp = d["tp"]
     node_x_full = torch.empty(nodes, tp.irreps_in1.dim, device=device) if world > 1 else d["node_x_local"]
@@ -199,6 +201,8 @@ def run_ours(args):
     ms_step = t.item() / args.steps
 
     # ---- end to end from pinned host memory through the public API
+    if args.skip_e2e:
+        return finish(args, rank, world, d, tp, nodes, degree, edges_total, ms_step, kernel_ms, clocks, None)
     e2e_steps = max(1, min(args.steps, 3))
     host = {k: d[k].cpu().pin_memory() for k in ("node_x_local", "vec", "src", "rowptr", "w")}
     out_host = torch.empty(out.shape, dtype=out.dtype).pin_memory()
@@ -232,6 +236,12 @@ def run_ours(args):
         torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
     e2e_ms = t.item() / e2e_steps
 
+    e2e = {"value": edges_total / (e2e_ms * 1e-3), "unit": "edges/s", "h2d_bytes_per_step": h2d * world,
+           "d2h_bytes_per_step": d2h * world, "steps": e2e_steps}
+    return finish(args, rank, world, d, tp, nodes, degree, edges_total, ms_step, kernel_ms, clocks, e2e)
+
+
+def finish(args, rank, world, d, tp, nodes, degree, edges_total, ms_step, kernel_ms, clocks, e2e):
     if rank != 0:
         if world > 1:
             torch.distributed.destroy_process_group()
@@ -241,7 +251,7 @@ def run_ours(args):
     k_ms = kernel_ms[len(kernel_ms) // 2]
     bytes_per_launch = algorithmic_bytes_per_edge(tp, nodes, edges_total) * d["e_local"]
     achieved = bytes_per_launch / (k_ms * 1e-3) / 1e9
-    traffic = NCU_TRAFFIC_BYTES.get(args.workload)
+    traffic = NCU_TRAFFIC_BYTES.get(args.workload) if nodes == WORKLOADS[args.workload][1] else None
     line = {
         "metric": "TP edges/sec (fused SH + uvu + scatter, fp32)",
         "value": edges_total / (ms_step * 1e-3),
@@ -259,12 +269,11 @@ def run_ours(args):
             "traffic": traffic, "peak_kind": f"of {peak_kind}", "kernel": "conv_fwd_kernel<1>",
             "kernel_ms": k_ms, "algorithmic_bytes_per_edge": algorithmic_bytes_per_edge(tp, nodes, edges_total),
         },
-        "e2e": {"value": edges_total / (e2e_ms * 1e-3), "unit": "edges/s", "h2d_bytes_per_step": h2d * world,
-                "d2h_bytes_per_step": d2h * world, "steps": e2e_steps},
+        "e2e": e2e,
         "gpu_launches": args.steps * 1,
         "clocks": clocks,
     }
-    if world == 1:
+    if world == 1 and not args.skip_cpu:
         line["cpu_baseline"] = cpu_baseline(args.workload, budget_s=12.0)
     print(json.dumps(line), flush=True)
     if world > 1:
@@ -378,6 +387,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS) + ["sh_l3"])
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--nodes", type=int, default=0, help="override the node count (smaller graphs for profiling)")
+    ap.add_argument("--skip-e2e", action="store_true", help="profiling runs: skip the host-buffer leg")
+    ap.add_argument("--skip-cpu", action="store_true", help="profiling runs: skip the CPU baseline leg")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
