@@ -69,22 +69,8 @@ def core() -> ctypes.CDLL:
         lib.e3b_fill_columns.argtypes = [c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_int, c_void_p]
         for name in ("e3b_sh_fwd", "e3b_sh_bwd", "e3b_csr_from_dst", "e3b_dense_fwd", "e3b_fill_columns"):
             getattr(lib, name).restype = c_int
-        _optional(lib)
         _core = lib
     return _core
-
-
-def _optional(lib: ctypes.CDLL) -> None:
-    """Entry points added after the first ABI version (present in every current build)."""
-    specs = {
-        "e3b_uvw_tc_fwd": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p],
-        "e3b_radial_fwd": None,
-    }
-    for name, argtypes in specs.items():
-        fn = getattr(lib, name, None)
-        if fn is not None and argtypes is not None:
-            fn.argtypes = argtypes
-            fn.restype = c_int
 
 
 def check(rc: int, what: str = "") -> None:
@@ -136,4 +122,46 @@ def uvu_layout_module(spec) -> LayoutModule:
     if mod.key != key:
         raise E3BError(f"layout module {so} was built for another layout ({mod.key} != {key})")
     _layout_cache[key] = mod
+    return mod
+
+
+class TcModule:
+    """A generated tensor-core module for one fully-connected ('uvw') layout."""
+
+    def __init__(self, path: str):
+        self.path = path
+        lib = ctypes.CDLL(path)
+        self.lib = lib
+        lib.e3b_layout_info.argtypes = [POINTER(c_int32)]
+        lib.e3b_layout_key.restype = c_char_p
+        lib.e3b_layout_last_error.restype = c_char_p
+        lib.e3b_uvw_tc_fwd.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p, c_void_p]
+        lib.e3b_uvw_tc_fwd.restype = c_int
+        dims = (c_int32 * 8)()
+        lib.e3b_layout_info(dims)
+        self.d1, self.d2, self.dout, self.wn = (int(dims[i]) for i in range(4))
+        self.key = lib.e3b_layout_key().decode()
+
+    def check(self, rc: int, what: str) -> None:
+        if rc != 0:
+            raise E3BError(f"{what} failed with status {rc}: {self.lib.e3b_layout_last_error().decode()}")
+
+
+_tc_cache: Dict[str, "TcModule"] = {}
+
+
+def uvw_tc_module(spec) -> TcModule:
+    key = spec.key()
+    mod = _tc_cache.get(key)
+    if mod is not None:
+        return mod
+    from .codegen import uvw_tc
+
+    so = os.path.join(_build.LAYOUT_DIR, f"uvwtc_{key}.so")
+    if not os.path.exists(so) or _build.nvcc_path() is not None:
+        so = _build.build_layout_module("uvwtc", key, uvw_tc.emit_module(spec))
+    mod = TcModule(so)
+    if mod.key != key:
+        raise E3BError(f"layout module {so} was built for another layout ({mod.key} != {key})")
+    _tc_cache[key] = mod
     return mod

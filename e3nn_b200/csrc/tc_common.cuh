@@ -33,7 +33,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 // Bounded wait: gives up after `limit` polls (or as soon as another thread of the block has
 // raised *abort), raises *abort itself and returns false.  No wait in these kernels is unbounded.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort, uint32_t limit = 4000000u) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort, uint32_t limit = 200000u) {
     for (uint32_t it = 0; it < limit; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((it & 63u) == 63u) {

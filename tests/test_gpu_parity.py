@@ -327,3 +327,29 @@ def test_conv_cfg3_layout_medium():
     ref = orc.conv_uvu(str(tp.irreps_in1), str(tp.irreps_in2), str(tp.irreps_out), _ins(tp), node_x.double(),
                        vec.double(), src, dst, w.double(), N, [0, 1, 2], scale=deg ** -0.5, chunk=4096)
     assert rel_err(out.cpu(), ref) < TOL
+
+
+# ----------------------------------------------------------------------------- tensor-core 'uvw' (tf32)
+TOL_TF32 = 2e-2  # stated bound for the tf32 tensor-core path
+
+
+@pytest.mark.parametrize("layout", [
+    ("32x0e+32x1o+32x2e", "1x0e+1x1o+1x2e", "32x0e+32x1o+32x2e"),          # BASELINE config 1
+    ("128x0e+64x1o+32x2e", "0e+1o+2e+3o", "128x0e+64x1o+32x2e"),          # BASELINE config 4
+])
+@pytest.mark.parametrize("Z", [1, 300, 5000])
+def test_uvw_tensor_core(layout, Z):
+    torch.manual_seed(Z)
+    tp = o3.FullyConnectedTensorProduct(*layout, math_mode="tf32").to(DEV)
+    with torch.no_grad():
+        for view in tp.weight_views():
+            view.div_((view.shape[0] * view.shape[1]) ** 0.5)  # ~N(0,1)/sqrt(fan_in) as in config 4
+    x, y = torch.randn(Z, tp.irreps_in1.dim), torch.randn(Z, tp.irreps_in2.dim)
+    with torch.no_grad():
+        out = tp(x.to(DEV), y.to(DEV))
+        torch.cuda.synchronize()
+    assert int(tp._last_tc_status.item()) == 0, "the kernel reported a timed-out wait"
+    ref = _oracle_tp(tp, x.double(), y.double(), tp.weight.detach().cpu().double())
+    err = rel_err(out.cpu(), ref)
+    assert err < TOL_TF32, err
+    assert err > 1e-6  # tf32 rounding must be visible: guards against silently running the fp32 kernel
