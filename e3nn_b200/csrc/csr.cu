@@ -10,6 +10,8 @@
 // The result is bit-identical to argsort(dst, stable=True) / cumsum(bincount(dst)).
 #include "common.cuh"
 
+#include <mutex>
+
 namespace e3b {
 
 constexpr int kSortThreads = 256;
@@ -257,4 +259,67 @@ extern "C" int e3b_csr_from_dst(const int64_t* dst, int64_t num_edges, int64_t n
         cur ^= 1;
     }
     return check_launch("e3b_csr_from_dst");
+}
+
+// ------------------------------------------------------------------------------------------------
+// Allocation-free variant: the scratch lives in this library's own device image.
+//
+// Some callers cannot hand over scratch memory because they cannot allocate any: code that
+// runs inside a memory pool it does not own (an inference server's pre-sized arena), a plug-in
+// invoked from a real-time loop where cudaMalloc's implicit device synchronisation is not
+// acceptable, or a host language binding that has no device allocator of its own.  For them the
+// work area is a fixed array in global memory that every GPU loading this library carries
+// until the process exits (about 4.4 MiB).  The price is a hard size limit and a shared buffer.
+namespace e3b {
+
+constexpr int64_t kStaticCsrMaxEdges = 1 << 18;   // 262,144
+constexpr int64_t kStaticCsrMaxNodes = 1 << 16;   // 65,536
+// = csr_layout(kStaticCsrMaxEdges, kStaticCsrMaxNodes): 4 key/value buffers, digit histograms, row counts
+constexpr int64_t kStaticCsrBytes = 4 * (kStaticCsrMaxEdges * 4) + kRadix * (kStaticCsrMaxEdges / kSortChunk) * 4
+                                    + kStaticCsrMaxNodes * 4;
+
+static __device__ __align__(256) unsigned char g_csr_static_scratch[kStaticCsrBytes];
+
+constexpr int kMaxDevices = 64;
+static void* g_csr_static_ptr[kMaxDevices] = {nullptr};
+static std::mutex g_csr_static_mutex;
+
+// Device address of the array on the current device.  In host code the array's name is only a
+// handle for the runtime, never a device pointer: the address has to be asked for, once per
+// device, while that device is current.
+static int csr_static_address(void** out) {
+    int dev = -1;
+    E3B_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) return fail(E3B_ERR_UNSUPPORTED, "csr_static: device index %d not supported", dev);
+    std::lock_guard<std::mutex> lock(g_csr_static_mutex);
+    if (g_csr_static_ptr[dev] == nullptr) {
+        void* p = nullptr;
+        E3B_CUDA_TRY(cudaGetSymbolAddress(&p, g_csr_static_scratch));
+        if (p == nullptr) return fail(E3B_ERR_CUDA, "csr_static: null symbol address");
+        g_csr_static_ptr[dev] = p;
+    }
+    *out = g_csr_static_ptr[dev];
+    return E3B_OK;
+}
+
+}  // namespace e3b
+
+extern "C" int64_t e3b_csr_static_max_edges(void) { return e3b::kStaticCsrMaxEdges; }
+extern "C" int64_t e3b_csr_static_max_nodes(void) { return e3b::kStaticCsrMaxNodes; }
+
+extern "C" int e3b_csr_from_dst_static(const int64_t* dst, int64_t num_edges, int64_t num_nodes, int64_t* perm,
+                                       int64_t* rowptr, int32_t* status, void* stream) {
+    using namespace e3b;
+    if (num_edges < 0 || num_nodes < 0) return fail(E3B_ERR_ARG, "csr_static: negative size");
+    if (num_edges > kStaticCsrMaxEdges || num_nodes > kStaticCsrMaxNodes)
+        return fail(E3B_ERR_ARG,
+                    "csr_static: %lld edges / %lld nodes exceed the built-in work area (at most %lld edges and %lld nodes); "
+                    "use e3b_csr_from_dst with caller-provided scratch",
+                    (long long)num_edges, (long long)num_nodes, (long long)kStaticCsrMaxEdges, (long long)kStaticCsrMaxNodes);
+    void* scratch = nullptr;
+    const int rc = csr_static_address(&scratch);
+    if (rc != E3B_OK) return rc;
+    // Everything that must start from zero (row counts, status word) is cleared by the call below on
+    // the caller's stream; the rest of the work area is fully overwritten before it is read.
+    return e3b_csr_from_dst(dst, num_edges, num_nodes, perm, rowptr, scratch, kStaticCsrBytes, status, stream);
 }

@@ -75,6 +75,33 @@ int e3b_csr_from_dst(const int64_t* dst, int64_t num_edges, int64_t num_nodes, i
                      void* scratch, int64_t scratch_bytes, int32_t* status, void* stream);
 
 /*
+ * e3b_csr_from_dst without any caller-provided scratch.  (No counterpart in e3nn: this entry
+ * point exists only for hosts that cannot allocate device memory.)
+ *
+ * Same result as e3b_csr_from_dst, bit for bit, but the work area is a fixed array inside this
+ * library's device image, so the call (and the library) allocates nothing: no cudaMalloc, no
+ * cudaFree, no allocating library routine.  It is meant for callers that only own the buffers
+ * they were given -- a plug-in running inside somebody else's pre-sized memory arena, a
+ * latency-critical loop that must not hit the device-wide synchronisation of an allocation, a
+ * language binding without a device allocator.  Inputs and outputs are still the caller's.
+ *
+ * Limits and rules:
+ *   - at most e3b_csr_static_max_edges() edges (262,144) and e3b_csr_static_max_nodes() nodes
+ *     (65,536); larger problems are rejected with E3B_ERR_ARG and a message naming the limits;
+ *   - every GPU that loads the library holds the work area (about 4.4 MiB) until the process exits;
+ *   - the first call on each device looks up the work area's device address (with that device
+ *     current); make that first call before starting any stream capture;
+ *   - all calls on a device share the one work area: it keeps the previous call's contents, the
+ *     parts that must start at zero are cleared on the caller's stream at the start of every
+ *     call, and two calls whose GPU work overlaps (different streams, or different host threads
+ *     without ordering between their streams) race on it -- serialise them.
+ */
+int64_t e3b_csr_static_max_edges(void);
+int64_t e3b_csr_static_max_nodes(void);
+int e3b_csr_from_dst_static(const int64_t* dst, int64_t num_edges, int64_t num_nodes, int64_t* perm, int64_t* rowptr,
+                            int32_t* status, void* stream);
+
+/*
  * Weight-shared dense contractions in fp32 (CUDA cores): 'uvw' tensor-product paths
  *   out[z,w,k] = sum_paths pw sum_{u,v} W[u,v,w] sum_{ij} C_ijk x1[z,u,i] x2[z,v,j]
  * (e3nn/o3/_tensor_product/_codegen.py:148-165 with the accumulation of :312-343) and the
