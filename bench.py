@@ -8,6 +8,11 @@ Workloads (synthetic, seeded; shapes and distributions of the BASELINE configura
   conv_l2_11   same graph, the 11-path layout (outputs restricted to the node irreps).
   conv_l3_23   the 'uvu' l<=3 layout (23 paths, 64x0e+64x1o+64x2e+64x3o), same graph shape.
   sh_l3        spherical harmonics lmax 3 on 4,194,304 edge vectors.
+  interaction_l3  one NequIP-style interaction block, forward + gradient w.r.t. positions: 262,144 atoms uniform in
+               a periodic cube at 0.05 / A^3, 5 A cutoff (~26 neighbours), features 64x0e+64x1o+64x2e+64x3o,
+               SH lmax 3, Bessel(8) -> 64 -> 1472 radial MLP, 23-path 'uvu', scatter / sqrt(n), Linear.
+  uvw_fctp     FullyConnectedTensorProduct 128x0e+64x1o+32x2e (x) 0e+1o+2e+3o -> same, shared weights,
+               1,048,576 rows, tcgen05 tf32 kernel, followed by o3.Linear (fp32) on the output.
 
 A "step" is one pass of the hot path over the whole graph.  `value` is timed with CUDA events on the
 launching stream with every input resident in HBM (inputs are far larger than L2, nothing is cached
@@ -158,6 +163,10 @@ def run_ours(args):
 
     if args.workload == "sh_l3":
         return run_sh(args, rank, world, device)
+    if args.workload == "uvw_fctp":
+        return run_uvw(args, rank, world, device)
+    if args.workload == "interaction_l3":
+        return run_interaction(args, rank, world, device)
     layout, nodes, degree = WORKLOADS[args.workload]
     if args.nodes > 0:
         nodes = args.nodes
@@ -318,6 +327,156 @@ def run_sh(args, rank, world, device):
     }), flush=True)
 
 
+def run_interaction(args, rank, world, device):
+    """BASELINE config 5 on one GPU (sharded runs: see DESIGN.md section 5)."""
+    import e3nn_b200
+    from e3nn_b200 import nn as bnn
+
+    n_atoms = args.nodes if args.nodes > 0 else 262_144
+    box = (n_atoms / 0.05) ** (1.0 / 3.0)
+    gen = torch.Generator().manual_seed(0)
+    pos_host = torch.rand(n_atoms, 3, generator=gen) * box
+    t0 = time.perf_counter()
+    src, dst, shift = bnn.radius_graph_pbc(pos_host, box, 5.0)
+    t_graph = time.perf_counter() - t0
+    E = src.numel()
+    block = bnn.InteractionBlock("64x0e+64x1o+64x2e+64x3o", 3, num_basis=8, hidden=64, r_max=5.0,
+                                 num_neighbors=E / n_atoms).to(device)
+    for prm in block.parameters():
+        prm.requires_grad_(False)
+    node_x = torch.randn(n_atoms, 1024, generator=gen).to(device)
+    G = torch.randn(n_atoms, 1024, generator=gen).to(device)
+    src_d, dst_d, shift_d = src.to(device), dst.to(device), shift.to(device)
+    _, rowptr = e3nn_b200.csr_from_dst(dst_d, n_atoms)
+    pos_d = pos_host.to(device)
+
+    def step(p_in):
+        p = p_in.detach().requires_grad_(True)
+        out = block(p, node_x, src_d, dst_d, rowptr, shift_d)
+        (out * G).sum().backward()
+        return p.grad
+
+    for _ in range(args.warmup):
+        g = step(pos_d)
+    torch.cuda.synchronize()
+    sampler = ClockSampler(device.index or 0)
+    sampler.start()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(args.steps):
+        g = step(pos_d)
+    stop.record()
+    torch.cuda.synchronize()
+    ms_step = start.elapsed_time(stop) / args.steps
+    clocks = sampler.stop()
+    # forward only, for context
+    with torch.no_grad():
+        start.record()
+        for _ in range(max(1, args.steps // 2)):
+            block(pos_d, node_x, src_d, dst_d, rowptr, shift_d)
+        stop.record()
+        torch.cuda.synchronize()
+    ms_fwd = start.elapsed_time(stop) / max(1, args.steps // 2)
+    # end to end: positions, features and graph from pinned host memory, gradient back to the host
+    e2e = None
+    if not args.skip_e2e:
+        host = {"pos": pos_host.pin_memory(), "x": node_x.cpu().pin_memory(), "src": src.pin_memory(),
+                "dst": dst.pin_memory(), "shift": shift.pin_memory(), "rowptr": rowptr.cpu().pin_memory()}
+        grad_host = torch.empty(n_atoms, 3).pin_memory()
+
+        def e2e_step():
+            d = {k: v.to(device, non_blocking=True) for k, v in host.items()}
+            p = d["pos"].requires_grad_(True)
+            out = block(p, d["x"], d["src"], d["dst"], d["rowptr"], d["shift"])
+            (out * G).sum().backward()
+            grad_host.copy_(p.grad, non_blocking=True)
+
+        e2e_step()
+        torch.cuda.synchronize()
+        n_e2e = max(1, min(args.steps, 3))
+        start.record()
+        for _ in range(n_e2e):
+            e2e_step()
+        stop.record()
+        torch.cuda.synchronize()
+        e2e_ms = start.elapsed_time(stop) / n_e2e
+        e2e = {"value": E / (e2e_ms * 1e-3), "unit": "edges/s", "steps": n_e2e,
+               "h2d_bytes_per_step": sum(v.numel() * v.element_size() for v in host.values()),
+               "d2h_bytes_per_step": grad_host.numel() * 4}
+    peak, peak_kind = measured_peaks()
+    tp = block.tp
+    line = {
+        "metric": "TP edges/sec (uvu l<=3, fp32), interaction block forward + d/d positions",
+        "value": E / (ms_step * 1e-3), "unit": "edges/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": "interaction_l3", "atoms": n_atoms, "edges": E, "neighbours_per_atom": E / n_atoms,
+                   "box": box, "cutoff": 5.0, "forward_ms": ms_fwd, "atoms_per_s": n_atoms / (ms_step * 1e-3),
+                   "neighbour_list_s_host": t_graph, "weight_numel": tp.weight_numel, "mid_dim": tp.irreps_out.dim,
+                   "radial_mlp": "cuBLAS fp32 via torch.matmul (not fused yet)",
+                   "l2": "per-edge weights (%.1f GB) far larger than the 126 MB L2" % (E * tp.weight_numel * 4 / 1e9),
+                   "parallelism": f"single GPU"},
+        "e2e": e2e, "gpu_launches": None, "clocks": clocks,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_uvw(args, rank, world, device):
+    """BASELINE config 4: rows are independent, so N GPUs run N replicas of rows/N each (no collective)."""
+    from e3nn_b200 import o3
+
+    rows_total = args.nodes if args.nodes > 0 else 1_048_576
+    rows = rows_total // world
+    tp = o3.FullyConnectedTensorProduct("128x0e+64x1o+32x2e", "0e+1o+2e+3o", "128x0e+64x1o+32x2e", math_mode="tf32").to(device)
+    lin = o3.Linear(tp.irreps_out, tp.irreps_out).to(device)
+    with torch.no_grad():
+        for view in tp.weight_views():
+            view.div_((view.shape[0] * view.shape[1]) ** 0.5)
+    gen = torch.Generator(device=device).manual_seed(rank)
+    x = torch.randn(rows, tp.irreps_in1.dim, device=device, generator=gen)
+    y = torch.randn(rows, tp.irreps_in2.dim, device=device, generator=gen)
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def timed(fn, n):
+        ts = []
+        for _ in range(n):
+            start.record()
+            r = fn()
+            stop.record()
+            torch.cuda.synchronize()
+            ts.append(start.elapsed_time(stop))
+        ts.sort()
+        return ts[len(ts) // 2], r
+
+    with torch.no_grad():
+        for _ in range(args.warmup):
+            out = lin(tp(x, y))
+        torch.cuda.synchronize()
+        ms_tp, mid = timed(lambda: tp(x, y), args.steps)
+        ms_lin, out = timed(lambda: lin(mid), max(3, args.steps // 4))
+        ms_both, out = timed(lambda: lin(tp(x, y)), args.steps)
+    if rank != 0:
+        return
+    peak, peak_kind = measured_peaks()
+    flops_tp, flops_lin = 282_624.0, 67_584.0
+    achieved_tf = flops_tp * rows / (ms_tp * 1e-3) / 1e12
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    tf32_peak = 0.5 * (json.load(open(peaks_path))["bf16_tflops"] if os.path.exists(peaks_path) else 1590.0)
+    print(json.dumps({
+        "metric": "uvw TP rows/sec (tf32 tensor cores) + Linear", "value": rows_total / (ms_both * 1e-3), "unit": "rows/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_both, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "tf32 operands, f32 accumulate (TP); f32 (Linear)", "data": "synthetic",
+        "config": {"workload": "uvw_fctp", "rows": rows_total, "tp_ms": ms_tp, "linear_ms": ms_lin,
+                   "l2": "inputs and outputs (4.1 GB) far larger than the 126 MB L2", "parallelism": f"replicas x{world}"},
+        "roofline": {"bound": "tensor", "achieved": achieved_tf, "peak": tf32_peak, "unit": "TFLOP/s",
+                     "frac": achieved_tf / tf32_peak, "traffic": None, "kernel": "uvw_tc_kernel",
+                     "peak_kind": "half of the measured bf16 burst peak (tf32 was not measured separately)",
+                     "hbm_achieved_gbs": 3904.0 * rows / (ms_tp * 1e-3) / 1e9, "hbm_peak_gbs": peak,
+                     "hbm_frac": 3904.0 * rows / (ms_tp * 1e-3) / 1e9 / peak},
+        "gpu_launches": args.steps * 4,
+    }), flush=True)
+
+
 # ------------------------------------------------------------------------------------------- CPU arm
 def cpu_conv_sample(workload: str, sample_edges: int, threads: int):
     """One pass of the oracle over a sample of the workload: returns seconds."""
@@ -385,7 +544,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS) + ["sh_l3"])
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS) + ["sh_l3", "uvw_fctp", "interaction_l3"])
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--nodes", type=int, default=0, help="override the node count (smaller graphs for profiling)")
     ap.add_argument("--skip-e2e", action="store_true", help="profiling runs: skip the host-buffer leg")

@@ -33,6 +33,7 @@ import numpy as np
 
 from ..o3._spec import TPSpec
 from ..o3._wigner import wigner_3j_numpy
+from . import uvu_tma
 
 
 def _f(v: float) -> str:
@@ -293,17 +294,22 @@ def emit_module(spec: TPSpec) -> str:
     y_load = f"float Y[{max(L.d2, 1)}];\n#pragma unroll\nfor (int j = 0; j < {L.d2}; ++j) Y[j] = yrow[j];"
 
     has_sh = sh_l is not None
-    sh_nc = (sh_l + 1) ** 2 if has_sh else 0
     warps_per_group = max(1, G // 32)
+    v2 = uvu_tma.emit(L)
+    v2_kernel = v2["kernel"] if v2 else ""
+    v2_launch = v2["launch"] if v2 else ""
 
     src = f"""// Generated by e3nn_b200/codegen/uvu.py -- do not edit.
 // layout: {spec.irreps_in1} (x) {spec.irreps_in2} -> {spec.irreps_out}, {len(L.paths)} 'uvu' paths, key {spec.key()}
 #include <cuda_runtime.h>
 #include <cstdint>
 #include "layout_common.cuh"
+#include "tc_common.cuh"
 {'#include "sh_gen.cuh"' if has_sh else ''}
 
 namespace {{
+
+int g_conv_impl = 0;   // 0: pick the fastest eligible kernel, 1: always the direct-load kernel
 
 constexpr int kD1 = {L.d1};
 constexpr int kD2 = {L.d2};
@@ -502,9 +508,12 @@ __global__ void __launch_bounds__(kThreads) conv_bwd_kernel(const float* __restr
     }}
 }}
 
+{v2_kernel}
 }}  // namespace
 
 // ================================================================= C ABI of the layout module
+extern "C" int e3b_conv_select(int impl) {{ g_conv_impl = impl; return {1 if v2 else 0}; }}
+
 extern "C" int e3b_layout_info(int32_t* dims) {{
     dims[0] = kD1; dims[1] = kD2; dims[2] = kDout; dims[3] = kWn; dims[4] = kShLmax; dims[5] = kG;
     return 0;
@@ -553,6 +562,7 @@ extern "C" int e3b_conv_fwd(const float* node_x, const float* x2, int in2_mode, 
     const int64_t blocks = (num_nodes + kRowsPerBlock - 1) / kRowsPerBlock;
     const unsigned grid = static_cast<unsigned>(blocks < 148LL * 64 ? blocks : 148LL * 64);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+{v2_launch}
     if (in2_mode == 1)
         conv_fwd_kernel<1><<<grid, kThreads, 0, s>>>(node_x, x2, edge_src, rowptr, perm, w, out, num_nodes, num_src, scale, status);
     else

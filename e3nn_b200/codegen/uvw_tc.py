@@ -117,23 +117,49 @@ def plan_groups(spec: TPSpec) -> Optional[List[TcGroup]]:
     return out
 
 
-def _producer_path_code(p: TcPath, dim: int) -> str:
-    """Row body for one path: expects xr (-> x1[z, u, 0]), yr (-> x2 row), writes a[k]."""
+ROW_BATCH = 8   # rows whose loads are issued together by a producer warp (memory-level parallelism)
+
+
+def _producer_path_code(p: TcPath, dim: int, d1_total: int, d2_total: int) -> str:
+    """Body of one `case` of the producer switch: fills this warp's 16 rows of every k sub-tile.
+
+    In scope: xbase (-> x1[z0, u, 0] of this lane's channel), ybase (-> x2[z0, 0]), z0, Z, pw (producer
+    warp index), lane, stage.  Rows past Z read row Z-1 (valid memory) and their values are never used.
+    """
     c = wigner_3j_numpy(p.l1, p.l2, p.l3) * p.pw
     d1, d2 = 2 * p.l1 + 1, 2 * p.l2 + 1
-    lines = [f"float xi[{d1}], yj[{d2}];"]
-    lines += [f"#pragma unroll\nfor (int i = 0; i < {d1}; ++i) xi[i] = xr[i];"]
-    lines += [f"#pragma unroll\nfor (int j = 0; j < {d2}; ++j) yj[j] = __ldg(yr + {p.off2} + j);"]
+    lines = [f"#pragma unroll\nfor (int batch = 0; batch < kRowsPerWarp / {ROW_BATCH}; ++batch) {{"]
+    lines.append(f"  float xi[{ROW_BATCH}][{d1}], yj[{ROW_BATCH}][{d2}];")
+    lines.append(f"#pragma unroll\n  for (int b = 0; b < {ROW_BATCH}; ++b) {{")
+    lines.append(f"    const int r = pw * kRowsPerWarp + batch * {ROW_BATCH} + b;")
+    lines.append("    const int64_t zr = (z0 + r < Z) ? r : (Z - 1 - z0);")
+    lines.append(f"    const float* xr = xbase + zr * {d1_total};")
+    lines.append(f"    const float* yr = ybase + zr * {d2_total} + {p.off2};")
+    lines.append(f"#pragma unroll\n    for (int i = 0; i < {d1}; ++i) xi[b][i] = xr[i];")
+    lines.append(f"#pragma unroll\n    for (int j = 0; j < {d2}; ++j) yj[b][j] = __ldg(yr + j);")
+    lines.append("  }")
+    lines.append(f"#pragma unroll\n  for (int b = 0; b < {ROW_BATCH}; ++b) {{")
+    lines.append(f"    const int r = pw * kRowsPerWarp + batch * {ROW_BATCH} + b;")
+    lines.append("    const uint32_t off = tc::sw128_offset(r, lane);")
     for k in range(dim):
         terms = []
         for i in range(d1):
             inner = [(j, c[i, j, k]) for j in range(d2) if c[i, j, k] != 0.0]
             if not inner:
                 continue
-            t = " + ".join(f"{_f(v)} * yj[{j}]" for j, v in inner)
-            terms.append(f"({t}) * xi[{i}]")
-        lines.append(f"a[{k}] = {' + '.join(terms) if terms else '0.0f'};")
+            t = " + ".join(f"{_f(v)} * yj[b][{j}]" for j, v in inner)
+            terms.append(f"({t}) * xi[b][{i}]")
+        expr = " + ".join(terms) if terms else "0.0f"
+        lines.append(f"    *reinterpret_cast<float*>(stage + {k} * TILE_BYTES + off) = tc::to_tf32({expr});")
+    lines.append("  }")
+    lines.append("}")
     return "\n".join(lines)
+
+
+def _chunk_cost(p: TcPath, dim: int) -> int:
+    """Relative cost of producing one 32-channel chunk of a path (loads + FMAs + stores per row)."""
+    c = wigner_3j_numpy(p.l1, p.l2, p.l3)
+    return 6 + (2 * p.l1 + 1) + (2 * p.l2 + 1) + 2 * int((c != 0).sum()) + 2 * dim
 
 
 def _indent(text: str, n: int) -> str:
@@ -163,8 +189,8 @@ def emit_module(spec: TPSpec) -> str:
         for pi, p in enumerate(g.paths):
             cases.append(
                 f"case {pi}: {{  // path {p.index}: l={p.l1} (x) l={p.l2} -> l={p.l3}\n"
-                f"    const float* xr = xrow + xoff + lane * {2 * p.l1 + 1};\n"
-                f"{_indent(_producer_path_code(p, g.dim), 4)}\n"
+                f"    const float* xbase = x1 + z0 * {d1} + xoff + lane * {2 * p.l1 + 1};\n"
+                f"{_indent(_producer_path_code(p, g.dim, d1, d2), 4)}\n"
                 f"    break; }}"
             )
         switch = "\n".join(cases)
@@ -253,24 +279,9 @@ __device__ __forceinline__ void run_group_{gi}(const float* __restrict__ x1, con
                 if (!tc::mbar_wait(&bar_empty[s], ph ^ 1u, abort_flag)) {{ ok = false; break; }}
                 uint8_t* stage = sA + s * STAGE_BYTES;
                 const int path = kCPath{gi}[c], xoff = kXOff{gi}[c];
-#pragma unroll 2
-                for (int rr = 0; rr < 128 / kProducerWarps; ++rr) {{
-                    const int r = pw * (128 / kProducerWarps) + rr;
-                    const int64_t z = z0 + r;
-                    float a[DIM];
-#pragma unroll
-                    for (int k = 0; k < DIM; ++k) a[k] = 0.0f;
-                    if (z < Z) {{
-                        const float* xrow = x1 + z * {d1};
-                        const float* yr = x2 + z * {d2};
-                        switch (path) {{
-{_indent(switch, 24)}
-                        }}
-                    }}
-                    const uint32_t off = tc::sw128_offset(r, lane);
-#pragma unroll
-                    for (int k = 0; k < DIM; ++k)
-                        *reinterpret_cast<float*>(stage + k * TILE_BYTES + off) = tc::to_tf32(a[k]);
+                const float* ybase = x2 + z0 * {d2};
+                switch (path) {{
+{_indent(switch, 16)}
                 }}
                 tc::fence_proxy_async_smem();
                 __syncwarp();
@@ -323,7 +334,7 @@ __device__ __forceinline__ void run_group_{gi}(const float* __restrict__ x1, con
     bounds_decl = "\n".join(
         f"    const int cta_begin{gi} = {'0' if gi == 0 else f'cta_end{gi-1}'}, cta_end{gi} = cta_begin{gi} + split.n[{gi}];" for gi in range(ngroups)
     )
-    work = [g.dim * g.k for g in groups]
+    work = [sum(_chunk_cost(g.paths[pi], g.dim) for pi, _ in g.chunks()) for g in groups]
     return f"""// Generated by e3nn_b200/codegen/uvw_tc.py -- do not edit.
 // layout: {spec.irreps_in1} (x) {spec.irreps_in2} -> {spec.irreps_out}, {sum(len(g.paths) for g in groups)} 'uvw' paths, key {spec.key()}
 #include <cuda_runtime.h>
@@ -338,6 +349,7 @@ constexpr int kProducerWarps = 8;
 constexpr int kMmaWarp = kEpilogueWarps + kProducerWarps;
 constexpr int kThreads = (kMmaWarp + 1) * 32;
 constexpr int kTmemCols = 512;
+constexpr int kRowsPerWarp = 128 / kProducerWarps;
 constexpr int kGroups = {ngroups};
 constexpr int kSmemBytes = {smem_max};
 

@@ -62,6 +62,7 @@ class _ConvFunction(torch.autograd.Function):
         ctx.save_for_backward(node_x, x2, weight, edge_src, rowptr, perm if perm is not None else torch.empty(0))
         ctx.meta = (mod, in2_mode, scale, perm is not None)
         ctx.status = status
+        mod.last_status = status
         return out
 
     @staticmethod
@@ -105,6 +106,8 @@ def conv_uvu(
     already sorted by destination).  With ``edge_attr_is_vector=True`` ``edge_attr`` holds the edge
     vectors ``[E, 3]`` and the spherical harmonics (``normalize=True, normalization='component'``) are
     evaluated inside the kernel; ``tp.irreps_in2`` must then be ``Y^0..Y^L``.
+    ``check_indices=True`` reads back the kernel's status word (a device synchronisation) and raises
+    ``IndexError`` if a source index was out of range.
     """
     _lib.require_cuda(node_features, edge_attr, weight, edge_src, rowptr)
     if tp._uvw_ids or tp.shared_weights:
@@ -124,4 +127,10 @@ def conv_uvu(
         node_features.contiguous(), edge_attr.contiguous(), weight.contiguous(), edge_src.contiguous(),
         rowptr.contiguous(), None if perm is None else perm.contiguous(), mod, in2_mode, float(scale),
     )
+    if check_indices:  # synchronises: reads the status word the kernel wrote
+        code = int(mod.last_status.item())
+        if code == 2:
+            raise IndexError("edge_src holds a value outside [0, num_nodes)")
+        if code != 0:
+            raise _lib.E3BError(f"fused convolution kernel reported status {code} (a bounded wait gave up)")
     return out

@@ -1,0 +1,77 @@
+"""One NequIP-style interaction block: the caller of the hot path, assembled from its kernels.
+
+Mirrors the data flow of ``e3nn/nn/models/v2106/points_convolution.py:99-113`` restricted to the steps
+on the accelerated path (no self-connection / node attributes):
+
+    edge_vec = pos[src] - pos[dst] + shift                       (gate_points_2101.py:328 sign convention)
+    w        = FullyConnectedNet([num_basis, hidden, weight_numel], silu)(bessel(|edge_vec|))
+    mid      = scatter(tp(x[src], Y(edge_vec), w), dst) / sqrt(num_neighbors)     -> e3b_conv_fwd
+    out      = Linear(mid)                                                         -> e3b_dense_fwd
+
+Gradients w.r.t. the positions flow through ``e3b_conv_bwd`` (per-edge weight and edge-vector
+cotangents, spherical harmonics included) and the transposed Linear plan; torch autograd connects
+them through the radial network.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+from .. import layouts
+from ..message_passing import conv_uvu
+from ..o3 import Irreps, Linear
+from ._fc import FullyConnectedNet, bessel
+
+
+def radius_graph_pbc(pos: torch.Tensor, box: float, cutoff: float) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Neighbour list of a periodic cubic box, both directions, sorted by destination (host, scipy).
+
+    Returns ``edge_src, edge_dst, shift`` with ``edge_vec = pos[src] - pos[dst] + shift``.  Set-up code:
+    a k-d tree on the host; a device cell list is future work.
+    """
+    import numpy as np
+    from scipy.spatial import cKDTree
+
+    p = pos.detach().cpu().double().numpy() % box
+    tree = cKDTree(p, boxsize=box)
+    pairs = tree.query_pairs(cutoff, output_type="ndarray")
+    src = np.concatenate([pairs[:, 0], pairs[:, 1]])
+    dst = np.concatenate([pairs[:, 1], pairs[:, 0]])
+    order = np.lexsort((src, dst))
+    src, dst = src[order], dst[order]
+    d = p[src] - p[dst]
+    shift = -box * np.round(d / box)
+    # positions may lie outside [0, box): express the shift relative to the given coordinates
+    raw = pos.detach().cpu().double().numpy()
+    shift = (p[src] - raw[src]) - (p[dst] - raw[dst]) + shift
+    dev = pos.device
+    return (torch.from_numpy(src).to(dev), torch.from_numpy(dst).to(dev),
+            torch.from_numpy(shift).to(device=dev, dtype=pos.dtype))
+
+
+class InteractionBlock(torch.nn.Module):
+    def __init__(self, irreps_node, lmax: int, num_basis: int = 8, hidden: int = 64, r_max: float = 5.0,
+                 num_neighbors: float = 1.0, irreps_out=None):
+        super().__init__()
+        self.irreps_node = Irreps(irreps_node)
+        self.irreps_sh = Irreps.spherical_harmonics(lmax)
+        self.irreps_out = Irreps(irreps_out) if irreps_out is not None else self.irreps_node
+        self.tp = layouts.conv_tensor_product(self.irreps_node, self.irreps_sh, self.irreps_out)
+        self.fc = FullyConnectedNet([num_basis, hidden, self.tp.weight_numel], torch.nn.functional.silu)
+        self.lin = Linear(self.tp.irreps_out, self.irreps_out)
+        self.num_basis, self.r_max, self.num_neighbors = num_basis, r_max, num_neighbors
+
+    def edge_weights(self, edge_vec: torch.Tensor) -> torch.Tensor:
+        return self.fc(bessel(edge_vec.norm(dim=-1), self.num_basis, self.r_max))
+
+    def forward(self, pos: torch.Tensor, node_features: torch.Tensor, edge_src: torch.Tensor, edge_dst: torch.Tensor,
+                rowptr: torch.Tensor, shift: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``edge_*`` must be sorted by destination and ``rowptr`` their CSR (`e3nn_b200.csr_from_dst`)."""
+        edge_vec = pos[edge_src] - pos[edge_dst]
+        if shift is not None:
+            edge_vec = edge_vec + shift
+        w = self.edge_weights(edge_vec)
+        mid = conv_uvu(self.tp, node_features, edge_vec, edge_src, rowptr, w, scale=self.num_neighbors ** -0.5,
+                       edge_attr_is_vector=True)
+        return self.lin(mid)

@@ -66,6 +66,14 @@ int e3b_conv_fwd(const float* node_x, const float* x2, int in2_mode, const int64
                  int64_t num_edges, float scale, int32_t* status, void* stream);
 
 /*
+ * Kernel selection for e3b_conv_fwd (testing / profiling; no reference counterpart).  impl 0: the
+ * bulk-copy pipelined kernel whenever the layout and the call are eligible (64-channel paths,
+ * in2_mode 1, perm == NULL, 16-byte aligned rows), else the direct-load kernel; impl 1: always the
+ * direct-load kernel.  Returns 1 if this module contains the pipelined kernel, else 0.
+ */
+int e3b_conv_select(int impl);
+
+/*
  * Gradient of e3b_conv_fwd w.r.t. the per-edge weights and x2 (rows or edge vectors, as
  * in2_mode says) for a cotangent grad_out [num_nodes, dout]; replaces autograd through the same
  * three reference steps.  grad_w [E, weight_numel], grad_x2 [E, d2] or [E, 3].

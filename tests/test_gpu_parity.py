@@ -353,3 +353,90 @@ def test_uvw_tensor_core(layout, Z):
     err = rel_err(out.cpu(), ref)
     assert err < TOL_TF32, err
     assert err > 1e-6  # tf32 rounding must be visible: guards against silently running the fp32 kernel
+
+
+# ----------------------------------------------------------------------------- bulk-copy pipelined convolution kernel
+@pytest.mark.parametrize("layout", ["cfg3_15", "cfg3_11", "cfg5_23"])
+def test_conv_pipelined_kernel(layout):
+    """64-channel layouts take the bulk-copy (TMA) pipelined kernel when the edges are sorted by
+    destination; it must agree with the oracle and with the direct-load kernel on a ragged graph
+    (empty rows, rows of one edge, one long row)."""
+    torch.manual_seed(3)
+    tp = layouts.bench_conv_tp(layout)
+    mod = tp._uvu_module()
+    assert mod.lib.e3b_conv_select(0) == 1, "module was generated without the pipelined kernel"
+    N = 700
+    deg = torch.randint(0, 9, (N,))
+    deg[5] = 0
+    deg[6] = 1
+    deg[77] = 96
+    deg[N - 1] = 0
+    dst = torch.repeat_interleave(torch.arange(N), deg)
+    E = dst.numel()
+    rowptr = torch.zeros(N + 1, dtype=torch.int64)
+    rowptr[1:] = torch.cumsum(deg, 0)
+    src = torch.randint(0, N, (E,))
+    node_x = torch.randn(N, tp.irreps_in1.dim)
+    vec = torch.randn(E, 3)
+    vec[3] = 0.0
+    w = torch.randn(E, tp.weight_numel)
+    args = (tp, node_x.to(DEV), vec.to(DEV), src.to(DEV), rowptr.to(DEV), w.to(DEV))
+    fast = e3nn_b200.conv_uvu(*args, scale=0.7, edge_attr_is_vector=True, check_indices=True)
+    mod.lib.e3b_conv_select(1)
+    try:
+        slow = e3nn_b200.conv_uvu(*args, scale=0.7, edge_attr_is_vector=True)
+    finally:
+        mod.lib.e3b_conv_select(0)
+    lmax = tp.irreps_in2.lmax
+    ref = orc.conv_uvu(str(tp.irreps_in1), str(tp.irreps_in2), str(tp.irreps_out), _ins(tp), node_x.double(),
+                       vec.double(), src, dst, w.double(), N, list(range(lmax + 1)), scale=0.7, chunk=2048)
+    err_fast, err_slow = rel_err(fast.cpu(), ref), rel_err(slow.cpu(), ref)
+    # one row sums 96 messages sequentially in fp32 while most rows sum ~4, and the metric divides by
+    # the global RMS: the long row dominates the error of both kernels alike
+    assert err_fast < 2e-5 and err_slow < 2e-5, (err_fast, err_slow)
+    assert rel_err(fast.cpu(), slow.cpu()) < 5e-6
+    assert torch.all(fast[5] == 0) and torch.all(fast[N - 1] == 0)
+    again = e3nn_b200.conv_uvu(*args, scale=0.7, edge_attr_is_vector=True)
+    assert torch.equal(fast, again)  # fixed summation order
+    bad = src.clone()
+    bad[10] = N + 5
+    with pytest.raises(IndexError):
+        e3nn_b200.conv_uvu(tp, node_x.to(DEV), vec.to(DEV), bad.to(DEV), rowptr.to(DEV), w.to(DEV),
+                           edge_attr_is_vector=True, check_indices=True)
+
+
+# ----------------------------------------------------------------------------- interaction block (forward + d/d positions)
+@pytest.mark.parametrize("irreps,lmax", [("8x0e+8x1o+8x2e", 2), ("64x0e+64x1o+64x2e+64x3o", 3)])
+def test_interaction_block_forward_and_position_gradient(irreps, lmax):
+    """BASELINE config 5 at reduced size: periodic box at density 0.05, 5 A cutoff, Bessel(8) -> 64 -> weights,
+    SH lmax, 'uvu', scatter / sqrt(n), Linear; loss = sum(out * G); gradient w.r.t. the positions."""
+    from e3nn_b200 import nn as bnn
+
+    torch.manual_seed(11)
+    n_atoms = 600
+    box = (n_atoms / 0.05) ** (1 / 3)
+    pos = torch.rand(n_atoms, 3) * box
+    src, dst, shift = bnn.radius_graph_pbc(pos, box, 5.0)
+    num_neighbors = src.numel() / n_atoms
+    block = bnn.InteractionBlock(irreps, lmax, num_basis=8, hidden=64, r_max=5.0, num_neighbors=num_neighbors).to(DEV)
+    node_x = torch.randn(n_atoms, block.irreps_node.dim)
+    G = torch.randn(n_atoms, block.irreps_out.dim)
+    perm, rowptr = e3nn_b200.csr_from_dst(dst.to(DEV), n_atoms)
+    assert torch.equal(perm.cpu(), torch.arange(src.numel()))  # the neighbour list is already sorted by destination
+
+    p = pos.clone().to(DEV).requires_grad_(True)
+    for prm in block.parameters():
+        prm.requires_grad_(False)
+    out = block(p, node_x.to(DEV), src.to(DEV), dst.to(DEV), rowptr, shift.to(DEV))
+    (out * G.to(DEV)).sum().backward()
+
+    tp = block.tp
+    p64 = pos.double().requires_grad_(True)
+    ref = orc.interaction_block(
+        str(tp.irreps_in1), str(tp.irreps_in2), str(tp.irreps_out), _ins(tp), str(block.irreps_out), p64,
+        node_x.double(), src, dst, shift.double(),
+        [block.fc.layer0.weight.detach().cpu().double(), block.fc.layer1.weight.detach().cpu().double()],
+        block.lin.weight.detach().cpu().double(), 8, 5.0, num_neighbors, list(range(lmax + 1)), chunk=4096)
+    (ref * G.double()).sum().backward()
+    assert rel_err(out.detach().cpu(), ref.detach()) < TOL
+    assert rel_err(p.grad.cpu(), p64.grad) < 5e-5   # gradient: long chain through sin/r, silu and the SH Jacobian
