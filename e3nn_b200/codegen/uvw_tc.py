@@ -82,14 +82,14 @@ class TcGroup:
     def nbuf(self) -> int:
         return 2 if 2 * self.dim * self.n <= 512 else 1
 
-    def nstage(self) -> int:
+    def nstage(self, y_bytes: int = 8192) -> int:
         b = self.n * self.k * 4
         stage = self.dim * STAGE_TILE_BYTES
-        n = (SMEM_LIMIT - 2048 - b) // stage
+        n = (SMEM_LIMIT - 2048 - y_bytes - b) // stage
         return int(max(0, min(n, 6)))
 
-    def smem_bytes(self) -> int:
-        return self.n * self.k * 4 + self.nstage() * self.dim * STAGE_TILE_BYTES + 1024 + 1024
+    def smem_bytes(self, y_bytes: int = 8192) -> int:
+        return self.n * self.k * 4 + self.nstage(y_bytes) * self.dim * STAGE_TILE_BYTES + y_bytes + 1024 + 1024
 
 
 def plan_groups(spec: TPSpec) -> Optional[List[TcGroup]]:
@@ -110,56 +110,54 @@ def plan_groups(spec: TPSpec) -> Optional[List[TcGroup]]:
         g.paths.append(TcPath(n, ir1.l, ir2.l, iro.l, m1, o1[ins.i_in1], o2[ins.i_in2], woffs[n], float(ins.path_weight)))
     out = [groups[k] for k in sorted(groups)]
     for g in out:
-        if g.dim * g.n > 512 or g.nstage() < 2:
+        if g.dim * g.n > 512 or g.nstage() < 2 or 128 * spec.irreps_in2.dim * 4 > 8192:
             return None
     if spec.irreps_out.dim % 4 != 0 or any(g.out_off % 4 != 0 for g in out):
         return None
     return out
 
 
-ROW_BATCH = 8   # rows whose loads are issued together by a producer warp (memory-level parallelism)
-
-
 def _producer_path_code(p: TcPath, dim: int, d1_total: int, d2_total: int) -> str:
-    """Body of one `case` of the producer switch: fills this warp's 16 rows of every k sub-tile.
+    """Body of one `case` of the producer switch: fills this warp's rows of every k sub-tile.
 
-    In scope: xbase (-> x1[z0, u, 0] of this lane's channel), ybase (-> x2[z0, 0]), z0, Z, pw (producer
-    warp index), lane, stage.  Rows past Z read row Z-1 (valid memory) and their values are never used.
+    In scope: xbase (-> x1[z0, u, 0] of this lane's channel), sy (this warp's rows of x2 in shared
+    memory, [kRowsPerWarp][D2]), z0, Z, pw (producer warp index), lane, stage.  All global loads of the
+    warp's rows are issued before the first use (one exposed latency per chunk); rows past Z read
+    row Z-1 (valid memory) and their values are never used.
     """
     c = wigner_3j_numpy(p.l1, p.l2, p.l3) * p.pw
     d1, d2 = 2 * p.l1 + 1, 2 * p.l2 + 1
-    lines = [f"#pragma unroll\nfor (int batch = 0; batch < kRowsPerWarp / {ROW_BATCH}; ++batch) {{"]
-    lines.append(f"  float xi[{ROW_BATCH}][{d1}], yj[{ROW_BATCH}][{d2}];")
-    lines.append(f"#pragma unroll\n  for (int b = 0; b < {ROW_BATCH}; ++b) {{")
-    lines.append(f"    const int r = pw * kRowsPerWarp + batch * {ROW_BATCH} + b;")
-    lines.append("    const int64_t zr = (z0 + r < Z) ? r : (Z - 1 - z0);")
-    lines.append(f"    const float* xr = xbase + zr * {d1_total};")
-    lines.append(f"    const float* yr = ybase + zr * {d2_total} + {p.off2};")
-    lines.append(f"#pragma unroll\n    for (int i = 0; i < {d1}; ++i) xi[b][i] = xr[i];")
-    lines.append(f"#pragma unroll\n    for (int j = 0; j < {d2}; ++j) yj[b][j] = __ldg(yr + j);")
-    lines.append("  }")
-    lines.append(f"#pragma unroll\n  for (int b = 0; b < {ROW_BATCH}; ++b) {{")
-    lines.append(f"    const int r = pw * kRowsPerWarp + batch * {ROW_BATCH} + b;")
-    lines.append("    const uint32_t off = tc::sw128_offset(r, lane);")
+    lines = [f"float xi[kRowsPerWarp][{d1}];"]
+    lines.append("#pragma unroll\nfor (int b = 0; b < kRowsPerWarp; ++b) {")
+    lines.append("  const int r = pw * kRowsPerWarp + b;")
+    lines.append("  const int64_t zr = (z0 + r < Z) ? r : (Z - 1 - z0);")
+    lines.append(f"  const float* xr = xbase + zr * {d1_total};")
+    lines.append(f"#pragma unroll\n  for (int i = 0; i < {d1}; ++i) xi[b][i] = xr[i];")
+    lines.append("}")
+    lines.append("#pragma unroll\nfor (int b = 0; b < kRowsPerWarp; ++b) {")
+    lines.append("  const int r = pw * kRowsPerWarp + b;")
+    lines.append("  const uint32_t off = tc::sw128_offset(r, lane);")
+    lines.append(f"  float yj[{d2}];")
+    lines.append(f"#pragma unroll\n  for (int j = 0; j < {d2}; ++j) yj[j] = sy[b * {d2_total} + {p.off2} + j];")
     for k in range(dim):
         terms = []
         for i in range(d1):
             inner = [(j, c[i, j, k]) for j in range(d2) if c[i, j, k] != 0.0]
             if not inner:
                 continue
-            t = " + ".join(f"{_f(v)} * yj[b][{j}]" for j, v in inner)
+            t = " + ".join(f"{_f(v)} * yj[{j}]" for j, v in inner)
             terms.append(f"({t}) * xi[b][{i}]")
         expr = " + ".join(terms) if terms else "0.0f"
-        lines.append(f"    *reinterpret_cast<float*>(stage + {k} * TILE_BYTES + off) = tc::to_tf32({expr});")
-    lines.append("  }")
+        lines.append(f"  *reinterpret_cast<float*>(stage + {k} * TILE_BYTES + off) = tc::to_tf32({expr});")
     lines.append("}")
     return "\n".join(lines)
 
 
 def _chunk_cost(p: TcPath, dim: int) -> int:
-    """Relative cost of producing one 32-channel chunk of a path (loads + FMAs + stores per row)."""
+    """Relative cost of producing one 32-channel chunk of a path: one exposed load latency plus
+    loads, FMAs and stores per row."""
     c = wigner_3j_numpy(p.l1, p.l2, p.l3)
-    return 6 + (2 * p.l1 + 1) + (2 * p.l2 + 1) + 2 * int((c != 0).sum()) + 2 * dim
+    return 40 + (2 * p.l1 + 1) + (2 * p.l2 + 1) + 2 * int((c != 0).sum()) + 2 * dim
 
 
 def _indent(text: str, n: int) -> str:
@@ -210,6 +208,7 @@ __device__ __forceinline__ void run_group_{gi}(const float* __restrict__ x1, con
     uint64_t* bar_acc_empty = bar_acc_full + NBUF;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_acc_empty + NBUF);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    float* sY = reinterpret_cast<float*>(sA + NSTAGE * STAGE_BYTES + 1024);   // [128][D2]: x2 rows of the tile
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
@@ -271,15 +270,22 @@ __device__ __forceinline__ void run_group_{gi}(const float* __restrict__ x1, con
         const int pw = warp - kEpilogueWarps;
         uint32_t it = 0;
         bool ok = true;
+        float* sy = sY + pw * kRowsPerWarp * {d2};
         for (int64_t t = cta; t < tiles && ok; t += nctas) {{
             const int64_t z0 = t * 128;
+            __syncwarp();
+            for (int idx = lane; idx < kRowsPerWarp * {d2}; idx += 32) {{   // this warp's rows of x2 -> shared memory
+                const int r = pw * kRowsPerWarp + idx / {d2};
+                const int64_t zr = (z0 + r < Z) ? r : (Z - 1 - z0);
+                sy[idx] = x2[(z0 + zr) * {d2} + idx % {d2}];
+            }}
+            __syncwarp();
             for (int c = 0; c < NCHUNK; ++c, ++it) {{
                 const int s = it % NSTAGE;
                 const uint32_t ph = (it / NSTAGE) & 1;
                 if (!tc::mbar_wait(&bar_empty[s], ph ^ 1u, abort_flag)) {{ ok = false; break; }}
                 uint8_t* stage = sA + s * STAGE_BYTES;
                 const int path = kCPath{gi}[c], xoff = kXOff{gi}[c];
-                const float* ybase = x2 + z0 * {d2};
                 switch (path) {{
 {_indent(switch, 16)}
                 }}

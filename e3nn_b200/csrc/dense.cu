@@ -27,6 +27,7 @@ constexpr int kTM = 8;   // rows per thread
 constexpr int kTN = 4;   // output channels per thread
 constexpr int kRowsPerPass = (kDenseThreads / 32) * kTM;  // 64
 constexpr int kColsPerPass = 32 * kTN;                    // 128
+constexpr int kKBlock = 32;                               // summation block of the contraction index
 
 struct DenseGroup { int out_off, mul_out, dim3, K, kent_start, w_stride; };
 
@@ -110,24 +111,39 @@ __global__ void __launch_bounds__(kDenseThreads) dense_fwd_kernel(const int32_t*
                     }
                 }
             } else if (r0 < RT && w0 < g.mul_out) {
-                for (int kk = 0; kk < g.K; ++kk) {
-                    const float4 a0 = *reinterpret_cast<const float4*>(sA + kk * kRowsPerPass + r0);
-                    const float4 a1 = *reinterpret_cast<const float4*>(sA + kk * kRowsPerPass + r0 + 4);
-                    const float a[kTM] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-                    float wv[kTN];
-                    const float* wp = W + sW[kk];
-                    if (VEC4) {
-                        const float4 t = __ldg(reinterpret_cast<const float4*>(wp + w0));
-                        wv[0] = t.x; wv[1] = t.y; wv[2] = t.z; wv[3] = t.w;
-                    } else {
+                // K is summed in blocks of kKBlock with a fresh partial accumulator per block: the fp32
+                // rounding error then grows with sqrt(kKBlock) + sqrt(K / kKBlock) instead of sqrt(K)
+                for (int kb = 0; kb < g.K; kb += kKBlock) {
+                    float part[kTM][kTN];
 #pragma unroll
-                        for (int j = 0; j < kTN; ++j)
-                            wv[j] = (w0 + j < g.mul_out) ? __ldg(wp + static_cast<int64_t>(w0 + j) * g.w_stride) : 0.0f;
+                    for (int i = 0; i < kTM; ++i)
+#pragma unroll
+                        for (int j = 0; j < kTN; ++j) part[i][j] = 0.0f;
+                    const int kend = min(kb + kKBlock, g.K);
+#pragma unroll 4
+                    for (int kk = kb; kk < kend; ++kk) {
+                        const float4 a0 = *reinterpret_cast<const float4*>(sA + kk * kRowsPerPass + r0);
+                        const float4 a1 = *reinterpret_cast<const float4*>(sA + kk * kRowsPerPass + r0 + 4);
+                        const float a[kTM] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+                        float wv[kTN];
+                        const float* wp = W + sW[kk];
+                        if (VEC4) {
+                            const float4 t = __ldg(reinterpret_cast<const float4*>(wp + w0));
+                            wv[0] = t.x; wv[1] = t.y; wv[2] = t.z; wv[3] = t.w;
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < kTN; ++j)
+                                wv[j] = (w0 + j < g.mul_out) ? __ldg(wp + static_cast<int64_t>(w0 + j) * g.w_stride) : 0.0f;
+                        }
+#pragma unroll
+                        for (int i = 0; i < kTM; ++i)
+#pragma unroll
+                            for (int j = 0; j < kTN; ++j) part[i][j] = fmaf(a[i], wv[j], part[i][j]);
                     }
 #pragma unroll
                     for (int i = 0; i < kTM; ++i)
 #pragma unroll
-                        for (int j = 0; j < kTN; ++j) acc[i][j] = fmaf(a[i], wv[j], acc[i][j]);
+                        for (int j = 0; j < kTN; ++j) acc[i][j] += part[i][j];
                 }
             }
             if (r0 < RT && w0 < g.mul_out) {

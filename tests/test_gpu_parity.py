@@ -438,5 +438,15 @@ def test_interaction_block_forward_and_position_gradient(irreps, lmax):
         [block.fc.layer0.weight.detach().cpu().double(), block.fc.layer1.weight.detach().cpu().double()],
         block.lin.weight.detach().cpu().double(), 8, 5.0, num_neighbors, list(range(lmax + 1)), chunk=4096)
     (ref * G.double()).sum().backward()
-    assert rel_err(out.detach().cpu(), ref.detach()) < TOL
+    # context: the same chain evaluated by the oracle in fp32 on the CPU.  With ~26 x 23 x 64 products per
+    # output behind a 64-term fp32 radial network, fp32 itself sits at about 1e-5 x RMS on this block;
+    # the kernels must not be worse than that.
+    ref32 = orc.interaction_block(
+        str(tp.irreps_in1), str(tp.irreps_in2), str(tp.irreps_out), _ins(tp), str(block.irreps_out), pos,
+        node_x, src, dst, shift,
+        [block.fc.layer0.weight.detach().cpu(), block.fc.layer1.weight.detach().cpu()],
+        block.lin.weight.detach().cpu(), 8, 5.0, num_neighbors, list(range(lmax + 1)), chunk=4096)
+    err32 = rel_err(ref32, ref.detach())
+    err = rel_err(out.detach().cpu(), ref.detach())
+    assert err < max(TOL, 1.5 * err32), (err, err32)
     assert rel_err(p.grad.cpu(), p64.grad) < 5e-5   # gradient: long chain through sin/r, silu and the SH Jacobian
