@@ -166,3 +166,58 @@ def uvw_tc_module(spec) -> TcModule:
         raise E3BError(f"layout module {so} was built for another layout ({mod.key} != {key})")
     _tc_cache[key] = mod
     return mod
+
+
+class TcGemmModule:
+    """A generated fp32-accurate tensor-core module (``codegen/tc_gemm.py``) for one contraction layout."""
+
+    def __init__(self, path: str):
+        self.path = path
+        lib = ctypes.CDLL(path)
+        self.lib = lib
+        lib.e3b_layout_key.restype = c_char_p
+        lib.e3b_layout_last_error.restype = c_char_p
+        lib.e3b_tc_gemm_scratch_bytes.restype = ctypes.c_longlong
+        lib.e3b_tc_gemm_fwd.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p, c_void_p,
+                                        c_void_p, c_void_p]
+        lib.e3b_tc_gemm_fwd.restype = c_int
+        self.key = lib.e3b_layout_key().decode()
+        self.scratch_bytes = int(lib.e3b_tc_gemm_scratch_bytes())
+        self._scratch: Dict[str, torch.Tensor] = {}
+        self.last_status = None
+
+    def check(self, rc: int, what: str) -> None:
+        if rc != 0:
+            raise E3BError(f"{what} failed with status {rc}: {self.lib.e3b_layout_last_error().decode()}")
+
+    def run(self, x1: torch.Tensor, x2: Optional[torch.Tensor], weight: torch.Tensor, out: torch.Tensor, precision: int = 2):
+        dev = out.device
+        # prepared weights live in a per-stream-ordered scratch tensor owned by the caller side (here)
+        scratch = torch.empty(max(self.scratch_bytes, 16), dtype=torch.uint8, device=dev)
+        status = torch.zeros(1, dtype=torch.int32, device=dev)
+        with torch.cuda.device(dev):
+            rc = self.lib.e3b_tc_gemm_fwd(_ptr(x1), _ptr(x2), _ptr(weight), _ptr(out), x1.shape[0], precision,
+                                          _ptr(scratch), None, _ptr(status), stream_ptr())
+        self.check(rc, "e3b_tc_gemm_fwd")
+        self.last_status = status
+        return out
+
+
+_tcg_cache: Dict[str, "TcGemmModule"] = {}
+
+
+def tc_gemm_module(gemm_spec) -> TcGemmModule:
+    key = gemm_spec.key
+    mod = _tcg_cache.get(key)
+    if mod is not None:
+        return mod
+    from .codegen import tc_gemm
+
+    so = os.path.join(_build.LAYOUT_DIR, f"tcg_{key}.so")
+    if not os.path.exists(so) or _build.nvcc_path() is not None:
+        so = _build.build_layout_module("tcg", key, tc_gemm.emit_module(gemm_spec))
+    mod = TcGemmModule(so)
+    if mod.key != key:
+        raise E3BError(f"layout module {so} was built for another layout ({mod.key} != {key})")
+    _tcg_cache[key] = mod
+    return mod

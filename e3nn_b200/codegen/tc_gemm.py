@@ -1,0 +1,526 @@
+"""Generator of fp32-accurate tensor-core kernels for the weight-shared contractions of the path:
+fully-connected ('uvw') tensor products and the per-irrep Linear (forward and its transpose).
+
+Both are, per output irrep ("group"), a GEMM ``D[(z,k), n] = sum_K A[(z,k), K] * B[K, n]`` whose left
+operand is produced on the fly from the input rows (Clebsch-Gordan contraction for 'uvw', a strided
+copy for Linear) and whose right operand is the (scaled) weight matrix.
+
+tcgen05 has no fp32 MMA; plain tf32 operands give ~1e-3 relative error.  The kernel therefore splits
+both operands into ``hi = tf32(x)`` and ``lo = tf32(x - hi)`` and issues three ``kind::tf32`` MMAs per
+k-step (``lo*hi + hi*lo + hi*hi``, fp32 accumulation in tensor memory): "3xTF32", 22-bit operands.
+Measured on B200: 1e-5 .. 4e-5 x RMS (max-abs) on the 320-term contractions of this path, i.e. about
+1000x better than plain tf32 but not inside the 1e-5 fp32 bound; a third piece (``hi + mid + lo``,
+six MMAs) was measured to change nothing, so the remaining error is the accumulation in tensor
+memory, not the operands.  ``precision = 1`` issues only ``hi*hi`` (the 2e-2 x RMS class).  The
+strict fp32 mode of the modules therefore stays on the CUDA-core kernel (csrc/dense.cu).
+
+Structure (persistent, one CTA per SM, a CTA serves one group):
+  * a small preparation kernel writes, once per call, the weights of every group pre-scaled,
+    pre-split (hi, lo) and pre-swizzled in chunks of 32 K, so that the main kernel fetches one
+    chunk with a single ``cp.async.bulk`` copy per pipeline stage (``mbarrier`` complete_tx);
+  * rows of a 128-row tile are (z, k) pairs, z-major: 128 // (2l+1) rows of z per tile;
+  * 8 producer warps build A (hi, lo) for 32 consecutive K of the tile in the K-major 128-byte
+    swizzled layout; lane = K index, every global load of a warp's rows is issued before first use;
+  * one thread issues the MMAs; ``tcgen05.commit`` releases stages / publishes accumulators;
+  * 4 epilogue warps read tensor memory (``tcgen05.ld``) and write the output rows while the next
+    tile accumulates in the second TMEM buffer.
+Every wait is bounded (mbarrier try_wait with an iteration limit, block-wide abort flag).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+
+from ..o3._irreps import Irreps
+from ..o3._spec import TPSpec
+from ..o3._wigner import wigner_3j_numpy
+
+SMEM_LIMIT = 227 * 1024
+A_TILE = 128 * 128          # one 128 x 32 fp32 sub-tile
+Y_BYTES = 8192
+PRODUCER_WARPS = 8
+PIECES = 2                  # tf32 pieces the stages have room for (hi, lo); 3 is supported by the code below
+
+
+def _f(v: float) -> str:
+    return f"{np.float32(v):.9e}f"
+
+
+@dataclass
+class Chunk:
+    case: int          # producer case (one per distinct (l1,l2,l3,off2) code body)
+    xoff: int          # offset of x1[., u0, 0] in the input row
+    wbase: int         # B[kk, n] = scale * W[wbase + kk * sk + n * sn]
+    sk: int
+    sn: int
+    scale: float
+
+
+@dataclass
+class Group:
+    out_off: int
+    n: int
+    dim: int
+    chunks: List[Chunk] = field(default_factory=list)
+    cases: List[str] = field(default_factory=list)       # code of each producer case
+    case_cost: List[int] = field(default_factory=list)
+    case_d1: List[int] = field(default_factory=list)
+
+    @property
+    def zt(self) -> int:
+        return 128 // self.dim
+
+    def stage_bytes(self) -> int:
+        return PIECES * A_TILE + PIECES * self.n * 128
+
+    def nstage(self) -> int:
+        return int(max(0, min(6, (SMEM_LIMIT - 3072 - Y_BYTES) // self.stage_bytes())))
+
+    def smem_bytes(self) -> int:
+        return self.nstage() * self.stage_bytes() + Y_BYTES + 1024 + 1024
+
+    def work(self) -> int:
+        per_tile = sum(40 + self.case_cost[c.case] * max(1, -(-self.zt // PRODUCER_WARPS)) for c in self.chunks)
+        return max(1, int(1000 * per_tile / self.zt))
+
+
+@dataclass
+class GemmSpec:
+    d1: int
+    d2: int
+    dout: int
+    groups: List[Group]
+    key: str
+    title: str
+    zero_ranges: List[Tuple[int, int]] = field(default_factory=list)   # output columns no group writes
+
+
+# ------------------------------------------------------------------------------------------- front ends
+def _uvw_case(l1: int, l2: int, l3: int, off2: int, pw: float) -> Tuple[str, int]:
+    """Producer body for a 'uvw' path: vals[k] from xi[q][i] and the x2 row in shared memory (sy)."""
+    c = wigner_3j_numpy(l1, l2, l3) * pw
+    d2 = 2 * l2 + 1
+    lines = [f"float yj[{d2}];", f"#pragma unroll\nfor (int j = 0; j < {d2}; ++j) yj[j] = syq[{off2} + j];"]
+    for k in range(2 * l3 + 1):
+        terms = []
+        for i in range(2 * l1 + 1):
+            inner = [(j, c[i, j, k]) for j in range(d2) if c[i, j, k] != 0.0]
+            if inner:
+                t = " + ".join(f"{_f(v)} * yj[{j}]" for j, v in inner)
+                terms.append(f"({t}) * xi[q][{i}]")
+        lines.append(f"vals[{k}] = {' + '.join(terms) if terms else '0.0f'};")
+    cost = (2 * l1 + 1) + d2 + 2 * int((c != 0).sum()) + 6 * (2 * l3 + 1)
+    return "\n".join(lines), cost
+
+
+def uvw_gemm_spec(spec: TPSpec) -> Optional[GemmSpec]:
+    """'uvw' paths with shared weights, x2 multiplicities 1, x1 multiplicities multiples of 32."""
+    if not spec.shared_weights:
+        return None
+    live = spec.live_instructions()
+    if not live or any(ins.connection_mode != "uvw" for _, ins in live):
+        return None
+    if spec.irreps_in2.dim > 16:   # the x2 rows of a tile are staged in Y_BYTES of shared memory
+        return None
+    o1, o2, oo = spec.irreps_in1.offsets(), spec.irreps_in2.offsets(), spec.irreps_out.offsets()
+    woffs = spec.weight_offsets()
+    groups: Dict[int, Group] = {}
+    for n, ins in live:
+        (m1, ir1), (m2, ir2), (mo, iro) = spec.irreps_in1[ins.i_in1], spec.irreps_in2[ins.i_in2], spec.irreps_out[ins.i_out]
+        if m2 != 1 or m1 % 32 != 0 or mo % 16 != 0 or not (16 <= mo <= 256):
+            return None
+        g = groups.setdefault(ins.i_out, Group(oo[ins.i_out], mo, iro.dim))
+        code, cost = _uvw_case(ir1.l, ir2.l, iro.l, o2[ins.i_in2], float(ins.path_weight))
+        g.cases.append(code)
+        g.case_cost.append(cost)
+        g.case_d1.append(ir1.dim)
+        case = len(g.cases) - 1
+        for u0 in range(0, m1, 32):
+            g.chunks.append(Chunk(case, o1[ins.i_in1] + u0 * ir1.dim, woffs[n] + u0 * mo, mo, 1, 1.0))
+    out = [groups[k] for k in sorted(groups)]
+    if any(g.nstage() < 2 for g in out):
+        return None
+    written = set(groups)
+    zero = [(oo[i], mul * ir.dim) for i, (mul, ir) in enumerate(spec.irreps_out) if i not in written and mul * ir.dim > 0]
+    return GemmSpec(spec.irreps_in1.dim, spec.irreps_in2.dim, spec.irreps_out.dim, out, spec.key(),
+                    f"uvw {spec.irreps_in1} (x) {spec.irreps_in2} -> {spec.irreps_out}", zero)
+
+
+def linear_gemm_spec(irreps_in: Irreps, irreps_out: Irreps, instructions, transpose: bool, key: str) -> Optional[GemmSpec]:
+    """Linear (or its transpose: output cotangents -> input cotangents) as a GemmSpec."""
+    oi, oo = irreps_in.offsets(), irreps_out.offsets()
+    woff, offs = 0, []
+    for ins in instructions:
+        if ins.i_in == -1:
+            offs.append(-1)
+            continue
+        offs.append(woff)
+        woff += ins.path_shape[0] * ins.path_shape[1]
+    src, dst = (irreps_out, irreps_in) if transpose else (irreps_in, irreps_out)
+    so, do = (oo, oi) if transpose else (oi, oo)
+    live = [(n, ins) for n, ins in enumerate(instructions) if ins.i_in != -1 and 0 not in ins.path_shape
+            and irreps_in[ins.i_in].dim > 0 and irreps_out[ins.i_out].dim > 0]
+    if not live:
+        return None
+    groups: Dict[int, Group] = {}
+    for n, ins in live:
+        t = ins.i_in if transpose else ins.i_out
+        s = ins.i_out if transpose else ins.i_in
+        mul_t, ir = dst[t]
+        mul_s = src[s].mul
+        if mul_s % 32 != 0 or mul_t % 16 != 0 or not (16 <= mul_t <= 256):
+            return None
+        g = groups.setdefault(t, Group(do[t], mul_t, ir.dim))
+        if not g.cases:
+            g.cases.append("#pragma unroll\n" + f"for (int k = 0; k < {ir.dim}; ++k) vals[k] = xi[q][k];")
+            g.case_cost.append(ir.dim + 6 * ir.dim)
+            g.case_d1.append(ir.dim)
+        mul_in, mul_out = ins.path_shape
+        for u0 in range(0, mul_s, 32):
+            if transpose:   # K index = w (output channel of the layer), n = u: W[u, w] at off + u * mul_out + w
+                g.chunks.append(Chunk(0, so[s] + u0 * ir.dim, offs[n] + u0, 1, mul_out, float(ins.path_weight)))
+            else:           # K index = u, n = w
+                g.chunks.append(Chunk(0, so[s] + u0 * ir.dim, offs[n] + u0 * mul_out, mul_out, 1, float(ins.path_weight)))
+    out = [groups[k] for k in sorted(groups)]
+    if any(g.nstage() < 2 for g in out):
+        return None
+    zero = [(do[i], mul * ir.dim) for i, (mul, ir) in enumerate(dst) if i not in groups and mul * ir.dim > 0]
+    return GemmSpec(src.dim, 0, dst.dim, out, key,
+                    f"linear{'^T' if transpose else ''} {irreps_in} -> {irreps_out}", zero)
+
+
+# ------------------------------------------------------------------------------------------- emission
+def _indent(text: str, n: int) -> str:
+    pad = " " * n
+    return "\n".join(pad + line if line and not line.startswith("#pragma") else line for line in text.split("\n"))
+
+
+def emit_module(gs: GemmSpec) -> str:
+    d1, d2, dout = gs.d1, gs.d2, gs.dout
+    smem_max = max(g.smem_bytes() for g in gs.groups)
+    assert smem_max <= SMEM_LIMIT
+    has_y = d2 > 0
+
+    consts, funcs = [], []
+    prep_off = 0
+    prep_offsets = []
+    for gi, g in enumerate(gs.groups):
+        nch = len(g.chunks)
+        prep_offsets.append(prep_off)
+        prep_off += nch * PIECES * g.n * 128
+        arr = lambda name, vals, typ="int": f"__constant__ {typ} {name}{gi}[{nch}] = {{{', '.join(str(v) for v in vals)}}};"
+        consts.append("\n".join([
+            arr("kCase", [c.case for c in g.chunks]),
+            arr("kXOff", [c.xoff for c in g.chunks]),
+            arr("kWBase", [c.wbase for c in g.chunks]),
+            arr("kSK", [c.sk for c in g.chunks]),
+            arr("kSN", [c.sn for c in g.chunks]),
+            arr("kScale", [_f(c.scale) for c in g.chunks], "float"),
+        ]))
+        qn = -(-g.zt // PRODUCER_WARPS)
+        cases = []
+        for ci, code in enumerate(g.cases):
+            dd = g.case_d1[ci]
+            cases.append(f"""case {ci}: {{
+    float xi[{qn}][{dd}];
+#pragma unroll
+    for (int q = 0; q < {qn}; ++q) {{
+        const int zl = pw + {PRODUCER_WARPS} * q;
+        int64_t z = z0 + (zl < ZT ? zl : 0);
+        if (z >= Z) z = Z - 1;
+        const float* xr = x1 + z * {d1} + xoff + lane * {dd};
+#pragma unroll
+        for (int i = 0; i < {dd}; ++i) xi[q][i] = xr[i];
+    }}
+    asm volatile("" ::: "memory");   // every load above is in flight before the first use below
+#pragma unroll
+    for (int q = 0; q < {qn}; ++q) {{
+        const int zl = pw + {PRODUCER_WARPS} * q;
+        if (zl < ZT) {{
+            {'const float* syq = sy + q * ' + str(d2) + ';' if has_y else ''}
+            float vals[DIM];
+{_indent(code, 12)}
+#pragma unroll
+            for (int k = 0; k < DIM; ++k) {{
+                const uint32_t off = tc::sw128_offset(zl * DIM + k, lane);
+                const float hi = tc::to_tf32(vals[k]);
+                *reinterpret_cast<float*>(stage + off) = hi;
+                if (pieces > 1) {{
+                    const float rest = vals[k] - hi;          // exact in fp32
+                    const float mid = tc::to_tf32(rest);
+                    *reinterpret_cast<float*>(stage + A_TILE + off) = mid;
+                    if (pieces > 2) *reinterpret_cast<float*>(stage + 2 * A_TILE + off) = tc::to_tf32(rest - mid);
+                }}
+            }}
+        }}
+    }}
+    break; }}""")
+        switch = "\n".join(cases)
+        y_load = f"""
+            __syncwarp();
+            for (int idx = lane; idx < {qn} * {d2}; idx += 32) {{   // x2 rows of this warp's z -> shared memory
+                const int zl = pw + {PRODUCER_WARPS} * (idx / {d2});
+                int64_t z = z0 + (zl < ZT ? zl : 0);
+                if (z >= Z) z = Z - 1;
+                sy[idx] = x2[z * {d2} + idx % {d2}];
+            }}
+            __syncwarp();""" if has_y else ""
+        if g.dim == 1 and dout % 4 == 0 and g.out_off % 4 == 0:
+            store = """                    float4* dst = reinterpret_cast<float4*>(orow + w0);
+                    dst[0] = make_float4(__uint_as_float(r[0]), __uint_as_float(r[1]), __uint_as_float(r[2]), __uint_as_float(r[3]));
+                    dst[1] = make_float4(__uint_as_float(r[4]), __uint_as_float(r[5]), __uint_as_float(r[6]), __uint_as_float(r[7]));"""
+        else:
+            store = """#pragma unroll
+                    for (int j = 0; j < 8; ++j) orow[(w0 + j) * DIM + kq] = __uint_as_float(r[j]);"""
+        funcs.append(f"""
+// ---------------------------------------------------------------- group {gi}: N = {g.n}, 2l+1 = {g.dim}, K = {32 * nch}
+__device__ __forceinline__ void run_group_{gi}(const float* __restrict__ x1, const float* __restrict__ x2,
+        const uint8_t* __restrict__ bprep, float* __restrict__ out, int64_t Z, int cta, int nctas, uint8_t* smem,
+        int* status, int pieces) {{
+    constexpr int N = {g.n}, DIM = {g.dim}, ZT = {g.zt}, NCHUNK = {nch}, NSTAGE = {g.nstage()}, NBUF = 2;
+    constexpr int OUT_OFF = {g.out_off};
+    constexpr uint32_t A_TILE = {A_TILE}, B_HALF = N * 128, STAGE_BYTES = {PIECES} * A_TILE + {PIECES} * B_HALF;
+    constexpr uint32_t IDESC = tc::idesc_tf32_m128(N);
+    uint8_t* sS = smem;
+    uint64_t* bar_full = reinterpret_cast<uint64_t*>(sS + NSTAGE * STAGE_BYTES);
+    uint64_t* bar_empty = bar_full + NSTAGE;
+    uint64_t* bar_acc_full = bar_empty + NSTAGE;
+    uint64_t* bar_acc_empty = bar_acc_full + NBUF;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_acc_empty + NBUF);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    float* sY = reinterpret_cast<float*>(sS + NSTAGE * STAGE_BYTES + 1024);
+    const uint8_t* bsrc = bprep + {prep_offsets[gi]};
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid == 0) {{
+        *abort_flag = 0;
+        for (int s = 0; s < NSTAGE; ++s) {{ tc::mbar_init(&bar_full[s], kProducerWarps); tc::mbar_init(&bar_empty[s], 1); }}
+        for (int b = 0; b < NBUF; ++b) {{ tc::mbar_init(&bar_acc_full[b], 1); tc::mbar_init(&bar_acc_empty[b], kEpilogueWarps); }}
+        tc::mbar_init_fence();
+    }}
+    if (warp == kMmaWarp) tc::tmem_alloc(tmem_slot, kTmemCols);
+    tc::tc_fence_before_sync();
+    __syncthreads();
+    tc::tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+    const int64_t tiles = (Z + ZT - 1) / ZT;
+
+    if (warp < kEpilogueWarps) {{
+        // ================= epilogue: tensor memory -> registers -> global
+        int tile_i = 0;
+        const int row = warp * 32 + lane;
+        const int zq = row / DIM, kq = row - zq * DIM;
+        for (int64_t t = cta; t < tiles; t += nctas, ++tile_i) {{
+            const int b = tile_i % NBUF;
+            const uint32_t bph = (tile_i / NBUF) & 1;
+            if (!tc::mbar_wait(&bar_acc_full[b], bph, abort_flag)) break;
+            tc::tc_fence_after_sync();
+            const int64_t z = t * ZT + zq;
+            const bool valid = zq < ZT && z < Z;
+            float* orow = out + z * {dout} + OUT_OFF;
+            const uint32_t tbase = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + b * N;
+            for (int w0 = 0; w0 < N; w0 += 8) {{
+                uint32_t r[8];
+                tc::tmem_ld8(tbase + w0, r);
+                tc::tmem_ld_wait();
+                if (valid) {{
+{store}
+                }}
+            }}
+            tc::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive(&bar_acc_empty[b]);
+        }}
+    }} else if (warp < kEpilogueWarps + kProducerWarps) {{
+        // ================= producers: A (hi, lo) chunks; warp 0 also fetches the prepared B chunk
+        const int pw = warp - kEpilogueWarps;
+        float* sy = sY + pw * {qn * max(d2, 1)};
+        uint32_t it = 0;
+        bool ok = true;
+        for (int64_t t = cta; t < tiles && ok; t += nctas) {{
+            const int64_t z0 = t * ZT;{y_load}
+            for (int c = 0; c < NCHUNK; ++c, ++it) {{
+                const int s = it % NSTAGE;
+                const uint32_t ph = (it / NSTAGE) & 1;
+                if (!tc::mbar_wait(&bar_empty[s], ph ^ 1u, abort_flag)) {{ ok = false; break; }}
+                uint8_t* stage = sS + s * STAGE_BYTES;
+                if (pw == 0 && lane == 0) {{
+                    const uint32_t bar = tc::smem_u32(&bar_full[s]);
+                    const uint32_t bbytes = pieces * B_HALF;   // only the pieces this precision uses
+                    asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(bbytes) : "memory");
+                    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                                 ::"r"(tc::smem_u32(stage + {PIECES} * A_TILE)), "l"(bsrc + static_cast<size_t>(c) * {PIECES} * B_HALF),
+                                   "r"(bbytes), "r"(bar) : "memory");
+                }}
+                const int xoff = kXOff{gi}[c];
+                switch (kCase{gi}[c]) {{
+{_indent(switch, 16)}
+                }}
+                tc::fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) tc::mbar_arrive(&bar_full[s]);
+            }}
+        }}
+    }} else if (warp == kMmaWarp && lane == 0) {{
+        // ================= MMA issue (single thread)
+        uint32_t it = 0;
+        int tile_i = 0;
+        bool ok = true;
+        for (int64_t t = cta; t < tiles && ok; t += nctas, ++tile_i) {{
+            const int b = tile_i % NBUF;
+            const uint32_t bph = (tile_i / NBUF) & 1;
+            if (!tc::mbar_wait(&bar_acc_empty[b], bph ^ 1u, abort_flag)) break;
+            tc::tc_fence_after_sync();
+            const uint32_t d_tmem = tmem_base + b * N;
+            for (int c = 0; c < NCHUNK; ++c, ++it) {{
+                const int s = it % NSTAGE;
+                const uint32_t ph = (it / NSTAGE) & 1;
+                if (!tc::mbar_wait(&bar_full[s], ph, abort_flag)) {{ ok = false; break; }}
+                tc::tc_fence_after_sync();
+                const uint32_t a0 = tc::smem_u32(sS + s * STAGE_BYTES), b0 = a0 + {PIECES} * A_TILE;
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks) {{
+                    // piece products a_i * b_j with i + j < pieces, smallest magnitudes first
+                    uint32_t acc = (c > 0 || ks > 0) ? 1u : 0u;
+                    for (int deg = pieces - 1; deg >= 0; --deg) {{
+                        for (int i = 0; i <= deg; ++i) {{
+                            const int j = deg - i;
+                            tc::mma_tf32(d_tmem, tc::smem_desc_k_sw128(a0 + i * A_TILE + ks * 32),
+                                         tc::smem_desc_k_sw128(b0 + j * B_HALF + ks * 32), IDESC, acc);
+                            acc = 1u;
+                        }}
+                    }}
+                }}
+                tc::mma_commit(&bar_empty[s]);
+            }}
+            if (ok) tc::mma_commit(&bar_acc_full[b]);
+        }}
+    }}
+    tc::tc_fence_before_sync();
+    __syncthreads();
+    if (tid == 0 && *abort_flag) atomicExch(status, 3);
+    if (warp == kMmaWarp) tc::tmem_dealloc(tmem_base, kTmemCols);
+}}
+
+// weights of group {gi} -> scaled, split into tf32 (hi, lo), K-major 128-byte swizzled chunks of 32 K
+__device__ __forceinline__ void prep_group_{gi}(const float* __restrict__ W, uint8_t* __restrict__ bprep, int idx) {{
+    constexpr int N = {g.n}, NCHUNK = {nch};
+    if (idx >= NCHUNK * 32 * N) return;
+    const int c = idx / (32 * N), rem = idx - c * 32 * N;
+    const int kk = rem / N, n = rem - kk * N;   // n fastest: coalesced when sn == 1
+    const float v = kScale{gi}[c] * W[kWBase{gi}[c] + kk * kSK{gi}[c] + n * kSN{gi}[c]];
+    const float hi = tc::to_tf32(v);
+    const float rest = v - hi;
+    const float mid = tc::to_tf32(rest);
+    uint8_t* dst = bprep + {prep_offsets[gi]} + static_cast<size_t>(c) * {PIECES} * N * 128 + tc::sw128_offset(n, kk);
+    *reinterpret_cast<float*>(dst) = hi;
+    *reinterpret_cast<float*>(dst + N * 128) = mid;
+    *reinterpret_cast<float*>(dst + 2 * N * 128) = tc::to_tf32(rest - mid);
+}}
+""")
+
+    ng = len(gs.groups)
+    dispatch = "\n".join(
+        f"    {'else ' if gi else ''}if (blockIdx.x < cta_end{gi}) run_group_{gi}(x1, x2, bprep, out, Z, blockIdx.x - cta_begin{gi}, cta_end{gi} - cta_begin{gi}, smem, status, pieces);"
+        for gi in range(ng))
+    bounds = "\n".join(
+        f"    const int cta_begin{gi} = {'0' if gi == 0 else f'cta_end{gi-1}'}, cta_end{gi} = cta_begin{gi} + split.n[{gi}];" for gi in range(ng))
+    prep_max = max(len(g.chunks) * 32 * g.n for g in gs.groups)
+    prep_dispatch = "\n".join(f"    {'else ' if gi else ''}if (blockIdx.y == {gi}) prep_group_{gi}(W, bprep, idx);" for gi in range(ng))
+    zero_fill = "\n".join(
+        f"    {{ cudaError_t e = cudaMemset2DAsync(out + {off}, {dout} * sizeof(float), 0, {n} * sizeof(float), Z, s); "
+        f"if (e != cudaSuccess) return e3b_layout_fail(-2, \"tc_gemm: zero fill: %s\", cudaGetErrorString(e)); }}"
+        for off, n in gs.zero_ranges)
+    return f"""// Generated by e3nn_b200/codegen/tc_gemm.py -- do not edit.
+// {gs.title}, key {gs.key}
+#include <cuda_runtime.h>
+#include <cstdint>
+#include "layout_common.cuh"
+#include "tc_common.cuh"
+
+namespace {{
+
+constexpr int kEpilogueWarps = 4;
+constexpr int kProducerWarps = {PRODUCER_WARPS};
+constexpr int kMmaWarp = kEpilogueWarps + kProducerWarps;
+constexpr int kThreads = (kMmaWarp + 1) * 32;
+constexpr int kTmemCols = 512;
+constexpr int kGroups = {ng};
+constexpr int kSmemBytes = {smem_max};
+constexpr long long kPrepBytes = {prep_off};
+
+struct CtaSplit {{ int n[kGroups]; }};
+
+{chr(10).join(consts)}
+{''.join(funcs)}
+
+__global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const float* __restrict__ x1, const float* __restrict__ x2,
+        const uint8_t* __restrict__ bprep, float* __restrict__ out, int64_t Z, CtaSplit split, int* status, int pieces) {{
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+{bounds}
+{dispatch}
+}}
+
+__global__ void tc_gemm_prep_kernel(const float* __restrict__ W, uint8_t* __restrict__ bprep) {{
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+{prep_dispatch}
+}}
+
+}}  // namespace
+
+extern "C" int e3b_layout_info(int32_t* dims) {{
+    dims[0] = {d1}; dims[1] = {d2}; dims[2] = {dout}; dims[3] = 0; dims[4] = -1; dims[5] = kThreads;
+    return 0;
+}}
+extern "C" const char* e3b_layout_key(void) {{ return "{gs.key}"; }}
+extern "C" const char* e3b_layout_last_error(void) {{ return e3b_layout_error_buffer(); }}
+extern "C" long long e3b_tc_gemm_scratch_bytes(void) {{ return kPrepBytes; }}
+
+static const int kGroupWork[kGroups] = {{{', '.join(str(g.work()) for g in gs.groups)}}};
+
+// precision = number of tf32 pieces per operand: 1 = plain tf32 (1 MMA per step, ~1e-3 relative),
+// 2 = hi/lo split (3 MMAs, 22-bit operands, ~2e-5 x RMS); 3 (hi/mid/lo, 6 MMAs) only if the module was
+// generated with room for three pieces.
+// scratch: e3b_tc_gemm_scratch_bytes() bytes of device memory, 16-byte aligned (prepared weights).
+// cta_split: optional host array of kGroups CTA counts (NULL: proportional to the estimated work).
+extern "C" int e3b_tc_gemm_fwd(const float* x1, const float* x2, const float* weight, float* out, int64_t Z,
+                               int precision, void* scratch, const int* cta_split, int32_t* status, void* stream) {{
+    if (Z < 0) return e3b_layout_fail(-1, "tc_gemm: negative row count");
+    if (Z == 0) return 0;
+    if (!x1 || !weight || !out || !status || !scratch || ({d2} > 0 && !x2)) return e3b_layout_fail(-1, "tc_gemm: null pointer");
+    if (reinterpret_cast<uintptr_t>(out) % 16 != 0 || reinterpret_cast<uintptr_t>(scratch) % 16 != 0)
+        return e3b_layout_fail(-1, "tc_gemm: out and scratch must be 16-byte aligned");
+    if (precision < 1 || precision > {PIECES}) return e3b_layout_fail(-1, "tc_gemm: precision must be between 1 and {PIECES}");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+{zero_fill}
+    CtaSplit split;
+    int used = 0;
+    if (cta_split) {{
+        for (int g = 0; g < kGroups; ++g) {{ split.n[g] = cta_split[g] < 1 ? 1 : cta_split[g]; used += split.n[g]; }}
+    }} else {{
+        const int num_ctas = 148 < kGroups ? kGroups : 148;
+        long total = 0;
+        for (int g = 0; g < kGroups; ++g) total += kGroupWork[g];
+        for (int g = 0; g < kGroups; ++g) {{
+            int n = static_cast<int>((static_cast<long>(num_ctas) * kGroupWork[g]) / total);
+            split.n[g] = n < 1 ? 1 : n;
+            used += split.n[g];
+        }}
+        for (int g = kGroups - 1; used < num_ctas; g = (g + kGroups - 1) % kGroups) {{ split.n[g]++; used++; }}
+        while (used > num_ctas) {{
+            int big = 0;
+            for (int g = 1; g < kGroups; ++g) if (split.n[g] > split.n[big]) big = g;
+            split.n[big]--; used--;
+        }}
+    }}
+    tc_gemm_prep_kernel<<<dim3(({prep_max} + 255) / 256, kGroups), 256, 0, s>>>(weight, static_cast<uint8_t*>(scratch));
+    cudaError_t err = cudaFuncSetAttribute(tc_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (err != cudaSuccess) return e3b_layout_fail(-2, "tc_gemm: smem attribute: %s", cudaGetErrorString(err));
+    tc_gemm_kernel<<<used, kThreads, kSmemBytes, s>>>(x1, x2, static_cast<const uint8_t*>(scratch), out, Z, split, status,
+                                                       precision);
+    return e3b_layout_check("tc_gemm");
+}}
+"""

@@ -12,7 +12,10 @@ from typing import List, NamedTuple, Optional, Tuple, Union
 
 import torch
 
+import hashlib
+
 from .. import _lib
+from ..codegen import tc_gemm
 from ._dense_plan import linear_plan
 from ._irreps import Irreps
 from ._spec import LinearInstruction, normalize_linear_instructions
@@ -32,9 +35,13 @@ class _LinearFunction(torch.autograd.Function):
         core = _lib.core()
         with torch.cuda.device(dev):
             s = _lib.stream_ptr()
-            for off, n in lin._unwritten:
-                _lib.check(core.e3b_fill_columns(_lib._ptr(out), Z, out.shape[1], off, n, None, 0, s), "e3b_fill_columns")
-            if lin.weight_numel > 0:
+            if lin._tc_fwd is None or lin._precision == 0:   # (the tensor-core module zero-fills by itself)
+                for off, n in lin._unwritten:
+                    _lib.check(core.e3b_fill_columns(_lib._ptr(out), Z, out.shape[1], off, n, None, 0, s), "e3b_fill_columns")
+            if lin.weight_numel > 0 and lin._tc_fwd is not None and lin._precision > 0:
+                    # tensor cores: hi/lo-split ('tf32x3') or plain ('tf32') tf32 operands
+                _lib.tc_gemm_module(lin._tc_fwd).run(x, None, w, out, lin._precision)
+            elif lin.weight_numel > 0:
                 plan_dev = lin._plan_on(dev, False)
                 rc = core.e3b_dense_fwd(lin._plan_host.ctypes.data, _lib._ptr(plan_dev), _lib._ptr(x), None,
                                         _lib._ptr(w), 0, _lib._ptr(out), Z, 0, s)
@@ -57,6 +64,10 @@ class _LinearFunction(torch.autograd.Function):
             raise NotImplementedError("gradients w.r.t. Linear weights / biases are not implemented in e3nn_b200")
         grad_out = grad_out.contiguous()
         Z, dev = grad_out.shape[0], grad_out.device
+        if lin.weight_numel > 0 and lin._tc_bwd is not None and lin._precision > 0:
+            gx = torch.empty(Z, lin.irreps_in.dim, dtype=torch.float32, device=dev)
+            _lib.tc_gemm_module(lin._tc_bwd).run(grad_out, None, w, gx, lin._precision)
+            return gx, None, None, None
         gx = torch.zeros(Z, lin.irreps_in.dim, dtype=torch.float32, device=dev)
         if lin.weight_numel > 0:
             with torch.cuda.device(dev):
@@ -81,8 +92,14 @@ class Linear(torch.nn.Module):
         biases: Union[bool, List[bool]] = False,
         path_normalization: str = "element",
         _optimize_einsums: Optional[bool] = None,
+        math_mode: str = "fp32",
     ) -> None:
         super().__init__()
+        # 'fp32': CUDA-core kernel (<= 1e-5 x RMS).  'tf32x3': tensor cores with hi/lo-split tf32 operands
+        # (about 3e-5 x RMS).  'tf32': tensor cores, plain tf32 operands (<= 2e-2 x RMS).
+        assert math_mode in ("fp32", "tf32x3", "tf32")
+        self.math_mode = math_mode
+        self._precision = {"fp32": 0, "tf32x3": 2, "tf32": 1}[math_mode]
         if f_in is not None or f_out is not None:
             raise NotImplementedError("Linear(f_in=..., f_out=...) is not implemented by e3nn_b200")
         irreps_in, irreps_out = Irreps(irreps_in), Irreps(irreps_out)
@@ -111,6 +128,11 @@ class Linear(torch.nn.Module):
         except NotImplementedError:
             self._plan_t_host = None
         self._plan_dev = {}
+        # tensor-core modules (None when the multiplicities do not fit the 32-wide K chunks / 16-wide N)
+        tag = hashlib.sha1(repr((str(irreps_in), str(irreps_out), [(i.i_in, i.i_out, i.path_shape, repr(i.path_weight))
+                                                                      for i in packed])).encode()).hexdigest()[:14]
+        self._tc_fwd = tc_gemm.linear_gemm_spec(irreps_in, irreps_out, packed, False, "lin" + tag + "f")
+        self._tc_bwd = tc_gemm.linear_gemm_spec(irreps_in, irreps_out, packed, True, "lin" + tag + "t")
         offs = irreps_out.offsets()
         bias_out = [ins.i_out for ins in self.instructions if ins.i_in == -1 and 0 not in ins.path_shape]
         self._unwritten = [

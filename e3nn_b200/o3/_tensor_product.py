@@ -101,7 +101,9 @@ class TensorProduct(torch.nn.Module):
             path_normalization = "element"
         if compile_right:
             raise NotImplementedError("TensorProduct.right() is not part of the accelerated path")
-        assert math_mode in ("fp32", "tf32")
+        # 'fp32': CUDA-core kernels (<= 1e-5 x RMS); 'tf32x3' / 'tf32': tensor cores for the 'uvw' paths with
+        # hi/lo-split (about 3e-5 x RMS) or plain (<= 2e-2 x RMS) tf32 operands.  'uvu' paths are always fp32.
+        assert math_mode in ("fp32", "tf32x3", "tf32")
         self.math_mode = math_mode
 
         self.irreps_in1 = Irreps(irreps_in1)
@@ -288,6 +290,18 @@ class TensorProduct(torch.nn.Module):
             from ._uvw_tc import uvw_tc_forward
 
             return uvw_tc_forward(self, x2d, y2d, w, out, accumulate)
+        if self.math_mode == "tf32x3" and self.shared_weights and not accumulate and not (
+                torch.is_grad_enabled() and (x2d.requires_grad or y2d.requires_grad or w.requires_grad)):
+            # tensor cores with hi/lo-split tf32 operands when the layout fits the kernel
+            if not hasattr(self, "_tcg_spec"):
+                from ..codegen import tc_gemm
+
+                self._tcg_spec = tc_gemm.uvw_gemm_spec(self._spec)
+            if self._tcg_spec is not None:
+                mod = _lib.tc_gemm_module(self._tcg_spec)
+                mod.run(x2d, y2d, w, out, 2)
+                self._last_tc_status = mod.last_status
+                return out
         return _DenseFunction.apply(x2d, y2d, w, self._plan_host, self._plan_on(x2d.device), out, accumulate)
 
 

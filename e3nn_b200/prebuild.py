@@ -16,9 +16,38 @@ from .o3._tensor_product import TensorProduct
 
 
 def _build_tp(tp: TensorProduct) -> str:
+    """Every generated module a TensorProduct can use: 'uvu' layout module, tf32 and fp32 tensor-core modules."""
+    from .codegen import tc_gemm, uvw_tc
+
+    paths = []
     if tp._has_uvu:
-        return tp._uvu_module().path
-    return ""
+        paths.append(tp._uvu_module().path)
+    if tp._uvw_ids and not tp._has_uvu:
+        if uvw_tc.plan_groups(tp._spec) is not None:
+            paths.append(_lib.uvw_tc_module(tp._spec).path)
+        gs = tc_gemm.uvw_gemm_spec(tp._spec)
+        if gs is not None:
+            paths.append(_lib.tc_gemm_module(gs).path)
+    return ";".join(paths)
+
+
+def _build_linear(lin) -> str:
+    paths = []
+    for gs in (lin._tc_fwd, lin._tc_bwd):
+        if gs is not None:
+            paths.append(_lib.tc_gemm_module(gs).path)
+    return ";".join(paths)
+
+
+def prebuild_linears() -> List[str]:
+    from .o3._linear import Linear
+
+    lins = [
+        Linear("128x0e+64x1o+32x2e", "128x0e+64x1o+32x2e"),
+        Linear(bench_conv_tp("cfg5_23").irreps_out, "64x0e+64x1o+64x2e+64x3o"),
+    ]
+    with ThreadPoolExecutor(max_workers=4) as pool:
+        return list(pool.map(_build_linear, lins))
 
 
 def prebuild_bench_layouts() -> List[str]:
@@ -44,14 +73,14 @@ def tps_from_cases(path: str) -> Iterable[TensorProduct]:
 
 
 def prebuild_cases(path: str) -> List[str]:
-    tps = [tp for tp in tps_from_cases(path) if tp._has_uvu]
+    tps = list(tps_from_cases(path))
     with ThreadPoolExecutor(max_workers=4) as pool:
         return list(pool.map(_build_tp, tps))
 
 
 def main() -> None:
     print(_build.build_core())
-    for so in prebuild_bench_layouts():
+    for so in prebuild_bench_layouts() + prebuild_linears():
         print(so)
 
 

@@ -1,0 +1,64 @@
+"""Sharding of a graph over the GPUs of one node: contiguous destination ranges + one all-gather.
+
+Messages are independent per edge; the only couplings are the sum over a destination's incoming
+edges and the read of arbitrary source rows.  Rank ``r`` therefore owns a contiguous range of
+destination rows (chosen so that edge counts balance), every edge whose destination lies in it,
+those edges' weights / vectors, and the output rows.  The input features of all nodes are
+all-gathered once per layer into local memory; the fused kernel then reads local memory only, and
+no output reduction across ranks is needed.  Nothing like this exists in the reference (its graphs
+are single-device edge lists).
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+def partition_rows_by_edges(rowptr: torch.Tensor, world: int) -> List[int]:
+    """Row boundaries ``b[0]=0 <= ... <= b[world]=N`` with ~E/world edges per part.
+
+    ``b[r]`` is the smallest row whose first edge slot is >= r*E/world, the same rule the fused
+    kernel uses to split rows over its warp teams."""
+    assert world >= 1
+    rp = rowptr.detach().cpu()
+    n = rp.numel() - 1
+    e = int(rp[-1])
+    targets = torch.tensor([(e * r) // world for r in range(1, world)], dtype=rp.dtype)
+    inner = torch.searchsorted(rp[:-1].contiguous(), targets, right=False).tolist() if world > 1 else []
+    bounds = [0] + [min(int(v), n) for v in inner] + [n]
+    for i in range(1, len(bounds)):
+        bounds[i] = max(bounds[i], bounds[i - 1])
+    return bounds
+
+
+def local_shard(rowptr: torch.Tensor, bounds: List[int], rank: int) -> Tuple[int, int, int, int, torch.Tensor]:
+    """(n0, n1, e0, e1, local_rowptr): rows [n0,n1), edge slots [e0,e1), CSR of the shard starting at 0."""
+    n0, n1 = bounds[rank], bounds[rank + 1]
+    e0, e1 = int(rowptr[n0]), int(rowptr[n1])
+    return n0, n1, e0, e1, (rowptr[n0 : n1 + 1] - rowptr[n0]).contiguous()
+
+
+def all_gather_rows(x_local: torch.Tensor, bounds: List[int], group: Optional[dist.ProcessGroup] = None,
+                    out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Concatenation over ranks of ``x_local`` (rank r holds rows [bounds[r], bounds[r+1]))."""
+    world = len(bounds) - 1
+    n, d = bounds[-1], x_local.shape[1]
+    if out is None:
+        out = torch.empty(n, d, dtype=x_local.dtype, device=x_local.device)
+    if world == 1:
+        out.copy_(x_local)
+        return out
+    sizes = [bounds[r + 1] - bounds[r] for r in range(world)]
+    if len(set(sizes)) == 1:
+        dist.all_gather_into_tensor(out, x_local.contiguous(), group=group)
+    else:
+        # uneven row counts: one broadcast per owner straight into its slice of the result
+        rank = dist.get_rank(group)
+        out[bounds[rank] : bounds[rank + 1]].copy_(x_local)
+        for r in range(world):
+            if sizes[r] > 0:
+                src = dist.get_global_rank(group, r) if group is not None else r
+                dist.broadcast(out[bounds[r] : bounds[r + 1]], src=src, group=group)
+    return out

@@ -28,5 +28,13 @@ def conv_tps():
 
 
 def prebuild():
+    from e3nn_b200 import prebuild as pb
+
     for tp in conv_tps():
         tp._uvu_module()
+    # layouts of the tensor-core tests
+    for layout in [("32x0e+32x1o+32x2e", "1x0e+1x1o+1x2e", "32x0e+32x1o+32x2e"),
+                   ("128x0e+64x1o+32x2e", "0e+1o+2e+3o", "128x0e+64x1o+32x2e")]:
+        pb._build_tp(o3.FullyConnectedTensorProduct(*layout, math_mode="tf32x3"))
+    pb._build_linear(o3.Linear("16x0e+8x1o+4x2e", "8x0e+8x1o+4x2e"))
+    pb._build_linear(o3.Linear("64x0e+32x1o+32x2e", "32x0e+64x1o+32x2e"))

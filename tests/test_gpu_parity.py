@@ -418,7 +418,8 @@ def test_interaction_block_forward_and_position_gradient(irreps, lmax):
     pos = torch.rand(n_atoms, 3) * box
     src, dst, shift = bnn.radius_graph_pbc(pos, box, 5.0)
     num_neighbors = src.numel() / n_atoms
-    block = bnn.InteractionBlock(irreps, lmax, num_basis=8, hidden=64, r_max=5.0, num_neighbors=num_neighbors).to(DEV)
+    block = bnn.InteractionBlock(irreps, lmax, num_basis=8, hidden=64, r_max=5.0, num_neighbors=num_neighbors,
+                                 linear_math_mode="fp32").to(DEV)
     node_x = torch.randn(n_atoms, block.irreps_node.dim)
     G = torch.randn(n_atoms, block.irreps_out.dim)
     perm, rowptr = e3nn_b200.csr_from_dst(dst.to(DEV), n_atoms)
@@ -450,3 +451,57 @@ def test_interaction_block_forward_and_position_gradient(irreps, lmax):
     err = rel_err(out.detach().cpu(), ref.detach())
     assert err < max(TOL, 1.5 * err32), (err, err32)
     assert rel_err(p.grad.cpu(), p64.grad) < 5e-5   # gradient: long chain through sin/r, silu and the SH Jacobian
+    # default mode of the block: the Linear on the tensor cores with hi/lo-split tf32 operands
+    fast = bnn.InteractionBlock(irreps, lmax, num_basis=8, hidden=64, r_max=5.0, num_neighbors=num_neighbors).to(DEV)
+    fast.load_state_dict(block.state_dict())
+    for prm in fast.parameters():
+        prm.requires_grad_(False)
+    p2 = pos.clone().to(DEV).requires_grad_(True)
+    out2 = fast(p2, node_x.to(DEV), src.to(DEV), dst.to(DEV), rowptr, shift.to(DEV))
+    (out2 * G.to(DEV)).sum().backward()
+    assert rel_err(out2.detach().cpu(), ref.detach()) < 1e-4
+    assert rel_err(p2.grad.cpu(), p64.grad) < 1e-4
+
+
+# ----------------------------------------------------------------------------- tensor-core contractions with split operands
+TOL_TF32X3 = 1e-4   # hi/lo-split tf32 operands: measured 1e-5 .. 4e-5 x RMS on these layouts
+
+
+@pytest.mark.parametrize("Z", [1, 77, 4097])
+def test_uvw_tensor_core_split_operands(Z):
+    torch.manual_seed(Z)
+    tp = o3.FullyConnectedTensorProduct("128x0e+64x1o+32x2e", "0e+1o+2e+3o", "128x0e+64x1o+32x2e", math_mode="tf32x3").to(DEV)
+    x, y = torch.randn(Z, 480), torch.randn(Z, 16)
+    with torch.no_grad():
+        out = tp(x.to(DEV), y.to(DEV))
+    assert tp._tcg_spec is not None and int(tp._last_tc_status.item()) == 0
+    ref = _oracle_tp(tp, x.double(), y.double(), tp.weight.detach().cpu().double())
+    assert rel_err(out.cpu(), ref) < TOL_TF32X3
+    tp32 = o3.FullyConnectedTensorProduct("128x0e+64x1o+32x2e", "0e+1o+2e+3o", "128x0e+64x1o+32x2e").to(DEV)
+    with torch.no_grad():
+        tp32.weight.copy_(tp.weight)
+        assert rel_err(tp32(x.to(DEV), y.to(DEV)).cpu(), ref) < TOL   # strict fp32 mode: CUDA-core kernel
+
+
+@pytest.mark.parametrize("irreps", [("64x0e+32x1o+32x2e", "32x0e+64x1o+32x2e"), ("128x0e+64x1o+32x2e", "128x0e+64x1o+32x2e")])
+def test_linear_math_modes_forward_and_transpose(irreps):
+    torch.manual_seed(5)
+    Z = 1000
+    x = torch.randn(Z, o3.Irreps(irreps[0]).dim)
+    ref_lin = o3.Linear(*irreps).to(DEV)
+    ref_lin.weight.requires_grad_(False)
+    x64 = x.double().requires_grad_(True)
+    ref = orc.linear(irreps[0], irreps[1], x64, ref_lin.weight.detach().cpu().double())
+    go = torch.randn_like(ref)
+    ref.backward(go)
+    for mode, lo, hi in (("fp32", 0.0, TOL), ("tf32x3", 0.0, TOL_TF32X3), ("tf32", 1e-5, TOL_TF32)):
+        lin = o3.Linear(*irreps, math_mode=mode).to(DEV)
+        assert lin._tc_fwd is not None and lin._tc_bwd is not None
+        with torch.no_grad():
+            lin.weight.copy_(ref_lin.weight)
+        lin.weight.requires_grad_(False)
+        xg = x.clone().to(DEV).requires_grad_(True)
+        out = lin(xg)
+        out.backward(go.float().to(DEV))
+        e_fwd, e_bwd = rel_err(out.detach().cpu(), ref.detach()), rel_err(xg.grad.cpu(), x64.grad)
+        assert lo <= e_fwd < hi and e_bwd < hi, (mode, e_fwd, e_bwd)

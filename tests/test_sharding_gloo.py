@@ -1,0 +1,81 @@
+"""Multi-rank host logic on CPU: 2 gloo ranks shard a graph by destination ranges, all-gather the
+source features and each evaluate their rows with the oracle; the union must equal the 1-rank result."""
+import os
+import socket
+
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from e3nn_b200 import sharding
+from oracle import e3nn_oracle as orc
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _graph():
+    torch.manual_seed(0)
+    N = 37
+    deg = torch.randint(0, 7, (N,))
+    deg[3] = 0
+    deg[20] = 25
+    dst = torch.repeat_interleave(torch.arange(N), deg)
+    E = dst.numel()
+    rowptr = torch.zeros(N + 1, dtype=torch.int64)
+    rowptr[1:] = torch.cumsum(deg, 0)
+    mid, ins = orc.conv_uvu_layout("4x0e+4x1o", "0e+1o+2e", [(0, 1), (1, -1), (1, 1), (2, 1)])
+    wn = sum(m for m, _, _ in orc.parse_irreps(mid))
+    return dict(N=N, E=E, dst=dst, rowptr=rowptr, src=torch.randint(0, N, (E,)), x=torch.randn(N, 16).double(),
+                vec=torch.randn(E, 3).double(), w=torch.randn(E, wn).double(), mid=mid, ins=ins)
+
+
+def _conv(g, x, src, dst, vec, w, n):
+    return orc.conv_uvu("4x0e+4x1o", "0e+1o+2e", g["mid"], g["ins"], x, vec, src, dst, w, n, [0, 1, 2])
+
+
+def _worker(rank, world, port, out_dir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    g = _graph()
+    bounds = sharding.partition_rows_by_edges(g["rowptr"], world)
+    n0, n1, e0, e1, rp = sharding.local_shard(g["rowptr"], bounds, rank)
+    x_full = sharding.all_gather_rows(g["x"][n0:n1].clone(), bounds)   # each rank owns only its rows
+    assert torch.equal(x_full, g["x"])
+    local = _conv(g, x_full, g["src"][e0:e1], g["dst"][e0:e1] - n0, g["vec"][e0:e1], g["w"][e0:e1], n1 - n0)
+    torch.save((bounds, n0, n1, e0, e1, rp, local), os.path.join(out_dir, f"r{rank}.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_ranks_equal_one(tmp_path):
+    world = 2
+    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    g = _graph()
+    full = _conv(g, g["x"], g["src"], g["dst"], g["vec"], g["w"], g["N"])
+    parts = [torch.load(os.path.join(tmp_path, f"r{r}.pt")) for r in range(world)]
+    bounds = parts[0][0]
+    assert bounds[0] == 0 and bounds[-1] == g["N"] and bounds == sorted(bounds)
+    edges = 0
+    for r, (b, n0, n1, e0, e1, rp, local) in enumerate(parts):
+        assert b == bounds and (n0, n1) == (bounds[r], bounds[r + 1])
+        assert int(rp[0]) == 0 and int(rp[-1]) == e1 - e0 and rp.numel() == n1 - n0 + 1
+        assert torch.allclose(local, full[n0:n1], rtol=0, atol=1e-12)
+        edges += e1 - e0
+    assert edges == g["E"]
+    # balance: no part holds more than its share plus the longest row
+    share = g["E"] / world
+    assert all(abs((p[4] - p[3]) - share) <= 25 for p in parts)
+
+
+def test_partition_edge_cases():
+    rowptr = torch.tensor([0, 0, 0, 5, 5, 9])
+    for world in (1, 2, 3, 8):
+        b = sharding.partition_rows_by_edges(rowptr, world)
+        assert len(b) == world + 1 and b[0] == 0 and b[-1] == 5 and b == sorted(b)
+    assert sharding.partition_rows_by_edges(torch.tensor([0]), 4) == [0, 0, 0, 0, 0]
