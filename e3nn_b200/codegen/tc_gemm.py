@@ -191,6 +191,41 @@ def linear_gemm_spec(irreps_in: Irreps, irreps_out: Irreps, instructions, transp
                     f"linear{'^T' if transpose else ''} {irreps_in} -> {irreps_out}", zero)
 
 
+def matmul_gemm_spec(k: int, n: int, transpose: bool, scale: float, key: str) -> Optional[GemmSpec]:
+    """``out[z, :] = scale * x[z, :] @ W`` with ``W`` row-major ``[k, n]`` (or, transposed, ``g @ W^T``):
+    the dense layers of the radial network.  Wide outputs are cut into column tiles of at most 256."""
+    if transpose:
+        if n % 32 != 0 or k % 16 != 0 or not (16 <= k <= 256):
+            return None
+        g = Group(0, k, 1)
+        g.cases.append("vals[0] = xi[q][0];")
+        g.case_cost.append(8)
+        g.case_d1.append(1)
+        for n0 in range(0, n, 32):
+            g.chunks.append(Chunk(0, n0, n0, 1, n, scale))
+        groups = [g]
+        d_in, d_out = n, k
+    else:
+        if k % 32 != 0 or n % 16 != 0:
+            return None
+        groups = []
+        col = 0
+        while col < n:
+            width = min(256, n - col)
+            g = Group(col, width, 1)
+            g.cases.append("vals[0] = xi[q][0];")
+            g.case_cost.append(8)
+            g.case_d1.append(1)
+            for k0 in range(0, k, 32):
+                g.chunks.append(Chunk(0, k0, k0 * n + col, n, 1, scale))
+            groups.append(g)
+            col += width
+        d_in, d_out = k, n
+    if any(g.nstage() < 2 for g in groups):
+        return None
+    return GemmSpec(d_in, 0, d_out, groups, key, f"matmul{'^T' if transpose else ''} [{k} x {n}] scale {scale!r}")
+
+
 # ------------------------------------------------------------------------------------------- emission
 def _indent(text: str, n: int) -> str:
     pad = " " * n
@@ -417,7 +452,7 @@ __device__ __forceinline__ void prep_group_{gi}(const float* __restrict__ W, uin
     uint8_t* dst = bprep + {prep_offsets[gi]} + static_cast<size_t>(c) * {PIECES} * N * 128 + tc::sw128_offset(n, kk);
     *reinterpret_cast<float*>(dst) = hi;
     *reinterpret_cast<float*>(dst + N * 128) = mid;
-    *reinterpret_cast<float*>(dst + 2 * N * 128) = tc::to_tf32(rest - mid);
+    {'*reinterpret_cast<float*>(dst + 2 * N * 128) = tc::to_tf32(rest - mid);' if PIECES >= 3 else ''}
 }}
 """)
 

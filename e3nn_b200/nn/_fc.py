@@ -3,10 +3,12 @@
 ``FullyConnectedNet`` mirrors ``e3nn/nn/_fc.py:52-88`` (weights ``layer{i}.weight`` of shape
 ``[h_in, h_out]`` ~ N(0,1), every layer divided by sqrt(h_in), hidden layers followed by the
 activation rescaled to unit second moment, ``e3nn/math/_normalize_activation.py:9-57``) and ``bessel``
-mirrors ``e3nn/math/_bessel.py:6-37``.  The two matrix products are plain dense GEMMs and are left to
-cuBLAS through ``torch.matmul`` in fp32; the elementwise parts are torch operators.  Nothing here is
-a hand-written kernel yet: fusing this network into the convolution kernel is the next step for the
-full interaction block.
+mirrors ``e3nn/math/_bessel.py:6-37``.  With ``math_mode='tf32x3'`` the layers whose widths fit
+(h_in % 32 == 0, h_out % 16 == 0: the 64 -> weight_numel layer) run on the tcgen05 kernel of
+``codegen/tc_gemm.py`` with hi/lo-split tf32 operands, forward and input gradient; other layers and
+``math_mode='fp32'`` are plain dense GEMMs left to cuBLAS through ``torch.matmul`` in fp32.  The
+elementwise parts are torch operators.  Fusing this network into the convolution kernel (so that the
+per-edge weights never reach HBM) is the next step for the full interaction block.
 """
 from __future__ import annotations
 
@@ -15,6 +17,9 @@ from functools import lru_cache
 from typing import Callable, List, Optional
 
 import torch
+
+from .. import _lib
+from ..codegen import tc_gemm
 
 
 @lru_cache(maxsize=None)
@@ -37,25 +42,73 @@ def bessel(x: torch.Tensor, n: int, x_max: float = 1.0) -> torch.Tensor:
     )
 
 
+class _ScaledMatmul(torch.autograd.Function):
+    """``scale * x @ W`` on the tensor cores (hi/lo-split tf32 operands); gradient w.r.t. ``x`` only."""
+
+    @staticmethod
+    def forward(ctx, x, weight, fwd_spec, bwd_spec):
+        out = torch.empty(x.shape[0], weight.shape[1], dtype=torch.float32, device=x.device)
+        _lib.tc_gemm_module(fwd_spec).run(x, None, weight, out, 2)
+        ctx.save_for_backward(weight)
+        ctx.bwd_spec = bwd_spec
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        (weight,) = ctx.saved_tensors
+        if ctx.needs_input_grad[1]:
+            raise NotImplementedError("weight gradients of the tensor-core radial layer are not implemented")
+        gx = torch.empty(grad_out.shape[0], weight.shape[0], dtype=torch.float32, device=grad_out.device)
+        _lib.tc_gemm_module(ctx.bwd_spec).run(grad_out.contiguous(), None, weight, gx, 2)
+        return gx, None, None, None
+
+
 class _Layer(torch.nn.Module):
-    def __init__(self, h_in: int, h_out: int, act: Optional[Callable], cst: float, var_in: float, var_out: float):
+    def __init__(self, h_in: int, h_out: int, act: Optional[Callable], cst: float, var_in: float, var_out: float,
+                 math_mode: str = "fp32"):
         super().__init__()
         self.weight = torch.nn.Parameter(torch.randn(h_in, h_out))
         self.act, self.cst = act, cst
         self.h_in, self.h_out, self.var_in, self.var_out = h_in, h_out, var_in, var_out
+        self.math_mode = math_mode
+        self._tc = None
+
+    def _scale(self) -> float:
+        if self.act is not None:
+            return 1.0 / (self.h_in * self.var_in) ** 0.5
+        return 1.0 / (self.h_in * self.var_in / self.var_out) ** 0.5
+
+    def _tc_specs(self):
+        if self._tc is None:
+            s = self._scale()
+            tag = f"mm{self.h_in}x{self.h_out}s{abs(hash(repr(s))) % 10**10}"
+            self._tc = (tc_gemm.matmul_gemm_spec(self.h_in, self.h_out, False, s, tag + "f"),
+                        tc_gemm.matmul_gemm_spec(self.h_in, self.h_out, True, s, tag + "t"))
+        return self._tc
+
+    def _matmul(self, x: torch.Tensor) -> torch.Tensor:
+        use_tc = (self.math_mode == "tf32x3" and x.is_cuda and x.dtype == torch.float32 and x.dim() == 2
+                  and not (torch.is_grad_enabled() and self.weight.requires_grad))
+        if use_tc:
+            fwd, bwd = self._tc_specs()
+            if fwd is not None and bwd is not None:
+                return _ScaledMatmul.apply(x.contiguous(), self.weight, fwd, bwd)
+        return x @ (self.weight * self._scale())
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        x = self._matmul(x)
         if self.act is not None:
-            x = x @ (self.weight / (self.h_in * self.var_in) ** 0.5)
             return self.act(x) * (self.cst * self.var_out ** 0.5)
-        return x @ (self.weight / (self.h_in * self.var_in / self.var_out) ** 0.5)
+        return x
 
 
 class FullyConnectedNet(torch.nn.Sequential):
     """``FullyConnectedNet(hs, act)`` with the reference's parameter names (``layer0.weight`` ...)."""
 
-    def __init__(self, hs: List[int], act=None, variance_in: int = 1, variance_out: int = 1, out_act: bool = False):
+    def __init__(self, hs: List[int], act=None, variance_in: int = 1, variance_out: int = 1, out_act: bool = False,
+                 math_mode: str = "fp32"):
         super().__init__()
+        assert math_mode in ("fp32", "tf32x3")
         self.hs = list(hs)
         cst = 1.0
         if act is not None:
@@ -70,7 +123,7 @@ class FullyConnectedNet(torch.nn.Sequential):
             last = i == len(self.hs) - 2
             var_out = variance_out if last else 1
             a = act if (not last or out_act) else None
-            setattr(self, f"layer{i}", _Layer(h1, h2, a, cst, var_in, var_out))
+            setattr(self, f"layer{i}", _Layer(h1, h2, a, cst, var_in, var_out, math_mode))
             var_in = var_out
 
     def __repr__(self) -> str:

@@ -52,13 +52,15 @@ def radius_graph_pbc(pos: torch.Tensor, box: float, cutoff: float) -> Tuple[torc
 
 class InteractionBlock(torch.nn.Module):
     def __init__(self, irreps_node, lmax: int, num_basis: int = 8, hidden: int = 64, r_max: float = 5.0,
-                 num_neighbors: float = 1.0, irreps_out=None, linear_math_mode: str = "tf32x3"):
+                 num_neighbors: float = 1.0, irreps_out=None, linear_math_mode: str = "tf32x3",
+                 radial_math_mode: str = "tf32x3"):
         super().__init__()
         self.irreps_node = Irreps(irreps_node)
         self.irreps_sh = Irreps.spherical_harmonics(lmax)
         self.irreps_out = Irreps(irreps_out) if irreps_out is not None else self.irreps_node
         self.tp = layouts.conv_tensor_product(self.irreps_node, self.irreps_sh, self.irreps_out)
-        self.fc = FullyConnectedNet([num_basis, hidden, self.tp.weight_numel], torch.nn.functional.silu)
+        self.fc = FullyConnectedNet([num_basis, hidden, self.tp.weight_numel], torch.nn.functional.silu,
+                                    math_mode=radial_math_mode)
         self.lin = Linear(self.tp.irreps_out, self.irreps_out, math_mode=linear_math_mode)
         self.num_basis, self.r_max, self.num_neighbors = num_basis, r_max, num_neighbors
 

@@ -78,9 +78,22 @@ def prebuild_cases(path: str) -> List[str]:
         return list(pool.map(_build_tp, tps))
 
 
+def prebuild_radial() -> List[str]:
+    """Tensor-core modules of the 64 -> weight_numel radial layers of the benchmark interaction block."""
+    from .nn._fc import _Layer
+
+    out = []
+    for wn in (bench_conv_tp("cfg5_23").weight_numel,):
+        layer = _Layer(64, wn, None, 1.0, 1, 1, "tf32x3")
+        for gs in layer._tc_specs():
+            if gs is not None:
+                out.append(_lib.tc_gemm_module(gs).path)
+    return out
+
+
 def main() -> None:
     print(_build.build_core())
-    for so in prebuild_bench_layouts() + prebuild_linears():
+    for so in prebuild_bench_layouts() + prebuild_linears() + prebuild_radial():
         print(so)
 
 

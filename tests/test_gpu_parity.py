@@ -419,7 +419,7 @@ def test_interaction_block_forward_and_position_gradient(irreps, lmax):
     src, dst, shift = bnn.radius_graph_pbc(pos, box, 5.0)
     num_neighbors = src.numel() / n_atoms
     block = bnn.InteractionBlock(irreps, lmax, num_basis=8, hidden=64, r_max=5.0, num_neighbors=num_neighbors,
-                                 linear_math_mode="fp32").to(DEV)
+                                 linear_math_mode="fp32", radial_math_mode="fp32").to(DEV)
     node_x = torch.randn(n_atoms, block.irreps_node.dim)
     G = torch.randn(n_atoms, block.irreps_out.dim)
     perm, rowptr = e3nn_b200.csr_from_dst(dst.to(DEV), n_atoms)
