@@ -40,6 +40,7 @@ from ..o3._wigner import wigner_3j_numpy
 SMEM_LIMIT = 227 * 1024
 A_TILE = 128 * 128          # one 128 x 32 fp32 sub-tile
 Y_BYTES = 8192
+EPI_BYTES = 4 * 32 * 64 * 4   # 4 epilogue warps x (32 rows x 64 columns) fp32
 PRODUCER_WARPS = 8
 PIECES = 2                  # tf32 pieces the stages have room for (hi, lo); 3 is supported by the code below
 
@@ -72,14 +73,24 @@ class Group:
     def zt(self) -> int:
         return 128 // self.dim
 
+    has_y: bool = True
+    aligned_out: bool = True   # output rows allow 16-byte stores
+
     def stage_bytes(self) -> int:
         return PIECES * A_TILE + PIECES * self.n * 128
 
+    def staged_epilogue(self) -> bool:
+        """dim == 1 groups transpose their output through shared memory for fully coalesced stores."""
+        return self.dim == 1 and self.n % 64 == 0 and self.aligned_out
+
+    def extra_bytes(self) -> int:
+        return (Y_BYTES if self.has_y else 0) + (EPI_BYTES if self.staged_epilogue() else 0)
+
     def nstage(self) -> int:
-        return int(max(0, min(6, (SMEM_LIMIT - 3072 - Y_BYTES) // self.stage_bytes())))
+        return int(max(0, min(6, (SMEM_LIMIT - 3072 - self.extra_bytes()) // self.stage_bytes())))
 
     def smem_bytes(self) -> int:
-        return self.nstage() * self.stage_bytes() + Y_BYTES + 1024 + 1024
+        return self.nstage() * self.stage_bytes() + self.extra_bytes() + 1024 + 1024
 
     def work(self) -> int:
         per_tile = sum(40 + self.case_cost[c.case] * max(1, -(-self.zt // PRODUCER_WARPS)) for c in self.chunks)
@@ -140,6 +151,9 @@ def uvw_gemm_spec(spec: TPSpec) -> Optional[GemmSpec]:
         for u0 in range(0, m1, 32):
             g.chunks.append(Chunk(case, o1[ins.i_in1] + u0 * ir1.dim, woffs[n] + u0 * mo, mo, 1, 1.0))
     out = [groups[k] for k in sorted(groups)]
+    for g in out:
+        g.has_y = True
+        g.aligned_out = spec.irreps_out.dim % 4 == 0 and g.out_off % 4 == 0
     if any(g.nstage() < 2 for g in out):
         return None
     written = set(groups)
@@ -184,6 +198,9 @@ def linear_gemm_spec(irreps_in: Irreps, irreps_out: Irreps, instructions, transp
             else:           # K index = u, n = w
                 g.chunks.append(Chunk(0, so[s] + u0 * ir.dim, offs[n] + u0 * mul_out, mul_out, 1, float(ins.path_weight)))
     out = [groups[k] for k in sorted(groups)]
+    for g in out:
+        g.has_y = False
+        g.aligned_out = dst.dim % 4 == 0 and g.out_off % 4 == 0
     if any(g.nstage() < 2 for g in out):
         return None
     zero = [(do[i], mul * ir.dim) for i, (mul, ir) in enumerate(dst) if i not in groups and mul * ir.dim > 0]
@@ -221,6 +238,9 @@ def matmul_gemm_spec(k: int, n: int, transpose: bool, scale: float, key: str) ->
             groups.append(g)
             col += width
         d_in, d_out = k, n
+    for g in groups:
+        g.has_y = False
+        g.aligned_out = d_out % 4 == 0 and g.out_off % 4 == 0
     if any(g.nstage() < 2 for g in groups):
         return None
     return GemmSpec(d_in, 0, d_out, groups, key, f"matmul{'^T' if transpose else ''} [{k} x {n}] scale {scale!r}")
@@ -255,44 +275,97 @@ def emit_module(gs: GemmSpec) -> str:
             arr("kScale", [_f(c.scale) for c in g.chunks], "float"),
         ]))
         qn = -(-g.zt // PRODUCER_WARPS)
+        def load_code(ci: int, xi: str, xoff: str) -> str:
+            dd = g.case_d1[ci]
+            return f"""#pragma unroll
+for (int q = 0; q < {qn}; ++q) {{{{
+    const float* xr = xrow[q] + ({xoff} + lane * {dd});
+#pragma unroll
+    for (int i = 0; i < {dd}; ++i) {xi}[q][i] = xr[i];
+}}}}""".replace("{{", "{").replace("}}", "}")
+
+        def compute_code(ci: int, xi: str, stage: str) -> str:
+            body = g.cases[ci].replace("xi[q]", f"{xi}[q]")
+            ysrc = f"const float* syq = sy + q * {d2};" if has_y else ""
+            return f"""#pragma unroll
+for (int q = 0; q < {qn}; ++q) {{{{
+    const int zl = pw + {PRODUCER_WARPS} * q;
+    if (zl < ZT) {{{{
+        {ysrc}
+        float vals[DIM];
+{_indent(body, 8)}
+#pragma unroll
+        for (int k = 0; k < DIM; ++k) {{{{
+            const uint32_t off = soff[q * DIM + k];
+            const float hi = tc::to_tf32(vals[k]);
+            *reinterpret_cast<float*>({stage} + off) = hi;
+            if (pieces > 1) {{{{
+                const float rest = vals[k] - hi;          // exact in fp32
+                const float mid = tc::to_tf32(rest);
+                *reinterpret_cast<float*>({stage} + A_TILE + off) = mid;
+                if (pieces > 2) *reinterpret_cast<float*>({stage} + 2 * A_TILE + off) = tc::to_tf32(rest - mid);
+            }}}}
+        }}}}
+    }}}}
+}}}}""".replace("{{", "{").replace("}}", "}")
+
         cases = []
         for ci, code in enumerate(g.cases):
             dd = g.case_d1[ci]
-            cases.append(f"""case {ci}: {{
-    float xi[{qn}][{dd}];
-#pragma unroll
-    for (int q = 0; q < {qn}; ++q) {{
-        const int zl = pw + {PRODUCER_WARPS} * q;
-        int64_t z = z0 + (zl < ZT ? zl : 0);
-        if (z >= Z) z = Z - 1;
-        const float* xr = x1 + z * {d1} + xoff + lane * {dd};
-#pragma unroll
-        for (int i = 0; i < {dd}; ++i) xi[q][i] = xr[i];
-    }}
-    asm volatile("" ::: "memory");   // every load above is in flight before the first use below
-#pragma unroll
-    for (int q = 0; q < {qn}; ++q) {{
-        const int zl = pw + {PRODUCER_WARPS} * q;
-        if (zl < ZT) {{
-            {'const float* syq = sy + q * ' + str(d2) + ';' if has_y else ''}
-            float vals[DIM];
-{_indent(code, 12)}
-#pragma unroll
-            for (int k = 0; k < DIM; ++k) {{
-                const uint32_t off = tc::sw128_offset(zl * DIM + k, lane);
-                const float hi = tc::to_tf32(vals[k]);
-                *reinterpret_cast<float*>(stage + off) = hi;
-                if (pieces > 1) {{
-                    const float rest = vals[k] - hi;          // exact in fp32
-                    const float mid = tc::to_tf32(rest);
-                    *reinterpret_cast<float*>(stage + A_TILE + off) = mid;
-                    if (pieces > 2) *reinterpret_cast<float*>(stage + 2 * A_TILE + off) = tc::to_tf32(rest - mid);
-                }}
-            }}
-        }}
-    }}
-    break; }}""")
+            cases.append(
+                f"case {ci}: {{\n    float xi[{qn}][{dd}];\n{_indent(load_code(ci, 'xi', 'xoff'), 4)}\n"
+                f"    asm volatile(\"\" ::: \"memory\");   // every load above is in flight before the first use below\n"
+                f"{_indent(compute_code(ci, 'xi', 'stage'), 4)}\n    break; }}"
+            )
+        # chunk batching: groups with a single cheap case load two chunks' rows before converting either,
+        # doubling the bytes a producer warp keeps in flight (these groups stream their A rows from HBM)
+        batch = 2 if (len(g.cases) == 1 and nch % 2 == 0 and qn * g.case_d1[0] <= 16 and g.nstage() >= 4) else 1
         switch = "\n".join(cases)
+        issue_b = lambda stage, bar, c: f"""if (pw == 0 && lane == 0) {{{{
+    const uint32_t bar = tc::smem_u32({bar});
+    const uint32_t bbytes = pieces * B_HALF;   // only the pieces this precision uses
+    asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(bbytes) : "memory");
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(tc::smem_u32({stage} + {PIECES} * A_TILE)), "l"(bsrc + static_cast<size_t>({c}) * {PIECES} * B_HALF),
+                   "r"(bbytes), "r"(bar) : "memory");
+}}}}""".replace("{{", "{").replace("}}", "}")
+        if batch == 1:
+            PRODUCER_LOOP = f"""            for (int c = 0; c < NCHUNK; ++c, ++it) {{
+                const int s = it % NSTAGE;
+                const uint32_t ph = (it / NSTAGE) & 1;
+                if (!tc::mbar_wait(&bar_empty[s], ph ^ 1u, abort_flag)) {{ ok = false; break; }}
+                uint8_t* stage = sS + s * STAGE_BYTES;
+{_indent(issue_b('stage', '&bar_full[s]', 'c'), 16)}
+                const int xoff = kXOff{gi}[c];
+                switch (kCase{gi}[c]) {{
+{_indent(switch, 16)}
+                }}
+                tc::fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) tc::mbar_arrive(&bar_full[s]);"""
+        else:
+            dd = g.case_d1[0]
+            PRODUCER_LOOP = f"""            for (int c = 0; c < NCHUNK; c += 2, it += 2) {{
+                const int s0 = it % NSTAGE, s1 = (it + 1) % NSTAGE;
+                const uint32_t ph0 = (it / NSTAGE) & 1, ph1 = ((it + 1) / NSTAGE) & 1;
+                if (!tc::mbar_wait(&bar_empty[s0], ph0 ^ 1u, abort_flag)) {{ ok = false; break; }}
+                if (!tc::mbar_wait(&bar_empty[s1], ph1 ^ 1u, abort_flag)) {{ ok = false; break; }}
+                uint8_t* stage0 = sS + s0 * STAGE_BYTES;
+                uint8_t* stage1 = sS + s1 * STAGE_BYTES;
+{_indent(issue_b('stage0', '&bar_full[s0]', 'c'), 16)}
+{_indent(issue_b('stage1', '&bar_full[s1]', '(c + 1)'), 16)}
+                float xa[{qn}][{dd}], xb[{qn}][{dd}];
+{_indent(load_code(0, 'xa', f'kXOff{gi}[c]'), 16)}
+{_indent(load_code(0, 'xb', f'kXOff{gi}[c + 1]'), 16)}
+                asm volatile("" ::: "memory");   // both chunks' loads are in flight before the first use below
+{_indent(compute_code(0, 'xa', 'stage0'), 16)}
+                tc::fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) tc::mbar_arrive(&bar_full[s0]);
+{_indent(compute_code(0, 'xb', 'stage1'), 16)}
+                tc::fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) tc::mbar_arrive(&bar_full[s1]);"""
         y_load = f"""
             __syncwarp();
             for (int idx = lane; idx < {qn} * {d2}; idx += 32) {{   // x2 rows of this warp's z -> shared memory
@@ -303,12 +376,62 @@ def emit_module(gs: GemmSpec) -> str:
             }}
             __syncwarp();""" if has_y else ""
         if g.dim == 1 and dout % 4 == 0 and g.out_off % 4 == 0:
-            store = """                    float4* dst = reinterpret_cast<float4*>(orow + w0);
-                    dst[0] = make_float4(__uint_as_float(r[0]), __uint_as_float(r[1]), __uint_as_float(r[2]), __uint_as_float(r[3]));
-                    dst[1] = make_float4(__uint_as_float(r[4]), __uint_as_float(r[5]), __uint_as_float(r[6]), __uint_as_float(r[7]));"""
+            store = """#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+                        reinterpret_cast<float4*>(orow + w0)[q] = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
+                                                                             __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));"""
         else:
             store = """#pragma unroll
-                    for (int j = 0; j < 8; ++j) orow[(w0 + j) * DIM + kq] = __uint_as_float(r[j]);"""
+                    for (int j = 0; j < 16; ++j) orow[(w0 + j) * DIM + kq] = __uint_as_float(r[j]);"""
+        if g.staged_epilogue():
+            EPILOGUE = f"""            // 64 columns at a time: registers -> this warp's staging tile (16-byte chunks XOR-swizzled by row,
+            // conflict free) -> read back two rows per instruction -> fully coalesced 256-byte row segments
+            float* se = sE + warp * (32 * 64);
+            for (int wb = 0; wb < N; wb += 64) {{{{
+                uint32_t r0[16], r1[16], r2[16], r3[16];
+                tc::tmem_ld16(tbase + wb, r0); tc::tmem_ld16(tbase + wb + 16, r1);
+                tc::tmem_ld16(tbase + wb + 32, r2); tc::tmem_ld16(tbase + wb + 48, r3);
+                tc::tmem_ld_wait();
+                float4* mine = reinterpret_cast<float4*>(se + lane * 64);
+                const int sw = lane & 15;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {{{{
+                    mine[(c) ^ sw] = make_float4(__uint_as_float(r0[4 * c]), __uint_as_float(r0[4 * c + 1]), __uint_as_float(r0[4 * c + 2]), __uint_as_float(r0[4 * c + 3]));
+                    mine[(c + 4) ^ sw] = make_float4(__uint_as_float(r1[4 * c]), __uint_as_float(r1[4 * c + 1]), __uint_as_float(r1[4 * c + 2]), __uint_as_float(r1[4 * c + 3]));
+                    mine[(c + 8) ^ sw] = make_float4(__uint_as_float(r2[4 * c]), __uint_as_float(r2[4 * c + 1]), __uint_as_float(r2[4 * c + 2]), __uint_as_float(r2[4 * c + 3]));
+                    mine[(c + 12) ^ sw] = make_float4(__uint_as_float(r3[4 * c]), __uint_as_float(r3[4 * c + 1]), __uint_as_float(r3[4 * c + 2]), __uint_as_float(r3[4 * c + 3]));
+                }}}}
+                __syncwarp();
+                const int half = lane >> 4, cc = lane & 15;
+#pragma unroll 4
+                for (int rr = 0; rr < 32; rr += 2) {{{{
+                    const int rl = rr + half;
+                    const float4 v = reinterpret_cast<const float4*>(se + rl * 64)[cc ^ (rl & 15)];
+                    const int64_t zr = t * ZT + warp * 32 + rl;
+                    if (zr < Z) reinterpret_cast<float4*>(out + zr * {dout} + OUT_OFF + wb)[cc] = v;
+                }}}}
+                __syncwarp();
+            }}}}""".replace("{{", "{").replace("}}", "}")
+        else:
+            EPILOGUE = f"""            // 16 columns per tcgen05.ld; the next load is in flight while the previous block is stored
+            // (a register block is only read after the wait that follows its load)
+            auto store16 = [&](const uint32_t (&r)[16], int w0) {{{{
+                if (valid) {{{{
+{store}
+                }}}}
+            }}}};
+            uint32_t ra[16], rb[16];
+            tc::tmem_ld16(tbase, ra);
+            for (int w0 = 0; w0 < N; w0 += 32) {{{{
+                tc::tmem_ld_wait();
+                if (w0 + 16 < N) tc::tmem_ld16(tbase + w0 + 16, rb);
+                store16(ra, w0);
+                if (w0 + 16 < N) {{{{
+                    tc::tmem_ld_wait();
+                    if (w0 + 32 < N) tc::tmem_ld16(tbase + w0 + 32, ra);
+                    store16(rb, w0 + 16);
+                }}}}
+            }}}}""".replace("{{", "{").replace("}}", "}")
         funcs.append(f"""
 // ---------------------------------------------------------------- group {gi}: N = {g.n}, 2l+1 = {g.dim}, K = {32 * nch}
 __device__ __forceinline__ void run_group_{gi}(const float* __restrict__ x1, const float* __restrict__ x2,
@@ -326,6 +449,7 @@ __device__ __forceinline__ void run_group_{gi}(const float* __restrict__ x1, con
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_acc_empty + NBUF);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     float* sY = reinterpret_cast<float*>(sS + NSTAGE * STAGE_BYTES + 1024);
+    float* sE = sY + {(Y_BYTES if g.has_y else 0) // 4};   // epilogue staging (only used by staged epilogues)
     const uint8_t* bsrc = bprep + {prep_offsets[gi]};
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -356,14 +480,7 @@ __device__ __forceinline__ void run_group_{gi}(const float* __restrict__ x1, con
             const bool valid = zq < ZT && z < Z;
             float* orow = out + z * {dout} + OUT_OFF;
             const uint32_t tbase = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + b * N;
-            for (int w0 = 0; w0 < N; w0 += 8) {{
-                uint32_t r[8];
-                tc::tmem_ld8(tbase + w0, r);
-                tc::tmem_ld_wait();
-                if (valid) {{
-{store}
-                }}
-            }}
+{EPILOGUE}
             tc::tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) tc::mbar_arrive(&bar_acc_empty[b]);
@@ -374,28 +491,22 @@ __device__ __forceinline__ void run_group_{gi}(const float* __restrict__ x1, con
         float* sy = sY + pw * {qn * max(d2, 1)};
         uint32_t it = 0;
         bool ok = true;
+        uint32_t soff[{qn} * DIM];          // swizzled byte offsets of this thread's elements in an A sub-tile
+#pragma unroll
+        for (int q = 0; q < {qn}; ++q)
+#pragma unroll
+            for (int k = 0; k < DIM; ++k) soff[q * DIM + k] = tc::sw128_offset((pw + {PRODUCER_WARPS} * q) * DIM + k, lane);
         for (int64_t t = cta; t < tiles && ok; t += nctas) {{
-            const int64_t z0 = t * ZT;{y_load}
-            for (int c = 0; c < NCHUNK; ++c, ++it) {{
-                const int s = it % NSTAGE;
-                const uint32_t ph = (it / NSTAGE) & 1;
-                if (!tc::mbar_wait(&bar_empty[s], ph ^ 1u, abort_flag)) {{ ok = false; break; }}
-                uint8_t* stage = sS + s * STAGE_BYTES;
-                if (pw == 0 && lane == 0) {{
-                    const uint32_t bar = tc::smem_u32(&bar_full[s]);
-                    const uint32_t bbytes = pieces * B_HALF;   // only the pieces this precision uses
-                    asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(bbytes) : "memory");
-                    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                                 ::"r"(tc::smem_u32(stage + {PIECES} * A_TILE)), "l"(bsrc + static_cast<size_t>(c) * {PIECES} * B_HALF),
-                                   "r"(bbytes), "r"(bar) : "memory");
-                }}
-                const int xoff = kXOff{gi}[c];
-                switch (kCase{gi}[c]) {{
-{_indent(switch, 16)}
-                }}
-                tc::fence_proxy_async_smem();
-                __syncwarp();
-                if (lane == 0) tc::mbar_arrive(&bar_full[s]);
+            const int64_t z0 = t * ZT;
+            const float* xrow[{qn}];          // input rows of this warp's z (rows past the end read the last row)
+#pragma unroll
+            for (int q = 0; q < {qn}; ++q) {{
+                const int zl = pw + {PRODUCER_WARPS} * q;
+                int64_t z = z0 + (zl < ZT ? zl : 0);
+                if (z >= Z) z = Z - 1;
+                xrow[q] = x1 + z * {d1};
+            }}{y_load}
+{PRODUCER_LOOP}
             }}
         }}
     }} else if (warp == kMmaWarp && lane == 0) {{

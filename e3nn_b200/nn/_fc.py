@@ -12,6 +12,7 @@ per-edge weights never reach HBM) is the next step for the full interaction bloc
 """
 from __future__ import annotations
 
+import hashlib
 import math
 from functools import lru_cache
 from typing import Callable, List, Optional
@@ -81,7 +82,7 @@ class _Layer(torch.nn.Module):
     def _tc_specs(self):
         if self._tc is None:
             s = self._scale()
-            tag = f"mm{self.h_in}x{self.h_out}s{abs(hash(repr(s))) % 10**10}"
+            tag = f"mm{self.h_in}x{self.h_out}s{hashlib.sha1(repr(s).encode()).hexdigest()[:10]}"
             self._tc = (tc_gemm.matmul_gemm_spec(self.h_in, self.h_out, False, s, tag + "f"),
                         tc_gemm.matmul_gemm_spec(self.h_in, self.h_out, True, s, tag + "t"))
         return self._tc
