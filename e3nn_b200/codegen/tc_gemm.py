@@ -345,7 +345,17 @@ for (int q = 0; q < {qn}; ++q) {{{{
                 if (lane == 0) tc::mbar_arrive(&bar_full[s]);"""
         else:
             dd = g.case_d1[0]
-            PRODUCER_LOOP = f"""            for (int c = 0; c < NCHUNK; c += 2, it += 2) {{
+            # software pipeline over chunk pairs: the loads of the next pair are issued (into registers) before
+            # this pair is converted, so a warp's load latency overlaps its own conversion work and barrier waits
+            PRODUCER_LOOP = f"""            float xa[{qn}][{dd}], xb[{qn}][{dd}], na[{qn}][{dd}], nb[{qn}][{dd}];
+{_indent(load_code(0, 'xa', f'kXOff{gi}[0]'), 12)}
+{_indent(load_code(0, 'xb', f'kXOff{gi}[1]'), 12)}
+            for (int c = 0; c < NCHUNK; c += 2, it += 2) {{
+                if (c + 2 < NCHUNK) {{
+{_indent(load_code(0, 'na', f'kXOff{gi}[c + 2]'), 20)}
+{_indent(load_code(0, 'nb', f'kXOff{gi}[c + 3]'), 20)}
+                }}
+                asm volatile("" ::: "memory");   // the next pair's loads are in flight before anything below
                 const int s0 = it % NSTAGE, s1 = (it + 1) % NSTAGE;
                 const uint32_t ph0 = (it / NSTAGE) & 1, ph1 = ((it + 1) / NSTAGE) & 1;
                 if (!tc::mbar_wait(&bar_empty[s0], ph0 ^ 1u, abort_flag)) {{ ok = false; break; }}
@@ -354,10 +364,6 @@ for (int q = 0; q < {qn}; ++q) {{{{
                 uint8_t* stage1 = sS + s1 * STAGE_BYTES;
 {_indent(issue_b('stage0', '&bar_full[s0]', 'c'), 16)}
 {_indent(issue_b('stage1', '&bar_full[s1]', '(c + 1)'), 16)}
-                float xa[{qn}][{dd}], xb[{qn}][{dd}];
-{_indent(load_code(0, 'xa', f'kXOff{gi}[c]'), 16)}
-{_indent(load_code(0, 'xb', f'kXOff{gi}[c + 1]'), 16)}
-                asm volatile("" ::: "memory");   // both chunks' loads are in flight before the first use below
 {_indent(compute_code(0, 'xa', 'stage0'), 16)}
                 tc::fence_proxy_async_smem();
                 __syncwarp();
@@ -365,7 +371,11 @@ for (int q = 0; q < {qn}; ++q) {{{{
 {_indent(compute_code(0, 'xb', 'stage1'), 16)}
                 tc::fence_proxy_async_smem();
                 __syncwarp();
-                if (lane == 0) tc::mbar_arrive(&bar_full[s1]);"""
+                if (lane == 0) tc::mbar_arrive(&bar_full[s1]);
+#pragma unroll
+                for (int q = 0; q < {qn}; ++q)
+#pragma unroll
+                    for (int i = 0; i < {dd}; ++i) {{ xa[q][i] = na[q][i]; xb[q][i] = nb[q][i]; }}"""
         y_load = f"""
             __syncwarp();
             for (int idx = lane; idx < {qn} * {d2}; idx += 32) {{   // x2 rows of this warp's z -> shared memory

@@ -129,10 +129,11 @@ __device__ __forceinline__ void mma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
+// Round to the nearest tf32 (10 explicit mantissa bits) with two full-rate integer operations
+// (round half away from zero in magnitude) instead of cvt.rna.tf32.f32, which issues on the
+// low-throughput conversion pipe.  NaN stays NaN, values within 2^-11 of FLT_MAX round to infinity.
 __device__ __forceinline__ float to_tf32(float x) {
-    uint32_t r;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
-    return __uint_as_float(r);
+    return __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xFFFFE000u);
 }
 
 // byte offset of element (row, col) in a K-major SWIZZLE_128B tile of 32 fp32 columns
