@@ -398,18 +398,29 @@ for (int q = 0; q < {qn}; ++q) {{{{
             // conflict free) -> read back two rows per instruction -> fully coalesced 256-byte row segments
             float* se = sE + warp * (32 * 64);
             for (int wb = 0; wb < N; wb += 64) {{{{
-                uint32_t r0[16], r1[16], r2[16], r3[16];
-                tc::tmem_ld16(tbase + wb, r0); tc::tmem_ld16(tbase + wb + 16, r1);
-                tc::tmem_ld16(tbase + wb + 32, r2); tc::tmem_ld16(tbase + wb + 48, r3);
-                tc::tmem_ld_wait();
                 float4* mine = reinterpret_cast<float4*>(se + lane * 64);
                 const int sw = lane & 15;
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {{{{
-                    mine[(c) ^ sw] = make_float4(__uint_as_float(r0[4 * c]), __uint_as_float(r0[4 * c + 1]), __uint_as_float(r0[4 * c + 2]), __uint_as_float(r0[4 * c + 3]));
-                    mine[(c + 4) ^ sw] = make_float4(__uint_as_float(r1[4 * c]), __uint_as_float(r1[4 * c + 1]), __uint_as_float(r1[4 * c + 2]), __uint_as_float(r1[4 * c + 3]));
-                    mine[(c + 8) ^ sw] = make_float4(__uint_as_float(r2[4 * c]), __uint_as_float(r2[4 * c + 1]), __uint_as_float(r2[4 * c + 2]), __uint_as_float(r2[4 * c + 3]));
-                    mine[(c + 12) ^ sw] = make_float4(__uint_as_float(r3[4 * c]), __uint_as_float(r3[4 * c + 1]), __uint_as_float(r3[4 * c + 2]), __uint_as_float(r3[4 * c + 3]));
+                for (int h = 0; h < 2; ++h) {{{{
+                    uint32_t r0[16], r1[16];
+                    tc::tmem_ld16(tbase + wb + 32 * h, r0); tc::tmem_ld16(tbase + wb + 32 * h + 16, r1);
+                    if (NACC == 2) {{{{   // second partial accumulator (odd k-steps): summed here in fp32
+                        uint32_t q0[16], q1[16];
+                        tc::tmem_ld16(tbase + N + wb + 32 * h, q0); tc::tmem_ld16(tbase + N + wb + 32 * h + 16, q1);
+                        tc::tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {{{{
+                            r0[j] = __float_as_uint(__uint_as_float(r0[j]) + __uint_as_float(q0[j]));
+                            r1[j] = __float_as_uint(__uint_as_float(r1[j]) + __uint_as_float(q1[j]));
+                        }}}}
+                    }}}} else {{{{
+                        tc::tmem_ld_wait();
+                    }}}}
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {{{{
+                        mine[(8 * h + c) ^ sw] = make_float4(__uint_as_float(r0[4 * c]), __uint_as_float(r0[4 * c + 1]), __uint_as_float(r0[4 * c + 2]), __uint_as_float(r0[4 * c + 3]));
+                        mine[(8 * h + c + 4) ^ sw] = make_float4(__uint_as_float(r1[4 * c]), __uint_as_float(r1[4 * c + 1]), __uint_as_float(r1[4 * c + 2]), __uint_as_float(r1[4 * c + 3]));
+                    }}}}
                 }}}}
                 __syncwarp();
                 const int half = lane >> 4, cc = lane & 15;
@@ -431,16 +442,15 @@ for (int q = 0; q < {qn}; ++q) {{{{
                 }}}}
             }}}};
             uint32_t ra[16], rb[16];
-            tc::tmem_ld16(tbase, ra);
-            for (int w0 = 0; w0 < N; w0 += 32) {{{{
+            for (int w0 = 0; w0 < N; w0 += 16) {{{{
+                tc::tmem_ld16(tbase + w0, ra);
+                if (NACC == 2) tc::tmem_ld16(tbase + N + w0, rb);
                 tc::tmem_ld_wait();
-                if (w0 + 16 < N) tc::tmem_ld16(tbase + w0 + 16, rb);
-                store16(ra, w0);
-                if (w0 + 16 < N) {{{{
-                    tc::tmem_ld_wait();
-                    if (w0 + 32 < N) tc::tmem_ld16(tbase + w0 + 32, ra);
-                    store16(rb, w0 + 16);
+                if (NACC == 2) {{{{
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) ra[j] = __float_as_uint(__uint_as_float(ra[j]) + __uint_as_float(rb[j]));
                 }}}}
+                store16(ra, w0);
             }}}}""".replace("{{", "{").replace("}}", "}")
         funcs.append(f"""
 // ---------------------------------------------------------------- group {gi}: N = {g.n}, 2l+1 = {g.dim}, K = {32 * nch}
@@ -448,6 +458,9 @@ __device__ __forceinline__ void run_group_{gi}(const float* __restrict__ x1, con
         const uint8_t* __restrict__ bprep, float* __restrict__ out, int64_t Z, int cta, int nctas, uint8_t* smem,
         int* status, int pieces) {{
     constexpr int N = {g.n}, DIM = {g.dim}, ZT = {g.zt}, NCHUNK = {nch}, NSTAGE = {g.nstage()}, NBUF = 2;
+    // partial accumulators per buffer: even / odd k-steps accumulate in different TMEM columns, which halves
+    // the length of each dependent MMA chain (and of the fp32 accumulation error); summed in the epilogue
+    constexpr int NACC = {2 if 4 * g.n <= 512 else 1};
     constexpr int OUT_OFF = {g.out_off};
     constexpr uint32_t A_TILE = {A_TILE}, B_HALF = N * 128, STAGE_BYTES = {PIECES} * A_TILE + {PIECES} * B_HALF;
     constexpr uint32_t IDESC = tc::idesc_tf32_m128(N);
@@ -489,7 +502,7 @@ __device__ __forceinline__ void run_group_{gi}(const float* __restrict__ x1, con
             const int64_t z = t * ZT + zq;
             const bool valid = zq < ZT && z < Z;
             float* orow = out + z * {dout} + OUT_OFF;
-            const uint32_t tbase = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + b * N;
+            const uint32_t tbase = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + b * (NACC * N);
 {EPILOGUE}
             tc::tc_fence_before_sync();
             __syncwarp();
@@ -529,26 +542,19 @@ __device__ __forceinline__ void run_group_{gi}(const float* __restrict__ x1, con
             const uint32_t bph = (tile_i / NBUF) & 1;
             if (!tc::mbar_wait(&bar_acc_empty[b], bph ^ 1u, abort_flag)) break;
             tc::tc_fence_after_sync();
-            const uint32_t d_tmem = tmem_base + b * N;
+            const uint32_t d_base = tmem_base + b * (NACC * N);
             for (int c = 0; c < NCHUNK; ++c, ++it) {{
                 const int s = it % NSTAGE;
                 const uint32_t ph = (it / NSTAGE) & 1;
                 if (!tc::mbar_wait(&bar_full[s], ph, abort_flag)) {{ ok = false; break; }}
                 tc::tc_fence_after_sync();
-                const uint32_t a0 = tc::smem_u32(sS + s * STAGE_BYTES), b0 = a0 + {PIECES} * A_TILE;
-#pragma unroll
-                for (int ks = 0; ks < 4; ++ks) {{
-                    // piece products a_i * b_j with i + j < pieces, smallest magnitudes first
-                    uint32_t acc = (c > 0 || ks > 0) ? 1u : 0u;
-                    for (int deg = pieces - 1; deg >= 0; --deg) {{
-                        for (int i = 0; i <= deg; ++i) {{
-                            const int j = deg - i;
-                            tc::mma_tf32(d_tmem, tc::smem_desc_k_sw128(a0 + i * A_TILE + ks * 32),
-                                         tc::smem_desc_k_sw128(b0 + j * B_HALF + ks * 32), IDESC, acc);
-                            acc = 1u;
-                        }}
-                    }}
-                }}
+                // descriptors differ from the stage's base descriptor only in the address field (bytes >> 4):
+                // everything below is compile-time offsets added to two 64-bit values, fully unrolled
+                const uint64_t adesc = tc::smem_desc_k_sw128(tc::smem_u32(sS + s * STAGE_BYTES));
+                const uint64_t bdesc = adesc + (({PIECES} * A_TILE) >> 4);
+                if (pieces == 1) tc::issue_chunk<1, N, NACC, A_TILE, B_HALF>(d_base, adesc, bdesc, IDESC, c > 0);
+                else if (pieces == 2) tc::issue_chunk<2, N, NACC, A_TILE, B_HALF>(d_base, adesc, bdesc, IDESC, c > 0);
+                else tc::issue_chunk<3, N, NACC, A_TILE, B_HALF>(d_base, adesc, bdesc, IDESC, c > 0);
                 tc::mma_commit(&bar_empty[s]);
             }}
             if (ok) tc::mma_commit(&bar_acc_full[b]);

@@ -124,6 +124,27 @@ __device__ __forceinline__ void mma_tf32(uint32_t d_tmem, uint64_t a_desc, uint6
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// All MMAs of one 32-wide K chunk (4 k-steps of 8): operand pieces a_i * b_j with i + j < P, smallest
+// magnitudes first; even / odd k-steps go to different partial accumulators when NACC == 2.
+// adesc / bdesc: descriptors of piece 0 at k-step 0; other pieces / k-steps are constant address offsets.
+template <int P, int N, int NACC, uint32_t A_TILE, uint32_t B_HALF>
+__device__ __forceinline__ void issue_chunk(uint32_t d_base, uint64_t adesc, uint64_t bdesc, uint32_t idesc, bool not_first_chunk) {
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks) {
+        const uint32_t d_tmem = d_base + (NACC == 2 ? (ks & 1) * N : 0);
+        uint32_t acc = (not_first_chunk || ks >= NACC) ? 1u : 0u;
+#pragma unroll
+        for (int deg = P - 1; deg >= 0; --deg) {
+#pragma unroll
+            for (int i = 0; i <= deg; ++i) {
+                const int j = deg - i;
+                mma_tf32(d_tmem, adesc + ((i * A_TILE + ks * 32) >> 4), bdesc + ((j * B_HALF + ks * 32) >> 4), idesc, acc);
+                acc = 1u;
+            }
+        }
+    }
+}
+
 // mbarrier arrive once every MMA issued so far by this thread has completed
 __device__ __forceinline__ void mma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
