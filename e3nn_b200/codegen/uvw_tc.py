@@ -309,15 +309,16 @@ __device__ __forceinline__ void run_group_{gi}(const float* __restrict__ x1, con
                 const uint32_t ph = (it / NSTAGE) & 1;
                 if (!tc::mbar_wait(&bar_full[s], ph, abort_flag)) {{ ok = false; break; }}
                 tc::tc_fence_after_sync();
-                const uint32_t a_base = tc::smem_u32(sA + s * STAGE_BYTES);
-                const uint32_t b_base = tc::smem_u32(sB + c * (N * 128));
+                // descriptors differ only in their address field (bytes >> 4): constant offsets on two values
+                const uint64_t adesc = tc::smem_desc_k_sw128(tc::smem_u32(sA + s * STAGE_BYTES));
+                const uint64_t bdesc = tc::smem_desc_k_sw128(tc::smem_u32(sB + c * (N * 128)));
+                const uint32_t d0 = tmem_base + b * (DIM * N);
 #pragma unroll
-                for (int k = 0; k < DIM; ++k) {{
+                for (int ks = 0; ks < 4; ++ks) {{
 #pragma unroll
-                    for (int ks = 0; ks < 4; ++ks) {{
-                        tc::mma_tf32(tmem_base + b * (DIM * N) + k * N,
-                                     tc::smem_desc_k_sw128(a_base + k * TILE_BYTES + ks * 32),
-                                     tc::smem_desc_k_sw128(b_base + ks * 32), IDESC, (c > 0 || ks > 0) ? 1u : 0u);
+                    for (int k = 0; k < DIM; ++k) {{
+                        tc::mma_tf32(d0 + k * N, adesc + ((k * TILE_BYTES + ks * 32) >> 4), bdesc + ((ks * 32) >> 4), IDESC,
+                                     (c > 0 || ks > 0) ? 1u : 0u);
                     }}
                 }}
                 tc::mma_commit(&bar_empty[s]);
