@@ -33,7 +33,7 @@ import numpy as np
 
 from ..o3._spec import TPSpec
 from ..o3._wigner import wigner_3j_numpy
-from . import uvu_tma
+from . import uvu_tma, uvu_tma_bwd
 
 
 def _f(v: float) -> str:
@@ -298,6 +298,10 @@ def emit_module(spec: TPSpec) -> str:
     v2 = uvu_tma.emit(L)
     v2_kernel = v2["kernel"] if v2 else ""
     v2_launch = v2["launch"] if v2 else ""
+    b2 = uvu_tma_bwd.emit(L) if v2 else None
+    if b2:
+        v2_kernel += b2["kernel"]
+    b2_launch = b2["launch"] if b2 else ""
 
     src = f"""// Generated by e3nn_b200/codegen/uvu.py -- do not edit.
 // layout: {spec.irreps_in1} (x) {spec.irreps_in2} -> {spec.irreps_out}, {len(L.paths)} 'uvu' paths, key {spec.key()}
@@ -582,6 +586,7 @@ extern "C" int e3b_conv_bwd(const float* node_x, const float* x2, int in2_mode, 
     const int64_t blocks = (num_nodes + kRowsPerBlock - 1) / kRowsPerBlock;
     const unsigned grid = static_cast<unsigned>(blocks < 148LL * 64 ? blocks : 148LL * 64);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+{b2_launch}
     if (in2_mode == 1)
         conv_bwd_kernel<1><<<grid, kThreads, 0, s>>>(node_x, x2, edge_src, rowptr, perm, w, grad_out, grad_w, grad_x2, num_nodes, num_src, scale, status);
     else

@@ -398,6 +398,21 @@ def test_conv_pipelined_kernel(layout):
     assert torch.all(fast[5] == 0) and torch.all(fast[N - 1] == 0)
     again = e3nn_b200.conv_uvu(*args, scale=0.7, edge_attr_is_vector=True)
     assert torch.equal(fast, again)  # fixed summation order
+    # gradients w.r.t. the per-edge weights and the edge vectors: pipelined kernel vs oracle autograd
+    vg = vec.clone().to(DEV).requires_grad_(True)
+    wg = w.clone().to(DEV).requires_grad_(True)
+    out_g = e3nn_b200.conv_uvu(tp, node_x.to(DEV), vg, src.to(DEV), rowptr.to(DEV), wg, scale=0.7, edge_attr_is_vector=True)
+    go = torch.randn(N, tp.irreps_out.dim)
+    out_g.backward(go.to(DEV))
+    v64, w64 = vec.double().requires_grad_(True), w.double().requires_grad_(True)
+    ref_g = orc.conv_uvu(str(tp.irreps_in1), str(tp.irreps_in2), str(tp.irreps_out), _ins(tp), node_x.double(), v64, src, dst,
+                         w64, N, list(range(lmax + 1)), scale=0.7, chunk=2048)
+    ref_g.backward(go.double())
+    assert rel_err(wg.grad.cpu(), w64.grad) < TOL
+    gv, gv_ref = vg.grad.cpu(), v64.grad.clone()
+    gv[3] = 0.0      # the zero vector has an unbounded derivative under normalisation
+    gv_ref[3] = 0.0
+    assert rel_err(gv, gv_ref) < 3e-5
     bad = src.clone()
     bad[10] = N + 5
     with pytest.raises(IndexError):
