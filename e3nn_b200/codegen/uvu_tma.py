@@ -74,8 +74,12 @@ def split_paths(layout) -> List[List]:
     return groups
 
 
-def _body(layout, paths) -> Tuple[str, str, str]:
-    """(accumulator declarations, per-edge body, output stores) for one warp of a team."""
+def _body(layout, paths, folded: bool) -> Tuple[str, str, str]:
+    """(accumulator declarations, per-edge body, output stores) for one warp of a team.
+
+    ``folded``: out_k += C_ijk ((x_i w) Y_j) with the constants in the multiply-adds (fewest instructions, the
+    choice when the paths are split over a team); otherwise the coupling table t_ik = sum_j C_ijk Y_j is
+    built per edge first (measured faster when one warp holds every path)."""
     spec = layout.spec
     o1 = spec.irreps_in1.offsets()
     oo = spec.irreps_out.offsets()
@@ -92,28 +96,51 @@ def _body(layout, paths) -> Tuple[str, str, str]:
         d = spec.irreps_in1[i1].ir.dim
         for i in range(d):
             body.append(f"const float2 X{i1}_{i} = make_float2(sx[{o1[i1]} + lane * {d} + {i}], sx[{o1[i1]} + (lane + 32) * {d} + {i}]);")
-    for p in paths:
-        c = wigner_3j_numpy(p.l1, p.l2, p.l3) * p.pw
-        body.append(f"{{ // path {p.index}: l={p.l1} (x) l={p.l2} -> l={p.l3}")
-        names = {}
-        for i in range(2 * p.l1 + 1):
+    if folded:
+        for j in range(layout.d2):
+            body.append(f"const float2 YY{j} = make_float2(Y[{j}], Y[{j}]);")
+        for p in paths:
+            # out_k += C_ijk * ((x_i w) Y_j): constants folded into the multiply-add, no per-edge coupling table
+            c = wigner_3j_numpy(p.l1, p.l2, p.l3) * p.pw
+            body.append(f"{{ // path {p.index}: l={p.l1} (x) l={p.l2} -> l={p.l3}")
+            body.append(f"  const float2 Wp = make_float2(sw[{p.woff} + lane], sw[{p.woff} + lane + 32]);")
+            for i in range(2 * p.l1 + 1):
+                if not (c[i] != 0.0).any():
+                    continue
+                body.append(f"  {{ const float2 XW = __fmul2_rn(X{p.i1}_{i}, Wp);")
+                for j in range(2 * p.l2 + 1):
+                    ks = [(k, c[i, j, k]) for k in range(2 * p.l3 + 1) if c[i, j, k] != 0.0]
+                    if not ks:
+                        continue
+                    body.append(f"    {{ const float2 P = __fmul2_rn(XW, YY{p.off2 + j});")
+                    for k, v in ks:
+                        body.append(f"      A{p.io}_{k} = __ffma2_rn(make_float2({_f(v)}, {_f(v)}), P, A{p.io}_{k});")
+                    body.append("    }")
+                body.append("  }")
+            body.append("}")
+    else:
+        for p in paths:
+            c = wigner_3j_numpy(p.l1, p.l2, p.l3) * p.pw
+            body.append(f"{{ // path {p.index}: l={p.l1} (x) l={p.l2} -> l={p.l3}")
+            names = {}
+            for i in range(2 * p.l1 + 1):
+                for k in range(2 * p.l3 + 1):
+                    terms = [(j, c[i, j, k]) for j in range(2 * p.l2 + 1) if c[i, j, k] != 0.0]
+                    if not terms:
+                        continue
+                    expr = " + ".join(f"{_f(v)} * Y[{p.off2 + j}]" for j, v in terms)
+                    body.append(f"  const float t{i}_{k} = {expr}; const float2 T{i}_{k} = make_float2(t{i}_{k}, t{i}_{k});")
+                    names[(i, k)] = f"T{i}_{k}"
+            body.append(f"  const float2 Wp = make_float2(sw[{p.woff} + lane], sw[{p.woff} + lane + 32]);")
             for k in range(2 * p.l3 + 1):
-                terms = [(j, c[i, j, k]) for j in range(2 * p.l2 + 1) if c[i, j, k] != 0.0]
+                terms = [(names[(i, k)], f"X{p.i1}_{i}") for i in range(2 * p.l1 + 1) if (i, k) in names]
                 if not terms:
                     continue
-                expr = " + ".join(f"{_f(v)} * Y[{p.off2 + j}]" for j, v in terms)
-                body.append(f"  const float t{i}_{k} = {expr}; const float2 T{i}_{k} = make_float2(t{i}_{k}, t{i}_{k});")
-                names[(i, k)] = f"T{i}_{k}"
-        body.append(f"  const float2 Wp = make_float2(sw[{p.woff} + lane], sw[{p.woff} + lane + 32]);")
-        for k in range(2 * p.l3 + 1):
-            terms = [(names[(i, k)], f"X{p.i1}_{i}") for i in range(2 * p.l1 + 1) if (i, k) in names]
-            if not terms:
-                continue
-            expr = f"__fmul2_rn({terms[0][0]}, {terms[0][1]})"
-            for t, x in terms[1:]:
-                expr = f"__ffma2_rn({t}, {x}, {expr})"
-            body.append(f"  A{p.io}_{k} = __ffma2_rn(Wp, {expr}, A{p.io}_{k});")
-        body.append("}")
+                expr = f"__fmul2_rn({terms[0][0]}, {terms[0][1]})"
+                for t, x in terms[1:]:
+                    expr = f"__ffma2_rn({t}, {x}, {expr})"
+                body.append(f"  A{p.io}_{k} = __ffma2_rn(Wp, {expr}, A{p.io}_{k});")
+            body.append("}")
     return "\n".join(decl), "\n".join(body), "\n".join(store)
 
 
@@ -122,7 +149,7 @@ def _indent(text: str, n: int) -> str:
     return "\n".join(pad + line if line else line for line in text.split("\n"))
 
 
-def emit(layout, depth: int = 4) -> Optional[Dict[str, str]]:
+def emit(layout, depth: int = 0) -> Optional[Dict[str, str]]:
     """Kernel source and launch code for an eligible layout (None otherwise)."""
     if not eligible(layout):
         return None
@@ -131,7 +158,13 @@ def emit(layout, depth: int = 4) -> Optional[Dict[str, str]]:
     T = len(groups)
     stage_w, stage_x = layout.wn * 4, layout.d1 * 4
     stage = (stage_w + stage_x + 127) // 128 * 128
-    teams = max(1, min(SMEM_BUDGET // (depth * stage), 16 // T, 8))
+    def teams_for(d: int) -> int:
+        return max(1, min(SMEM_BUDGET // (d * stage), 16 // T, 8))
+
+    if depth == 0:
+        # four stages in flight unless three let one more team (more warps to issue from) fit in shared memory
+        depth = 3 if teams_for(3) > teams_for(4) else 4
+    teams = teams_for(depth)
     lmax = layout.sh_lmax()
     # outputs nobody writes (possible in hand-written layouts): zero-filled by warp 0 of the team
     zero_ranges = []
@@ -142,7 +175,7 @@ def emit(layout, depth: int = 4) -> Optional[Dict[str, str]]:
 
     funcs = []
     for tw, paths in enumerate(groups):
-        decl, body, store = _body(layout, paths)
+        decl, body, store = _body(layout, paths, folded=T > 1)
         leader = "true" if tw == 0 else "false"
         funcs.append(f"""
 __device__ __forceinline__ void v2_team_warp_{tw}(const float* __restrict__ node_x, const float* __restrict__ vec,
