@@ -275,7 +275,7 @@ def finish(args, rank, world, d, tp, nodes, degree, edges_total, ms_step, kernel
         },
         "roofline": {
             "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-            "traffic": traffic, "peak_kind": f"of {peak_kind}", "kernel": "conv_fwd_kernel<1>",
+            "traffic": traffic, "peak_kind": f"of {peak_kind}", "kernel": "conv_fwd_tma_kernel",
             "kernel_ms": k_ms, "algorithmic_bytes_per_edge": algorithmic_bytes_per_edge(tp, nodes, edges_total),
         },
         "e2e": e2e,
@@ -374,11 +374,9 @@ def run_interaction(args, rank, world, device):
     tp = block.tp
 
     def forward(p, xs):
-        edge_vec = p[src_d] - p[dst_glob] + shift_d
-        w = block.edge_weights(edge_vec)
-        mid = e3nn_b200.conv_uvu(tp, xs, edge_vec, src_d, rowptr, w, scale=block.num_neighbors ** -0.5,
-                                 edge_attr_is_vector=True)
-        return block.lin(mid)
+        # the block's own forward: global indices into the (replicated) positions and the gathered features,
+        # the rank's local CSR -> the rank's output rows
+        return block(p, xs, src_d, dst_glob, rowptr, shift_d)
 
     def step(p_in):
         if world > 1:
@@ -469,10 +467,7 @@ def run_interaction(args, rank, world, device):
                 sharding.all_gather_rows(xs, bounds, out=x_full)
                 xs = x_full
             p = d["pos"].requires_grad_(True)
-            edge_vec = p[d["src"]] - p[d["dst"]] + d["shift"]
-            wts = block.edge_weights(edge_vec)
-            mid = e3nn_b200.conv_uvu(tp, xs, edge_vec, d["src"], d["rowptr"], wts, scale=scale, edge_attr_is_vector=True)
-            (block.lin(mid) * G).sum().backward()
+            (block(p, xs, d["src"], d["dst"], d["rowptr"], d["shift"]) * G).sum().backward()
             if world > 1:
                 torch.distributed.all_reduce(p.grad)
             grad_host.copy_(p.grad, non_blocking=True)
@@ -516,7 +511,7 @@ def run_interaction(args, rank, world, device):
                    "l2": "per-edge weights and their gradient (2 x %.1f GB) far larger than the 126 MB L2" % (e_loc * wn * 4 / 1e9),
                    "parallelism": f"dst-range x{world}" + (" + allgather(node features) + allreduce(dpos)" if world > 1 else "")},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": None, "peak_kind": f"of {peak_kind}", "kernel": "conv_bwd_kernel<1>", "kernel_ms": bwd_ms,
+                     "traffic": None, "peak_kind": f"of {peak_kind}", "kernel": "conv_bwd_tma_kernel", "kernel_ms": bwd_ms,
                      "algorithmic_bytes_per_launch": bwd_bytes},
         "e2e": e2e,
         "gpu_launches": args.steps * 12,

@@ -67,7 +67,12 @@ def core() -> ctypes.CDLL:
         lib.e3b_csr_from_dst.argtypes = [c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p]
         lib.e3b_dense_fwd.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int, c_void_p]
         lib.e3b_fill_columns.argtypes = [c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_int, c_void_p]
-        for name in ("e3b_sh_fwd", "e3b_sh_bwd", "e3b_csr_from_dst", "e3b_dense_fwd", "e3b_fill_columns"):
+        lib.e3b_radial_embed_fwd.argtypes = [c_void_p] * 5 + [c_int64, c_int64, c_int, c_int, c_float, c_float, c_float, c_int,
+                                             c_void_p, c_void_p, c_void_p, c_void_p]
+        lib.e3b_radial_embed_bwd.argtypes = [c_void_p] * 7 + [c_int64, c_int64, c_int, c_int, c_float, c_float, c_float, c_int,
+                                             c_void_p, c_void_p, c_void_p]
+        for name in ("e3b_sh_fwd", "e3b_sh_bwd", "e3b_csr_from_dst", "e3b_dense_fwd", "e3b_fill_columns",
+                     "e3b_radial_embed_fwd", "e3b_radial_embed_bwd"):
             getattr(lib, name).restype = c_int
         _core = lib
     return _core

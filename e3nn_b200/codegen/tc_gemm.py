@@ -75,6 +75,7 @@ class Group:
 
     has_y: bool = True
     aligned_out: bool = True   # output rows allow 16-byte stores
+    plain: bool = False        # A is the input rows themselves (dense layer): 16-byte loads and stores
 
     def stage_bytes(self) -> int:
         return PIECES * A_TILE + PIECES * self.n * 128
@@ -241,6 +242,7 @@ def matmul_gemm_spec(k: int, n: int, transpose: bool, scale: float, key: str) ->
     for g in groups:
         g.has_y = False
         g.aligned_out = d_out % 4 == 0 and g.out_off % 4 == 0
+        g.plain = d_in % 4 == 0
     if any(g.nstage() < 2 for g in groups):
         return None
     return GemmSpec(d_in, 0, d_out, groups, key, f"matmul{'^T' if transpose else ''} [{k} x {n}] scale {scale!r}")
@@ -385,6 +387,95 @@ for (int q = 0; q < {qn}; ++q) {{{{
                 sy[idx] = x2[z * {d2} + idx % {d2}];
             }}
             __syncwarp();""" if has_y else ""
+        if g.plain:
+            assert g.dim == 1 and g.zt == 128 and PRODUCER_WARPS == 8 and not has_y
+            B = 2 if (nch % 2 == 0 and g.nstage() >= 4) else 1     # chunks per step (loaded together, one step ahead)
+            ld = lambda dst, ptr, c: "\n".join(
+                f"{dst}[{j}] = *reinterpret_cast<const float4*>({ptr}[{j}] + kXOff{gi}[{c}]);" for j in range(4))
+            loads_first = "\n".join(ld(f"cur{b}", "xp", f"{b}") for b in range(B))
+            loads_same = "\n".join(ld(f"nxt{b}", "xp", f"c + {B + b}") for b in range(B))
+            loads_next = "\n".join(ld(f"nxt{b}", "xq", f"{b}") for b in range(B))
+            steps = []
+            for b in range(B):
+                steps.append(f"""{{
+    const int s = (it + {b}) % NSTAGE;
+    uint8_t* stage = sS + s * STAGE_BYTES;
+{_indent(issue_b('stage', '&bar_full[s]', f'(c + {b})'), 4)}
+#pragma unroll
+    for (int j = 0; j < 4; ++j) tc::split_store4<A_TILE>(cur{b}[j], stage + po[j], pieces);
+    tc::fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) tc::mbar_arrive(&bar_full[s]);
+}}""")
+            waits = "\n".join(
+                f"if (!tc::mbar_wait(&bar_empty[(it + {b}) % NSTAGE], (((it + {b}) / NSTAGE) & 1) ^ 1u, abort_flag)) {{ ok = false; break; }}"
+                for b in range(B))
+            rotate = "\n".join(f"for (int j = 0; j < 4; ++j) cur{b}[j] = nxt{b}[j];" for b in range(B))
+            decl = ", ".join(f"cur{b}[4], nxt{b}[4]" for b in range(B))
+            PRODUCER_BLOCK = f"""        // rows of A are the input rows: a lane moves 16 bytes (4 consecutive K) of one row, 8 lanes one 128-byte
+        // row segment; a warp owns 16 consecutive rows of the tile.  The loads of the next step (next chunks of
+        // this tile or the first chunks of the CTA's next tile) are in flight while this step is converted.
+        uint32_t po[4];
+        const int pc4 = lane & 7;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {{
+            const int r = pw * 16 + 4 * j + (lane >> 3);
+            po[j] = (r >> 3) * 1024 + (r & 7) * 128 + ((pc4 ^ (r & 7)) << 4);
+        }}
+        auto row_ptrs = [&](int64_t t, const float* (&xp)[4]) {{
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {{
+                int64_t z = t * ZT + pw * 16 + 4 * j + (lane >> 3);
+                if (z >= Z) z = Z - 1;            // rows past the end read the last row (their output is not stored)
+                xp[j] = x1 + z * {d1} + 4 * pc4;
+            }}
+        }};
+        float4 {decl};
+        const float* xp[4];
+        const float* xq[4];
+        if (cta < tiles) {{
+            row_ptrs(cta, xp);
+{_indent(loads_first, 12)}
+        }}
+        for (int64_t t = cta; t < tiles && ok; t += nctas) {{
+            const bool more = t + nctas < tiles;
+            if (more) row_ptrs(t + nctas, xq);
+            for (int c = 0; c < NCHUNK; c += {B}, it += {B}) {{
+                if (c + {B} < NCHUNK) {{
+{_indent(loads_same, 20)}
+                }} else if (more) {{
+{_indent(loads_next, 20)}
+                }}
+                asm volatile("" ::: "memory");   // the next step's loads are issued before anything below
+{_indent(waits, 16)}
+{_indent(chr(10).join(steps), 16)}
+#pragma unroll
+{_indent(rotate, 16)}
+            }}
+#pragma unroll
+            for (int j = 0; j < 4; ++j) xp[j] = xq[j];
+        }}
+"""
+        else:
+            PRODUCER_BLOCK = f"""        uint32_t soff[{qn} * DIM];          // swizzled byte offsets of this thread's elements in an A sub-tile
+#pragma unroll
+        for (int q = 0; q < {qn}; ++q)
+#pragma unroll
+            for (int k = 0; k < DIM; ++k) soff[q * DIM + k] = tc::sw128_offset((pw + {PRODUCER_WARPS} * q) * DIM + k, lane);
+        for (int64_t t = cta; t < tiles && ok; t += nctas) {{
+            const int64_t z0 = t * ZT;
+            const float* xrow[{qn}];          // input rows of this warp's z (rows past the end read the last row)
+#pragma unroll
+            for (int q = 0; q < {qn}; ++q) {{
+                const int zl = pw + {PRODUCER_WARPS} * q;
+                int64_t z = z0 + (zl < ZT ? zl : 0);
+                if (z >= Z) z = Z - 1;
+                xrow[q] = x1 + z * {d1};
+            }}{y_load}
+{PRODUCER_LOOP}
+            }}
+        }}
+"""
         if g.dim == 1 and dout % 4 == 0 and g.out_off % 4 == 0:
             store = """#pragma unroll
                     for (int q = 0; q < 4; ++q)
@@ -514,24 +605,7 @@ __device__ __forceinline__ void run_group_{gi}(const float* __restrict__ x1, con
         float* sy = sY + pw * {qn * max(d2, 1)};
         uint32_t it = 0;
         bool ok = true;
-        uint32_t soff[{qn} * DIM];          // swizzled byte offsets of this thread's elements in an A sub-tile
-#pragma unroll
-        for (int q = 0; q < {qn}; ++q)
-#pragma unroll
-            for (int k = 0; k < DIM; ++k) soff[q * DIM + k] = tc::sw128_offset((pw + {PRODUCER_WARPS} * q) * DIM + k, lane);
-        for (int64_t t = cta; t < tiles && ok; t += nctas) {{
-            const int64_t z0 = t * ZT;
-            const float* xrow[{qn}];          // input rows of this warp's z (rows past the end read the last row)
-#pragma unroll
-            for (int q = 0; q < {qn}; ++q) {{
-                const int zl = pw + {PRODUCER_WARPS} * q;
-                int64_t z = z0 + (zl < ZT ? zl : 0);
-                if (z >= Z) z = Z - 1;
-                xrow[q] = x1 + z * {d1};
-            }}{y_load}
-{PRODUCER_LOOP}
-            }}
-        }}
+{PRODUCER_BLOCK}
     }} else if (warp == kMmaWarp && lane == 0) {{
         // ================= MMA issue (single thread)
         uint32_t it = 0;
@@ -656,6 +730,8 @@ extern "C" int e3b_tc_gemm_fwd(const float* x1, const float* x2, const float* we
     if (reinterpret_cast<uintptr_t>(out) % 16 != 0 || reinterpret_cast<uintptr_t>(scratch) % 16 != 0)
         return e3b_layout_fail(-1, "tc_gemm: out and scratch must be 16-byte aligned");
     if (precision < 1 || precision > {PIECES}) return e3b_layout_fail(-1, "tc_gemm: precision must be between 1 and {PIECES}");
+    if ({'true' if any(g.plain for g in gs.groups) else 'false'} && reinterpret_cast<uintptr_t>(x1) % 16 != 0)
+        return e3b_layout_fail(-1, "tc_gemm: x1 must be 16-byte aligned");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
 {zero_fill}
     CtaSplit split;

@@ -74,7 +74,7 @@ def split_paths(layout) -> List[List]:
     return groups
 
 
-def _body(layout, paths, folded: bool) -> Tuple[str, str, str]:
+def _body(layout, paths, folded: bool) -> Tuple[List[str], str, str]:
     """(accumulator declarations, per-edge body, output stores) for one warp of a team.
 
     ``folded``: out_k += C_ijk ((x_i w) Y_j) with the constants in the multiply-adds (fewest instructions, the
@@ -85,13 +85,15 @@ def _body(layout, paths, folded: bool) -> Tuple[str, str, str]:
     oo = spec.irreps_out.offsets()
     decl, body, store = [], [], []
     slots = sorted({p.io for p in paths})
+    acc: Dict[Tuple[int, int], str] = {}
     for io in slots:
         dim = spec.irreps_out[io].ir.dim
         for k in range(dim):
-            decl.append(f"float2 A{io}_{k} = make_float2(0.0f, 0.0f);")
-            store.append(f"orow[{oo[io]} + lane * {dim} + {k}] = A{io}_{k}.x * scale; "
-                         f"orow[{oo[io]} + (lane + 32) * {dim} + {k}] = A{io}_{k}.y * scale; "
-                         f"A{io}_{k} = make_float2(0.0f, 0.0f);")
+            a = acc[(io, k)] = f"A{len(acc)}"      # registers are shared by the roles: role-local numbering
+            decl.append(a)
+            store.append(f"orow[{oo[io]} + lane * {dim} + {k}] = {a}.x * scale; "
+                         f"orow[{oo[io]} + (lane + 32) * {dim} + {k}] = {a}.y * scale; "
+                         f"{a} = make_float2(0.0f, 0.0f);")
     for i1 in sorted({p.i1 for p in paths}):
         d = spec.irreps_in1[i1].ir.dim
         for i in range(d):
@@ -114,7 +116,7 @@ def _body(layout, paths, folded: bool) -> Tuple[str, str, str]:
                         continue
                     body.append(f"    {{ const float2 P = __fmul2_rn(XW, YY{p.off2 + j});")
                     for k, v in ks:
-                        body.append(f"      A{p.io}_{k} = __ffma2_rn(make_float2({_f(v)}, {_f(v)}), P, A{p.io}_{k});")
+                        body.append(f"      {acc[(p.io, k)]} = __ffma2_rn(make_float2({_f(v)}, {_f(v)}), P, {acc[(p.io, k)]});")
                     body.append("    }")
                 body.append("  }")
             body.append("}")
@@ -139,9 +141,9 @@ def _body(layout, paths, folded: bool) -> Tuple[str, str, str]:
                 expr = f"__fmul2_rn({terms[0][0]}, {terms[0][1]})"
                 for t, x in terms[1:]:
                     expr = f"__ffma2_rn({t}, {x}, {expr})"
-                body.append(f"  A{p.io}_{k} = __ffma2_rn(Wp, {expr}, A{p.io}_{k});")
+                body.append(f"  {acc[(p.io, k)]} = __ffma2_rn(Wp, {expr}, {acc[(p.io, k)]});")
             body.append("}")
-    return "\n".join(decl), "\n".join(body), "\n".join(store)
+    return decl, "\n".join(body), "\n".join(store)
 
 
 def _indent(text: str, n: int) -> str:
@@ -159,7 +161,7 @@ def emit(layout, depth: int = 0) -> Optional[Dict[str, str]]:
     stage_w, stage_x = layout.wn * 4, layout.d1 * 4
     stage = (stage_w + stage_x + 127) // 128 * 128
     def teams_for(d: int) -> int:
-        return max(1, min(SMEM_BUDGET // (d * stage), 16 // T, 8))
+        return max(1, min(SMEM_BUDGET // (d * stage + 32 * 20 * 4), 16 // T, 8))
 
     if depth == 0:
         # four stages in flight unless three let one more team (more warps to issue from) fit in shared memory
@@ -173,23 +175,108 @@ def emit(layout, depth: int = 0) -> Optional[Dict[str, str]]:
             zero_ranges.append((spec.irreps_out.offsets()[io], mul * ir.dim))
     zero_code = "\n".join(f"for (int c = lane; c < {n}; c += 32) orow[{off} + c] = 0.0f;" for off, n in zero_ranges)
 
-    funcs = []
-    for tw, paths in enumerate(groups):
-        decl, body, store = _body(layout, paths, folded=T > 1)
-        leader = "true" if tw == 0 else "false"
-        funcs.append(f"""
-__device__ __forceinline__ void v2_team_warp_{tw}(const float* __restrict__ node_x, const float* __restrict__ vec,
+    parts = [_body(layout, paths, folded=T > 1) for paths in groups]
+    n_acc = max(len(p[0]) for p in parts)
+    decl = "\n".join(f"float2 A{i} = make_float2(0.0f, 0.0f);" for i in range(n_acc))
+
+    def switch(texts: List[str], pad: int) -> str:
+        if T == 1:
+            return _indent(texts[0], pad)
+        lines = ["switch (tw) {"]
+        for tw, text in enumerate(texts):
+            lines.append(f"case {tw}: {{")
+            lines.append(_indent(text, 4))
+            lines.append("} break;")
+        lines.append("default: break;")
+        lines.append("}")
+        return _indent("\n".join(lines), pad)
+
+    stores = [p[2] + ("\n" + zero_code if tw == 0 and zero_code else "") for tw, p in enumerate(parts)]
+    kernel = f"""
+// ================================================================= bulk-copy pipelined fused convolution
+constexpr int kV2T = {T};                 // warps per team (each owns a subset of the paths)
+constexpr int kV2Teams = {teams};         // teams per CTA
+constexpr int kV2Threads = kV2T * kV2Teams * 32;
+constexpr int kV2Depth = {depth};         // ring stages (edges in flight) per team
+constexpr int kV2StageW = {stage_w};      // bytes: one edge's weight row
+constexpr int kV2StageX = {stage_x};      // bytes: one gathered source-feature row
+constexpr int kV2StageBytes = {stage};
+constexpr int kV2RingBytes = kV2Depth * kV2StageBytes;
+constexpr int kV2YStride = 20;            // floats per edge of the harmonics batch (16-byte aligned rows)
+constexpr int kV2SmemBytes = kV2Teams * kV2RingBytes + kV2Teams * 2 * kV2Depth * 8 + 128 + kV2Teams * 32 * kV2YStride * 4;
+
+__device__ __forceinline__ void v2_issue(uint8_t* stage, uint64_t* bar, const float* wrow, const float* xrow) {{
+    const uint32_t b = tc::smem_u32(bar);
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(b), "r"(kV2StageW + kV2StageX) : "memory");
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(tc::smem_u32(stage)), "l"(wrow), "r"(kV2StageW), "r"(b) : "memory");
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(tc::smem_u32(stage + kV2StageW)), "l"(xrow), "r"(kV2StageX), "r"(b) : "memory");
+}}
+
+// barrier of the T warps of one team (hardware barrier 1 + team; every lane of every warp of the team calls it)
+template <int T>
+__device__ __forceinline__ void v2_team_sync(int team) {{
+    if (T == 1) __syncwarp();
+    else asm volatile("bar.sync %0, %1;" ::"r"(team + 1), "r"(T * 32) : "memory");
+}}
+
+// One lane per edge: harmonics of a batch of <= 32 consecutive edges into shared memory.
+__device__ __forceinline__ void v2_batch_harmonics(const float* __restrict__ vec, int64_t e0, int64_t e_hi, float* ybuf, int lane) {{
+    const int64_t ee = e0 + lane;
+    if (ee < e_hi) {{
+        const float vx = vec[ee * 3], vy = vec[ee * 3 + 1], vz = vec[ee * 3 + 2];
+        const float inv = 1.0f / fmaxf(sqrtf(vx * vx + vy * vy + vz * vz), 1e-12f);
+        float Y[kD2];
+        e3b_sh_fwd<kShLmax>(vx * inv, vy * inv, vz * inv, Y);
+#pragma unroll
+        for (int j = 0; j < kD2; ++j) ybuf[lane * kV2YStride + j] = Y[j];
+    }}
+}}
+
+// smallest n in [0, num_nodes] with rowptr[n] >= target
+__device__ __forceinline__ int64_t v2_lower_bound(const int64_t* __restrict__ rowptr, int64_t num_nodes, int64_t target) {{
+    int64_t lo = 0, hi = num_nodes;
+    while (lo < hi) {{
+        const int64_t mid = (lo + hi) >> 1;
+        if (rowptr[mid] < target) lo = mid + 1; else hi = mid;
+    }}
+    return lo;
+}}
+
+// The warps of a team run one copy of the loop code and differ only in the two switch statements (per-path
+// arithmetic, stores of their output slots): the hot code stays inside the SM's instruction cache.
+__global__ void __launch_bounds__(kV2Threads, 1) conv_fwd_tma_kernel(const float* __restrict__ node_x, const float* __restrict__ vec,
         const int64_t* __restrict__ edge_src, const int64_t* __restrict__ rowptr, const float* __restrict__ w,
-        float* __restrict__ out, int64_t n_lo, int64_t n_hi, int64_t num_src, float scale, uint8_t* ring,
-        uint64_t* full, uint64_t* empty, volatile int* abort_flag, int* status, int lane) {{
-    constexpr bool kLeader = {leader};
+        float* __restrict__ out, int64_t num_nodes, int64_t num_src, int64_t num_edges, float scale, int* __restrict__ status) {{
+    extern __shared__ __align__(128) uint8_t v2_smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int team = warp / kV2T, tw = warp % kV2T;
+    uint8_t* ring = v2_smem + team * kV2RingBytes;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(v2_smem + kV2Teams * kV2RingBytes);
+    uint64_t* full = bars + team * 2 * kV2Depth;
+    uint64_t* empty = full + kV2Depth;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + kV2Teams * 2 * kV2Depth);
+    float* ybuf = reinterpret_cast<float*>(v2_smem + kV2Teams * kV2RingBytes + kV2Teams * 2 * kV2Depth * 8 + 128) + team * 32 * kV2YStride;
+    if (threadIdx.x == 0) *abort_flag = 0;
+    if (tw == 0 && lane == 0) {{
+        for (int s = 0; s < kV2Depth; ++s) {{ tc::mbar_init(&full[s], 1); tc::mbar_init(&empty[s], kV2T); }}
+        tc::mbar_init_fence();
+    }}
+    __syncthreads();
+    // contiguous destination range of this team, balanced by edge count
+    const int64_t team_id = static_cast<int64_t>(blockIdx.x) * kV2Teams + team;
+    const int64_t num_teams = static_cast<int64_t>(gridDim.x) * kV2Teams;
+    const int64_t n_lo = team_id == 0 ? 0 : v2_lower_bound(rowptr, num_nodes, (num_edges * team_id) / num_teams);
+    const int64_t n_hi = team_id + 1 == num_teams ? num_nodes : v2_lower_bound(rowptr, num_nodes, (num_edges * (team_id + 1)) / num_teams);
     if (n_lo >= n_hi) return;
+    const bool leader = tw == 0 && lane == 0;
     int64_t e = rowptr[n_lo];
     const int64_t e_hi = rowptr[n_hi];
     int64_t issue = e;          // next edge to stage (leader lane only)
     int64_t src_pref = 0;
     bool ok = true;
-    if (kLeader && lane == 0) {{
+    if (leader) {{
         for (int s = 0; s < kV2Depth && issue < e_hi; ++s, ++issue) {{
             int64_t sidx = edge_src[issue];
             if (sidx < 0 || sidx >= num_src) {{ atomicExch(status, 2); sidx = 0; }}
@@ -197,31 +284,36 @@ __device__ __forceinline__ void v2_team_warp_{tw}(const float* __restrict__ node
         }}
         if (issue < e_hi) src_pref = edge_src[issue];
     }}
-    float vx = 0.f, vy = 0.f, vz = 0.f;
-    if (e < e_hi) {{ vx = vec[e * 3]; vy = vec[e * 3 + 1]; vz = vec[e * 3 + 2]; }}
 {_indent(decl, 4)}
     uint32_t it = 0;
     int64_t seg_end = rowptr[n_lo + 1];
-    for (int64_t n = n_lo; n < n_hi && ok; ++n) {{
+    for (int64_t n = n_lo; n < n_hi; ++n) {{
         const int64_t e_end = seg_end;
         if (n + 2 <= n_hi) seg_end = rowptr[n + 2];   // next row's end, fetched one row ahead
         for (; e < e_end; ++e, ++it) {{
+            const int slot = static_cast<int>(it & 31u);
+            if (slot == 0) {{
+                // batch boundary: the harmonics are per-edge scalar work, evaluated one lane per edge
+                __syncwarp();
+                v2_team_sync<kV2T>(team);
+                if (tw == 0) v2_batch_harmonics(vec, e, e_hi, ybuf, lane);
+                __syncwarp();
+                v2_team_sync<kV2T>(team);
+            }}
+            if (!ok) continue;      // a wait gave up: keep the loop (and the team barriers) going without work
             const int s = it % kV2Depth;
             const uint32_t ph = (it / kV2Depth) & 1u;
-            float nvx = 0.f, nvy = 0.f, nvz = 0.f;
-            if (e + 1 < e_hi) {{ nvx = vec[(e + 1) * 3]; nvy = vec[(e + 1) * 3 + 1]; nvz = vec[(e + 1) * 3 + 2]; }}
-            if (!tc::mbar_wait(&full[s], ph, abort_flag)) {{ ok = false; break; }}
+            ok = __all_sync(0xffffffffu, tc::mbar_wait(&full[s], ph, abort_flag));
+            if (!ok) continue;
             const float* sw = reinterpret_cast<const float*>(ring + s * kV2StageBytes);
             const float* sx = reinterpret_cast<const float*>(ring + s * kV2StageBytes + kV2StageW);
             float Y[kD2];
-            {{
-                const float inv = 1.0f / fmaxf(sqrtf(vx * vx + vy * vy + vz * vz), 1e-12f);
-                e3b_sh_fwd<kShLmax>(vx * inv, vy * inv, vz * inv, Y);
-            }}
-{_indent(body, 12)}
+#pragma unroll
+            for (int j = 0; j < kD2; ++j) Y[j] = ybuf[slot * kV2YStride + j];
+{switch([p[1] for p in parts], 12)}
             __syncwarp();
             if (lane == 0) tc::mbar_arrive(&empty[s]);
-            if (kLeader && lane == 0 && it > 0 && issue < e_hi) {{
+            if (leader && it > 0 && issue < e_hi) {{
                 // refill the stage released one iteration ago (the other warps of the team had an edge of slack)
                 const int sp = (it - 1) % kV2Depth;
                 const uint32_t php = ((it - 1) / kV2Depth) & 1u;
@@ -234,79 +326,17 @@ __device__ __forceinline__ void v2_team_warp_{tw}(const float* __restrict__ node
                     if (issue < e_hi) src_pref = edge_src[issue];
                 }}
             }}
-            vx = nvx; vy = nvy; vz = nvz;
         }}
-        if (!ok) break;
-        float* orow = out + n * kDout;
-{_indent(store, 8)}
-{_indent(zero_code if tw == 0 else "", 8)}
+        if (ok) {{
+            float* orow = out + n * kDout;
+{switch(stores, 12)}
+        }}
     }}
     if (!ok) {{
         if (lane == 0) atomicExch(status, 3);
         // give copies that are still in flight time to land before this warp's shared memory can go away
         for (int q = 0; q < 2000; ++q) __nanosleep(500);
     }}
-}}
-""")
-
-    dispatch = "\n".join(
-        f"    {'else ' if tw else ''}if (tw == {tw}) v2_team_warp_{tw}(node_x, vec, edge_src, rowptr, w, out, n_lo, n_hi, num_src, scale, ring, full, empty, abort_flag, status, lane);"
-        for tw in range(T)
-    )
-    kernel = f"""
-// ================================================================= bulk-copy pipelined fused convolution
-constexpr int kV2T = {T};                 // warps per team (each owns a subset of the paths)
-constexpr int kV2Teams = {teams};         // teams per CTA
-constexpr int kV2Threads = kV2T * kV2Teams * 32;
-constexpr int kV2Depth = {depth};         // ring stages (edges in flight) per team
-constexpr int kV2StageW = {stage_w};      // bytes: one edge's weight row
-constexpr int kV2StageX = {stage_x};      // bytes: one gathered source-feature row
-constexpr int kV2StageBytes = {stage};
-constexpr int kV2RingBytes = kV2Depth * kV2StageBytes;
-constexpr int kV2SmemBytes = kV2Teams * kV2RingBytes + kV2Teams * 2 * kV2Depth * 8 + 128;
-
-__device__ __forceinline__ void v2_issue(uint8_t* stage, uint64_t* bar, const float* wrow, const float* xrow) {{
-    const uint32_t b = tc::smem_u32(bar);
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(b), "r"(kV2StageW + kV2StageX) : "memory");
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(tc::smem_u32(stage)), "l"(wrow), "r"(kV2StageW), "r"(b) : "memory");
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(tc::smem_u32(stage + kV2StageW)), "l"(xrow), "r"(kV2StageX), "r"(b) : "memory");
-}}
-{''.join(funcs)}
-// smallest n in [0, num_nodes] with rowptr[n] >= target
-__device__ __forceinline__ int64_t v2_lower_bound(const int64_t* __restrict__ rowptr, int64_t num_nodes, int64_t target) {{
-    int64_t lo = 0, hi = num_nodes;
-    while (lo < hi) {{
-        const int64_t mid = (lo + hi) >> 1;
-        if (rowptr[mid] < target) lo = mid + 1; else hi = mid;
-    }}
-    return lo;
-}}
-
-__global__ void __launch_bounds__(kV2Threads, 1) conv_fwd_tma_kernel(const float* __restrict__ node_x, const float* __restrict__ vec,
-        const int64_t* __restrict__ edge_src, const int64_t* __restrict__ rowptr, const float* __restrict__ w,
-        float* __restrict__ out, int64_t num_nodes, int64_t num_src, int64_t num_edges, float scale, int* __restrict__ status) {{
-    extern __shared__ __align__(128) uint8_t v2_smem[];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int team = warp / kV2T, tw = warp % kV2T;
-    uint8_t* ring = v2_smem + team * kV2RingBytes;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(v2_smem + kV2Teams * kV2RingBytes);
-    uint64_t* full = bars + team * 2 * kV2Depth;
-    uint64_t* empty = full + kV2Depth;
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + kV2Teams * 2 * kV2Depth);
-    if (threadIdx.x == 0) *abort_flag = 0;
-    if (tw == 0 && lane == 0) {{
-        for (int s = 0; s < kV2Depth; ++s) {{ tc::mbar_init(&full[s], 1); tc::mbar_init(&empty[s], kV2T); }}
-        tc::mbar_init_fence();
-    }}
-    __syncthreads();
-    // contiguous destination range of this team, balanced by edge count
-    const int64_t team_id = static_cast<int64_t>(blockIdx.x) * kV2Teams + team;
-    const int64_t num_teams = static_cast<int64_t>(gridDim.x) * kV2Teams;
-    const int64_t n_lo = team_id == 0 ? 0 : v2_lower_bound(rowptr, num_nodes, (num_edges * team_id) / num_teams);
-    const int64_t n_hi = team_id + 1 == num_teams ? num_nodes : v2_lower_bound(rowptr, num_nodes, (num_edges * (team_id + 1)) / num_teams);
-{dispatch}
 }}
 """
     launch = """

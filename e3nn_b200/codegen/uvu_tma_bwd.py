@@ -136,7 +136,7 @@ def emit(layout, depth: int = 3, max_warps: int = 12) -> Optional[Dict[str, str]
     T = len(groups)
     stage_w, stage_x = layout.wn * 4, layout.d1 * 4
     stage = (stage_w + stage_x + 127) // 128 * 128
-    teams = max(1, min(SMEM_BUDGET // (depth * stage), max_warps // T, 8))
+    teams = max(1, min(SMEM_BUDGET // (depth * stage + 32 * 20 * 4 + T * 32 * 17 * 4), max_warps // T, 8))
     d2 = layout.d2
     dy_decl = "\n".join(f"float2 DY{j} = make_float2(0.0f, 0.0f); const float2 YY{j} = make_float2(Y[{j}], Y[{j}]);"
                         for j in range(d2))
@@ -165,28 +165,10 @@ constexpr int kB2Teams = {teams};
 constexpr int kB2Threads = kB2T * kB2Teams * 32;
 constexpr int kB2Depth = {depth};
 constexpr int kB2RingBytes = kB2Depth * kV2StageBytes;
-constexpr int kB2YStride = 20;                             // floats per edge of the harmonics batch (16-byte aligned rows)
+constexpr int kB2YStride = kV2YStride;
 constexpr int kB2DyStride = 17;                            // floats per edge of a warp's partial grad_Y (conflict-free columns)
 constexpr int kB2BatchFloats = 32 * kB2YStride + kB2T * 32 * kB2DyStride;
 constexpr int kB2SmemBytes = kB2Teams * kB2RingBytes + kB2Teams * 2 * kB2Depth * 8 + 128 + kB2Teams * kB2BatchFloats * 4;
-
-// barrier of the warps of one team (hardware barrier 1 + team; every lane of every warp of the team calls it)
-__device__ __forceinline__ void b2_team_sync(int team) {{
-    asm volatile("bar.sync %0, %1;" ::"r"(team + 1), "r"(kB2T * 32) : "memory");
-}}
-
-// One lane per edge: harmonics of a batch of <= 32 consecutive edges.
-__device__ __forceinline__ void b2_batch_harmonics(const float* __restrict__ vec, int64_t e0, int64_t e_hi, float* ybuf, int lane) {{
-    const int64_t ee = e0 + lane;
-    if (ee < e_hi) {{
-        const float vx = vec[ee * 3], vy = vec[ee * 3 + 1], vz = vec[ee * 3 + 2];
-        const float inv = 1.0f / fmaxf(sqrtf(vx * vx + vy * vy + vz * vz), 1e-12f);
-        float Y[kD2];
-        e3b_sh_fwd<kShLmax>(vx * inv, vy * inv, vz * inv, Y);
-#pragma unroll
-        for (int j = 0; j < kD2; ++j) ybuf[lane * kB2YStride + j] = Y[j];
-    }}
-}}
 
 // One lane per edge: sum the warps' partial grad_Y of a finished batch, apply the harmonics Jacobian, store.
 __device__ __forceinline__ void b2_batch_finish(const float* __restrict__ vec, float* __restrict__ grad_vec, int64_t e0, int count,
@@ -276,13 +258,13 @@ __global__ void __launch_bounds__(kB2Threads, 1) conv_bwd_tma_kernel(const float
             if (slot == 0) {{
                 // batch boundary: harmonics and their Jacobian are per-edge scalar work, done one lane per edge
                 __syncwarp();
-                b2_team_sync(team);
+                v2_team_sync<kB2T>(team);
                 if (tw == 0) {{
                     if (it > 0) b2_batch_finish(vec, grad_vec, e - 32, 32, dybuf, lane);
-                    b2_batch_harmonics(vec, e, e_hi, ybuf, lane);
+                    v2_batch_harmonics(vec, e, e_hi, ybuf, lane);
                 }}
                 __syncwarp();
-                b2_team_sync(team);
+                v2_team_sync<kB2T>(team);
             }}
             if (!ok) continue;      // a wait gave up: keep the loop (and the team barriers) going without work
             const int s = it % kB2Depth;
@@ -322,7 +304,7 @@ __global__ void __launch_bounds__(kB2Threads, 1) conv_bwd_tma_kernel(const float
     {{
         const int count = (it & 31u) != 0u ? static_cast<int>(it & 31u) : (it > 0 ? 32 : 0);
         __syncwarp();
-        b2_team_sync(team);
+        v2_team_sync<kB2T>(team);
         if (tw == 0 && ok) b2_batch_finish(vec, grad_vec, e - count, count, dybuf, lane);
     }}
     if (!ok) {{

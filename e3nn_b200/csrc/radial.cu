@@ -1,0 +1,297 @@
+// Edge embedding of an interaction block in one kernel per direction: edge vectors from positions, the
+// Bessel radial basis and the first (narrow) layer of the radial network with its activation.
+//
+//   edge_vec = pos[src] - pos[dst] + shift                        (e3nn/nn/models/gate_points_2101.py:328)
+//   B_k      = sqrt(2/c) sin(k pi r / c) / r,  k = 1..num_basis   (e3nn/math/_bessel.py:6-37)
+//   h        = act_scale * act((B @ W0) * w_scale)                (e3nn/nn/_fc.py:38-48, 70-88)
+//
+// The reference evaluates these as a few dozen elementwise launches over [E, .] temporaries.  Here a warp
+// takes 32 edges at a time: first one lane per edge (vector, radius and basis; the basis in fp64 through the
+// Chebyshev recurrence of sin(k theta), because fp32 argument reduction alone costs a digit of the 1e-5
+// error budget), then one edge per step with the hidden units across the lanes (coalesced rows of h).
+// The gradient kernel recomputes the pre-activations instead of storing [E, hidden], reduces the basis
+// cotangent over the lanes by recursive halving and adds the position gradient with float atomics.
+#include "common.cuh"
+
+namespace e3b {
+namespace {
+
+constexpr int kMaxBasis = 16;
+constexpr int kEmbedWarps = 8;
+
+enum Act { kSilu = 0, kTanh = 1, kRelu = 2, kIdentity = 3 };
+
+__device__ __forceinline__ float act_fwd(int kind, float x) {
+    switch (kind) {
+        case kSilu: return x / (1.0f + expf(-x));
+        case kTanh: return tanhf(x);
+        case kRelu: return fmaxf(x, 0.0f);
+        default: return x;
+    }
+}
+__device__ __forceinline__ float act_grad(int kind, float x) {
+    switch (kind) {
+        case kSilu: {
+            const float s = 1.0f / (1.0f + expf(-x));
+            return s * (1.0f + x * (1.0f - s));
+        }
+        case kTanh: {
+            const float t = tanhf(x);
+            return 1.0f - t * t;
+        }
+        case kRelu: return x > 0.0f ? 1.0f : 0.0f;
+        default: return 1.0f;
+    }
+}
+
+struct EdgeGeom {
+    float vx, vy, vz;
+    double r;
+    int64_t s, d;
+};
+
+// vector and radius of edge e (one lane per edge); indices out of range raise status 2 and are clamped
+__device__ __forceinline__ EdgeGeom edge_geom(const float* __restrict__ pos, const int64_t* __restrict__ src,
+                                              const int64_t* __restrict__ dst, const float* __restrict__ shift, int64_t e,
+                                              int64_t num_nodes, int* status) {
+    EdgeGeom g;
+    g.s = src[e];
+    g.d = dst[e];
+    if (g.s < 0 || g.s >= num_nodes || g.d < 0 || g.d >= num_nodes) {
+        atomicExch(status, 2);
+        g.s = g.s < 0 ? 0 : (g.s >= num_nodes ? num_nodes - 1 : g.s);
+        g.d = g.d < 0 ? 0 : (g.d >= num_nodes ? num_nodes - 1 : g.d);
+    }
+    g.vx = pos[g.s * 3] - pos[g.d * 3];
+    g.vy = pos[g.s * 3 + 1] - pos[g.d * 3 + 1];
+    g.vz = pos[g.s * 3 + 2] - pos[g.d * 3 + 2];
+    if (shift) {
+        g.vx += shift[e * 3];
+        g.vy += shift[e * 3 + 1];
+        g.vz += shift[e * 3 + 2];
+    }
+    g.r = sqrt(static_cast<double>(g.vx) * g.vx + static_cast<double>(g.vy) * g.vy + static_cast<double>(g.vz) * g.vz);
+    return g;
+}
+
+// B_k (and optionally dB_k/dr) for k = 1..nb in fp64: sin(k theta), cos(k theta) by the Chebyshev recurrence
+__device__ __forceinline__ void bessel_basis(double r, int nb, double r_max, float* basis, float* dbasis) {
+    const double c0 = sqrt(2.0 / r_max);
+    const double a = 3.14159265358979323846 / r_max;
+    if (r == 0.0) {
+        for (int k = 1; k <= nb; ++k) {
+            basis[k - 1] = static_cast<float>(c0 * k * a);
+            if (dbasis) dbasis[k - 1] = 0.0f;
+        }
+        return;
+    }
+    double s1, c1;
+    sincos(a * r, &s1, &c1);
+    const double inv = 1.0 / r;
+    double s_prev = 0.0, s_cur = s1, c_prev = 1.0, c_cur = c1;
+    for (int k = 1; k <= nb; ++k) {
+        basis[k - 1] = static_cast<float>(c0 * s_cur * inv);
+        if (dbasis) dbasis[k - 1] = static_cast<float>(c0 * (k * a * c_cur * r - s_cur) * inv * inv);
+        const double s_next = 2.0 * c1 * s_cur - s_prev;
+        const double c_next = 2.0 * c1 * c_cur - c_prev;
+        s_prev = s_cur; s_cur = s_next;
+        c_prev = c_cur; c_cur = c_next;
+    }
+}
+
+// H2 = hidden / 32 hidden units per lane (unit j of a lane is column lane + 32 j)
+template <int H2>
+__global__ void __launch_bounds__(kEmbedWarps * 32) radial_embed_fwd_kernel(
+        const float* __restrict__ pos, const int64_t* __restrict__ src, const int64_t* __restrict__ dst,
+        const float* __restrict__ shift, const float* __restrict__ w0, int64_t num_edges, int64_t num_nodes, int nb,
+        float r_max, float w_scale, float act_scale, int act, float* __restrict__ edge_vec, float* __restrict__ h,
+        int* __restrict__ status) {
+    __shared__ float s_basis[kEmbedWarps][32][kMaxBasis + 1];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr int H = 32 * H2;
+    float w[kMaxBasis][H2];
+#pragma unroll
+    for (int k = 0; k < kMaxBasis; ++k)
+#pragma unroll
+        for (int j = 0; j < H2; ++j) w[k][j] = k < nb ? w0[k * H + lane + 32 * j] * w_scale : 0.0f;
+    const int64_t batches = (num_edges + 31) / 32;
+    for (int64_t b = static_cast<int64_t>(blockIdx.x) * kEmbedWarps + warp; b < batches;
+         b += static_cast<int64_t>(gridDim.x) * kEmbedWarps) {
+        const int64_t e = b * 32 + lane;
+        if (e < num_edges) {
+            const EdgeGeom g = edge_geom(pos, src, dst, shift, e, num_nodes, status);
+            edge_vec[e * 3] = g.vx; edge_vec[e * 3 + 1] = g.vy; edge_vec[e * 3 + 2] = g.vz;
+            bessel_basis(g.r, nb, r_max, s_basis[warp][lane], nullptr);
+        }
+        __syncwarp();
+        const int count = static_cast<int>(num_edges - b * 32 < 32 ? num_edges - b * 32 : 32);
+        for (int i = 0; i < count; ++i) {
+            float pre[H2];
+#pragma unroll
+            for (int j = 0; j < H2; ++j) pre[j] = 0.0f;
+#pragma unroll
+            for (int k = 0; k < kMaxBasis; ++k) {
+                if (k < nb) {
+                    const float bk = s_basis[warp][i][k];
+#pragma unroll
+                    for (int j = 0; j < H2; ++j) pre[j] = fmaf(bk, w[k][j], pre[j]);
+                }
+            }
+            float* hrow = h + (b * 32 + i) * H;
+#pragma unroll
+            for (int j = 0; j < H2; ++j) hrow[lane + 32 * j] = act_scale * act_fwd(act, pre[j]);
+        }
+        __syncwarp();
+    }
+}
+
+// one step of a recursive-halving reduction over the lanes: lanes with bit O set keep the upper half
+template <int O, int HALF>
+__device__ __forceinline__ void halve(float* v, int lane) {
+    const bool up = (lane & O) != 0;
+#pragma unroll
+    for (int i = 0; i < HALF; ++i) {
+        const float send = up ? v[i] : v[i + HALF];
+        const float keep = up ? v[i + HALF] : v[i];
+        v[i] = keep + __shfl_xor_sync(0xffffffffu, send, O);
+    }
+}
+
+template <int H2>
+__global__ void __launch_bounds__(kEmbedWarps * 32) radial_embed_bwd_kernel(
+        const float* __restrict__ pos, const int64_t* __restrict__ src, const int64_t* __restrict__ dst,
+        const float* __restrict__ shift, const float* __restrict__ w0, const float* __restrict__ grad_h,
+        const float* __restrict__ grad_vec, int64_t num_edges, int64_t num_nodes, int nb, float r_max, float w_scale,
+        float act_scale, int act, float* __restrict__ grad_pos, int* __restrict__ status) {
+    __shared__ float s_basis[kEmbedWarps][32][kMaxBasis + 1];
+    __shared__ float s_cot[kEmbedWarps][32][kMaxBasis + 1];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr int H = 32 * H2;
+    float w[kMaxBasis][H2];
+#pragma unroll
+    for (int k = 0; k < kMaxBasis; ++k)
+#pragma unroll
+        for (int j = 0; j < H2; ++j) w[k][j] = k < nb ? w0[k * H + lane + 32 * j] * w_scale : 0.0f;
+    const int64_t batches = (num_edges + 31) / 32;
+    for (int64_t b = static_cast<int64_t>(blockIdx.x) * kEmbedWarps + warp; b < batches;
+         b += static_cast<int64_t>(gridDim.x) * kEmbedWarps) {
+        const int64_t e = b * 32 + lane;
+        EdgeGeom g;
+        float dbasis[kMaxBasis];
+#pragma unroll
+        for (int k = 0; k < kMaxBasis; ++k) dbasis[k] = 0.0f;
+        if (e < num_edges) {
+            g = edge_geom(pos, src, dst, shift, e, num_nodes, status);
+            bessel_basis(g.r, nb, r_max, s_basis[warp][lane], dbasis);
+        }
+        __syncwarp();
+        const int count = static_cast<int>(num_edges - b * 32 < 32 ? num_edges - b * 32 : 32);
+        for (int i = 0; i < count; ++i) {
+            float pre[H2];
+#pragma unroll
+            for (int j = 0; j < H2; ++j) pre[j] = 0.0f;
+#pragma unroll
+            for (int k = 0; k < kMaxBasis; ++k) {
+                if (k < nb) {
+                    const float bk = s_basis[warp][i][k];
+#pragma unroll
+                    for (int j = 0; j < H2; ++j) pre[j] = fmaf(bk, w[k][j], pre[j]);
+                }
+            }
+            const float* grow = grad_h + (b * 32 + i) * H;
+            float cot[kMaxBasis];
+#pragma unroll
+            for (int k = 0; k < kMaxBasis; ++k) cot[k] = 0.0f;
+#pragma unroll
+            for (int j = 0; j < H2; ++j) {
+                const float dpre = grow[lane + 32 * j] * act_scale * act_grad(act, pre[j]);
+#pragma unroll
+                for (int k = 0; k < kMaxBasis; ++k) cot[k] = fmaf(w[k][j], dpre, cot[k]);
+            }
+            halve<16, 8>(cot, lane); halve<8, 4>(cot, lane); halve<4, 2>(cot, lane); halve<2, 1>(cot, lane);
+            cot[0] += __shfl_xor_sync(0xffffffffu, cot[0], 1);
+            // after the four halvings lane l holds component (l >> 1) & 15 (bit 4 chose the upper 8, bit 3 the upper 4, ...)
+            if ((lane & 1) == 0) s_cot[warp][i][(lane >> 1) & 15] = cot[0];
+        }
+        __syncwarp();
+        if (e < num_edges) {
+            double dr = 0.0;
+#pragma unroll
+            for (int k = 0; k < kMaxBasis; ++k)
+                if (k < nb) dr += static_cast<double>(s_cot[warp][lane][k]) * dbasis[k];
+            float gx = 0.0f, gy = 0.0f, gz = 0.0f;
+            if (grad_vec) { gx = grad_vec[e * 3]; gy = grad_vec[e * 3 + 1]; gz = grad_vec[e * 3 + 2]; }
+            if (g.r > 0.0) {
+                const double f = dr / g.r;
+                gx += static_cast<float>(f * g.vx); gy += static_cast<float>(f * g.vy); gz += static_cast<float>(f * g.vz);
+            }
+            atomicAdd(grad_pos + g.s * 3, gx); atomicAdd(grad_pos + g.s * 3 + 1, gy); atomicAdd(grad_pos + g.s * 3 + 2, gz);
+            atomicAdd(grad_pos + g.d * 3, -gx); atomicAdd(grad_pos + g.d * 3 + 1, -gy); atomicAdd(grad_pos + g.d * 3 + 2, -gz);
+        }
+        __syncwarp();
+    }
+}
+
+int check_embed_args(int64_t num_edges, int64_t num_nodes, int num_basis, int hidden, int act) {
+    if (num_edges < 0 || num_nodes < 0) return fail(E3B_ERR_ARG, "radial_embed: negative size");
+    if (num_basis < 1 || num_basis > kMaxBasis) return fail(E3B_ERR_ARG, "radial_embed: num_basis must be in 1..%d", kMaxBasis);
+    if (hidden != 32 && hidden != 64 && hidden != 96 && hidden != 128)
+        return fail(E3B_ERR_ARG, "radial_embed: hidden must be 32, 64, 96 or 128");
+    if (act < 0 || act > kIdentity) return fail(E3B_ERR_ARG, "radial_embed: unknown activation %d", act);
+    return E3B_OK;
+}
+
+int embed_grid(int64_t num_edges) {
+    const int64_t want = ceil_div(ceil_div(num_edges, 32), kEmbedWarps);
+    const int64_t cap = static_cast<int64_t>(kNumSMs) * 8;
+    return static_cast<int>(want < cap ? want : cap);
+}
+
+}  // namespace
+}  // namespace e3b
+
+extern "C" int e3b_radial_embed_fwd(const float* pos, const int64_t* edge_src, const int64_t* edge_dst, const float* shift,
+                                    const float* w0, int64_t num_edges, int64_t num_nodes, int num_basis, int hidden,
+                                    float r_max, float w_scale, float act_scale, int act, float* edge_vec, float* h,
+                                    int32_t* status, void* stream) {
+    using namespace e3b;
+    if (int rc = check_embed_args(num_edges, num_nodes, num_basis, hidden, act)) return rc;
+    if (num_edges == 0) return E3B_OK;
+    if (!pos || !edge_src || !edge_dst || !w0 || !edge_vec || !h || !status) return fail(E3B_ERR_ARG, "radial_embed_fwd: null pointer");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int grid = embed_grid(num_edges), threads = kEmbedWarps * 32;
+#define E3B_LAUNCH(H2)                                                                                                   \
+    radial_embed_fwd_kernel<H2><<<grid, threads, 0, s>>>(pos, edge_src, edge_dst, shift, w0, num_edges, num_nodes, num_basis, \
+                                                         r_max, w_scale, act_scale, act, edge_vec, h, status)
+    switch (hidden / 32) {
+        case 1: E3B_LAUNCH(1); break;
+        case 2: E3B_LAUNCH(2); break;
+        case 3: E3B_LAUNCH(3); break;
+        default: E3B_LAUNCH(4); break;
+    }
+#undef E3B_LAUNCH
+    return check_launch("radial_embed_fwd");
+}
+
+extern "C" int e3b_radial_embed_bwd(const float* pos, const int64_t* edge_src, const int64_t* edge_dst, const float* shift,
+                                    const float* w0, const float* grad_h, const float* grad_edge_vec, int64_t num_edges,
+                                    int64_t num_nodes, int num_basis, int hidden, float r_max, float w_scale,
+                                    float act_scale, int act, float* grad_pos, int32_t* status, void* stream) {
+    using namespace e3b;
+    if (int rc = check_embed_args(num_edges, num_nodes, num_basis, hidden, act)) return rc;
+    if (num_edges == 0) return E3B_OK;
+    if (!pos || !edge_src || !edge_dst || !w0 || !grad_h || !grad_pos || !status) return fail(E3B_ERR_ARG, "radial_embed_bwd: null pointer");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int grid = embed_grid(num_edges), threads = kEmbedWarps * 32;
+#define E3B_LAUNCH(H2)                                                                                                   \
+    radial_embed_bwd_kernel<H2><<<grid, threads, 0, s>>>(pos, edge_src, edge_dst, shift, w0, grad_h, grad_edge_vec, num_edges, \
+                                                         num_nodes, num_basis, r_max, w_scale, act_scale, act, grad_pos, status)
+    switch (hidden / 32) {
+        case 1: E3B_LAUNCH(1); break;
+        case 2: E3B_LAUNCH(2); break;
+        case 3: E3B_LAUNCH(3); break;
+        default: E3B_LAUNCH(4); break;
+    }
+#undef E3B_LAUNCH
+    return check_launch("radial_embed_bwd");
+}

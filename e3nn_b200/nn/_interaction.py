@@ -21,6 +21,7 @@ import torch
 from .. import layouts
 from ..message_passing import conv_uvu
 from ..o3 import Irreps, Linear
+from ._edge_embed import edge_embed
 from ._fc import FullyConnectedNet, bessel
 
 
@@ -73,10 +74,20 @@ class InteractionBlock(torch.nn.Module):
     def forward(self, pos: torch.Tensor, node_features: torch.Tensor, edge_src: torch.Tensor, edge_dst: torch.Tensor,
                 rowptr: torch.Tensor, shift: Optional[torch.Tensor] = None) -> torch.Tensor:
         """``edge_*`` must be sorted by destination and ``rowptr`` their CSR (`e3nn_b200.csr_from_dst`)."""
-        edge_vec = pos[edge_src] - pos[edge_dst]
-        if shift is not None:
-            edge_vec = edge_vec + shift
-        w = self.edge_weights(edge_vec)
+        layer0 = self.fc.layer0
+        fused = (pos.is_cuda and pos.dtype == torch.float32 and len(self.fc.hs) == 3 and self.num_basis <= 16
+                 and self.fc.hs[1] in (32, 64, 96, 128) and not (torch.is_grad_enabled() and layer0.weight.requires_grad))
+        if fused:
+            # vectors, Bessel basis and the first radial layer in one kernel (and one for their gradient)
+            act = getattr(layer0.act, "__name__", None) if layer0.act is not None else None
+            edge_vec, h = edge_embed(pos, edge_src, edge_dst, shift, layer0.weight, self.r_max, layer0._scale(),
+                                     layer0.cst * layer0.var_out ** 0.5, act)
+            w = self.fc.layer1(h)
+        else:
+            edge_vec = pos[edge_src] - pos[edge_dst]
+            if shift is not None:
+                edge_vec = edge_vec + shift
+            w = self.edge_weights(edge_vec)
         mid = conv_uvu(self.tp, node_features, edge_vec, edge_src, rowptr, w, scale=self.num_neighbors ** -0.5,
                        edge_attr_is_vector=True)
         return self.lin(mid)

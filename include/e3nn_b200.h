@@ -102,6 +102,30 @@ int e3b_csr_from_dst_static(const int64_t* dst, int64_t num_edges, int64_t num_n
                             int32_t* status, void* stream);
 
 /*
+ * Edge embedding of an interaction block, one kernel per direction:
+ *   edge_vec[e] = pos[src[e]] - pos[dst[e]] + shift[e]        (e3nn/nn/models/gate_points_2101.py:328)
+ *   B[e,k]      = sqrt(2/r_max) sin(k pi r / r_max) / r, k = 1..num_basis, r = |edge_vec[e]|
+ *                                                             (e3nn/math/_bessel.py:6-37)
+ *   h[e,:]      = act_scale * act(w_scale * B[e,:] @ w0)      (first layer of FullyConnectedNet,
+ *                                                              e3nn/nn/_fc.py:38-48 and :70-88)
+ * pos [num_nodes,3]; edge_src, edge_dst [num_edges] int64; shift [num_edges,3] or NULL; w0 row-major
+ * [num_basis, hidden]; num_basis <= 16; hidden in {32, 64, 96, 128}; act: 0 silu, 1 tanh, 2 relu, 3 identity.
+ * Outputs edge_vec [num_edges,3] and h [num_edges,hidden].  An index outside [0, num_nodes) sets *status = 2
+ * (device word, zeroed by the caller) and is clamped.
+ *
+ * e3b_radial_embed_bwd: cotangents grad_h [num_edges,hidden] and grad_edge_vec [num_edges,3] (or NULL) are
+ * pulled back to the positions; the result is ADDED to grad_pos [num_nodes,3] (float atomics; the caller
+ * zeroes it).  Replaces autograd through the same reference lines.
+ */
+int e3b_radial_embed_fwd(const float* pos, const int64_t* edge_src, const int64_t* edge_dst, const float* shift,
+                         const float* w0, int64_t num_edges, int64_t num_nodes, int num_basis, int hidden, float r_max,
+                         float w_scale, float act_scale, int act, float* edge_vec, float* h, int32_t* status, void* stream);
+int e3b_radial_embed_bwd(const float* pos, const int64_t* edge_src, const int64_t* edge_dst, const float* shift,
+                         const float* w0, const float* grad_h, const float* grad_edge_vec, int64_t num_edges,
+                         int64_t num_nodes, int num_basis, int hidden, float r_max, float w_scale, float act_scale, int act,
+                         float* grad_pos, int32_t* status, void* stream);
+
+/*
  * Weight-shared dense contractions in fp32 (CUDA cores): 'uvw' tensor-product paths
  *   out[z,w,k] = sum_paths pw sum_{u,v} W[u,v,w] sum_{ij} C_ijk x1[z,u,i] x2[z,v,j]
  * (e3nn/o3/_tensor_product/_codegen.py:148-165 with the accumulation of :312-343) and the

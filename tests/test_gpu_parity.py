@@ -478,6 +478,50 @@ def test_interaction_block_forward_and_position_gradient(irreps, lmax):
     assert rel_err(p2.grad.cpu(), p64.grad) < 1e-4
 
 
+# ----------------------------------------------------------------------------- fused edge embedding
+@pytest.mark.gpu
+@pytest.mark.parametrize("act,hidden,nb,with_shift", [("silu", 64, 8, True), ("tanh", 32, 5, False), ("relu", 128, 16, True)])
+def test_edge_embed_matches_fp64_chain(act, hidden, nb, with_shift):
+    """edge_vec, Bessel basis and first radial layer in one kernel, and their pull-back to the positions,
+    against the same chain written with torch operators in fp64 (e3nn/math/_bessel.py:6-37, e3nn/nn/_fc.py:38-48)."""
+    from e3nn_b200 import nn as bnn
+
+    torch.manual_seed(5)
+    N, E, c = 300, 4001, 5.0          # E is not a multiple of the 32-edge batches
+    pos = torch.rand(N, 3) * 6.0
+    src = torch.randint(0, N, (E,))
+    dst = torch.randint(0, N, (E,))
+    src[7] = dst[7]                   # a zero-length edge (r = 0 branch of the basis)
+    shift = torch.randn(E, 3) * 0.3 if with_shift else None
+    if shift is not None:
+        shift[7] = 0.0
+    w0 = torch.randn(nb, hidden)
+    w_scale, act_scale = nb ** -0.5, bnn.normalize2mom_constant(act)
+    gh, gv = torch.randn(E, hidden), torch.randn(E, 3)
+
+    f = {"silu": torch.nn.functional.silu, "tanh": torch.tanh, "relu": torch.relu}[act]
+    p64 = pos.double().requires_grad_(True)
+    vec64 = p64[src] - p64[dst] + (shift.double() if shift is not None else 0.0)
+    r = vec64.pow(2).sum(-1).clamp_min(1e-300).sqrt() * (vec64.pow(2).sum(-1) > 0)
+    h64 = act_scale * f(bnn.bessel(r, nb, c) @ (w0.double() * w_scale))
+    ((h64 * gh.double()).sum() + (vec64 * gv.double()).sum()).backward()
+
+    p = pos.clone().to(DEV).requires_grad_(True)
+    vec, h = bnn.edge_embed(p, src.to(DEV), dst.to(DEV), shift.to(DEV) if shift is not None else None, w0.to(DEV), c,
+                            w_scale, act_scale, act, check_indices=True)
+    ((h * gh.to(DEV)).sum() + (vec * gv.to(DEV)).sum()).backward()
+    assert rel_err(vec.detach().cpu(), vec64.detach()) < 1e-6
+    assert rel_err(h.detach().cpu(), h64.detach()) < TOL
+    assert rel_err(p.grad.cpu(), p64.grad) < TOL
+    bad = src.clone()
+    bad[11] = N
+    with pytest.raises(IndexError):
+        bnn.edge_embed(pos.to(DEV), bad.to(DEV), dst.to(DEV), None, w0.to(DEV), c, w_scale, act_scale, act, check_indices=True)
+    # empty edge list
+    v0, h0 = bnn.edge_embed(pos.to(DEV), src[:0].to(DEV), dst[:0].to(DEV), None, w0.to(DEV), c, w_scale, act_scale, act)
+    assert v0.shape == (0, 3) and h0.shape == (0, hidden)
+
+
 # ----------------------------------------------------------------------------- tensor-core contractions with split operands
 TOL_TF32X3 = 1e-4   # hi/lo-split tf32 operands: measured 1e-5 .. 4e-5 x RMS on these layouts
 
