@@ -77,8 +77,16 @@ class Group:
     aligned_out: bool = True   # output rows allow 16-byte stores
     plain: bool = False        # A is the input rows themselves (dense layer): 16-byte loads and stores
 
+    def resident_bytes(self) -> int:
+        """Bytes of the prepared B operand when all of it stays in shared memory for the life of the CTA:
+        groups with K <= 128 (at most four chunks), where re-fetching B for every row tile would move as
+        many bytes as the output itself.  0 when B is streamed with the A chunks."""
+        total = len(self.chunks) * PIECES * self.n * 128
+        room = SMEM_LIMIT - 3072 - self.extra_bytes() - total
+        return total if (0 < len(self.chunks) <= 4 and room >= 3 * PIECES * A_TILE) else 0
+
     def stage_bytes(self) -> int:
-        return PIECES * A_TILE + PIECES * self.n * 128
+        return PIECES * A_TILE + (0 if self.resident_bytes() else PIECES * self.n * 128)
 
     def staged_epilogue(self) -> bool:
         """dim == 1 groups transpose their output through shared memory for fully coalesced stores."""
@@ -88,10 +96,10 @@ class Group:
         return (Y_BYTES if self.has_y else 0) + (EPI_BYTES if self.staged_epilogue() else 0)
 
     def nstage(self) -> int:
-        return int(max(0, min(6, (SMEM_LIMIT - 3072 - self.extra_bytes()) // self.stage_bytes())))
+        return int(max(0, min(6, (SMEM_LIMIT - 3072 - self.extra_bytes() - self.resident_bytes()) // self.stage_bytes())))
 
     def smem_bytes(self) -> int:
-        return self.nstage() * self.stage_bytes() + self.extra_bytes() + 1024 + 1024
+        return self.resident_bytes() + self.nstage() * self.stage_bytes() + self.extra_bytes() + 1024 + 1024
 
     def work(self) -> int:
         per_tile = sum(40 + self.case_cost[c.case] * max(1, -(-self.zt // PRODUCER_WARPS)) for c in self.chunks)
@@ -229,7 +237,7 @@ def matmul_gemm_spec(k: int, n: int, transpose: bool, scale: float, key: str) ->
         groups = []
         col = 0
         while col < n:
-            width = min(256, n - col)
+            width = min(192 if k <= 128 else 256, n - col)
             g = Group(col, width, 1)
             g.cases.append("vals[0] = xi[q][0];")
             g.case_cost.append(8)
@@ -323,7 +331,7 @@ for (int q = 0; q < {qn}; ++q) {{{{
         # doubling the bytes a producer warp keeps in flight (these groups stream their A rows from HBM)
         batch = 2 if (len(g.cases) == 1 and nch % 2 == 0 and qn * g.case_d1[0] <= 16 and g.nstage() >= 4) else 1
         switch = "\n".join(cases)
-        issue_b = lambda stage, bar, c: f"""if (pw == 0 && lane == 0) {{{{
+        issue_b = lambda stage, bar, c: "" if g.resident_bytes() else f"""if (pw == 0 && lane == 0) {{{{
     const uint32_t bar = tc::smem_u32({bar});
     const uint32_t bbytes = pieces * B_HALF;   // only the pieces this precision uses
     asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(bbytes) : "memory");
@@ -553,14 +561,17 @@ __device__ __forceinline__ void run_group_{gi}(const float* __restrict__ x1, con
     // the length of each dependent MMA chain (and of the fp32 accumulation error); summed in the epilogue
     constexpr int NACC = {2 if 4 * g.n <= 512 else 1};
     constexpr int OUT_OFF = {g.out_off};
-    constexpr uint32_t A_TILE = {A_TILE}, B_HALF = N * 128, STAGE_BYTES = {PIECES} * A_TILE + {PIECES} * B_HALF;
+    constexpr uint32_t A_TILE = {A_TILE}, B_HALF = N * 128, STAGE_BYTES = {g.stage_bytes()};
+    constexpr uint32_t RESIDENT_BYTES = {g.resident_bytes()};   // > 0: the whole prepared B stays in shared memory
     constexpr uint32_t IDESC = tc::idesc_tf32_m128(N);
-    uint8_t* sS = smem;
+    uint8_t* sB = smem;
+    uint8_t* sS = smem + RESIDENT_BYTES;
     uint64_t* bar_full = reinterpret_cast<uint64_t*>(sS + NSTAGE * STAGE_BYTES);
     uint64_t* bar_empty = bar_full + NSTAGE;
     uint64_t* bar_acc_full = bar_empty + NSTAGE;
     uint64_t* bar_acc_empty = bar_acc_full + NBUF;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_acc_empty + NBUF);
+    uint64_t* bar_b = bar_acc_empty + NBUF;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_b + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     float* sY = reinterpret_cast<float*>(sS + NSTAGE * STAGE_BYTES + 1024);
     float* sE = sY + {(Y_BYTES if g.has_y else 0) // 4};   // epilogue staging (only used by staged epilogues)
@@ -571,6 +582,7 @@ __device__ __forceinline__ void run_group_{gi}(const float* __restrict__ x1, con
         *abort_flag = 0;
         for (int s = 0; s < NSTAGE; ++s) {{ tc::mbar_init(&bar_full[s], kProducerWarps); tc::mbar_init(&bar_empty[s], 1); }}
         for (int b = 0; b < NBUF; ++b) {{ tc::mbar_init(&bar_acc_full[b], 1); tc::mbar_init(&bar_acc_empty[b], kEpilogueWarps); }}
+        tc::mbar_init(bar_b, 1);
         tc::mbar_init_fence();
     }}
     if (warp == kMmaWarp) tc::tmem_alloc(tmem_slot, kTmemCols);
@@ -605,12 +617,23 @@ __device__ __forceinline__ void run_group_{gi}(const float* __restrict__ x1, con
         float* sy = sY + pw * {qn * max(d2, 1)};
         uint32_t it = 0;
         bool ok = true;
+        if (RESIDENT_BYTES > 0 && pw == 0 && lane == 0 && cta < tiles) {{
+            // the group's whole prepared B: one bulk copy per chunk, one barrier for all of them
+            const uint32_t bar = tc::smem_u32(bar_b);
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(RESIDENT_BYTES) : "memory");
+            for (int c = 0; c < NCHUNK; ++c)
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                             ::"r"(tc::smem_u32(sB + c * {PIECES} * B_HALF)), "l"(bsrc + static_cast<size_t>(c) * {PIECES} * B_HALF),
+                               "r"({PIECES} * B_HALF), "r"(bar) : "memory");
+        }}
 {PRODUCER_BLOCK}
     }} else if (warp == kMmaWarp && lane == 0) {{
         // ================= MMA issue (single thread)
         uint32_t it = 0;
         int tile_i = 0;
         bool ok = true;
+        if (RESIDENT_BYTES > 0 && cta < tiles) ok = tc::mbar_wait(bar_b, 0, abort_flag, 2000000u);
+        const uint64_t bdesc_resident = tc::smem_desc_k_sw128(tc::smem_u32(sB));
         for (int64_t t = cta; t < tiles && ok; t += nctas, ++tile_i) {{
             const int b = tile_i % NBUF;
             const uint32_t bph = (tile_i / NBUF) & 1;
@@ -625,7 +648,8 @@ __device__ __forceinline__ void run_group_{gi}(const float* __restrict__ x1, con
                 // descriptors differ from the stage's base descriptor only in the address field (bytes >> 4):
                 // everything below is compile-time offsets added to two 64-bit values, fully unrolled
                 const uint64_t adesc = tc::smem_desc_k_sw128(tc::smem_u32(sS + s * STAGE_BYTES));
-                const uint64_t bdesc = adesc + (({PIECES} * A_TILE) >> 4);
+                const uint64_t bdesc = RESIDENT_BYTES > 0 ? bdesc_resident + static_cast<uint64_t>(c) * (({PIECES} * B_HALF) >> 4)
+                                                          : adesc + (({PIECES} * A_TILE) >> 4);
                 if (pieces == 1) tc::issue_chunk<1, N, NACC, A_TILE, B_HALF>(d_base, adesc, bdesc, IDESC, c > 0);
                 else if (pieces == 2) tc::issue_chunk<2, N, NACC, A_TILE, B_HALF>(d_base, adesc, bdesc, IDESC, c > 0);
                 else tc::issue_chunk<3, N, NACC, A_TILE, B_HALF>(d_base, adesc, bdesc, IDESC, c > 0);
