@@ -339,6 +339,10 @@ def interaction_problem(n_atoms: int, seed: int = 0):
     return box, pos, src, dst, shift, time.perf_counter() - t0
 
 
+# DRAM bytes per edge of conv_bwd_tma_kernel (layout l3_23) from an ncu capture of a 16,384-atom case
+NCU_CONV_BWD_L3_TRAFFIC_PER_EDGE = 15690
+
+
 def run_interaction(args, rank, world, device):
     """BASELINE config 5: interaction block, forward + gradient w.r.t. positions.
 
@@ -511,7 +515,10 @@ def run_interaction(args, rank, world, device):
                    "l2": "per-edge weights and their gradient (2 x %.1f GB) far larger than the 126 MB L2" % (e_loc * wn * 4 / 1e9),
                    "parallelism": f"dst-range x{world}" + (" + allgather(node features) + allreduce(dpos)" if world > 1 else "")},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": None, "peak_kind": f"of {peak_kind}", "kernel": "conv_bwd_tma_kernel", "kernel_ms": bwd_ms,
+                     "traffic": NCU_CONV_BWD_L3_TRAFFIC_PER_EDGE * e_loc,
+                     "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch on 428,990 edges "
+                                       "(15,690 B/edge), scaled by the edge count",
+                     "peak_kind": f"of {peak_kind}", "kernel": "conv_bwd_tma_kernel", "kernel_ms": bwd_ms,
                      "algorithmic_bytes_per_launch": bwd_bytes},
         "e2e": e2e,
         "gpu_launches": args.steps * 12,
@@ -562,7 +569,7 @@ def run_uvw(args, rank, world, device):
     rows_total = args.nodes if args.nodes > 0 else 1_048_576
     rows = rows_total // world
     tp = o3.FullyConnectedTensorProduct("128x0e+64x1o+32x2e", "0e+1o+2e+3o", "128x0e+64x1o+32x2e", math_mode="tf32").to(device)
-    lin = o3.Linear(tp.irreps_out, tp.irreps_out).to(device)
+    lin = o3.Linear(tp.irreps_out, tp.irreps_out, math_mode="tf32x3").to(device)
     with torch.no_grad():
         for view in tp.weight_views():
             view.div_((view.shape[0] * view.shape[1]) ** 0.5)
@@ -599,7 +606,7 @@ def run_uvw(args, rank, world, device):
     print(json.dumps({
         "metric": "uvw TP rows/sec (tf32 tensor cores) + Linear", "value": rows_total / (ms_both * 1e-3), "unit": "rows/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_both, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "tf32 operands, f32 accumulate (TP); f32 (Linear)", "data": "synthetic",
+        "scaling": "weak", "vs_baseline": None, "dtype": "tf32 operands, f32 accumulate (TP); hi/lo-split tf32 operands (Linear)", "data": "synthetic",
         "config": {"workload": "uvw_fctp", "rows": rows_total, "tp_ms": ms_tp, "linear_ms": ms_lin,
                    "l2": "inputs and outputs (4.1 GB) far larger than the 126 MB L2", "parallelism": f"replicas x{world}"},
         "roofline": {"bound": "tensor", "achieved": achieved_tf, "peak": tf32_peak, "unit": "TFLOP/s",

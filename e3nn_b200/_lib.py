@@ -101,7 +101,10 @@ class LayoutModule:
         lib.e3b_conv_bwd.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                      c_void_p, c_void_p, c_int64, c_int64, c_int64, c_float, c_void_p, c_void_p]
         lib.e3b_conv_select.argtypes = [c_int]
-        for name in ("e3b_uvu_fwd", "e3b_uvu_bwd", "e3b_conv_fwd", "e3b_conv_bwd", "e3b_layout_info", "e3b_conv_select"):
+        lib.e3b_conv_bwd_x.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                       c_int64, c_int64, c_int64, c_float, c_void_p, c_void_p]
+        for name in ("e3b_uvu_fwd", "e3b_uvu_bwd", "e3b_conv_fwd", "e3b_conv_bwd", "e3b_layout_info", "e3b_conv_select",
+                     "e3b_conv_bwd_x"):
             getattr(lib, name).restype = c_int
         dims = (c_int32 * 8)()
         lib.e3b_layout_info(dims)

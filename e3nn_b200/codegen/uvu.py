@@ -228,6 +228,35 @@ def emit_backward_body(layout: UvuLayout, want_dx: bool = True) -> str:
     return "\n".join(out)
 
 
+def emit_dx_body(layout: UvuLayout) -> str:
+    """Per-(edge, u) cotangent of the first operand only: ``dxi<i1>[i] = sum_paths sum_k t_ik w g_k``.
+
+    In scope: ``u``, ``Y``/``yrow``, ``wrow``, ``g<io>[k]``.  Does not read the first operand at all."""
+    spec = layout.spec
+    out: List[str] = []
+    for i1 in layout.in1_used:
+        dim = spec.irreps_in1[i1].ir.dim
+        out.append(f"float dxi{i1}[{dim}];")
+        out.append(f"#pragma unroll\nfor (int i = 0; i < {dim}; ++i) dxi{i1}[i] = 0.0f;")
+    for p in layout.paths:
+        out.append(f"// path {p.index}: l={p.l1} (x) l={p.l2} -> l={p.l3}")
+        out.append(f"if (u < {p.mul1}) {{")
+        for v in range(p.mul2):
+            out.append("  {")
+            t_lines, t = _t_pairs(p, v, layout)
+            out += ["    " + line for line in t_lines]
+            wname = f"wrow[{p.woff} + u * {p.mul2} + {v}]" if p.woff >= 0 else "1.0f"
+            for k in range(2 * p.l3 + 1):
+                out.append(f"    const float wg{k} = {wname} * g{p.io}[{k}];")
+            for i in range(2 * p.l1 + 1):
+                terms = [f"{t[(i, k)]} * wg{k}" for k in range(2 * p.l3 + 1) if (i, k) in t]
+                if terms:
+                    out.append(f"    dxi{p.i1}[{i}] += {' + '.join(terms)};")
+            out.append("  }")
+        out.append("}")
+    return "\n".join(out)
+
+
 def _indent(text: str, n: int) -> str:
     pad = " " * n
     return "\n".join(pad + line if line else line for line in text.split("\n"))
@@ -291,6 +320,11 @@ def emit_module(spec: TPSpec) -> str:
     fwd_body = emit_forward_body(L)
     bwd_body = emit_backward_body(L, want_dx=True)
     bwd_body_nodx = emit_backward_body(L, want_dx=False)
+    dx_body = emit_dx_body(L)
+    dx_atomic = "\n".join(
+        f"if (u < {spec.irreps_in1[i1].mul}) {{\n#pragma unroll\n  for (int i = 0; i < {spec.irreps_in1[i1].ir.dim}; ++i) "
+        f"atomicAdd(dxrow + {spec.irreps_in1.offsets()[i1]} + u * {spec.irreps_in1[i1].ir.dim} + i, dxi{i1}[i]);\n}}"
+        for i1 in L.in1_used)
     y_load = f"float Y[{max(L.d2, 1)}];\n#pragma unroll\nfor (int j = 0; j < {L.d2}; ++j) Y[j] = yrow[j];"
 
     has_sh = sh_l is not None
@@ -425,6 +459,41 @@ __global__ void __launch_bounds__(kThreads) conv_fwd_kernel(const float* __restr
         }}
 {_indent(chr(10).join(acc_store_conv), 8)}
 {_indent(zero_code, 8)}
+    }}
+}}
+
+// ---------------------------------------------------------------- gradient of conv_fwd w.r.t. the node features
+// grad_node_x[src[e], u, i] += sum_paths sum_k t_ik(Y_e) w[e, p, u] g[dst, p, u, k]: one group per destination
+// row (its cotangent stays in registers), float atomics into the zeroed table (sources are not sorted).
+template <int IN2_MODE>
+__global__ void __launch_bounds__(kThreads) conv_bwd_x_kernel(const float* __restrict__ x2, const int64_t* __restrict__ edge_src,
+        const int64_t* __restrict__ rowptr, const int64_t* __restrict__ perm, const float* __restrict__ w,
+        const float* __restrict__ gout, float* __restrict__ grad_node_x, int64_t num_nodes, int64_t num_src, float scale,
+        int* __restrict__ status) {{
+    const int u = threadIdx.x % kG;
+    const int slot = threadIdx.x / kG;
+    for (int64_t n = static_cast<int64_t>(blockIdx.x) * kRowsPerBlock + slot; n < num_nodes;
+         n += static_cast<int64_t>(gridDim.x) * kRowsPerBlock) {{
+        const float* grow = gout + n * kDout;
+{_indent(chr(10).join(g_load_conv), 8)}
+        const int64_t e_begin = rowptr[n], e_end = rowptr[n + 1];
+        for (int64_t ee = e_begin; ee < e_end; ++ee) {{
+            const int64_t e = perm ? perm[ee] : ee;
+            const int64_t s = edge_src[e];
+            if (s < 0 || s >= num_src) {{ if (u == 0) atomicExch(status, 2); continue; }}
+            const float* wrow = w + e * kWn;
+            float* dxrow = grad_node_x + s * kD1;
+            float Y[kD2 > 0 ? kD2 : 1];
+            if (IN2_MODE == 1) {{
+                e3b_sh_unit<kShLmax>(x2 + e * 3, Y);
+            }} else {{
+                const float* yrow = x2 + e * kD2;
+#pragma unroll
+                for (int j = 0; j < kD2; ++j) Y[j] = yrow[j];
+            }}
+{_indent(dx_body, 12)}
+{_indent(dx_atomic, 12)}
+        }}
     }}
 }}
 
@@ -592,6 +661,29 @@ extern "C" int e3b_conv_bwd(const float* node_x, const float* x2, int in2_mode, 
     else
         conv_bwd_kernel<0><<<grid, kThreads, 0, s>>>(node_x, x2, edge_src, rowptr, perm, w, grad_out, grad_w, grad_x2, num_nodes, num_src, scale, status);
     return e3b_layout_check("conv_bwd");
+}}
+
+// Gradient of e3b_conv_fwd w.r.t. the node features: grad_node_x [num_src, kD1] is overwritten.
+extern "C" int e3b_conv_bwd_x(const float* x2, int in2_mode, const int64_t* edge_src, const int64_t* rowptr,
+                              const int64_t* perm, const float* w, const float* grad_out, float* grad_node_x,
+                              int64_t num_nodes, int64_t num_src, int64_t num_edges, float scale, int32_t* status,
+                              void* stream) {{
+    if (num_nodes < 0 || num_edges < 0 || num_src < 0) return e3b_layout_fail(-1, "conv_bwd_x: negative size");
+    if (num_src == 0) return 0;
+    if (!grad_node_x) return e3b_layout_fail(-1, "conv_bwd_x: null pointer");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    cudaError_t err = cudaMemsetAsync(grad_node_x, 0, sizeof(float) * kD1 * static_cast<size_t>(num_src), s);
+    if (err != cudaSuccess) return e3b_layout_fail(-2, "conv_bwd_x: memset: %s", cudaGetErrorString(err));
+    if (num_nodes == 0 || num_edges == 0) return 0;
+    if (!rowptr || !grad_out || !status || !x2 || !edge_src || (kWn > 0 && !w)) return e3b_layout_fail(-1, "conv_bwd_x: null pointer");
+    if (in2_mode == 1 && kShLmax < 0) return e3b_layout_fail(-3, "conv_bwd_x: irreps_in2 is not Y^0..Y^L, pass rows instead");
+    const int64_t blocks = (num_nodes + kRowsPerBlock - 1) / kRowsPerBlock;
+    const unsigned grid = static_cast<unsigned>(blocks < 148LL * 64 ? blocks : 148LL * 64);
+    if (in2_mode == 1)
+        conv_bwd_x_kernel<1><<<grid, kThreads, 0, s>>>(x2, edge_src, rowptr, perm, w, grad_out, grad_node_x, num_nodes, num_src, scale, status);
+    else
+        conv_bwd_x_kernel<0><<<grid, kThreads, 0, s>>>(x2, edge_src, rowptr, perm, w, grad_out, grad_node_x, num_nodes, num_src, scale, status);
+    return e3b_layout_check("conv_bwd_x");
 }}
 """
     return src

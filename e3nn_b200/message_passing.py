@@ -69,10 +69,19 @@ class _ConvFunction(torch.autograd.Function):
     def backward(ctx, grad_out):
         node_x, x2, weight, edge_src, rowptr, perm = ctx.saved_tensors
         mod, in2_mode, scale, has_perm = ctx.meta
-        if ctx.needs_input_grad[0]:
-            raise NotImplementedError("gradient of the fused convolution w.r.t. node features is not implemented")
         grad_out = grad_out.contiguous()
         N, E = rowptr.numel() - 1, edge_src.numel()
+        gx = None
+        if ctx.needs_input_grad[0]:
+            gx = torch.empty_like(node_x)
+            st = torch.zeros(1, dtype=torch.int32, device=node_x.device)
+            with torch.cuda.device(node_x.device):
+                rc = mod.lib.e3b_conv_bwd_x(_lib._ptr(x2), in2_mode, _lib._ptr(edge_src), _lib._ptr(rowptr),
+                                            _lib._ptr(perm) if has_perm else None, _lib._ptr(weight), _lib._ptr(grad_out),
+                                            _lib._ptr(gx), N, node_x.shape[0], E, scale, _lib._ptr(st), _lib.stream_ptr())
+            mod.check(rc, "e3b_conv_bwd_x")
+            if not (ctx.needs_input_grad[1] or ctx.needs_input_grad[2]):
+                return gx, None, None, None, None, None, None, None, None
         gw = torch.empty_like(weight)
         gx2 = torch.empty_like(x2)
         status = torch.zeros(1, dtype=torch.int32, device=node_x.device)
@@ -82,7 +91,7 @@ class _ConvFunction(torch.autograd.Function):
                                       _lib._ptr(gw), _lib._ptr(gx2), N, node_x.shape[0], E, scale, _lib._ptr(status),
                                       _lib.stream_ptr())
         mod.check(rc, "e3b_conv_bwd")
-        return None, gx2, gw, None, None, None, None, None, None
+        return gx, gx2, gw, None, None, None, None, None, None
 
 
 def conv_uvu(

@@ -82,6 +82,17 @@ int e3b_conv_bwd(const float* node_x, const float* x2, int in2_mode, const int64
                  const int64_t* perm, const float* w, const float* grad_out, float* grad_w, float* grad_x2,
                  int64_t num_nodes, int64_t num_src, int64_t num_edges, float scale, int32_t* status, void* stream);
 
+/*
+ * Gradient of e3b_conv_fwd w.r.t. the node features, the transpose of the gather
+ * x[edge_src] (e3nn/nn/models/v2106/points_convolution.py:105) composed with the tensor product:
+ *   grad_node_x[src[e], u, i] += sum_paths sum_k (sum_j C_ijk Y_e[j]) w[e, p, u] grad_out[dst(e), p, u, k].
+ * grad_node_x [num_src, d1] is overwritten (zeroed, then accumulated with float atomics: edges are
+ * sorted by destination, not by source).  The other arguments are those of e3b_conv_bwd.
+ */
+int e3b_conv_bwd_x(const float* x2, int in2_mode, const int64_t* edge_src, const int64_t* rowptr, const int64_t* perm,
+                   const float* w, const float* grad_out, float* grad_node_x, int64_t num_nodes, int64_t num_src,
+                   int64_t num_edges, float scale, int32_t* status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

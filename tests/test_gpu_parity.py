@@ -281,10 +281,11 @@ def test_conv_random_layouts_forward_backward(idx):
     perm, rowptr = e3nn_b200.csr_from_dst(dst.to(DEV), N)
     vg = vec.clone().to(DEV).requires_grad_(True)
     wg = w.clone().to(DEV).requires_grad_(True)
-    out = e3nn_b200.conv_uvu(tp, node_x.to(DEV), vg, src.to(DEV), rowptr, wg, perm=perm, scale=0.3,
+    xg = node_x.clone().to(DEV).requires_grad_(True)
+    out = e3nn_b200.conv_uvu(tp, xg, vg, src.to(DEV), rowptr, wg, perm=perm, scale=0.3,
                              edge_attr_is_vector=True)
-    v64, w64 = vec.double().requires_grad_(True), w.double().requires_grad_(True)
-    ref = orc.conv_uvu(str(tp.irreps_in1), str(tp.irreps_in2), str(tp.irreps_out), _ins(tp), node_x.double(), v64, src,
+    v64, w64, x64 = vec.double().requires_grad_(True), w.double().requires_grad_(True), node_x.double().requires_grad_(True)
+    ref = orc.conv_uvu(str(tp.irreps_in1), str(tp.irreps_in2), str(tp.irreps_out), _ins(tp), x64, v64, src,
                        dst, w64, N, list(range(lmax + 1)), scale=0.3)
     assert rel_err(out.detach().cpu(), ref.detach()) < TOL
     go = torch.randn_like(ref)
@@ -292,6 +293,13 @@ def test_conv_random_layouts_forward_backward(idx):
     out.backward(go.float().to(DEV))
     assert rel_err(wg.grad.cpu(), w64.grad) < TOL
     assert rel_err(vg.grad.cpu(), v64.grad) < 2e-5
+    # node features: the transpose of the gather, accumulated with float atomics (order not fixed)
+    assert rel_err(xg.grad.cpu(), x64.grad) < TOL
+    # only the node features require a gradient: the weight / vector kernel is skipped
+    x2 = node_x.clone().to(DEV).requires_grad_(True)
+    out2 = e3nn_b200.conv_uvu(tp, x2, vec.to(DEV), src.to(DEV), rowptr, w.to(DEV), perm=perm, scale=0.3, edge_attr_is_vector=True)
+    out2.backward(go.float().to(DEV))
+    assert rel_err(x2.grad.cpu(), x64.grad) < TOL
 
 
 def test_conv_deterministic_and_sorted_equals_permuted():
