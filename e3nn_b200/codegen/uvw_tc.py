@@ -352,7 +352,7 @@ __device__ __forceinline__ void run_group_{gi}(const float* __restrict__ x1, con
 namespace {{
 
 constexpr int kEpilogueWarps = 4;
-constexpr int kProducerWarps = 8;
+constexpr int kProducerWarps = 16;
 constexpr int kMmaWarp = kEpilogueWarps + kProducerWarps;
 constexpr int kThreads = (kMmaWarp + 1) * 32;
 constexpr int kTmemCols = 512;
