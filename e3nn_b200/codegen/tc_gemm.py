@@ -41,7 +41,7 @@ SMEM_LIMIT = 227 * 1024
 A_TILE = 128 * 128          # one 128 x 32 fp32 sub-tile
 Y_BYTES = 8192
 EPI_BYTES = 4 * 32 * 64 * 4   # 4 epilogue warps x (32 rows x 64 columns) fp32
-PRODUCER_WARPS = 8
+PRODUCER_WARPS = 8          # default; GemmSpec.producer_warps selects 8 or 16 per module
 PIECES = 2                  # tf32 pieces the stages have room for (hi, lo); 3 is supported by the code below
 
 
@@ -57,6 +57,9 @@ class Chunk:
     sk: int
     sn: int
     scale: float
+    # column blocks of equal width with their own weight slice and scale (several paths side by side in N);
+    # None: one block, (wbase, scale)
+    blocks: Optional[List[Tuple[int, float]]] = None
 
 
 @dataclass
@@ -115,6 +118,9 @@ class GemmSpec:
     key: str
     title: str
     zero_ranges: List[Tuple[int, int]] = field(default_factory=list)   # output columns no group writes
+    # 8 producer warps (13 warps per CTA, 128 registers each) suit contractions bound by their output stores
+    # (K <= 128); 16 (21 warps, 80 registers) hide the operand-load latency of long-K contractions
+    producer_warps: int = 8
 
 
 # ------------------------------------------------------------------------------------------- front ends
@@ -168,7 +174,7 @@ def uvw_gemm_spec(spec: TPSpec) -> Optional[GemmSpec]:
     written = set(groups)
     zero = [(oo[i], mul * ir.dim) for i, (mul, ir) in enumerate(spec.irreps_out) if i not in written and mul * ir.dim > 0]
     return GemmSpec(spec.irreps_in1.dim, spec.irreps_in2.dim, spec.irreps_out.dim, out, spec.key(),
-                    f"uvw {spec.irreps_in1} (x) {spec.irreps_in2} -> {spec.irreps_out}", zero)
+                    f"uvw {spec.irreps_in1} (x) {spec.irreps_in2} -> {spec.irreps_out}", zero, producer_warps=16)
 
 
 def linear_gemm_spec(irreps_in: Irreps, irreps_out: Irreps, instructions, transpose: bool, key: str) -> Optional[GemmSpec]:
@@ -207,6 +213,24 @@ def linear_gemm_spec(irreps_in: Irreps, irreps_out: Irreps, instructions, transp
             else:           # K index = u, n = w
                 g.chunks.append(Chunk(0, so[s] + u0 * ir.dim, offs[n] + u0 * mul_out, mul_out, 1, float(ins.path_weight)))
     out = [groups[k] for k in sorted(groups)]
+    if transpose:
+        # Neighbouring output slots fed by the same input block (the paths of one l in a convolution layout)
+        # become one group with the paths side by side in N: the shared A operand is loaded, split and stored
+        # once per group instead of once per path.
+        merged: List[Group] = []
+        for g in out:
+            m = merged[-1] if merged else None
+            width = len(m.chunks[0].blocks) if (m and m.chunks[0].blocks) else 1
+            limit = 192 if g.dim == 1 else 256
+            if (m is not None and m.dim == g.dim and m.n // width == g.n and m.n + g.n <= limit
+                    and g.out_off == m.out_off + m.n * m.dim and len(m.chunks) == len(g.chunks)
+                    and all(a.xoff == b.xoff and a.sk == b.sk and a.sn == b.sn for a, b in zip(m.chunks, g.chunks))):
+                for a, b in zip(m.chunks, g.chunks):
+                    a.blocks = (a.blocks or [(a.wbase, a.scale)]) + [(b.wbase, b.scale)]
+                m.n += g.n
+            else:
+                merged.append(g)
+        out = merged
     for g in out:
         g.has_y = False
         g.aligned_out = dst.dim % 4 == 0 and g.out_off % 4 == 0
@@ -214,7 +238,8 @@ def linear_gemm_spec(irreps_in: Irreps, irreps_out: Irreps, instructions, transp
         return None
     zero = [(do[i], mul * ir.dim) for i, (mul, ir) in enumerate(dst) if i not in groups and mul * ir.dim > 0]
     return GemmSpec(src.dim, 0, dst.dim, out, key,
-                    f"linear{'^T' if transpose else ''} {irreps_in} -> {irreps_out}", zero)
+                    f"linear{'^T' if transpose else ''} {irreps_in} -> {irreps_out}", zero,
+                    producer_warps=8 if transpose else 16)
 
 
 def matmul_gemm_spec(k: int, n: int, transpose: bool, scale: float, key: str) -> Optional[GemmSpec]:
@@ -253,7 +278,8 @@ def matmul_gemm_spec(k: int, n: int, transpose: bool, scale: float, key: str) ->
         g.plain = d_in % 4 == 0
     if any(g.nstage() < 2 for g in groups):
         return None
-    return GemmSpec(d_in, 0, d_out, groups, key, f"matmul{'^T' if transpose else ''} [{k} x {n}] scale {scale!r}")
+    return GemmSpec(d_in, 0, d_out, groups, key, f"matmul{'^T' if transpose else ''} [{k} x {n}] scale {scale!r}",
+                    producer_warps=16 if transpose else 8)
 
 
 # ------------------------------------------------------------------------------------------- emission
@@ -264,6 +290,8 @@ def _indent(text: str, n: int) -> str:
 
 def emit_module(gs: GemmSpec) -> str:
     d1, d2, dout = gs.d1, gs.d2, gs.dout
+    PRODUCER_WARPS = gs.producer_warps
+    assert PRODUCER_WARPS in (8, 16)
     smem_max = max(g.smem_bytes() for g in gs.groups)
     assert smem_max <= SMEM_LIMIT
     has_y = d2 > 0
@@ -275,14 +303,17 @@ def emit_module(gs: GemmSpec) -> str:
         nch = len(g.chunks)
         prep_offsets.append(prep_off)
         prep_off += nch * PIECES * g.n * 128
-        arr = lambda name, vals, typ="int": f"__constant__ {typ} {name}{gi}[{nch}] = {{{', '.join(str(v) for v in vals)}}};"
+        arr = lambda name, vals, typ="int": f"__constant__ {typ} {name}{gi}[{len(vals)}] = {{{', '.join(str(v) for v in vals)}}};"
+        nblk = len(g.chunks[0].blocks) if g.chunks[0].blocks else 1
+        assert all((len(c.blocks) if c.blocks else 1) == nblk for c in g.chunks) and g.n % nblk == 0
+        cblocks = [c.blocks if c.blocks else [(c.wbase, c.scale)] for c in g.chunks]
         consts.append("\n".join([
             arr("kCase", [c.case for c in g.chunks]),
             arr("kXOff", [c.xoff for c in g.chunks]),
-            arr("kWBase", [c.wbase for c in g.chunks]),
+            arr("kWBase", [wb for blks in cblocks for wb, _ in blks]),
             arr("kSK", [c.sk for c in g.chunks]),
             arr("kSN", [c.sn for c in g.chunks]),
-            arr("kScale", [_f(c.scale) for c in g.chunks], "float"),
+            arr("kScale", [_f(sc) for blks in cblocks for _, sc in blks], "float"),
         ]))
         qn = -(-g.zt // PRODUCER_WARPS)
         def load_code(ci: int, xi: str, xoff: str) -> str:
@@ -396,10 +427,12 @@ for (int q = 0; q < {qn}; ++q) {{{{
             }}
             __syncwarp();""" if has_y else ""
         if g.plain:
-            assert g.dim == 1 and g.zt == 128 and PRODUCER_WARPS == 8 and not has_y
+            assert g.dim == 1 and g.zt == 128 and 128 % (4 * PRODUCER_WARPS) == 0 and not has_y
+            RPW = 128 // PRODUCER_WARPS      # rows of the tile per producer warp
+            NJ = RPW // 4                    # 16-byte loads per lane and chunk
             B = 2 if (nch % 2 == 0 and g.nstage() >= 4) else 1     # chunks per step (loaded together, one step ahead)
             ld = lambda dst, ptr, c: "\n".join(
-                f"{dst}[{j}] = *reinterpret_cast<const float4*>({ptr}[{j}] + kXOff{gi}[{c}]);" for j in range(4))
+                f"{dst}[{j}] = *reinterpret_cast<const float4*>({ptr}[{j}] + kXOff{gi}[{c}]);" for j in range(NJ))
             loads_first = "\n".join(ld(f"cur{b}", "xp", f"{b}") for b in range(B))
             loads_same = "\n".join(ld(f"nxt{b}", "xp", f"c + {B + b}") for b in range(B))
             loads_next = "\n".join(ld(f"nxt{b}", "xq", f"{b}") for b in range(B))
@@ -410,7 +443,7 @@ for (int q = 0; q < {qn}; ++q) {{{{
     uint8_t* stage = sS + s * STAGE_BYTES;
 {_indent(issue_b('stage', '&bar_full[s]', f'(c + {b})'), 4)}
 #pragma unroll
-    for (int j = 0; j < 4; ++j) tc::split_store4<A_TILE>(cur{b}[j], stage + po[j], pieces);
+    for (int j = 0; j < {NJ}; ++j) tc::split_store4<A_TILE>(cur{b}[j], stage + po[j], pieces);
     tc::fence_proxy_async_smem();
     __syncwarp();
     if (lane == 0) tc::mbar_arrive(&bar_full[s]);
@@ -418,29 +451,29 @@ for (int q = 0; q < {qn}; ++q) {{{{
             waits = "\n".join(
                 f"if (!tc::mbar_wait(&bar_empty[(it + {b}) % NSTAGE], (((it + {b}) / NSTAGE) & 1) ^ 1u, abort_flag)) {{ ok = false; break; }}"
                 for b in range(B))
-            rotate = "\n".join(f"for (int j = 0; j < 4; ++j) cur{b}[j] = nxt{b}[j];" for b in range(B))
-            decl = ", ".join(f"cur{b}[4], nxt{b}[4]" for b in range(B))
+            rotate = "\n".join(f"for (int j = 0; j < {NJ}; ++j) cur{b}[j] = nxt{b}[j];" for b in range(B))
+            decl = ", ".join(f"cur{b}[{NJ}], nxt{b}[{NJ}]" for b in range(B))
             PRODUCER_BLOCK = f"""        // rows of A are the input rows: a lane moves 16 bytes (4 consecutive K) of one row, 8 lanes one 128-byte
-        // row segment; a warp owns 16 consecutive rows of the tile.  The loads of the next step (next chunks of
+        // row segment; a warp owns {RPW} consecutive rows of the tile.  The loads of the next step (next chunks of
         // this tile or the first chunks of the CTA's next tile) are in flight while this step is converted.
-        uint32_t po[4];
+        uint32_t po[{NJ}];
         const int pc4 = lane & 7;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {{
-            const int r = pw * 16 + 4 * j + (lane >> 3);
+        for (int j = 0; j < {NJ}; ++j) {{
+            const int r = pw * {RPW} + 4 * j + (lane >> 3);
             po[j] = (r >> 3) * 1024 + (r & 7) * 128 + ((pc4 ^ (r & 7)) << 4);
         }}
-        auto row_ptrs = [&](int64_t t, const float* (&xp)[4]) {{
+        auto row_ptrs = [&](int64_t t, const float* (&xp)[{NJ}]) {{
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {{
-                int64_t z = t * ZT + pw * 16 + 4 * j + (lane >> 3);
+            for (int j = 0; j < {NJ}; ++j) {{
+                int64_t z = t * ZT + pw * {RPW} + 4 * j + (lane >> 3);
                 if (z >= Z) z = Z - 1;            // rows past the end read the last row (their output is not stored)
                 xp[j] = x1 + z * {d1} + 4 * pc4;
             }}
         }};
         float4 {decl};
-        const float* xp[4];
-        const float* xq[4];
+        const float* xp[{NJ}];
+        const float* xq[{NJ}];
         if (cta < tiles) {{
             row_ptrs(cta, xp);
 {_indent(loads_first, 12)}
@@ -461,7 +494,7 @@ for (int q = 0; q < {qn}; ++q) {{{{
 {_indent(rotate, 16)}
             }}
 #pragma unroll
-            for (int j = 0; j < 4; ++j) xp[j] = xq[j];
+            for (int j = 0; j < {NJ}; ++j) xp[j] = xq[j];
         }}
 """
         else:
@@ -670,7 +703,9 @@ __device__ __forceinline__ void prep_group_{gi}(const float* __restrict__ W, uin
     if (idx >= NCHUNK * 32 * N) return;
     const int c = idx / (32 * N), rem = idx - c * 32 * N;
     const int kk = rem / N, n = rem - kk * N;   // n fastest: coalesced when sn == 1
-    const float v = kScale{gi}[c] * W[kWBase{gi}[c] + kk * kSK{gi}[c] + n * kSN{gi}[c]];
+    constexpr int NBLK = {len(g.chunks[0].blocks) if g.chunks[0].blocks else 1}, BW = N / NBLK;   // column blocks with their own weight slice
+    const int blk = n / BW, nn = n - blk * BW;
+    const float v = kScale{gi}[c * NBLK + blk] * W[kWBase{gi}[c * NBLK + blk] + kk * kSK{gi}[c] + nn * kSN{gi}[c]];
     const float hi = tc::to_tf32(v);
     const float rest = v - hi;
     const float mid = tc::to_tf32(rest);
