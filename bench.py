@@ -327,16 +327,28 @@ def run_sh(args, rank, world, device):
     }), flush=True)
 
 
-def interaction_problem(n_atoms: int, seed: int = 0):
-    """Positions and neighbour list of BASELINE config 5 at `n_atoms` (host tensors, edges sorted by destination)."""
+def interaction_problem(n_atoms: int, seed: int = 0, device=None):
+    """Positions and neighbour list of BASELINE config 5 at `n_atoms` (host tensors, edges sorted by destination).
+
+    With `device` the list is built by the device cell list (timed with a synchronisation on both sides, after
+    one untimed call); without it by the host k-d tree (the CPU arms)."""
     from e3nn_b200 import nn as bnn
 
     box = (n_atoms / 0.05) ** (1.0 / 3.0)
     gen = torch.Generator().manual_seed(seed)
     pos = torch.rand(n_atoms, 3, generator=gen) * box
+    if device is None:
+        t0 = time.perf_counter()
+        src, dst, shift = bnn.radius_graph_pbc(pos, box, 5.0)
+        return box, pos, src, dst, shift, time.perf_counter() - t0
+    pos_d = pos.to(device)
+    bnn.neighbor_list_pbc(pos_d, box, 5.0)
+    torch.cuda.synchronize()
     t0 = time.perf_counter()
-    src, dst, shift = bnn.radius_graph_pbc(pos, box, 5.0)
-    return box, pos, src, dst, shift, time.perf_counter() - t0
+    src, dst, shift, _ = bnn.neighbor_list_pbc(pos_d, box, 5.0)
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    return box, pos, src.cpu(), dst.cpu(), shift.cpu(), dt
 
 
 # DRAM bytes per edge of conv_bwd_tma_kernel (layout l3_23) from an ncu capture of a 16,384-atom case
@@ -354,7 +366,7 @@ def run_interaction(args, rank, world, device):
     from e3nn_b200 import sharding
 
     n_atoms = args.nodes if args.nodes > 0 else 262_144
-    box, pos_host, src, dst, shift, t_graph = interaction_problem(n_atoms)
+    box, pos_host, src, dst, shift, t_graph = interaction_problem(n_atoms, device=device)
     E = src.numel()
     rowptr_host = torch.zeros(n_atoms + 1, dtype=torch.int64)
     rowptr_host[1:] = torch.cumsum(torch.bincount(dst, minlength=n_atoms), 0)
@@ -509,7 +521,7 @@ def run_interaction(args, rank, world, device):
         "data": "synthetic",
         "config": {"workload": "interaction_l3", "atoms": n_atoms, "edges": E, "neighbours_per_atom": E / n_atoms,
                    "box": box, "cutoff": 5.0, "atoms_per_s": n_atoms / (ms_step * 1e-3),
-                   "neighbour_list_s_host": t_graph, "weight_numel": wn, "mid_dim": dmid,
+                   "neighbour_list_s_device": t_graph, "weight_numel": wn, "mid_dim": dmid,
                    "conv_fwd_ms": fwd_ms, "conv_fwd_hbm_frac": fwd_bytes / (fwd_ms * 1e-3) / 1e9 / peak,
                    "per_edge_weights": "materialised in HBM (%.1f GB per rank), radial network not fused yet" % (e_loc * wn * 4 / 1e9),
                    "l2": "per-edge weights and their gradient (2 x %.1f GB) far larger than the 126 MB L2" % (e_loc * wn * 4 / 1e9),

@@ -8,7 +8,7 @@ from __future__ import annotations
 import ctypes
 import os
 import threading
-from ctypes import POINTER, c_char_p, c_float, c_int, c_int32, c_int64, c_void_p
+from ctypes import POINTER, c_char_p, c_double, c_float, c_int, c_int32, c_int64, c_void_p
 from typing import Dict, Optional
 
 import torch
@@ -71,8 +71,13 @@ def core() -> ctypes.CDLL:
                                              c_void_p, c_void_p, c_void_p, c_void_p]
         lib.e3b_radial_embed_bwd.argtypes = [c_void_p] * 7 + [c_int64, c_int64, c_int, c_int, c_float, c_float, c_float, c_int,
                                              c_void_p, c_void_p, c_void_p]
+        lib.e3b_neighbor_scratch_bytes.argtypes = [c_int64, c_double, c_double]
+        lib.e3b_neighbor_scratch_bytes.restype = c_int64
+        lib.e3b_neighbor_count.argtypes = [c_void_p, c_int64, c_double, c_double, c_void_p, c_int64, c_void_p, c_void_p]
+        lib.e3b_neighbor_fill.argtypes = [c_void_p, c_int64, c_double, c_double, c_void_p, c_int64, c_void_p, c_void_p,
+                                          c_void_p, c_void_p, c_void_p]
         for name in ("e3b_sh_fwd", "e3b_sh_bwd", "e3b_csr_from_dst", "e3b_dense_fwd", "e3b_fill_columns",
-                     "e3b_radial_embed_fwd", "e3b_radial_embed_bwd"):
+                     "e3b_radial_embed_fwd", "e3b_radial_embed_bwd", "e3b_neighbor_count", "e3b_neighbor_fill"):
             getattr(lib, name).restype = c_int
         _core = lib
     return _core

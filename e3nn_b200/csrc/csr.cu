@@ -9,6 +9,7 @@
 // Row pointers come from a histogram of dst and a single-block exclusive scan.
 // The result is bit-identical to argsort(dst, stable=True) / cumsum(bincount(dst)).
 #include "common.cuh"
+#include "scan.cuh"
 
 #include <mutex>
 
@@ -68,43 +69,6 @@ __global__ void csr_prepare_kernel(const int64_t* __restrict__ dst, int64_t E, i
     }
 }
 
-// Exclusive scan of counts[N] into rowptr[N+1] (int64) by one block of 1024 threads.
-__global__ void __launch_bounds__(1024) csr_rowptr_kernel(const int32_t* __restrict__ counts, int64_t N,
-                                                          int64_t* __restrict__ rowptr) {
-    __shared__ int64_t warp_sums[32];
-    __shared__ int64_t carry;
-    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
-    if (t == 0) carry = 0;
-    __syncthreads();
-    for (int64_t base = 0; base < N; base += 1024) {
-        const int64_t i = base + t;
-        int64_t v = i < N ? counts[i] : 0;
-        int64_t incl = v;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const int64_t up = __shfl_up_sync(0xffffffffu, incl, o);
-            if (lane >= o) incl += up;
-        }
-        if (lane == 31) warp_sums[warp] = incl;
-        __syncthreads();
-        if (warp == 0) {
-            int64_t w = warp_sums[lane];
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const int64_t up = __shfl_up_sync(0xffffffffu, w, o);
-                if (lane >= o) w += up;
-            }
-            warp_sums[lane] = w;  // inclusive over warps
-        }
-        __syncthreads();
-        const int64_t before = carry + (warp > 0 ? warp_sums[warp - 1] : 0) + (incl - v);
-        if (i < N) rowptr[i] = before;
-        __syncthreads();
-        if (t == 1023) carry = before + v;
-        __syncthreads();
-    }
-    if (t == 0) rowptr[N] = carry;
-}
 
 __global__ void __launch_bounds__(kSortThreads) radix_hist_kernel(const uint32_t* __restrict__ keys, int64_t E, int shift,
                                                                   uint32_t* __restrict__ hist, int64_t nblocks) {
@@ -234,7 +198,7 @@ extern "C" int e3b_csr_from_dst(const int64_t* dst, int64_t num_edges, int64_t n
     if (N > 0) E3B_CUDA_TRY(cudaMemsetAsync(sc.counts, 0, static_cast<size_t>(N) * 4, s));
     const int grid = static_cast<int>(std::min<int64_t>(ceil_div(std::max<int64_t>(E, 1), 256), kNumSMs * 8));
     if (E > 0) csr_prepare_kernel<<<grid, 256, 0, s>>>(dst, E, N, sc.keys[0], sc.vals[0], sc.counts, status);
-    csr_rowptr_kernel<<<1, 1024, 0, s>>>(sc.counts, N, rowptr);
+    exclusive_scan_i32_kernel<<<1, 1024, 0, s>>>(sc.counts, N, rowptr);
     if (E == 0) return check_launch("e3b_csr_from_dst");
 
     int bits = 0;

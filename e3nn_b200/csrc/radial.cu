@@ -99,8 +99,8 @@ __device__ __forceinline__ void bessel_basis(double r, int nb, double r_max, flo
     }
 }
 
-// H2 = hidden / 32 hidden units per lane (unit j of a lane is column lane + 32 j)
-template <int H2>
+// H2 = hidden / 32 hidden units per lane (unit j of a lane is column lane + 32 j); NB = basis count padded to 8 or 16
+template <int H2, int NB>
 __global__ void __launch_bounds__(kEmbedWarps * 32) radial_embed_fwd_kernel(
         const float* __restrict__ pos, const int64_t* __restrict__ src, const int64_t* __restrict__ dst,
         const float* __restrict__ shift, const float* __restrict__ w0, int64_t num_edges, int64_t num_nodes, int nb,
@@ -109,9 +109,9 @@ __global__ void __launch_bounds__(kEmbedWarps * 32) radial_embed_fwd_kernel(
     __shared__ float s_basis[kEmbedWarps][32][kMaxBasis + 1];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     constexpr int H = 32 * H2;
-    float w[kMaxBasis][H2];
+    float w[NB][H2];
 #pragma unroll
-    for (int k = 0; k < kMaxBasis; ++k)
+    for (int k = 0; k < NB; ++k)
 #pragma unroll
         for (int j = 0; j < H2; ++j) w[k][j] = k < nb ? w0[k * H + lane + 32 * j] * w_scale : 0.0f;
     const int64_t batches = (num_edges + 31) / 32;
@@ -130,7 +130,7 @@ __global__ void __launch_bounds__(kEmbedWarps * 32) radial_embed_fwd_kernel(
 #pragma unroll
             for (int j = 0; j < H2; ++j) pre[j] = 0.0f;
 #pragma unroll
-            for (int k = 0; k < kMaxBasis; ++k) {
+            for (int k = 0; k < NB; ++k) {
                 if (k < nb) {
                     const float bk = s_basis[warp][i][k];
 #pragma unroll
@@ -157,7 +157,7 @@ __device__ __forceinline__ void halve(float* v, int lane) {
     }
 }
 
-template <int H2>
+template <int H2, int NB>
 __global__ void __launch_bounds__(kEmbedWarps * 32) radial_embed_bwd_kernel(
         const float* __restrict__ pos, const int64_t* __restrict__ src, const int64_t* __restrict__ dst,
         const float* __restrict__ shift, const float* __restrict__ w0, const float* __restrict__ grad_h,
@@ -167,9 +167,9 @@ __global__ void __launch_bounds__(kEmbedWarps * 32) radial_embed_bwd_kernel(
     __shared__ float s_cot[kEmbedWarps][32][kMaxBasis + 1];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     constexpr int H = 32 * H2;
-    float w[kMaxBasis][H2];
+    float w[NB][H2];
 #pragma unroll
-    for (int k = 0; k < kMaxBasis; ++k)
+    for (int k = 0; k < NB; ++k)
 #pragma unroll
         for (int j = 0; j < H2; ++j) w[k][j] = k < nb ? w0[k * H + lane + 32 * j] * w_scale : 0.0f;
     const int64_t batches = (num_edges + 31) / 32;
@@ -191,7 +191,7 @@ __global__ void __launch_bounds__(kEmbedWarps * 32) radial_embed_bwd_kernel(
 #pragma unroll
             for (int j = 0; j < H2; ++j) pre[j] = 0.0f;
 #pragma unroll
-            for (int k = 0; k < kMaxBasis; ++k) {
+            for (int k = 0; k < NB; ++k) {
                 if (k < nb) {
                     const float bk = s_basis[warp][i][k];
 #pragma unroll
@@ -199,19 +199,27 @@ __global__ void __launch_bounds__(kEmbedWarps * 32) radial_embed_bwd_kernel(
                 }
             }
             const float* grow = grad_h + (b * 32 + i) * H;
-            float cot[kMaxBasis];
+            float cot[NB];
 #pragma unroll
-            for (int k = 0; k < kMaxBasis; ++k) cot[k] = 0.0f;
+            for (int k = 0; k < NB; ++k) cot[k] = 0.0f;
 #pragma unroll
             for (int j = 0; j < H2; ++j) {
                 const float dpre = grow[lane + 32 * j] * act_scale * act_grad(act, pre[j]);
 #pragma unroll
-                for (int k = 0; k < kMaxBasis; ++k) cot[k] = fmaf(w[k][j], dpre, cot[k]);
+                for (int k = 0; k < NB; ++k) cot[k] = fmaf(w[k][j], dpre, cot[k]);
             }
-            halve<16, 8>(cot, lane); halve<8, 4>(cot, lane); halve<4, 2>(cot, lane); halve<2, 1>(cot, lane);
-            cot[0] += __shfl_xor_sync(0xffffffffu, cot[0], 1);
-            // after the four halvings lane l holds component (l >> 1) & 15 (bit 4 chose the upper 8, bit 3 the upper 4, ...)
-            if ((lane & 1) == 0) s_cot[warp][i][(lane >> 1) & 15] = cot[0];
+            if (NB == 16) {
+                halve<16, NB / 2>(cot, lane); halve<8, 4>(cot, lane); halve<4, 2>(cot, lane); halve<2, 1>(cot, lane);
+                cot[0] += __shfl_xor_sync(0xffffffffu, cot[0], 1);
+                // after the four halvings lane l holds component (l >> 1) & 15 (bit 4 chose the upper 8, bit 3 the upper 4, ...)
+                if ((lane & 1) == 0) s_cot[warp][i][(lane >> 1) & 15] = cot[0];
+            } else {
+                halve<16, 4>(cot, lane); halve<8, 2>(cot, lane); halve<4, 1>(cot, lane);
+                cot[0] += __shfl_xor_sync(0xffffffffu, cot[0], 2);
+                cot[0] += __shfl_xor_sync(0xffffffffu, cot[0], 1);
+                // three halvings over lane bits 4, 3, 2: lane l holds component (l >> 2) & 7
+                if ((lane & 3) == 0) s_cot[warp][i][(lane >> 2) & 7] = cot[0];
+            }
         }
         __syncwarp();
         if (e < num_edges) {
@@ -261,7 +269,9 @@ extern "C" int e3b_radial_embed_fwd(const float* pos, const int64_t* edge_src, c
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const int grid = embed_grid(num_edges), threads = kEmbedWarps * 32;
 #define E3B_LAUNCH(H2)                                                                                                   \
-    radial_embed_fwd_kernel<H2><<<grid, threads, 0, s>>>(pos, edge_src, edge_dst, shift, w0, num_edges, num_nodes, num_basis, \
+    if (num_basis <= 8) E3B_LAUNCH_NB(H2, 8); else E3B_LAUNCH_NB(H2, 16)
+#define E3B_LAUNCH_NB(H2, NBP)                                                                                           \
+    radial_embed_fwd_kernel<H2, NBP><<<grid, threads, 0, s>>>(pos, edge_src, edge_dst, shift, w0, num_edges, num_nodes, num_basis, \
                                                          r_max, w_scale, act_scale, act, edge_vec, h, status)
     switch (hidden / 32) {
         case 1: E3B_LAUNCH(1); break;
@@ -270,6 +280,7 @@ extern "C" int e3b_radial_embed_fwd(const float* pos, const int64_t* edge_src, c
         default: E3B_LAUNCH(4); break;
     }
 #undef E3B_LAUNCH
+#undef E3B_LAUNCH_NB
     return check_launch("radial_embed_fwd");
 }
 
@@ -284,7 +295,9 @@ extern "C" int e3b_radial_embed_bwd(const float* pos, const int64_t* edge_src, c
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const int grid = embed_grid(num_edges), threads = kEmbedWarps * 32;
 #define E3B_LAUNCH(H2)                                                                                                   \
-    radial_embed_bwd_kernel<H2><<<grid, threads, 0, s>>>(pos, edge_src, edge_dst, shift, w0, grad_h, grad_edge_vec, num_edges, \
+    if (num_basis <= 8) E3B_LAUNCH_NB(H2, 8); else E3B_LAUNCH_NB(H2, 16)
+#define E3B_LAUNCH_NB(H2, NBP)                                                                                           \
+    radial_embed_bwd_kernel<H2, NBP><<<grid, threads, 0, s>>>(pos, edge_src, edge_dst, shift, w0, grad_h, grad_edge_vec, num_edges, \
                                                          num_nodes, num_basis, r_max, w_scale, act_scale, act, grad_pos, status)
     switch (hidden / 32) {
         case 1: E3B_LAUNCH(1); break;
@@ -293,5 +306,6 @@ extern "C" int e3b_radial_embed_bwd(const float* pos, const int64_t* edge_src, c
         default: E3B_LAUNCH(4); break;
     }
 #undef E3B_LAUNCH
+#undef E3B_LAUNCH_NB
     return check_launch("radial_embed_bwd");
 }

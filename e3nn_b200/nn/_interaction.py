@@ -26,11 +26,49 @@ from ._fc import FullyConnectedNet, bessel
 
 
 def radius_graph_pbc(pos: torch.Tensor, box: float, cutoff: float) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
-    """Neighbour list of a periodic cubic box, both directions, sorted by destination (host, scipy).
+    """Neighbour list of a periodic cubic box, both directions, sorted by destination then source.
 
-    Returns ``edge_src, edge_dst, shift`` with ``edge_vec = pos[src] - pos[dst] + shift``.  Set-up code:
-    a k-d tree on the host; a device cell list is future work.
+    Returns ``edge_src, edge_dst, shift`` with ``edge_vec = pos[src] - pos[dst] + shift``
+    (``gate_points_2101.py:328``).  CUDA positions with ``box >= 3 * cutoff`` use the device cell list
+    (``e3b_neighbor_count`` / ``e3b_neighbor_fill``; ``neighbor_list_pbc`` also returns the CSR row pointers);
+    host positions use a k-d tree (scipy), which is also the checker of the device builder in the tests.
     """
+    if pos.is_cuda and box >= 3.0 * cutoff:
+        src, dst, shift, _ = neighbor_list_pbc(pos, box, cutoff)
+        return src, dst, shift
+    return _radius_graph_pbc_host(pos, box, cutoff)
+
+
+def neighbor_list_pbc(pos: torch.Tensor, box: float, cutoff: float):
+    """Device cell list: ``edge_src, edge_dst, shift, rowptr`` (edges sorted by destination, then source)."""
+    from .. import _lib
+
+    if not pos.is_cuda:
+        raise NotImplementedError("neighbor_list_pbc runs on CUDA tensors only (use radius_graph_pbc for host positions)")
+    if box < 3.0 * cutoff:
+        raise NotImplementedError("the cell list needs box >= 3 * cutoff")
+    pos32 = pos.detach().to(torch.float32).contiguous()
+    n, dev = pos32.shape[0], pos32.device
+    core = _lib.core()
+    nbytes = core.e3b_neighbor_scratch_bytes(n, float(box), float(cutoff))
+    scratch = torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=dev)
+    rowptr = torch.empty(n + 1, dtype=torch.int64, device=dev)
+    with torch.cuda.device(dev):
+        rc = core.e3b_neighbor_count(_lib._ptr(pos32), n, float(box), float(cutoff), _lib._ptr(scratch), scratch.numel(),
+                                     _lib._ptr(rowptr), _lib.stream_ptr())
+        _lib.check(rc, "e3b_neighbor_count")
+        num_edges = int(rowptr[n].item())       # the one synchronisation: the caller allocates the edge arrays
+        src = torch.empty(num_edges, dtype=torch.int64, device=dev)
+        dst = torch.empty(num_edges, dtype=torch.int64, device=dev)
+        shift = torch.empty(num_edges, 3, dtype=torch.float32, device=dev)
+        if num_edges > 0:
+            rc = core.e3b_neighbor_fill(_lib._ptr(pos32), n, float(box), float(cutoff), _lib._ptr(scratch), scratch.numel(),
+                                        _lib._ptr(rowptr), _lib._ptr(src), _lib._ptr(dst), _lib._ptr(shift), _lib.stream_ptr())
+            _lib.check(rc, "e3b_neighbor_fill")
+    return src, dst, shift.to(pos.dtype), rowptr
+
+
+def _radius_graph_pbc_host(pos: torch.Tensor, box: float, cutoff: float) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     import numpy as np
     from scipy.spatial import cKDTree
 

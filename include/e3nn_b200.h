@@ -102,6 +102,24 @@ int e3b_csr_from_dst_static(const int64_t* dst, int64_t num_edges, int64_t num_n
                             int32_t* status, void* stream);
 
 /*
+ * Neighbour list of a periodic cubic box (cell list on the device), the graph construction every caller of
+ * the path needs: e3nn ships only the O(N^2) radius_graph (e3nn/nn/models/gate_points_2101.py:27-32)
+ * and fixes the convention edge_vec = pos[src] - pos[dst] + shift (gate_points_2101.py:328,
+ * docs/guide/periodic_boundary_conditions.rst:134-136).  One edge per ordered pair src != dst whose
+ * nearest-image distance is <= cutoff; edges sorted by destination, then by source; rowptr is their CSR.
+ * Requires box >= 3 * cutoff (E3B_ERR_UNSUPPORTED otherwise).  Two calls, because the caller allocates:
+ *   e3b_neighbor_count -> rowptr [num_atoms + 1] (rowptr[num_atoms] = number of edges, read it back),
+ *   e3b_neighbor_fill  -> edge_src, edge_dst [E] int64 and shift [E,3] float.
+ * scratch: e3b_neighbor_scratch_bytes(...) bytes of device memory, 256-byte aligned, the same buffer
+ * (untouched in between) for both calls.  The result does not depend on scheduling (rows are sorted).
+ */
+int64_t e3b_neighbor_scratch_bytes(int64_t num_atoms, double box, double cutoff);
+int e3b_neighbor_count(const float* pos, int64_t num_atoms, double box, double cutoff, void* scratch, int64_t scratch_bytes,
+                       int64_t* rowptr, void* stream);
+int e3b_neighbor_fill(const float* pos, int64_t num_atoms, double box, double cutoff, void* scratch, int64_t scratch_bytes,
+                      const int64_t* rowptr, int64_t* edge_src, int64_t* edge_dst, float* shift, void* stream);
+
+/*
  * Edge embedding of an interaction block, one kernel per direction:
  *   edge_vec[e] = pos[src[e]] - pos[dst[e]] + shift[e]        (e3nn/nn/models/gate_points_2101.py:328)
  *   B[e,k]      = sqrt(2/r_max) sin(k pi r / r_max) / r, k = 1..num_basis, r = |edge_vec[e]|

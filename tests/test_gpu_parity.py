@@ -486,6 +486,56 @@ def test_interaction_block_forward_and_position_gradient(irreps, lmax):
     assert rel_err(p2.grad.cpu(), p64.grad) < 1e-4
 
 
+# ----------------------------------------------------------------------------- device neighbour list (cell list)
+@pytest.mark.parametrize("n_atoms,inside", [(2000, True), (5000, False), (40, True)])
+def test_neighbor_list_matches_kdtree(n_atoms, inside):
+    """Device cell list against the host k-d tree builder: identical (dst, src)-sorted index lists (bit-exact),
+    the same shifts, and rowptr = cumsum(bincount(dst)).  `inside=False` puts a third of the atoms outside the box."""
+    from e3nn_b200 import nn as bnn
+    from e3nn_b200.nn._interaction import _radius_graph_pbc_host
+
+    torch.manual_seed(n_atoms)
+    box = max((n_atoms / 0.05) ** (1 / 3), 15.5)
+    pos = torch.rand(n_atoms, 3) * box
+    if not inside:
+        pos[::3] += box * torch.randint(-2, 3, (pos[::3].shape[0], 3)).float()
+    src_h, dst_h, shift_h = _radius_graph_pbc_host(pos, box, 5.0)
+    src, dst, shift, rowptr = bnn.neighbor_list_pbc(pos.to(DEV), box, 5.0)
+    assert torch.equal(src.cpu(), src_h) and torch.equal(dst.cpu(), dst_h)
+    assert (shift.cpu() - shift_h).abs().max().item() < 1e-4
+    ref_rowptr = torch.zeros(n_atoms + 1, dtype=torch.int64)
+    ref_rowptr[1:] = torch.cumsum(torch.bincount(dst_h, minlength=n_atoms), 0)
+    assert torch.equal(rowptr.cpu(), ref_rowptr)
+    # every edge vector is within the cutoff and the list is symmetric
+    vec = pos.to(DEV)[src] - pos.to(DEV)[dst] + shift
+    assert vec.norm(dim=-1).max().item() <= 5.0 + 1e-3
+    fwd = set(zip(src.cpu().tolist(), dst.cpu().tolist()))
+    assert all((d, s) in fwd for s, d in list(fwd)[:2000])
+    # run-to-run identical (rows are sorted after the atomics-ordered scatter)
+    src2, dst2, shift2, _ = bnn.neighbor_list_pbc(pos.to(DEV), box, 5.0)
+    assert torch.equal(src, src2) and torch.equal(shift, shift2)
+    # the dispatching front end picks the device builder for CUDA positions
+    s3, d3, _ = bnn.radius_graph_pbc(pos.to(DEV), box, 5.0)
+    assert torch.equal(s3, src) and torch.equal(d3, dst)
+
+
+def test_neighbor_list_edge_cases():
+    from e3nn_b200 import nn as bnn
+
+    empty = bnn.neighbor_list_pbc(torch.zeros(0, 3, device=DEV), 20.0, 5.0)
+    assert empty[0].numel() == 0 and empty[3].tolist() == [0]
+    lone = bnn.neighbor_list_pbc(torch.tensor([[1.0, 2.0, 3.0]], device=DEV), 20.0, 5.0)
+    assert lone[0].numel() == 0 and lone[3].tolist() == [0, 0]
+    with pytest.raises(NotImplementedError):
+        bnn.neighbor_list_pbc(torch.rand(10, 3, device=DEV), 12.0, 5.0)      # box < 3 x cutoff
+    # two atoms across the periodic boundary see each other through the image
+    pair = torch.tensor([[0.5, 10.0, 10.0], [19.5, 10.0, 10.0]], device=DEV)
+    src, dst, shift, rowptr = bnn.neighbor_list_pbc(pair, 20.0, 5.0)
+    assert src.tolist() == [1, 0] and dst.tolist() == [0, 1] and rowptr.tolist() == [0, 1, 2]
+    vec = pair[src] - pair[dst] + shift
+    assert torch.allclose(vec, torch.tensor([[-1.0, 0.0, 0.0], [1.0, 0.0, 0.0]], device=DEV))
+
+
 # ----------------------------------------------------------------------------- fused edge embedding
 @pytest.mark.gpu
 @pytest.mark.parametrize("act,hidden,nb,with_shift", [("silu", 64, 8, True), ("tanh", 32, 5, False), ("relu", 128, 16, True)])
