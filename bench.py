@@ -389,16 +389,18 @@ def run_interaction(args, rank, world, device):
     x_full = torch.empty(n_atoms, 1024, device=device) if world > 1 else x_local
     tp = block.tp
 
-    def forward(p, xs):
+    def forward(p, xs, before_conv=None):
         # the block's own forward: global indices into the (replicated) positions and the gathered features,
         # the rank's local CSR -> the rank's output rows
-        return block(p, xs, src_d, dst_glob, rowptr, shift_d)
+        return block(p, xs, src_d, dst_glob, rowptr, shift_d, before_conv=before_conv)
 
     def step(p_in):
+        wait = None
         if world > 1:
-            sharding.all_gather_rows(x_local, bounds, out=x_full)
+            # asynchronous: the transfer overlaps the edge embedding and the radial layers, which do not read features
+            _, wait = sharding.all_gather_rows(x_local, bounds, out=x_full, async_op=True)
         p = p_in.detach().requires_grad_(True)
-        (forward(p, x_full) * G).sum().backward()
+        (forward(p, x_full, wait) * G).sum().backward()
         if world > 1:
             torch.distributed.all_reduce(p.grad)
         return p.grad
@@ -478,12 +480,12 @@ def run_interaction(args, rank, world, device):
 
         def e2e_step():
             d = {k: v.to(device, non_blocking=True) for k, v in host.items()}
-            xs = d["x"]
+            xs, wait = d["x"], None
             if world > 1:
-                sharding.all_gather_rows(xs, bounds, out=x_full)
+                _, wait = sharding.all_gather_rows(xs, bounds, out=x_full, async_op=True)
                 xs = x_full
             p = d["pos"].requires_grad_(True)
-            (block(p, xs, d["src"], d["dst"], d["rowptr"], d["shift"]) * G).sum().backward()
+            (block(p, xs, d["src"], d["dst"], d["rowptr"], d["shift"], before_conv=wait) * G).sum().backward()
             if world > 1:
                 torch.distributed.all_reduce(p.grad)
             grad_host.copy_(p.grad, non_blocking=True)

@@ -41,24 +41,42 @@ def local_shard(rowptr: torch.Tensor, bounds: List[int], rank: int) -> Tuple[int
 
 
 def all_gather_rows(x_local: torch.Tensor, bounds: List[int], group: Optional[dist.ProcessGroup] = None,
-                    out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Concatenation over ranks of ``x_local`` (rank r holds rows [bounds[r], bounds[r+1]))."""
+                    out: Optional[torch.Tensor] = None, async_op: bool = False):
+    """Concatenation over ranks of ``x_local`` (rank r holds rows [bounds[r], bounds[r+1])).
+
+    Returns ``out``; with ``async_op`` returns ``(out, wait)`` where ``wait()`` makes the current stream wait for
+    the collective (NCCL runs it on its own stream, so work enqueued before ``wait()`` overlaps the transfer).
+    Uneven row counts: NCCL gathers them as one group of broadcasts (``all_gather`` on a list of slices);
+    backends without that (gloo) get one broadcast per owner.
+    """
     world = len(bounds) - 1
     n, d = bounds[-1], x_local.shape[1]
     if out is None:
         out = torch.empty(n, d, dtype=x_local.dtype, device=x_local.device)
+    works = []
     if world == 1:
         out.copy_(x_local)
-        return out
-    sizes = [bounds[r + 1] - bounds[r] for r in range(world)]
-    if len(set(sizes)) == 1:
-        dist.all_gather_into_tensor(out, x_local.contiguous(), group=group)
     else:
-        # uneven row counts: one broadcast per owner straight into its slice of the result
-        rank = dist.get_rank(group)
-        out[bounds[rank] : bounds[rank + 1]].copy_(x_local)
-        for r in range(world):
-            if sizes[r] > 0:
-                src = dist.get_global_rank(group, r) if group is not None else r
-                dist.broadcast(out[bounds[r] : bounds[r + 1]], src=src, group=group)
+        sizes = [bounds[r + 1] - bounds[r] for r in range(world)]
+        x_local = x_local.contiguous()
+        if len(set(sizes)) == 1:
+            works.append(dist.all_gather_into_tensor(out, x_local, group=group, async_op=True))
+        elif dist.get_backend(group) == "nccl":
+            works.append(dist.all_gather([out[bounds[r] : bounds[r + 1]] for r in range(world)], x_local, group=group,
+                                         async_op=True))
+        else:
+            rank = dist.get_rank(group)
+            out[bounds[rank] : bounds[rank + 1]].copy_(x_local)
+            for r in range(world):
+                if sizes[r] > 0:
+                    src = dist.get_global_rank(group, r) if group is not None else r
+                    works.append(dist.broadcast(out[bounds[r] : bounds[r + 1]], src=src, group=group, async_op=True))
+
+    def wait() -> None:
+        for w in works:
+            w.wait()
+
+    if async_op:
+        return out, wait
+    wait()
     return out
