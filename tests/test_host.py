@@ -148,3 +148,20 @@ def test_layout_module_exports_every_declared_symbol():
     for name in _declared_symbols("e3nn_b200_layout.h"):
         assert hasattr(mod.lib, name), f"{name} declared in include/e3nn_b200_layout.h but not exported"
     assert (mod.d1, mod.d2, mod.dout, mod.wn, mod.sh_lmax) == (72, 9, tp.irreps_out.dim, tp.weight_numel, 2)
+
+
+def test_tensor_core_modules_export_every_declared_symbol():
+    """include/e3nn_b200_tc.h: the tcg module exports e3b_tc_gemm_*, the uvwtc module e3b_uvw_tc_fwd (load only)."""
+    from e3nn_b200 import _lib, o3
+    from e3nn_b200.codegen import tc_gemm
+
+    names = _declared_symbols("e3nn_b200_tc.h")
+    assert {"e3b_tc_gemm_fwd", "e3b_tc_gemm_scratch_bytes", "e3b_uvw_tc_fwd"} <= set(names)
+    gs = tc_gemm.matmul_gemm_spec(64, 128, False, 0.125, "hosttest64x128")
+    mod = _lib.tc_gemm_module(gs)
+    for name in ("e3b_tc_gemm_fwd", "e3b_tc_gemm_scratch_bytes", "e3b_layout_info", "e3b_layout_key", "e3b_layout_last_error"):
+        assert hasattr(mod.lib, name), f"{name} not exported by the tc_gemm module"
+    tp = o3.FullyConnectedTensorProduct("32x0e+32x1o", "0e+1o", "32x0e+32x1o", math_mode="tf32")
+    tc = _lib.uvw_tc_module(tp._spec if hasattr(tp, "_spec") else tp.spec)
+    for name in ("e3b_uvw_tc_fwd", "e3b_layout_info", "e3b_layout_key", "e3b_layout_last_error"):
+        assert hasattr(tc.lib, name), f"{name} not exported by the uvw_tc module"
