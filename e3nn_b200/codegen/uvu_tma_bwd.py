@@ -128,7 +128,7 @@ def _indent(text: str, n: int) -> str:
     return "\n".join(pad + line if line else line for line in text.split("\n"))
 
 
-def emit(layout, depth: int = 3, max_warps: int = 12) -> Optional[Dict[str, str]]:
+def emit(layout, depth: int = 4, max_warps: int = 12) -> Optional[Dict[str, str]]:
     """Backward kernel source + launch code; relies on v2_issue / v2_lower_bound of the forward kernel text."""
     if not eligible(layout):
         return None
