@@ -1,9 +1,10 @@
 // Spherical harmonics of edge vectors: forward and vector-Jacobian product.
 //
-// One thread evaluates one vector with straight-line generated polynomials (sh_gen.cuh);
-// a tile of 128 vectors is staged through shared memory in both directions so that every
-// global access of the block is a contiguous, fully used 128-byte line even though each
-// thread produces (lmax+1)^2 values.  The kernel is bound by HBM: 12 B in, 4*(lmax+1)^2 B out.
+// One thread evaluates one vector with straight-line generated polynomials (sh_gen.cuh).
+// The (lmax+1)^2 values per vector are transposed through shared memory (tiles of 128 vectors) so
+// that every global access of the block is a contiguous, fully used line, moved 16 bytes per thread
+// when (lmax+1)^2 is a multiple of 4; the 12-byte vectors are read and written directly (a warp's
+// 384 bytes are contiguous).  The kernel is bound by HBM: 12 B in, 4*(lmax+1)^2 B out.
 #include "common.cuh"
 #include "sh_gen.cuh"
 
@@ -24,18 +25,16 @@ __global__ void __launch_bounds__(kShTile) sh_fwd_kernel(const float* __restrict
     constexpr int NC = (L + 1) * (L + 1);
     constexpr int LD = kShTile + 1;  // padded leading dimension: conflict-free column writes
     extern __shared__ float smem[];
-    float* s_in = smem;               // [3 * kShTile]
     float* s_out = smem + 3 * kShTile;  // [NC][LD]
 
     const int64_t e0 = static_cast<int64_t>(blockIdx.x) * kShTile;
     const int cnt = static_cast<int>(min(static_cast<int64_t>(kShTile), n - e0));
     const int t = threadIdx.x;
 
-    for (int i = t; i < 3 * cnt; i += kShTile) s_in[i] = xyz[e0 * 3 + i];
-    __syncthreads();
-
     if (t < cnt) {
-        float x = s_in[3 * t], y = s_in[3 * t + 1], z = s_in[3 * t + 2];
+        // three 4-byte loads per thread; the warp's 384 bytes are contiguous, every line is fully used
+        const float* v = xyz + (e0 + t) * 3;
+        float x = v[0], y = v[1], z = v[2];
         if (normalize) {
             const float inv = 1.0f / fmaxf(sqrtf(x * x + y * y + z * z), 1e-12f);
             x *= inv; y *= inv; z *= inv;
@@ -52,9 +51,19 @@ __global__ void __launch_bounds__(kShTile) sh_fwd_kernel(const float* __restrict
     __syncthreads();
 
     float* dst = out + e0 * NC;
-    for (int i = t; i < cnt * NC; i += kShTile) {
-        const int e = i / NC, c = i - e * NC;
-        dst[i] = s_out[c * LD + e];
+    if (NC % 4 == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
+        // 16-byte stores: four consecutive components of one vector per thread, consecutive threads consecutive addresses
+        constexpr int Q = NC / 4 > 0 ? NC / 4 : 1;
+        for (int i = t; i < cnt * Q; i += kShTile) {
+            const int e = i / Q, c = (i - e * Q) * 4;
+            reinterpret_cast<float4*>(dst)[i] =
+                make_float4(s_out[c * LD + e], s_out[(c + 1) * LD + e], s_out[(c + 2) * LD + e], s_out[(c + 3) * LD + e]);
+        }
+    } else {
+        for (int i = t; i < cnt * NC; i += kShTile) {
+            const int e = i / NC, c = i - e * NC;
+            dst[i] = s_out[c * LD + e];
+        }
     }
 }
 
@@ -65,24 +74,31 @@ __global__ void __launch_bounds__(kShTile) sh_bwd_kernel(const float* __restrict
     constexpr int NC = (L + 1) * (L + 1);
     constexpr int LD = kShTile + 1;
     extern __shared__ float smem[];
-    float* s_in = smem;                 // [3 * kShTile], reused for the result
     float* s_g = smem + 3 * kShTile;    // [NC][LD]
 
     const int64_t e0 = static_cast<int64_t>(blockIdx.x) * kShTile;
     const int cnt = static_cast<int>(min(static_cast<int64_t>(kShTile), n - e0));
     const int t = threadIdx.x;
 
-    for (int i = t; i < 3 * cnt; i += kShTile) s_in[i] = xyz[e0 * 3 + i];
     const float* src = gout + e0 * NC;
-    for (int i = t; i < cnt * NC; i += kShTile) {
-        const int e = i / NC, c = i - e * NC;
-        s_g[c * LD + e] = src[i];
+    if (NC % 4 == 0 && (reinterpret_cast<uintptr_t>(gout) & 15) == 0) {
+        constexpr int Q = NC / 4 > 0 ? NC / 4 : 1;
+        for (int i = t; i < cnt * Q; i += kShTile) {   // 16-byte loads, transposed into shared memory
+            const int e = i / Q, c = (i - e * Q) * 4;
+            const float4 v = reinterpret_cast<const float4*>(src)[i];
+            s_g[c * LD + e] = v.x; s_g[(c + 1) * LD + e] = v.y; s_g[(c + 2) * LD + e] = v.z; s_g[(c + 3) * LD + e] = v.w;
+        }
+    } else {
+        for (int i = t; i < cnt * NC; i += kShTile) {
+            const int e = i / NC, c = i - e * NC;
+            s_g[c * LD + e] = src[i];
+        }
     }
     __syncthreads();
 
-    float rx = 0.f, ry = 0.f, rz = 0.f;
     if (t < cnt) {
-        const float vx = s_in[3 * t], vy = s_in[3 * t + 1], vz = s_in[3 * t + 2];
+        const float* v = xyz + (e0 + t) * 3;
+        const float vx = v[0], vy = v[1], vz = v[2];
         float x = vx, y = vy, z = vz, inv = 1.0f;
         const float len = sqrtf(vx * vx + vy * vy + vz * vz);
         if (normalize) {
@@ -108,12 +124,9 @@ __global__ void __launch_bounds__(kShTile) sh_bwd_kernel(const float* __restrict
                 gx *= inv; gy *= inv; gz *= inv;
             }
         }
-        rx = gx; ry = gy; rz = gz;
+        float* r = gxyz + (e0 + t) * 3;   // the warp's 384 bytes are contiguous
+        r[0] = gx; r[1] = gy; r[2] = gz;
     }
-    __syncthreads();
-    if (t < cnt) { s_in[3 * t] = rx; s_in[3 * t + 1] = ry; s_in[3 * t + 2] = rz; }
-    __syncthreads();
-    for (int i = t; i < 3 * cnt; i += kShTile) gxyz[e0 * 3 + i] = s_in[i];
 }
 
 template <int L>
