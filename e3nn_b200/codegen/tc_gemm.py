@@ -121,6 +121,9 @@ class GemmSpec:
     # 8 producer warps (13 warps per CTA, 128 registers each) suit contractions bound by their output stores
     # (K <= 128); 16 (21 warps, 80 registers) hide the operand-load latency of long-K contractions
     producer_warps: int = 8
+    # dense layers: the raw fp32 rows are the hi operand piece (the tensor core ignores the low 13 mantissa
+    # bits), brought into the swizzled stage by 2-D tensor-map TMA copies issued by a dedicated warp
+    tma_a: bool = False
 
 
 # ------------------------------------------------------------------------------------------- front ends
@@ -279,7 +282,7 @@ def matmul_gemm_spec(k: int, n: int, transpose: bool, scale: float, key: str) ->
     if any(g.nstage() < 2 for g in groups):
         return None
     return GemmSpec(d_in, 0, d_out, groups, key, f"matmul{'^T' if transpose else ''} [{k} x {n}] scale {scale!r}",
-                    producer_warps=16 if transpose else 8)
+                    producer_warps=16 if transpose else 8, tma_a=all(g.plain for g in groups))
 
 
 # ------------------------------------------------------------------------------------------- emission
@@ -362,7 +365,7 @@ for (int q = 0; q < {qn}; ++q) {{{{
         # doubling the bytes a producer warp keeps in flight (these groups stream their A rows from HBM)
         batch = 2 if (len(g.cases) == 1 and nch % 2 == 0 and qn * g.case_d1[0] <= 16 and g.nstage() >= 4) else 1
         switch = "\n".join(cases)
-        issue_b = lambda stage, bar, c: "" if g.resident_bytes() else f"""if (pw == 0 && lane == 0) {{{{
+        issue_b_body = lambda stage, bar, c: "" if g.resident_bytes() else f"""{{{{
     const uint32_t bar = tc::smem_u32({bar});
     const uint32_t bbytes = pieces * B_HALF;   // only the pieces this precision uses
     asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(bbytes) : "memory");
@@ -370,6 +373,7 @@ for (int q = 0; q < {qn}; ++q) {{{{
                  ::"r"(tc::smem_u32({stage} + {PIECES} * A_TILE)), "l"(bsrc + static_cast<size_t>({c}) * {PIECES} * B_HALF),
                    "r"(bbytes), "r"(bar) : "memory");
 }}}}""".replace("{{", "{").replace("}}", "}")
+        issue_b = lambda stage, bar, c: "" if g.resident_bytes() else "if (pw == 0 && lane == 0) " + issue_b_body(stage, bar, c)
         if batch == 1:
             PRODUCER_LOOP = f"""            for (int c = 0; c < NCHUNK; ++c, ++it) {{
                 const int s = it % NSTAGE;
@@ -426,7 +430,40 @@ for (int q = 0; q < {qn}; ++q) {{{{
                 sy[idx] = x2[z * {d2} + idx % {d2}];
             }}
             __syncwarp();""" if has_y else ""
-        if g.plain:
+        if g.plain and gs.tma_a:
+            assert g.dim == 1 and g.zt == 128 and 128 % (4 * PRODUCER_WARPS) == 0 and not has_y
+            RPW = 128 // PRODUCER_WARPS
+            NJ = RPW // 4
+            PRODUCER_BLOCK = f"""        // The stage's hi tile is the raw fp32 data, written by a tensor-map TMA copy (issued by the TMA warp).
+        // A lane owns 16 bytes (4 consecutive K) of {NJ} rows: it reads them back, forms lo = x - trunc(x) rounded
+        // to tf32 and stores the lo tile.  With one piece per operand there is nothing to convert.
+        uint32_t po[{NJ}];
+        const int pc4 = lane & 7;
+#pragma unroll
+        for (int j = 0; j < {NJ}; ++j) {{
+            const int r = pw * {RPW} + 4 * j + (lane >> 3);
+            po[j] = (r >> 3) * 1024 + (r & 7) * 128 + ((pc4 ^ (r & 7)) << 4);
+        }}
+        for (int64_t t = cta; t < tiles && ok; t += nctas) {{
+            for (int c = 0; c < NCHUNK; ++c, ++it) {{
+                const int s = it % NSTAGE;
+                const uint32_t ph = (it / NSTAGE) & 1;
+                if (!tc::mbar_wait(&bar_raw[s], ph, abort_flag)) {{ ok = false; break; }}
+                uint8_t* stage = sS + s * STAGE_BYTES;
+                if (pieces > 1) {{
+#pragma unroll
+                    for (int j = 0; j < {NJ}; ++j) {{
+                        const float4 v = *reinterpret_cast<const float4*>(stage + po[j]);
+                        *reinterpret_cast<float4*>(stage + A_TILE + po[j]) = tc::lo_piece4(v);
+                    }}
+                    tc::fence_proxy_async_smem();
+                }}
+                __syncwarp();
+                if (lane == 0) tc::mbar_arrive(&bar_full[s]);
+            }}
+        }}
+"""
+        elif g.plain:
             assert g.dim == 1 and g.zt == 128 and 128 % (4 * PRODUCER_WARPS) == 0 and not has_y
             RPW = 128 // PRODUCER_WARPS      # rows of the tile per producer warp
             NJ = RPW // 4                    # 16-byte loads per lane and chunk
@@ -584,11 +621,30 @@ for (int q = 0; q < {qn}; ++q) {{{{
                 }}}}
                 store16(ra, w0);
             }}}}""".replace("{{", "{").replace("}}", "}")
+        if g.plain and gs.tma_a:
+            TMA_ROLE = f"""    if (warp == kMmaWarp + 1 && lane == 0) {{
+        // ================= TMA issue (single thread): raw A tiles (and the streamed B chunks) as far ahead as the
+        // ring allows; completion of a tile is signalled on bar_raw, which the producer warps wait on
+        uint32_t it = 0;
+        bool ok = true;
+        for (int64_t t = cta; t < tiles && ok; t += nctas) {{
+            for (int c = 0; c < NCHUNK; ++c, ++it) {{
+                const int s = it % NSTAGE;
+                const uint32_t ph = (it / NSTAGE) & 1;
+                if (!tc::mbar_wait(&bar_empty[s], ph ^ 1u, abort_flag)) {{ ok = false; break; }}
+                uint8_t* stage = sS + s * STAGE_BYTES;
+                tc::tma_load_2d(stage, tmap, kXOff{gi}[c], static_cast<int32_t>(t * ZT), &bar_raw[s], A_TILE);
+{_indent(issue_b_body('stage', '&bar_full[s]', 'c'), 16)}
+            }}
+        }}
+    }}"""
+        else:
+            TMA_ROLE = ""
         funcs.append(f"""
 // ---------------------------------------------------------------- group {gi}: N = {g.n}, 2l+1 = {g.dim}, K = {32 * nch}
 __device__ __forceinline__ void run_group_{gi}(const float* __restrict__ x1, const float* __restrict__ x2,
         const uint8_t* __restrict__ bprep, float* __restrict__ out, int64_t Z, int cta, int nctas, uint8_t* smem,
-        int* status, int pieces) {{
+        int* status, int pieces, const CUtensorMap* tmap) {{
     constexpr int N = {g.n}, DIM = {g.dim}, ZT = {g.zt}, NCHUNK = {nch}, NSTAGE = {g.nstage()}, NBUF = 2;
     // partial accumulators per buffer: even / odd k-steps accumulate in different TMEM columns, which halves
     // the length of each dependent MMA chain (and of the fp32 accumulation error); summed in the epilogue
@@ -604,7 +660,8 @@ __device__ __forceinline__ void run_group_{gi}(const float* __restrict__ x1, con
     uint64_t* bar_acc_full = bar_empty + NSTAGE;
     uint64_t* bar_acc_empty = bar_acc_full + NBUF;
     uint64_t* bar_b = bar_acc_empty + NBUF;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_b + 1);
+    uint64_t* bar_raw = bar_b + 1;            // [NSTAGE] completion of the TMA copy of a stage's raw A tile
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_raw + NSTAGE);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     float* sY = reinterpret_cast<float*>(sS + NSTAGE * STAGE_BYTES + 1024);
     float* sE = sY + {(Y_BYTES if g.has_y else 0) // 4};   // epilogue staging (only used by staged epilogues)
@@ -616,6 +673,7 @@ __device__ __forceinline__ void run_group_{gi}(const float* __restrict__ x1, con
         for (int s = 0; s < NSTAGE; ++s) {{ tc::mbar_init(&bar_full[s], kProducerWarps); tc::mbar_init(&bar_empty[s], 1); }}
         for (int b = 0; b < NBUF; ++b) {{ tc::mbar_init(&bar_acc_full[b], 1); tc::mbar_init(&bar_acc_empty[b], kEpilogueWarps); }}
         tc::mbar_init(bar_b, 1);
+        for (int s = 0; s < NSTAGE; ++s) tc::mbar_init(&bar_raw[s], 1);
         tc::mbar_init_fence();
     }}
     if (warp == kMmaWarp) tc::tmem_alloc(tmem_slot, kTmemCols);
@@ -691,6 +749,7 @@ __device__ __forceinline__ void run_group_{gi}(const float* __restrict__ x1, con
             if (ok) tc::mma_commit(&bar_acc_full[b]);
         }}
     }}
+{TMA_ROLE}
     tc::tc_fence_before_sync();
     __syncthreads();
     if (tid == 0 && *abort_flag) atomicExch(status, 3);
@@ -718,7 +777,7 @@ __device__ __forceinline__ void prep_group_{gi}(const float* __restrict__ W, uin
 
     ng = len(gs.groups)
     dispatch = "\n".join(
-        f"    {'else ' if gi else ''}if (blockIdx.x < cta_end{gi}) run_group_{gi}(x1, x2, bprep, out, Z, blockIdx.x - cta_begin{gi}, cta_end{gi} - cta_begin{gi}, smem, status, pieces);"
+        f"    {'else ' if gi else ''}if (blockIdx.x < cta_end{gi}) run_group_{gi}(x1, x2, bprep, out, Z, blockIdx.x - cta_begin{gi}, cta_end{gi} - cta_begin{gi}, smem, status, pieces, &tmap_a);"
         for gi in range(ng))
     bounds = "\n".join(
         f"    const int cta_begin{gi} = {'0' if gi == 0 else f'cta_end{gi-1}'}, cta_end{gi} = cta_begin{gi} + split.n[{gi}];" for gi in range(ng))
@@ -730,8 +789,10 @@ __device__ __forceinline__ void prep_group_{gi}(const float* __restrict__ W, uin
         for off, n in gs.zero_ranges)
     return f"""// Generated by e3nn_b200/codegen/tc_gemm.py -- do not edit.
 // {gs.title}, key {gs.key}
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <cstdint>
+#include <cstring>
 #include "layout_common.cuh"
 #include "tc_common.cuh"
 
@@ -740,7 +801,7 @@ namespace {{
 constexpr int kEpilogueWarps = 4;
 constexpr int kProducerWarps = {PRODUCER_WARPS};
 constexpr int kMmaWarp = kEpilogueWarps + kProducerWarps;
-constexpr int kThreads = (kMmaWarp + 1) * 32;
+constexpr int kThreads = (kMmaWarp + 1 + {1 if gs.tma_a else 0}) * 32;   // + the TMA warp of dense-layer modules
 constexpr int kTmemCols = 512;
 constexpr int kGroups = {ng};
 constexpr int kSmemBytes = {smem_max};
@@ -752,7 +813,8 @@ struct CtaSplit {{ int n[kGroups]; }};
 {''.join(funcs)}
 
 __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const float* __restrict__ x1, const float* __restrict__ x2,
-        const uint8_t* __restrict__ bprep, float* __restrict__ out, int64_t Z, CtaSplit split, int* status, int pieces) {{
+        const uint8_t* __restrict__ bprep, float* __restrict__ out, int64_t Z, CtaSplit split, int* status, int pieces,
+        const __grid_constant__ CUtensorMap tmap_a) {{
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
 {bounds}
@@ -816,8 +878,15 @@ extern "C" int e3b_tc_gemm_fwd(const float* x1, const float* x2, const float* we
     tc_gemm_prep_kernel<<<dim3(({prep_max} + 255) / 256, kGroups), 256, 0, s>>>(weight, static_cast<uint8_t*>(scratch));
     cudaError_t err = cudaFuncSetAttribute(tc_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (err != cudaSuccess) return e3b_layout_fail(-2, "tc_gemm: smem attribute: %s", cudaGetErrorString(err));
+    CUtensorMap tmap;
+    std::memset(&tmap, 0, sizeof(tmap));
+    if ({'true' if gs.tma_a else 'false'}) {{
+        // x1 as a [Z, {d1}] fp32 matrix, boxes of 128 rows x 32 columns, 128-byte swizzle: the layout the MMA reads
+        const int rc = tc::encode_tensor_map_2d(&tmap, x1, {d1}, Z, 32, 128);
+        if (rc != 0) return e3b_layout_fail(-2, "tc_gemm: cuTensorMapEncodeTiled failed (%d)", rc);
+    }}
     tc_gemm_kernel<<<used, kThreads, kSmemBytes, s>>>(x1, x2, static_cast<const uint8_t*>(scratch), out, Z, split, status,
-                                                       precision);
+                                                       precision, tmap);
     return e3b_layout_check("tc_gemm");
 }}
 """

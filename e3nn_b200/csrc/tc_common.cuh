@@ -1,6 +1,7 @@
 // Blackwell (sm_100a) primitives used by the tensor-core kernels: mbarriers with bounded
 // waits, tcgen05 MMA / TMEM access, shared-memory matrix descriptors.  Inline PTX only.
 #pragma once
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <cstdint>
 
@@ -171,10 +172,63 @@ __device__ __forceinline__ void split_store4(float4 v, uint8_t* dst, int pieces)
         hi.y = __uint_as_float(__float_as_uint(v.y) & 0xFFFFE000u);
         hi.z = __uint_as_float(__float_as_uint(v.z) & 0xFFFFE000u);
         hi.w = __uint_as_float(__float_as_uint(v.w) & 0xFFFFE000u);
+#ifdef E3B_EXPERIMENT_RAW_HI
+        *reinterpret_cast<float4*>(dst) = v;      // experiment: does the tensor core ignore the low 13 mantissa bits?
+#else
         *reinterpret_cast<float4*>(dst) = hi;
+#endif
         *reinterpret_cast<float4*>(dst + TILE) =
             make_float4(to_tf32(v.x - hi.x), to_tf32(v.y - hi.y), to_tf32(v.z - hi.z), to_tf32(v.w - hi.w));
     }
+}
+
+// lo pieces of four raw fp32 values whose hi pieces are the values themselves (the tensor core reads only
+// sign, exponent and the top 10 mantissa bits of a tf32 operand): lo = x - trunc(x), rounded to tf32
+__device__ __forceinline__ float4 lo_piece4(float4 v) {
+    return make_float4(to_tf32(v.x - __uint_as_float(__float_as_uint(v.x) & 0xFFFFE000u)),
+                       to_tf32(v.y - __uint_as_float(__float_as_uint(v.y) & 0xFFFFE000u)),
+                       to_tf32(v.z - __uint_as_float(__float_as_uint(v.z) & 0xFFFFE000u)),
+                       to_tf32(v.w - __uint_as_float(__float_as_uint(v.w) & 0xFFFFE000u)));
+}
+
+// ---------------------------------------------------------------- tensor-map TMA (2-D tiles)
+// One box of the tensor map -> shared memory (no multicast, this CTA only); completion as `bytes` on `bar`.
+// x (innermost coordinate, in elements) times the element size must be a multiple of 16 bytes.
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int32_t x, int32_t y, uint64_t* bar,
+                                            uint32_t bytes) {
+    const uint32_t b = smem_u32(bar);
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(b), "r"(bytes) : "memory");
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(b)
+                 : "memory");
+}
+
+// Host: row-major fp32 matrix [rows, cols] (row stride = cols) as a 2-D tensor map with boxes of
+// box_rows x box_cols, 128-byte swizzle, zero fill outside the matrix.  Returns 0 or a driver error code
+// (-1: the driver entry point is not available).  The driver is reached through the runtime's entry-point
+// query, so nothing links against libcuda.
+inline int encode_tensor_map_2d(CUtensorMap* map, const float* base, int64_t cols, int64_t rows, uint32_t box_cols,
+                                uint32_t box_rows) {
+    typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static EncodeFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess || !p)
+            return -1;
+        fn = reinterpret_cast<EncodeFn>(p);
+    }
+    const cuuint64_t gdim[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+    const cuuint64_t gstride[1] = {static_cast<cuuint64_t>(cols) * sizeof(float)};
+    const cuuint32_t box[2] = {box_cols, box_rows};
+    const cuuint32_t estride[2] = {1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), gdim, gstride, box, estride,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return static_cast<int>(r);
 }
 
 // byte offset of element (row, col) in a K-major SWIZZLE_128B tile of 32 fp32 columns
