@@ -28,7 +28,9 @@ import numpy as np
 from ..o3._wigner import wigner_3j_numpy
 from . import uvu_tma
 
-G_FLOATS_PER_WARP = 72      # cotangent registers (2 per output component) one warp may hold
+G_FLOATS_PER_WARP = 100     # cotangent registers (2 per output component) one warp may hold: measured on the
+                            # 23-path l<=3 layout, teams of 2 fat warps (240 registers, 8 warps per SM) beat teams of
+                            # 3 or 4 (9-12 warps) by 12-25 %: every warp repeats the reduction and the staging loads
 SMEM_BUDGET = 200 * 1024
 
 
@@ -43,8 +45,6 @@ def eligible(layout) -> bool:
 def split_slots(layout) -> List[List]:
     total = 2 * sum(layout.spec.irreps_out[io].ir.dim for io in layout.out_used)
     T = max(1, -(-total // G_FLOATS_PER_WARP))
-    if T == 3:
-        T = 4   # warp w runs on scheduler w % 4: with T in {1, 2, 4} a scheduler fetches the code of one role only
     if T == 1:
         return [list(layout.paths)]
     slots: Dict[int, List] = {}
@@ -128,12 +128,16 @@ def _indent(text: str, n: int) -> str:
     return "\n".join(pad + line if line else line for line in text.split("\n"))
 
 
-def emit(layout, depth: int = 4, max_warps: int = 12) -> Optional[Dict[str, str]]:
+def emit(layout, depth: int = 4, max_warps: int = 0) -> Optional[Dict[str, str]]:
     """Backward kernel source + launch code; relies on v2_issue / v2_lower_bound of the forward kernel text."""
     if not eligible(layout):
         return None
     groups = split_slots(layout)
     T = len(groups)
+    if max_warps == 0:
+        # register budget: a warp holding more than 72 cotangent floats needs about 240 registers per thread
+        per_warp = max(2 * g_count(layout, paths) for paths in groups)
+        max_warps = 8 if per_warp > 72 else 12
     stage_w, stage_x = layout.wn * 4, layout.d1 * 4
     stage = (stage_w + stage_x + 127) // 128 * 128
     teams = max(1, min(SMEM_BUDGET // (depth * stage + 32 * 20 * 4 + T * 32 * 17 * 4), max_warps // T, 8))

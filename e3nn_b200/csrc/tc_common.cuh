@@ -172,11 +172,7 @@ __device__ __forceinline__ void split_store4(float4 v, uint8_t* dst, int pieces)
         hi.y = __uint_as_float(__float_as_uint(v.y) & 0xFFFFE000u);
         hi.z = __uint_as_float(__float_as_uint(v.z) & 0xFFFFE000u);
         hi.w = __uint_as_float(__float_as_uint(v.w) & 0xFFFFE000u);
-#ifdef E3B_EXPERIMENT_RAW_HI
-        *reinterpret_cast<float4*>(dst) = v;      // experiment: does the tensor core ignore the low 13 mantissa bits?
-#else
         *reinterpret_cast<float4*>(dst) = hi;
-#endif
         *reinterpret_cast<float4*>(dst + TILE) =
             make_float4(to_tf32(v.x - hi.x), to_tf32(v.y - hi.y), to_tf32(v.z - hi.z), to_tf32(v.w - hi.w));
     }
