@@ -151,7 +151,7 @@ def _indent(text: str, n: int) -> str:
     return "\n".join(pad + line if line else line for line in text.split("\n"))
 
 
-def emit(layout, depth: int = 0) -> Optional[Dict[str, str]]:
+def emit(layout, depth: int = 0, max_warps: int = 16) -> Optional[Dict[str, str]]:
     """Kernel source and launch code for an eligible layout (None otherwise)."""
     if not eligible(layout):
         return None
@@ -161,7 +161,7 @@ def emit(layout, depth: int = 0) -> Optional[Dict[str, str]]:
     stage_w, stage_x = layout.wn * 4, layout.d1 * 4
     stage = (stage_w + stage_x + 127) // 128 * 128
     def teams_for(d: int) -> int:
-        return max(1, min(SMEM_BUDGET // (d * stage + 32 * 20 * 4), 16 // T, 8))
+        return max(1, min(SMEM_BUDGET // (d * stage + 32 * 20 * 4), max_warps // T, 8))
 
     if depth == 0:
         # four stages in flight unless three let one more team (more warps to issue from) fit in shared memory
