@@ -178,10 +178,12 @@ def emit_module(spec: TPSpec) -> str:
         wbase = [g.paths[pi].woff + u0 * g.n for pi, u0 in chunks]
         xoff = [g.paths[pi].off1 + u0 * (2 * g.paths[pi].l1 + 1) for pi, u0 in chunks]
         cpath = [pi for pi, _ in chunks]
+        cd1 = [2 * g.paths[pi].l1 + 1 for pi, _ in chunks]
         consts.append(
             f"__constant__ int kWBase{gi}[{len(chunks)}] = {{{', '.join(map(str, wbase))}}};\n"
             f"__constant__ int kXOff{gi}[{len(chunks)}] = {{{', '.join(map(str, xoff))}}};\n"
-            f"__constant__ int kCPath{gi}[{len(chunks)}] = {{{', '.join(map(str, cpath))}}};"
+            f"__constant__ int kCPath{gi}[{len(chunks)}] = {{{', '.join(map(str, cpath))}}};\n"
+            f"__constant__ int kCD1{gi}[{len(chunks)}] = {{{', '.join(map(str, cd1))}}};"
         )
         cases = []
         for pi, p in enumerate(g.paths):
@@ -281,6 +283,22 @@ __device__ __forceinline__ void run_group_{gi}(const float* __restrict__ x1, con
             }}
             __syncwarp();
             for (int c = 0; c < NCHUNK; ++c, ++it) {{
+                {{
+                    // the x1 values of the chunk two ahead (of this tile, or of the CTA's next tile) are
+                    // requested into L2 now: no registers are held, and the loads that follow find them closer
+                    const bool same = c + 2 < NCHUNK;
+                    const int cn = same ? c + 2 : (c + 2 - NCHUNK < NCHUNK ? c + 2 - NCHUNK : NCHUNK - 1);
+                    const int64_t zn = same ? z0 : z0 + static_cast<int64_t>(nctas) * 128;
+                    if (zn < Z) {{
+                        const float* nb = x1 + kXOff{gi}[cn] + lane * kCD1{gi}[cn];
+#pragma unroll
+                        for (int b = 0; b < kRowsPerWarp; ++b) {{
+                            int64_t z = zn + pw * kRowsPerWarp + b;
+                            if (z >= Z) z = Z - 1;
+                            asm volatile("prefetch.global.L2 [%0];" ::"l"(nb + z * {d1}));
+                        }}
+                    }}
+                }}
                 const int s = it % NSTAGE;
                 const uint32_t ph = (it / NSTAGE) & 1;
                 if (!tc::mbar_wait(&bar_empty[s], ph ^ 1u, abort_flag)) {{ ok = false; break; }}
