@@ -352,7 +352,7 @@ def interaction_problem(n_atoms: int, seed: int = 0, device=None):
 
 
 # DRAM bytes per edge of conv_bwd_tma_kernel (layout l3_23) from an ncu capture of a 16,384-atom case
-NCU_CONV_BWD_L3_TRAFFIC_PER_EDGE = 15690
+NCU_CONV_BWD_L3_TRAFFIC_PER_EDGE = 15718
 
 
 def run_interaction(args, rank, world, device):
@@ -531,7 +531,7 @@ def run_interaction(args, rank, world, device):
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": NCU_CONV_BWD_L3_TRAFFIC_PER_EDGE * e_loc,
                      "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch on 428,990 edges "
-                                       "(15,690 B/edge), scaled by the edge count",
+                                       "(15,718 B/edge), scaled by the edge count",
                      "peak_kind": f"of {peak_kind}", "kernel": "conv_bwd_tma_kernel", "kernel_ms": bwd_ms,
                      "algorithmic_bytes_per_launch": bwd_bytes},
         "e2e": e2e,

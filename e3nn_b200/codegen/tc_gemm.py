@@ -313,6 +313,7 @@ def emit_module(gs: GemmSpec) -> str:
         consts.append("\n".join([
             arr("kCase", [c.case for c in g.chunks]),
             arr("kXOff", [c.xoff for c in g.chunks]),
+            arr("kCD1", [g.case_d1[c.case] for c in g.chunks]),
             arr("kWBase", [wb for blks in cblocks for wb, _ in blks]),
             arr("kSK", [c.sk for c in g.chunks]),
             arr("kSN", [c.sn for c in g.chunks]),
@@ -376,6 +377,23 @@ for (int q = 0; q < {qn}; ++q) {{{{
         issue_b = lambda stage, bar, c: "" if g.resident_bytes() else "if (pw == 0 && lane == 0) " + issue_b_body(stage, bar, c)
         if batch == 1:
             PRODUCER_LOOP = f"""            for (int c = 0; c < NCHUNK; ++c, ++it) {{
+                {{
+                    // the input values of the chunk two ahead (of this tile, or of the CTA's next tile) are requested
+                    // into L2 now: no registers are held, and the loads that follow find them closer
+                    const bool same = c + 2 < NCHUNK;
+                    const int cn = same ? c + 2 : (c + 2 - NCHUNK < NCHUNK ? c + 2 - NCHUNK : NCHUNK - 1);
+                    const int64_t shift_rows = same ? 0 : static_cast<int64_t>(nctas) * ZT;
+                    if (z0 + shift_rows < Z) {{
+                        const int poff = kXOff{gi}[cn] + lane * kCD1{gi}[cn];
+#pragma unroll
+                        for (int q = 0; q < {qn}; ++q) {{
+                            const int zl = pw + {PRODUCER_WARPS} * q;
+                            int64_t z = z0 + shift_rows + (zl < ZT ? zl : 0);
+                            if (z >= Z) z = Z - 1;
+                            asm volatile("prefetch.global.L2 [%0];" ::"l"(x1 + z * {d1} + poff));
+                        }}
+                    }}
+                }}
                 const int s = it % NSTAGE;
                 const uint32_t ph = (it / NSTAGE) & 1;
                 if (!tc::mbar_wait(&bar_empty[s], ph ^ 1u, abort_flag)) {{ ok = false; break; }}

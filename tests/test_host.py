@@ -165,3 +165,22 @@ def test_tensor_core_modules_export_every_declared_symbol():
     tc = _lib.uvw_tc_module(tp._spec if hasattr(tp, "_spec") else tp.spec)
     for name in ("e3b_uvw_tc_fwd", "e3b_layout_info", "e3b_layout_key", "e3b_layout_last_error"):
         assert hasattr(tc.lib, name), f"{name} not exported by the uvw_tc module"
+
+
+def test_cpu_tensors_are_rejected_by_the_new_entry_points():
+    """No CPU fallback: the device-only front ends raise, the host neighbour list still works and is sorted."""
+    import torch
+    from e3nn_b200 import nn as bnn
+
+    pos = torch.rand(50, 3) * 16.0
+    with pytest.raises(NotImplementedError):
+        bnn.neighbor_list_pbc(pos, 16.0, 5.0)
+    with pytest.raises(NotImplementedError):
+        bnn.edge_embed(pos, torch.zeros(3, dtype=torch.int64), torch.ones(3, dtype=torch.int64), None, torch.randn(8, 64),
+                       5.0, 1.0, 1.0, "silu")
+    src, dst, shift = bnn.radius_graph_pbc(pos, 16.0, 5.0)
+    assert src.numel() == dst.numel() == shift.shape[0] and src.numel() % 2 == 0
+    key = dst * 50 + src
+    assert torch.all(key[1:] > key[:-1])                       # sorted by destination, then source, no duplicates
+    vec = pos[src] - pos[dst] + shift
+    assert float(vec.norm(dim=-1).max()) <= 5.0 + 1e-5
