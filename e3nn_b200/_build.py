@@ -21,7 +21,7 @@ CSRC = os.path.join(PKG, "csrc")
 LIB_DIR = os.path.join(PKG, "lib")
 LAYOUT_DIR = os.path.join(PKG, "_layouts")
 CORE_LIB = os.path.join(LIB_DIR, "libe3nn_b200.so")
-CORE_SOURCES = ["abi.cu", "sh.cu", "csr.cu", "dense.cu", "radial.cu", "neighbor.cu"]
+CORE_SOURCES = ["abi.cu", "sh.cu", "csr.cu", "dense.cu", "radial.cu", "neighbor.cu", "gate.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -76,8 +76,11 @@ def core() -> ctypes.CDLL:
         lib.e3b_neighbor_count.argtypes = [c_void_p, c_int64, c_double, c_double, c_void_p, c_int64, c_void_p, c_void_p]
         lib.e3b_neighbor_fill.argtypes = [c_void_p, c_int64, c_double, c_double, c_void_p, c_int64, c_void_p, c_void_p,
                                           c_void_p, c_void_p, c_void_p]
+        lib.e3b_gate_fwd.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]
+        lib.e3b_gate_bwd.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]
         for name in ("e3b_sh_fwd", "e3b_sh_bwd", "e3b_csr_from_dst", "e3b_dense_fwd", "e3b_fill_columns",
-                     "e3b_radial_embed_fwd", "e3b_radial_embed_bwd", "e3b_neighbor_count", "e3b_neighbor_fill"):
+                     "e3b_radial_embed_fwd", "e3b_radial_embed_bwd", "e3b_neighbor_count", "e3b_neighbor_fill",
+                     "e3b_gate_fwd", "e3b_gate_bwd"):
             getattr(lib, name).restype = c_int
         _core = lib
     return _core

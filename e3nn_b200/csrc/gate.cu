@@ -1,0 +1,120 @@
+// Gate non-linearity on rows of irreps features: the step after the Linear in every model
+// (e3nn/nn/_gate.py:35-144 with e3nn/nn/_activation.py:9-111 and the 'uuu' product of
+// e3nn/o3/_tensor_product/_sub.py ElementwiseTensorProduct, which for a scalar second operand is a plain
+// per-channel multiplication):
+//
+//   out = [ c_i * phi_i(scalars_i) ]  (+)  [ gated_j * c_j * phi_j(gates_j) ]
+//
+// The reference runs an Extract (three narrow + cat), two Activations (narrow + cat per block) and a
+// generated tensor product; here one elementwise kernel per direction reads a row once and writes it once.
+// The irreps bookkeeping lives on the host: per OUTPUT column {input column, gate column or -1,
+// activation code, constant}, per INPUT column {kind, first output column, count, partner column}.
+#include "common.cuh"
+
+namespace e3b {
+namespace {
+
+enum GateAct { kGSilu = 0, kGTanh = 1, kGRelu = 2, kGIdentity = 3, kGSigmoid = 4, kGAbs = 5 };
+
+__device__ __forceinline__ float gate_act(int kind, float x) {
+    switch (kind) {
+        case kGSilu: return x / (1.0f + expf(-x));
+        case kGTanh: return tanhf(x);
+        case kGRelu: return fmaxf(x, 0.0f);
+        case kGSigmoid: return 1.0f / (1.0f + expf(-x));
+        case kGAbs: return fabsf(x);
+        default: return x;
+    }
+}
+__device__ __forceinline__ float gate_act_grad(int kind, float x) {
+    switch (kind) {
+        case kGSilu: {
+            const float s = 1.0f / (1.0f + expf(-x));
+            return s * (1.0f + x * (1.0f - s));
+        }
+        case kGTanh: {
+            const float t = tanhf(x);
+            return 1.0f - t * t;
+        }
+        case kGRelu: return x > 0.0f ? 1.0f : 0.0f;
+        case kGSigmoid: {
+            const float s = 1.0f / (1.0f + expf(-x));
+            return s * (1.0f - s);
+        }
+        case kGAbs: return x > 0.0f ? 1.0f : (x < 0.0f ? -1.0f : 0.0f);
+        default: return 1.0f;
+    }
+}
+
+// out_tbl[j] = {input column, gate column or -1, activation code}, out_cst[j] = constant
+__global__ void gate_fwd_kernel(const float* __restrict__ x, const int32_t* __restrict__ out_tbl, const float* __restrict__ out_cst,
+                                float* __restrict__ out, int64_t rows, int din, int dout) {
+    const int64_t total = rows * dout;
+    for (int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
+         idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int64_t z = idx / dout;
+        const int j = static_cast<int>(idx - z * dout);
+        const int src = out_tbl[3 * j], gate = out_tbl[3 * j + 1], act = out_tbl[3 * j + 2];
+        const float* xr = x + z * din;
+        const float v = xr[src];
+        out[idx] = gate < 0 ? out_cst[j] * gate_act(act, v) : v * (out_cst[j] * gate_act(act, xr[gate]));
+    }
+}
+
+// in_tbl[c] = {kind, first output column, count, partner, activation code}, in_cst[c] = constant:
+// kind 0 = scalar, 1 = gated component (partner = its gate's input column, activation of that gate),
+// 2 = gate (count = 2l+1 components of its channel, partner = input column of the first component),
+// 3 = column no output depends on
+__global__ void gate_bwd_kernel(const float* __restrict__ x, const float* __restrict__ gout, const int32_t* __restrict__ in_tbl,
+                                const float* __restrict__ in_cst, float* __restrict__ gin, int64_t rows, int din, int dout) {
+    const int64_t total = rows * din;
+    for (int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
+         idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int64_t z = idx / din;
+        const int c = static_cast<int>(idx - z * din);
+        const int kind = in_tbl[5 * c], o0 = in_tbl[5 * c + 1], cnt = in_tbl[5 * c + 2], partner = in_tbl[5 * c + 3],
+                  act = in_tbl[5 * c + 4];
+        const float* xr = x + z * din;
+        const float* gr = gout + z * dout;
+        float g = 0.0f;
+        if (kind == 0) {
+            g = gr[o0] * in_cst[c] * gate_act_grad(act, xr[c]);
+        } else if (kind == 1) {
+            g = gr[o0] * (in_cst[c] * gate_act(act, xr[partner]));
+        } else if (kind == 2) {
+            float acc = 0.0f;
+            for (int m = 0; m < cnt; ++m) acc = fmaf(gr[o0 + m], xr[partner + m], acc);
+            g = acc * in_cst[c] * gate_act_grad(act, xr[c]);
+        }
+        gin[idx] = g;
+    }
+}
+
+int gate_grid(int64_t total) {
+    const int64_t want = ceil_div(total, 256);
+    const int64_t cap = static_cast<int64_t>(kNumSMs) * 32;
+    return static_cast<int>(want < cap ? (want < 1 ? 1 : want) : cap);
+}
+
+}  // namespace
+}  // namespace e3b
+
+extern "C" int e3b_gate_fwd(const float* x, const int32_t* out_table, const float* out_const, float* out, int64_t rows,
+                            int din, int dout, void* stream) {
+    using namespace e3b;
+    if (rows < 0 || din < 0 || dout < 0) return fail(E3B_ERR_ARG, "gate_fwd: negative size");
+    if (rows == 0 || dout == 0) return E3B_OK;
+    if (!x || !out_table || !out_const || !out) return fail(E3B_ERR_ARG, "gate_fwd: null pointer");
+    gate_fwd_kernel<<<gate_grid(rows * dout), 256, 0, static_cast<cudaStream_t>(stream)>>>(x, out_table, out_const, out, rows, din, dout);
+    return check_launch("gate_fwd");
+}
+
+extern "C" int e3b_gate_bwd(const float* x, const float* grad_out, const int32_t* in_table, const float* in_const,
+                            float* grad_x, int64_t rows, int din, int dout, void* stream) {
+    using namespace e3b;
+    if (rows < 0 || din < 0 || dout < 0) return fail(E3B_ERR_ARG, "gate_bwd: negative size");
+    if (rows == 0 || din == 0) return E3B_OK;
+    if (!x || !grad_out || !in_table || !in_const || !grad_x) return fail(E3B_ERR_ARG, "gate_bwd: null pointer");
+    gate_bwd_kernel<<<gate_grid(rows * din), 256, 0, static_cast<cudaStream_t>(stream)>>>(x, grad_out, in_table, in_const, grad_x, rows, din, dout);
+    return check_launch("gate_bwd");
+}

@@ -1,5 +1,6 @@
 from ._edge_embed import edge_embed
+from ._gate import Gate
 from ._fc import FullyConnectedNet, bessel, normalize2mom_constant
 from ._interaction import InteractionBlock, neighbor_list_pbc, radius_graph_pbc
 
-__all__ = ["edge_embed", "FullyConnectedNet", "bessel", "normalize2mom_constant", "InteractionBlock", "radius_graph_pbc", "neighbor_list_pbc"]
+__all__ = ["Gate", "edge_embed", "FullyConnectedNet", "bessel", "normalize2mom_constant", "InteractionBlock", "radius_graph_pbc", "neighbor_list_pbc"]

@@ -26,7 +26,8 @@ from ..codegen import tc_gemm
 @lru_cache(maxsize=None)
 def normalize2mom_constant(name: str = "silu") -> float:
     """<f(z)^2>^{-1/2} for z ~ N(0,1), estimated exactly like the reference: 1e6 samples, seed 0, fp64."""
-    f = {"silu": torch.nn.functional.silu, "tanh": torch.tanh, "relu": torch.relu}[name]
+    f = {"silu": torch.nn.functional.silu, "tanh": torch.tanh, "relu": torch.relu, "sigmoid": torch.sigmoid,
+         "abs": torch.abs}[name]
     gen = torch.Generator(device="cpu").manual_seed(0)
     z = torch.randn(1_000_000, generator=gen, dtype=torch.float64)
     return f(z).pow(2).mean().pow(-0.5).item()

@@ -144,6 +144,24 @@ int e3b_radial_embed_bwd(const float* pos, const int64_t* edge_src, const int64_
                          float* grad_pos, int32_t* status, void* stream);
 
 /*
+ * Gate non-linearity on rows (e3nn/nn/_gate.py:127-144: Extract, two Activations of
+ * e3nn/nn/_activation.py:80-98 and the scalar-gate ElementwiseTensorProduct, fused):
+ *   out[z, j] = c_j * act_j(x[z, src_j])                      for scalar outputs,
+ *   out[z, j] = x[z, src_j] * c_j * act_j(x[z, gate_j])       for gated components.
+ * The irreps bookkeeping is done by the host and passed as device tables:
+ *   out_table [dout,3] int32 = {src column, gate column or -1, activation}, out_const [dout] float;
+ *   in_table  [din,5]  int32 = {kind, first output column, count, partner column, activation},
+ *   in_const  [din] float; kind 0 scalar, 1 gated component (partner = its gate), 2 gate (count = 2l+1
+ *   components starting at input column `partner` / output column `first`), 3 unused column.
+ * activation: 0 silu, 1 tanh, 2 relu, 3 identity, 4 sigmoid, 5 abs.  x [rows,din], out [rows,dout];
+ * e3b_gate_bwd writes grad_x [rows,din] for a cotangent grad_out [rows,dout] (replaces autograd).
+ */
+int e3b_gate_fwd(const float* x, const int32_t* out_table, const float* out_const, float* out, int64_t rows, int din,
+                 int dout, void* stream);
+int e3b_gate_bwd(const float* x, const float* grad_out, const int32_t* in_table, const float* in_const, float* grad_x,
+                 int64_t rows, int din, int dout, void* stream);
+
+/*
  * Weight-shared dense contractions in fp32 (CUDA cores): 'uvw' tensor-product paths
  *   out[z,w,k] = sum_paths pw sum_{u,v} W[u,v,w] sum_{ij} C_ijk x1[z,u,i] x2[z,v,j]
  * (e3nn/o3/_tensor_product/_codegen.py:148-165 with the accumulation of :312-343) and the

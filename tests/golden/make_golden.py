@@ -5,7 +5,8 @@ variable, default ``/root/reference``).  The only missing dependency of the refe
 ``opt_einsum_fx`` (a contraction-order optimiser that does not change the mathematics),
 is replaced by an identity stand-in before ``import e3nn``.
 
-    python tests/golden/make_golden.py
+    python tests/golden/make_golden.py              (everything)
+    python tests/golden/make_golden.py --only-gate  (only the Gate cases, leaving the other files untouched)
 
 Every case stores its fp32 inputs and the reference's fp64 output on those inputs
 (inputs upcast to fp64), plus the reference's own fp32 output for context.  The files
@@ -60,7 +61,40 @@ def conv_layout(o3, irreps_node, irreps_edge, keep):
     return mid, ins
 
 
+GATE_CASES = {
+    "gate_mixed": ("16x0e+8x0o", ["silu", "tanh"], "8x0e+4x0o", ["sigmoid", "tanh"], "8x1o+4x2e"),
+    "gate_l3": ("32x0e", ["silu"], "24x0e", ["sigmoid"], "8x1o+8x2e+8x3o"),
+    "gate_abs_identity": ("4x0o", ["abs"], "6x0e", [None], "2x1e+4x1o"),
+    "gate_no_scalars": ("", [], "3x0e", ["relu"], "3x2e"),
+}
+
+
+def gate_cases(meta):
+    """Gate.forward of the reference on seeded rows (e3nn/nn/_gate.py:127-144); activations are stored by name."""
+    from e3nn.nn import Gate
+
+    fn = {"silu": torch.nn.functional.silu, "tanh": torch.tanh, "sigmoid": torch.sigmoid, "abs": torch.abs,
+          "relu": torch.relu, None: None}
+    gen = torch.Generator().manual_seed(1234)
+    for name, (sc, act_s, ga, act_g, gd) in GATE_CASES.items():
+        g = Gate(sc, [fn[a] for a in act_s], ga, [fn[a] for a in act_g], gd)
+        x = torch.randn(9, g.irreps_in.dim, generator=gen)
+        out64 = g(x.double())
+        np.savez_compressed(os.path.join(HERE, f"{name}.npz"), x=_np(x), out_f64=_np(out64))
+        meta["cases"][name] = {"irreps_scalars": sc, "act_scalars": act_s, "irreps_gates": ga, "act_gates": act_g,
+                               "irreps_gated": gd, "irreps_in": str(g.irreps_in), "irreps_out": str(g.irreps_out)}
+
+
 def main():
+    if "--only-gate" in sys.argv:
+        _import_reference()
+        with open(os.path.join(HERE, "meta.json")) as f:
+            meta = json.load(f)
+        gate_cases(meta)
+        with open(os.path.join(HERE, "meta.json"), "w") as f:
+            json.dump(meta, f, indent=1)
+        print("gate golden vectors written to", HERE)
+        return
     e3nn, o3 = _import_reference()
     from e3nn.math import bessel
     from e3nn.nn import FullyConnectedNet
@@ -239,6 +273,8 @@ def main():
         "irreps_node": "8x0e+8x1o+8x2e", "irreps_edge": "0e+1o+2e", "irreps_mid": str(mid),
         "instructions": [list(i) for i in ins], "num_nodes": N, "scale": 0.5,
     }
+
+    gate_cases(meta)
 
     with open(os.path.join(HERE, "meta.json"), "w") as f:
         json.dump(meta, f, indent=1)

@@ -536,6 +536,34 @@ def test_neighbor_list_edge_cases():
     assert torch.allclose(vec, torch.tensor([[-1.0, 0.0, 0.0], [1.0, 0.0, 0.0]], device=DEV))
 
 
+# ----------------------------------------------------------------------------- Gate
+@pytest.mark.parametrize("name", ["gate_mixed", "gate_l3", "gate_abs_identity", "gate_no_scalars"])
+def test_gate_golden_and_gradient(golden, golden_meta, name):
+    """Gate kernel against the reference's output on the golden rows, and its gradient against autograd through
+    the oracle (fp64) on larger seeded rows with leading batch dimensions."""
+    from e3nn_b200 import nn as bnn
+
+    fn = {"silu": torch.nn.functional.silu, "tanh": torch.tanh, "sigmoid": torch.sigmoid, "abs": torch.abs,
+          "relu": torch.relu, None: None}
+    g, m = golden(name), golden_meta["cases"][name]
+    gate = bnn.Gate(m["irreps_scalars"], [fn[a] for a in m["act_scalars"]], m["irreps_gates"],
+                    [fn[a] for a in m["act_gates"]], m["irreps_gated"]).to(DEV)
+    out = gate(torch.from_numpy(g["x"]).to(DEV))
+    assert rel_err(out.cpu(), torch.from_numpy(g["out_f64"])) < TOL
+    torch.manual_seed(3)
+    x = torch.randn(5, 301, gate.irreps_in.dim)
+    go = torch.randn(5, 301, gate.irreps_out.dim)
+    x64 = x.double().requires_grad_(True)
+    ref = orc.gate(m["irreps_scalars"], m["act_scalars"], m["irreps_gates"], m["act_gates"], m["irreps_gated"], x64)
+    ref.backward(go.double())
+    xg = x.clone().to(DEV).requires_grad_(True)
+    o = gate(xg)
+    assert o.shape == ref.shape and rel_err(o.detach().cpu(), ref.detach()) < TOL
+    o.backward(go.to(DEV))
+    assert rel_err(xg.grad.cpu(), x64.grad) < TOL
+    assert gate(torch.zeros(0, gate.irreps_in.dim, device=DEV)).shape == (0, gate.irreps_out.dim)
+
+
 # ----------------------------------------------------------------------------- fused edge embedding
 @pytest.mark.gpu
 @pytest.mark.parametrize("act,hidden,nb,with_shift", [("silu", 64, 8, True), ("tanh", 32, 5, False), ("relu", 128, 16, True)])

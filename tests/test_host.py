@@ -184,3 +184,26 @@ def test_cpu_tensors_are_rejected_by_the_new_entry_points():
     assert torch.all(key[1:] > key[:-1])                       # sorted by destination, then source, no duplicates
     vec = pos[src] - pos[dst] + shift
     assert float(vec.norm(dim=-1).max()) <= 5.0 + 1e-5
+
+
+def test_gate_module_bookkeeping_matches_reference(golden_meta):
+    """irreps_in / irreps_out of the drop-in Gate equal the reference's (stored with the golden vectors); the error
+    conventions of e3nn/nn/_gate.py:91-101 and e3nn/nn/_activation.py:38-57 are kept."""
+    import torch
+    from e3nn_b200 import nn as bnn
+
+    fn = {"silu": torch.nn.functional.silu, "tanh": torch.tanh, "sigmoid": torch.sigmoid, "abs": torch.abs,
+          "relu": torch.relu, None: None}
+    for name in ("gate_mixed", "gate_l3", "gate_abs_identity", "gate_no_scalars"):
+        m = golden_meta["cases"][name]
+        g = bnn.Gate(m["irreps_scalars"], [fn[a] for a in m["act_scalars"]], m["irreps_gates"],
+                     [fn[a] for a in m["act_gates"]], m["irreps_gated"])
+        assert str(g.irreps_in) == m["irreps_in"] and str(g.irreps_out) == m["irreps_out"]
+    with pytest.raises(ValueError):
+        bnn.Gate("4x0e", [torch.tanh], "3x0e", [torch.tanh], "4x1o")          # 3 gates for 4 gated irreps
+    with pytest.raises(ValueError):
+        bnn.Gate("4x1o", [None], "4x0e", [torch.tanh], "4x1o")               # non-scalar "scalars"
+    with pytest.raises(ValueError):
+        bnn.Gate("4x0o", [torch.nn.functional.silu], "", [], "")              # odd scalar, activation without parity
+    with pytest.raises(NotImplementedError):
+        bnn.Gate("4x0e", [torch.tanh], "4x0e", [torch.tanh], "4x1o")(torch.zeros(2, 20))   # CPU tensor

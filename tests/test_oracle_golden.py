@@ -113,3 +113,12 @@ def test_conv_small(golden, golden_meta):
     assert rel_err(out, torch.from_numpy(g["out_f64"])) < 1e-12
     perm, rowptr = orc.csr_from_dst(dst, m["num_nodes"])
     assert torch.equal(dst[perm], torch.sort(dst).values) and rowptr[-1] == dst.numel()
+
+
+@pytest.mark.parametrize("name", ["gate_mixed", "gate_l3", "gate_abs_identity", "gate_no_scalars"])
+def test_gate(golden, golden_meta, name):
+    """Gate.forward of the reference (e3nn/nn/_gate.py:127-144) on its sorted input layout."""
+    g, m = golden(name), golden_meta["cases"][name]
+    x = torch.from_numpy(g["x"]).double()
+    out = orc.gate(m["irreps_scalars"], m["act_scalars"], m["irreps_gates"], m["act_gates"], m["irreps_gated"], x)
+    assert rel_err(out, torch.from_numpy(g["out_f64"])) < 1e-12
