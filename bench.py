@@ -8,6 +8,7 @@ Workloads (synthetic, seeded; shapes and distributions of the BASELINE configura
   conv_l2_11   same graph, the 11-path layout (outputs restricted to the node irreps).
   conv_l3_23   the 'uvu' l<=3 layout (23 paths, 64x0e+64x1o+64x2e+64x3o), same graph shape.
   sh_l3        spherical harmonics lmax 3 on 4,194,304 edge vectors.
+  gate         Gate non-linearity (64 scalars, 192 gates, 64x1o+64x2e+64x3o gated) on 1,048,576 rows, forward.
   interaction_l3  one NequIP-style interaction block, forward + gradient w.r.t. positions: 262,144 atoms uniform in
                a periodic cube at 0.05 / A^3, 5 A cutoff (~26 neighbours), features 64x0e+64x1o+64x2e+64x3o,
                SH lmax 3, Bessel(8) -> 64 -> 1472 radial MLP, 23-path 'uvu', scatter / sqrt(n), Linear.
@@ -163,6 +164,8 @@ def run_ours(args):
 
     if args.workload == "sh_l3":
         return run_sh(args, rank, world, device)
+    if args.workload == "gate":
+        return run_gate(args, rank, world, device)
     if args.workload == "uvw_fctp":
         return run_uvw(args, rank, world, device)
     if args.workload == "interaction_l3":
@@ -323,6 +326,45 @@ def run_sh(args, rank, world, device):
         "config": {"workload": "sh_l3", "edges": n_total, "l2": "256 MB buffer written between timed launches"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": None, "peak_kind": f"of {peak_kind}", "kernel": "sh_fwd_kernel<3>"},
+        "gpu_launches": args.steps,
+    }), flush=True)
+
+
+def run_gate(args, rank, world, device):
+    """Gate after the Linear of an l <= 3 block: 64 scalars (silu), 192 gates (sigmoid), 64x1o+64x2e+64x3o gated."""
+    from e3nn_b200 import nn as bnn
+
+    rows_total = args.nodes if args.nodes > 0 else 1_048_576
+    rows = rows_total // world
+    gate = bnn.Gate("64x0e", [torch.nn.functional.silu], "192x0e", [torch.sigmoid], "64x1o+64x2e+64x3o").to(device)
+    gen = torch.Generator(device=device).manual_seed(rank)
+    x = torch.randn(rows, gate.irreps_in.dim, device=device, generator=gen)
+    for _ in range(args.warmup):
+        out = gate(x)
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    times = []
+    for _ in range(args.steps):
+        start.record()
+        out = gate(x)
+        stop.record()
+        torch.cuda.synchronize()
+        times.append(start.elapsed_time(stop))
+    times.sort()
+    ms = times[len(times) // 2]
+    if rank != 0:
+        return
+    peak, peak_kind = measured_peaks()
+    nbytes = 4.0 * rows * (gate.irreps_in.dim + gate.irreps_out.dim)
+    achieved = nbytes / (ms * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": "Gate rows/sec (l<=3, fp32)", "value": rows_total / (ms * 1e-3), "unit": "rows/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "gate", "rows": rows_total, "irreps_in": str(gate.irreps_in), "irreps_out": str(gate.irreps_out),
+                   "l2": "rows in + out (%.1f GB) far larger than the 126 MB L2" % (nbytes / 1e9)},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": None, "peak_kind": f"of {peak_kind}", "kernel": "gate_fwd_kernel"},
         "gpu_launches": args.steps,
     }), flush=True)
 
@@ -712,7 +754,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS) + ["sh_l3", "uvw_fctp", "interaction_l3"])
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS) + ["sh_l3", "uvw_fctp", "interaction_l3", "gate"])
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--nodes", type=int, default=0, help="override the node count (smaller graphs for profiling)")
     ap.add_argument("--skip-e2e", action="store_true", help="profiling runs: skip the host-buffer leg")

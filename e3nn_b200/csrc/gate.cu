@@ -46,18 +46,28 @@ __device__ __forceinline__ float gate_act_grad(int kind, float x) {
     }
 }
 
+// A thread owns one column (its table entry stays in registers) and walks the rows: consecutive threads touch
+// consecutive addresses, no per-element index arithmetic beyond one multiply-add per row.
 // out_tbl[j] = {input column, gate column or -1, activation code}, out_cst[j] = constant
-__global__ void gate_fwd_kernel(const float* __restrict__ x, const int32_t* __restrict__ out_tbl, const float* __restrict__ out_cst,
-                                float* __restrict__ out, int64_t rows, int din, int dout) {
-    const int64_t total = rows * dout;
-    for (int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
-         idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-        const int64_t z = idx / dout;
-        const int j = static_cast<int>(idx - z * dout);
-        const int src = out_tbl[3 * j], gate = out_tbl[3 * j + 1], act = out_tbl[3 * j + 2];
-        const float* xr = x + z * din;
-        const float v = xr[src];
-        out[idx] = gate < 0 ? out_cst[j] * gate_act(act, v) : v * (out_cst[j] * gate_act(act, xr[gate]));
+__global__ void __launch_bounds__(256) gate_fwd_kernel(const float* __restrict__ x, const int32_t* __restrict__ out_tbl,
+                                                       const float* __restrict__ out_cst, float* __restrict__ out, int64_t rows,
+                                                       int din, int dout) {
+    const int j = blockIdx.y * blockDim.x + threadIdx.x;
+    if (j >= dout) return;
+    const int src = out_tbl[3 * j], gate = out_tbl[3 * j + 1], act = out_tbl[3 * j + 2];
+    const float cst = out_cst[j];
+    // four rows per trip: their loads are independent and in flight together
+    for (int64_t z0 = static_cast<int64_t>(blockIdx.x) * 4; z0 < rows; z0 += static_cast<int64_t>(gridDim.x) * 4) {
+        float v[4], gv[4];
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            const int64_t z = z0 + r < rows ? z0 + r : rows - 1;
+            v[r] = x[z * din + src];
+            gv[r] = gate < 0 ? 0.0f : x[z * din + gate];
+        }
+#pragma unroll
+        for (int r = 0; r < 4; ++r)
+            if (z0 + r < rows) out[(z0 + r) * dout + j] = gate < 0 ? cst * gate_act(act, v[r]) : v[r] * (cst * gate_act(act, gv[r]));
     }
 }
 
@@ -65,35 +75,38 @@ __global__ void gate_fwd_kernel(const float* __restrict__ x, const int32_t* __re
 // kind 0 = scalar, 1 = gated component (partner = its gate's input column, activation of that gate),
 // 2 = gate (count = 2l+1 components of its channel, partner = input column of the first component),
 // 3 = column no output depends on
-__global__ void gate_bwd_kernel(const float* __restrict__ x, const float* __restrict__ gout, const int32_t* __restrict__ in_tbl,
-                                const float* __restrict__ in_cst, float* __restrict__ gin, int64_t rows, int din, int dout) {
-    const int64_t total = rows * din;
-    for (int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
-         idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-        const int64_t z = idx / din;
-        const int c = static_cast<int>(idx - z * din);
-        const int kind = in_tbl[5 * c], o0 = in_tbl[5 * c + 1], cnt = in_tbl[5 * c + 2], partner = in_tbl[5 * c + 3],
-                  act = in_tbl[5 * c + 4];
+__global__ void __launch_bounds__(256) gate_bwd_kernel(const float* __restrict__ x, const float* __restrict__ gout,
+                                                       const int32_t* __restrict__ in_tbl, const float* __restrict__ in_cst,
+                                                       float* __restrict__ gin, int64_t rows, int din, int dout) {
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= din) return;
+    const int kind = in_tbl[5 * c], o0 = in_tbl[5 * c + 1], cnt = in_tbl[5 * c + 2], partner = in_tbl[5 * c + 3],
+              act = in_tbl[5 * c + 4];
+    const float cst = in_cst[c];
+    for (int64_t z = blockIdx.x; z < rows; z += gridDim.x) {
         const float* xr = x + z * din;
         const float* gr = gout + z * dout;
         float g = 0.0f;
         if (kind == 0) {
-            g = gr[o0] * in_cst[c] * gate_act_grad(act, xr[c]);
+            g = gr[o0] * cst * gate_act_grad(act, xr[c]);
         } else if (kind == 1) {
-            g = gr[o0] * (in_cst[c] * gate_act(act, xr[partner]));
+            g = gr[o0] * (cst * gate_act(act, xr[partner]));
         } else if (kind == 2) {
             float acc = 0.0f;
             for (int m = 0; m < cnt; ++m) acc = fmaf(gr[o0 + m], xr[partner + m], acc);
-            g = acc * in_cst[c] * gate_act_grad(act, xr[c]);
+            g = acc * cst * gate_act_grad(act, xr[c]);
         }
-        gin[idx] = g;
+        gin[z * din + c] = g;
     }
 }
 
-int gate_grid(int64_t total) {
-    const int64_t want = ceil_div(total, 256);
-    const int64_t cap = static_cast<int64_t>(kNumSMs) * 32;
-    return static_cast<int>(want < cap ? (want < 1 ? 1 : want) : cap);
+// grid: y covers the columns in blocks of 256, x walks the rows with enough blocks to fill the machine
+dim3 gate_grid(int64_t rows, int cols) {
+    const int ny = (cols + 255) / 256;
+    int64_t nx = (static_cast<int64_t>(kNumSMs) * 16 + ny - 1) / ny;
+    if (nx > rows) nx = rows;
+    if (nx < 1) nx = 1;
+    return dim3(static_cast<unsigned>(nx), static_cast<unsigned>(ny));
 }
 
 }  // namespace
@@ -105,7 +118,7 @@ extern "C" int e3b_gate_fwd(const float* x, const int32_t* out_table, const floa
     if (rows < 0 || din < 0 || dout < 0) return fail(E3B_ERR_ARG, "gate_fwd: negative size");
     if (rows == 0 || dout == 0) return E3B_OK;
     if (!x || !out_table || !out_const || !out) return fail(E3B_ERR_ARG, "gate_fwd: null pointer");
-    gate_fwd_kernel<<<gate_grid(rows * dout), 256, 0, static_cast<cudaStream_t>(stream)>>>(x, out_table, out_const, out, rows, din, dout);
+    gate_fwd_kernel<<<gate_grid(rows, dout), 256, 0, static_cast<cudaStream_t>(stream)>>>(x, out_table, out_const, out, rows, din, dout);
     return check_launch("gate_fwd");
 }
 
@@ -115,6 +128,6 @@ extern "C" int e3b_gate_bwd(const float* x, const float* grad_out, const int32_t
     if (rows < 0 || din < 0 || dout < 0) return fail(E3B_ERR_ARG, "gate_bwd: negative size");
     if (rows == 0 || din == 0) return E3B_OK;
     if (!x || !grad_out || !in_table || !in_const || !grad_x) return fail(E3B_ERR_ARG, "gate_bwd: null pointer");
-    gate_bwd_kernel<<<gate_grid(rows * din), 256, 0, static_cast<cudaStream_t>(stream)>>>(x, grad_out, in_table, in_const, grad_x, rows, din, dout);
+    gate_bwd_kernel<<<gate_grid(rows, din), 256, 0, static_cast<cudaStream_t>(stream)>>>(x, grad_out, in_table, in_const, grad_x, rows, din, dout);
     return check_launch("gate_bwd");
 }
