@@ -520,12 +520,31 @@ def run_interaction(args, rank, world, device):
                 "shift": shift[e0:e1].contiguous().pin_memory(), "rowptr": rowptr_local.pin_memory()}
         grad_host = torch.empty(n_atoms, 3).pin_memory()
 
+        copy_stream = torch.cuda.Stream(device=device)
+        x_dev = torch.empty(n1 - n0, 1024, device=device)
+
         def e2e_step():
-            d = {k: v.to(device, non_blocking=True) for k, v in host.items()}
-            xs, wait = d["x"], None
-            if world > 1:
-                _, wait = sharding.all_gather_rows(xs, bounds, out=x_full, async_op=True)
-                xs = x_full
+            # the graph and the positions are needed first: main stream.  The feature rows (the bulk of the bytes) are
+            # not read before the convolution: their upload (and, sharded, the all-gather that follows it) runs on a
+            # second stream under the edge embedding and the radial layer
+            main = torch.cuda.current_stream()
+            copy_stream.wait_stream(main)            # x_dev's previous reader (last step's kernels) is done
+            with torch.cuda.stream(copy_stream):
+                x_dev.copy_(host["x"], non_blocking=True)
+                gather_wait = None
+                xs = x_dev
+                if world > 1:
+                    _, gather_wait = sharding.all_gather_rows(x_dev, bounds, out=x_full, async_op=True)
+                    xs = x_full
+                uploaded = torch.cuda.Event()
+                uploaded.record(copy_stream)
+            d = {k: v.to(device, non_blocking=True) for k, v in host.items() if k != "x"}
+
+            def wait():
+                torch.cuda.current_stream().wait_event(uploaded)
+                if gather_wait is not None:
+                    gather_wait()
+
             p = d["pos"].requires_grad_(True)
             (block(p, xs, d["src"], d["dst"], d["rowptr"], d["shift"], before_conv=wait) * G).sum().backward()
             if world > 1:
