@@ -67,10 +67,9 @@ def core() -> ctypes.CDLL:
         lib.e3b_csr_from_dst.argtypes = [c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p]
         lib.e3b_dense_fwd.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int, c_void_p]
         lib.e3b_fill_columns.argtypes = [c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_int, c_void_p]
-        lib.e3b_radial_embed_fwd.argtypes = [c_void_p] * 5 + [c_int64, c_int64, c_int, c_int, c_float, c_float, c_float, c_int,
-                                             c_void_p, c_void_p, c_void_p, c_void_p]
-        lib.e3b_radial_embed_bwd.argtypes = [c_void_p] * 7 + [c_int64, c_int64, c_int, c_int, c_float, c_float, c_float, c_int,
-                                             c_void_p, c_void_p, c_void_p]
+        spec = [c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_float, c_float, c_int]
+        lib.e3b_radial_embed_fwd.argtypes = [c_void_p] * 5 + [c_int64, c_int64] + spec + [c_void_p, c_void_p, c_void_p, c_void_p]
+        lib.e3b_radial_embed_bwd.argtypes = [c_void_p] * 7 + [c_int64, c_int64] + spec + [c_void_p, c_void_p, c_void_p]
         lib.e3b_neighbor_scratch_bytes.argtypes = [c_int64, c_double, c_double]
         lib.e3b_neighbor_scratch_bytes.restype = c_int64
         lib.e3b_neighbor_count.argtypes = [c_void_p, c_int64, c_double, c_double, c_void_p, c_int64, c_void_p, c_void_p]

@@ -2,8 +2,10 @@
 // Bessel radial basis and the first (narrow) layer of the radial network with its activation.
 //
 //   edge_vec = pos[src] - pos[dst] + shift                        (e3nn/nn/models/gate_points_2101.py:328)
-//   B_k      = sqrt(2/c) sin(k pi r / c) / r,  k = 1..num_basis   (e3nn/math/_bessel.py:6-37)
-//   h        = act_scale * act((B @ W0) * w_scale)                (e3nn/nn/_fc.py:38-48, 70-88)
+//   B_k      = sqrt(2/c) sin(k pi r / c) / r,  k = 1..num_basis   (e3nn/math/_bessel.py:6-37), or one of the
+//              soft_one_hot_linspace families                       (e3nn/math/_soft_one_hot_linspace.py:100-140)
+//   h        = act_scale * act((B @ W0) * w_scale) [* smooth_cutoff(r / end)]   (e3nn/nn/_fc.py:38-48, 70-88;
+//                                                                 e3nn/nn/models/gate_points_2101.py:136-141)
 //
 // The reference evaluates these as a few dozen elementwise launches over [E, .] temporaries.  Here a warp
 // takes 32 edges at a time: first one lane per edge (vector, radius and basis; the basis in fp64 through the
@@ -74,40 +76,111 @@ __device__ __forceinline__ EdgeGeom edge_geom(const float* __restrict__ pos, con
     return g;
 }
 
-// B_k (and optionally dB_k/dr) for k = 1..nb in fp64: sin(k theta), cos(k theta) by the Chebyshev recurrence
-__device__ __forceinline__ void bessel_basis(double r, int nb, double r_max, float* basis, float* dbasis) {
-    const double c0 = sqrt(2.0 / r_max);
-    const double a = 3.14159265358979323846 / r_max;
-    if (r == 0.0) {
+// Parameters of the radial embedding, passed by value to the kernels.
+//   kind 0: e3nn.math.bessel(r, nb, end)                         (e3nn/math/_bessel.py:6-37)
+//   kind 1-5: soft_one_hot_linspace(r, start, end, nb, basis, cutoff) with basis gaussian, cosine, smooth_finite,
+//             fourier, bessel                                     (e3nn/math/_soft_one_hot_linspace.py:100-140)
+//   scale: factor on every basis value (models multiply by sqrt(nb));
+//   envelope 1: h is multiplied by smooth_cutoff(r / end)          (e3nn/nn/models/gate_points_2101.py:136-141)
+struct RadialSpec {
+    int kind, cutoff, envelope, nb;
+    double start, end, scale;
+};
+
+__device__ __forceinline__ double soft_unit_step(double x) { return x > 0.0 ? exp(-1.0 / x) : 0.0; }
+__device__ __forceinline__ double soft_unit_step_grad(double x) { return x > 0.0 ? exp(-1.0 / x) / (x * x) : 0.0; }
+
+// basis[k] (and optionally d basis[k] / dr), k = 0..nb-1, evaluated in fp64 and rounded once
+__device__ __forceinline__ void radial_basis(const RadialSpec& sp, double r, float* basis, float* dbasis) {
+    const int nb = sp.nb;
+    const double pi = 3.14159265358979323846;
+    if (sp.kind == 0 || sp.kind == 5) {
+        // sqrt(2/c) sin(k pi x / c) / x: sin(k theta), cos(k theta) by the Chebyshev recurrence
+        const double x = sp.kind == 0 ? r : r - sp.start;
+        const double c = sp.kind == 0 ? sp.end : sp.end - sp.start;
+        const double c0 = sqrt(2.0 / c) * sp.scale, a = pi / c;
+        const bool inside = sp.kind == 0 || !sp.cutoff || (x > 0.0 && x < c);
+        if (x == 0.0 || !inside) {
+            for (int k = 1; k <= nb; ++k) {
+                basis[k - 1] = static_cast<float>(inside ? c0 * k * a : 0.0);   // the x -> 0 limit (kind 0 defines it so)
+                if (dbasis) dbasis[k - 1] = 0.0f;
+            }
+            return;
+        }
+        double s1, c1;
+        sincos(a * x, &s1, &c1);
+        const double inv = 1.0 / x;
+        double s_prev = 0.0, s_cur = s1, c_prev = 1.0, c_cur = c1;
         for (int k = 1; k <= nb; ++k) {
-            basis[k - 1] = static_cast<float>(c0 * k * a);
-            if (dbasis) dbasis[k - 1] = 0.0f;
+            basis[k - 1] = static_cast<float>(c0 * s_cur * inv);
+            if (dbasis) dbasis[k - 1] = static_cast<float>(c0 * (k * a * c_cur * x - s_cur) * inv * inv);
+            const double s_next = 2.0 * c1 * s_cur - s_prev, c_next = 2.0 * c1 * c_cur - c_prev;
+            s_prev = s_cur; s_cur = s_next;
+            c_prev = c_cur; c_cur = c_next;
         }
         return;
     }
-    double s1, c1;
-    sincos(a * r, &s1, &c1);
-    const double inv = 1.0 / r;
-    double s_prev = 0.0, s_cur = s1, c_prev = 1.0, c_cur = c1;
-    for (int k = 1; k <= nb; ++k) {
-        basis[k - 1] = static_cast<float>(c0 * s_cur * inv);
-        if (dbasis) dbasis[k - 1] = static_cast<float>(c0 * (k * a * c_cur * r - s_cur) * inv * inv);
-        const double s_next = 2.0 * c1 * s_cur - s_prev;
-        const double c_next = 2.0 * c1 * c_cur - c_prev;
-        s_prev = s_cur; s_cur = s_next;
-        c_prev = c_cur; c_cur = c_next;
+    if (sp.kind == 4) {   // fourier
+        const double span = sp.end - sp.start, x = (r - sp.start) / span;
+        const double norm = sp.scale / sqrt(0.25 + nb / 2.0);
+        for (int k = 0; k < nb; ++k) {
+            double f, df;
+            if (!sp.cutoff) {
+                f = cos(pi * k * x); df = -pi * k * sin(pi * k * x) / span;
+            } else {
+                const bool inside = x > 0.0 && x < 1.0;
+                f = inside ? sin(pi * (k + 1) * x) : 0.0;
+                df = inside ? pi * (k + 1) * cos(pi * (k + 1) * x) / span : 0.0;
+            }
+            basis[k] = static_cast<float>(norm * f);
+            if (dbasis) dbasis[k] = static_cast<float>(norm * df);
+        }
+        return;
     }
+    // gaussian, cosine, smooth_finite on nb centres: linspace(start, end, nb), or the interior of nb + 2 points
+    const double step = sp.cutoff ? (sp.end - sp.start) / (nb + 1) : (nb > 1 ? (sp.end - sp.start) / (nb - 1) : 0.0);
+    for (int k = 0; k < nb; ++k) {
+        const double centre = sp.start + (sp.cutoff ? k + 1 : k) * step;
+        const double d = (r - centre) / step;
+        double f, df;
+        if (sp.kind == 1) {
+            f = exp(-d * d) / 1.12; df = f * (-2.0 * d);
+        } else if (sp.kind == 2) {
+            const bool inside = d < 1.0 && d > -1.0;
+            f = inside ? cos(0.5 * pi * d) : 0.0; df = inside ? -0.5 * pi * sin(0.5 * pi * d) : 0.0;
+        } else {
+            const double cst = 8.433573722839355;   // 1.14136 e^2 as the reference evaluates it (in float32)
+            const double a1 = soft_unit_step(d + 1.0), a2 = soft_unit_step(1.0 - d);
+            f = cst * a1 * a2;
+            df = cst * (soft_unit_step_grad(d + 1.0) * a2 - a1 * soft_unit_step_grad(1.0 - d));
+        }
+        basis[k] = static_cast<float>(sp.scale * f);
+        if (dbasis) dbasis[k] = static_cast<float>(sp.scale * df / step);
+    }
+}
+
+// smooth_cutoff(r / end) and its derivative with respect to r
+__device__ __forceinline__ void radial_envelope(const RadialSpec& sp, double r, float& env, float& denv) {
+    env = 1.0f; denv = 0.0f;
+    if (sp.envelope != 1) return;
+    const double u = 2.0 * (r / sp.end - 1.0), pi = 3.14159265358979323846;
+    if (u > 0.0) { env = 0.0f; return; }
+    if (u < -1.0) return;
+    env = static_cast<float>(0.5 * (1.0 - cos(pi * u)));
+    denv = static_cast<float>(0.5 * pi * sin(pi * u) * 2.0 / sp.end);
 }
 
 // H2 = hidden / 32 hidden units per lane (unit j of a lane is column lane + 32 j); NB = basis count padded to 8 or 16
 template <int H2, int NB>
 __global__ void __launch_bounds__(kEmbedWarps * 32) radial_embed_fwd_kernel(
         const float* __restrict__ pos, const int64_t* __restrict__ src, const int64_t* __restrict__ dst,
-        const float* __restrict__ shift, const float* __restrict__ w0, int64_t num_edges, int64_t num_nodes, int nb,
-        float r_max, float w_scale, float act_scale, int act, float* __restrict__ edge_vec, float* __restrict__ h,
+        const float* __restrict__ shift, const float* __restrict__ w0, int64_t num_edges, int64_t num_nodes, RadialSpec sp,
+        float w_scale, float act_scale, int act, float* __restrict__ edge_vec, float* __restrict__ h,
         int* __restrict__ status) {
     __shared__ float s_basis[kEmbedWarps][32][kMaxBasis + 1];
+    __shared__ float s_env[kEmbedWarps][32];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nb = sp.nb;
     constexpr int H = 32 * H2;
     float w[NB][H2];
 #pragma unroll
@@ -121,7 +194,10 @@ __global__ void __launch_bounds__(kEmbedWarps * 32) radial_embed_fwd_kernel(
         if (e < num_edges) {
             const EdgeGeom g = edge_geom(pos, src, dst, shift, e, num_nodes, status);
             edge_vec[e * 3] = g.vx; edge_vec[e * 3 + 1] = g.vy; edge_vec[e * 3 + 2] = g.vz;
-            bessel_basis(g.r, nb, r_max, s_basis[warp][lane], nullptr);
+            radial_basis(sp, g.r, s_basis[warp][lane], nullptr);
+            float env, denv;
+            radial_envelope(sp, g.r, env, denv);
+            s_env[warp][lane] = env;
         }
         __syncwarp();
         const int count = static_cast<int>(num_edges - b * 32 < 32 ? num_edges - b * 32 : 32);
@@ -139,7 +215,7 @@ __global__ void __launch_bounds__(kEmbedWarps * 32) radial_embed_fwd_kernel(
             }
             float* hrow = h + (b * 32 + i) * H;
 #pragma unroll
-            for (int j = 0; j < H2; ++j) hrow[lane + 32 * j] = act_scale * act_fwd(act, pre[j]);
+            for (int j = 0; j < H2; ++j) hrow[lane + 32 * j] = (s_env[warp][i] * act_scale) * act_fwd(act, pre[j]);
         }
         __syncwarp();
     }
@@ -161,11 +237,14 @@ template <int H2, int NB>
 __global__ void __launch_bounds__(kEmbedWarps * 32) radial_embed_bwd_kernel(
         const float* __restrict__ pos, const int64_t* __restrict__ src, const int64_t* __restrict__ dst,
         const float* __restrict__ shift, const float* __restrict__ w0, const float* __restrict__ grad_h,
-        const float* __restrict__ grad_vec, int64_t num_edges, int64_t num_nodes, int nb, float r_max, float w_scale,
+        const float* __restrict__ grad_vec, int64_t num_edges, int64_t num_nodes, RadialSpec sp, float w_scale,
         float act_scale, int act, float* __restrict__ grad_pos, int* __restrict__ status) {
     __shared__ float s_basis[kEmbedWarps][32][kMaxBasis + 1];
     __shared__ float s_cot[kEmbedWarps][32][kMaxBasis + 1];
+    __shared__ float s_env[kEmbedWarps][32];     // envelope value of the batch's edges
+    __shared__ float s_genv[kEmbedWarps][32];    // cotangent of the envelope
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nb = sp.nb;
     constexpr int H = 32 * H2;
     float w[NB][H2];
 #pragma unroll
@@ -177,12 +256,15 @@ __global__ void __launch_bounds__(kEmbedWarps * 32) radial_embed_bwd_kernel(
          b += static_cast<int64_t>(gridDim.x) * kEmbedWarps) {
         const int64_t e = b * 32 + lane;
         EdgeGeom g;
+        float env = 1.0f, denv = 0.0f;
         float dbasis[kMaxBasis];
 #pragma unroll
         for (int k = 0; k < kMaxBasis; ++k) dbasis[k] = 0.0f;
         if (e < num_edges) {
             g = edge_geom(pos, src, dst, shift, e, num_nodes, status);
-            bessel_basis(g.r, nb, r_max, s_basis[warp][lane], dbasis);
+            radial_basis(sp, g.r, s_basis[warp][lane], dbasis);
+            radial_envelope(sp, g.r, env, denv);
+            s_env[warp][lane] = env;
         }
         __syncwarp();
         const int count = static_cast<int>(num_edges - b * 32 < 32 ? num_edges - b * 32 : 32);
@@ -202,9 +284,13 @@ __global__ void __launch_bounds__(kEmbedWarps * 32) radial_embed_bwd_kernel(
             float cot[NB];
 #pragma unroll
             for (int k = 0; k < NB; ++k) cot[k] = 0.0f;
+            const float envi = s_env[warp][i];
+            float genv = 0.0f;
 #pragma unroll
             for (int j = 0; j < H2; ++j) {
-                const float dpre = grow[lane + 32 * j] * act_scale * act_grad(act, pre[j]);
+                const float gh = grow[lane + 32 * j];
+                if (sp.envelope) genv = fmaf(gh * act_scale, act_fwd(act, pre[j]), genv);
+                const float dpre = gh * (envi * act_scale) * act_grad(act, pre[j]);
 #pragma unroll
                 for (int k = 0; k < NB; ++k) cot[k] = fmaf(w[k][j], dpre, cot[k]);
             }
@@ -220,10 +306,15 @@ __global__ void __launch_bounds__(kEmbedWarps * 32) radial_embed_bwd_kernel(
                 // three halvings over lane bits 4, 3, 2: lane l holds component (l >> 2) & 7
                 if ((lane & 3) == 0) s_cot[warp][i][(lane >> 2) & 7] = cot[0];
             }
+            if (sp.envelope) {
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) genv += __shfl_xor_sync(0xffffffffu, genv, o);
+                if (lane == 0) s_genv[warp][i] = genv;
+            }
         }
         __syncwarp();
         if (e < num_edges) {
-            double dr = 0.0;
+            double dr = sp.envelope ? static_cast<double>(s_genv[warp][lane]) * denv : 0.0;
 #pragma unroll
             for (int k = 0; k < kMaxBasis; ++k)
                 if (k < nb) dr += static_cast<double>(s_cot[warp][lane][k]) * dbasis[k];
@@ -258,12 +349,30 @@ int embed_grid(int64_t num_edges) {
 }  // namespace
 }  // namespace e3b
 
+namespace e3b {
+namespace {
+int make_spec(RadialSpec* sp, int basis, int cutoff, int envelope, int num_basis, float start, float end, float basis_scale) {
+    if (basis < 0 || basis > 5) return fail(E3B_ERR_ARG, "radial_embed: unknown basis %d", basis);
+    if (envelope < 0 || envelope > 1) return fail(E3B_ERR_ARG, "radial_embed: unknown envelope %d", envelope);
+    if (!(end > start)) return fail(E3B_ERR_ARG, "radial_embed: end must be larger than start");
+    if (basis == 0 && start != 0.0f) return fail(E3B_ERR_ARG, "radial_embed: the plain Bessel basis starts at 0");
+    if ((basis >= 1 && basis <= 3) && !cutoff && num_basis < 2) return fail(E3B_ERR_ARG, "radial_embed: this basis needs two centres");
+    sp->kind = basis; sp->cutoff = cutoff != 0; sp->envelope = envelope; sp->nb = num_basis;
+    sp->start = start; sp->end = end; sp->scale = basis_scale;
+    return E3B_OK;
+}
+}  // namespace
+}  // namespace e3b
+
 extern "C" int e3b_radial_embed_fwd(const float* pos, const int64_t* edge_src, const int64_t* edge_dst, const float* shift,
                                     const float* w0, int64_t num_edges, int64_t num_nodes, int num_basis, int hidden,
-                                    float r_max, float w_scale, float act_scale, int act, float* edge_vec, float* h,
+                                    int basis, int cutoff, int envelope, float start, float end, float basis_scale,
+                                    float w_scale, float act_scale, int act, float* edge_vec, float* h,
                                     int32_t* status, void* stream) {
     using namespace e3b;
     if (int rc = check_embed_args(num_edges, num_nodes, num_basis, hidden, act)) return rc;
+    RadialSpec sp;
+    if (int rc = make_spec(&sp, basis, cutoff, envelope, num_basis, start, end, basis_scale)) return rc;
     if (num_edges == 0) return E3B_OK;
     if (!pos || !edge_src || !edge_dst || !w0 || !edge_vec || !h || !status) return fail(E3B_ERR_ARG, "radial_embed_fwd: null pointer");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -271,8 +380,8 @@ extern "C" int e3b_radial_embed_fwd(const float* pos, const int64_t* edge_src, c
 #define E3B_LAUNCH(H2)                                                                                                   \
     if (num_basis <= 8) E3B_LAUNCH_NB(H2, 8); else E3B_LAUNCH_NB(H2, 16)
 #define E3B_LAUNCH_NB(H2, NBP)                                                                                           \
-    radial_embed_fwd_kernel<H2, NBP><<<grid, threads, 0, s>>>(pos, edge_src, edge_dst, shift, w0, num_edges, num_nodes, num_basis, \
-                                                         r_max, w_scale, act_scale, act, edge_vec, h, status)
+    radial_embed_fwd_kernel<H2, NBP><<<grid, threads, 0, s>>>(pos, edge_src, edge_dst, shift, w0, num_edges, num_nodes, sp, \
+                                                              w_scale, act_scale, act, edge_vec, h, status)
     switch (hidden / 32) {
         case 1: E3B_LAUNCH(1); break;
         case 2: E3B_LAUNCH(2); break;
@@ -286,10 +395,13 @@ extern "C" int e3b_radial_embed_fwd(const float* pos, const int64_t* edge_src, c
 
 extern "C" int e3b_radial_embed_bwd(const float* pos, const int64_t* edge_src, const int64_t* edge_dst, const float* shift,
                                     const float* w0, const float* grad_h, const float* grad_edge_vec, int64_t num_edges,
-                                    int64_t num_nodes, int num_basis, int hidden, float r_max, float w_scale,
-                                    float act_scale, int act, float* grad_pos, int32_t* status, void* stream) {
+                                    int64_t num_nodes, int num_basis, int hidden, int basis, int cutoff, int envelope,
+                                    float start, float end, float basis_scale, float w_scale, float act_scale, int act,
+                                    float* grad_pos, int32_t* status, void* stream) {
     using namespace e3b;
     if (int rc = check_embed_args(num_edges, num_nodes, num_basis, hidden, act)) return rc;
+    RadialSpec sp;
+    if (int rc = make_spec(&sp, basis, cutoff, envelope, num_basis, start, end, basis_scale)) return rc;
     if (num_edges == 0) return E3B_OK;
     if (!pos || !edge_src || !edge_dst || !w0 || !grad_h || !grad_pos || !status) return fail(E3B_ERR_ARG, "radial_embed_bwd: null pointer");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -297,8 +409,8 @@ extern "C" int e3b_radial_embed_bwd(const float* pos, const int64_t* edge_src, c
 #define E3B_LAUNCH(H2)                                                                                                   \
     if (num_basis <= 8) E3B_LAUNCH_NB(H2, 8); else E3B_LAUNCH_NB(H2, 16)
 #define E3B_LAUNCH_NB(H2, NBP)                                                                                           \
-    radial_embed_bwd_kernel<H2, NBP><<<grid, threads, 0, s>>>(pos, edge_src, edge_dst, shift, w0, grad_h, grad_edge_vec, num_edges, \
-                                                         num_nodes, num_basis, r_max, w_scale, act_scale, act, grad_pos, status)
+    radial_embed_bwd_kernel<H2, NBP><<<grid, threads, 0, s>>>(pos, edge_src, edge_dst, shift, w0, grad_h, grad_edge_vec,  \
+                                                              num_edges, num_nodes, sp, w_scale, act_scale, act, grad_pos, status)
     switch (hidden / 32) {
         case 1: E3B_LAUNCH(1); break;
         case 2: E3B_LAUNCH(2); break;

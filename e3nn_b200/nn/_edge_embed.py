@@ -14,13 +14,16 @@ import torch
 from .. import _lib
 
 _ACT = {"silu": 0, "tanh": 1, "relu": 2, None: 3}
+# "bessel" = e3nn.math.bessel; the others = soft_one_hot_linspace(..., basis=<name>) ("soft_bessel" = its basis="bessel")
+_BASIS = {"bessel": 0, "gaussian": 1, "cosine": 2, "smooth_finite": 3, "fourier": 4, "soft_bessel": 5}
+_ENVELOPE = {None: 0, "smooth_cutoff": 1}
 
 
 class _EdgeEmbedFunction(torch.autograd.Function):
     last_status = None   # device status word of the most recent forward launch
 
     @staticmethod
-    def forward(ctx, pos, edge_src, edge_dst, shift, w0, r_max, w_scale, act_scale, act):
+    def forward(ctx, pos, edge_src, edge_dst, shift, w0, spec, w_scale, act_scale, act):
         E, N = edge_src.numel(), pos.shape[0]
         nb, hidden = w0.shape
         edge_vec = torch.empty(E, 3, dtype=torch.float32, device=pos.device)
@@ -29,18 +32,18 @@ class _EdgeEmbedFunction(torch.autograd.Function):
         with torch.cuda.device(pos.device):
             rc = _lib.core().e3b_radial_embed_fwd(
                 _lib._ptr(pos), _lib._ptr(edge_src), _lib._ptr(edge_dst), _lib._ptr(shift) if shift is not None else None,
-                _lib._ptr(w0), E, N, nb, hidden, r_max, w_scale, act_scale, act, _lib._ptr(edge_vec), _lib._ptr(h),
+                _lib._ptr(w0), E, N, nb, hidden, *spec, w_scale, act_scale, act, _lib._ptr(edge_vec), _lib._ptr(h),
                 _lib._ptr(status), _lib.stream_ptr())
         _lib.check(rc, "e3b_radial_embed_fwd")
         ctx.save_for_backward(pos, edge_src, edge_dst, shift if shift is not None else torch.empty(0), w0)
-        ctx.meta = (shift is not None, r_max, w_scale, act_scale, act)
+        ctx.meta = (shift is not None, spec, w_scale, act_scale, act)
         _EdgeEmbedFunction.last_status = status
         return edge_vec, h
 
     @staticmethod
     def backward(ctx, grad_vec, grad_h):
         pos, edge_src, edge_dst, shift, w0 = ctx.saved_tensors
-        has_shift, r_max, w_scale, act_scale, act = ctx.meta
+        has_shift, spec, w_scale, act_scale, act = ctx.meta
         if ctx.needs_input_grad[4]:
             raise NotImplementedError("the fused edge embedding has no gradient w.r.t. the first-layer weights")
         E, N = edge_src.numel(), pos.shape[0]
@@ -53,15 +56,21 @@ class _EdgeEmbedFunction(torch.autograd.Function):
             rc = _lib.core().e3b_radial_embed_bwd(
                 _lib._ptr(pos), _lib._ptr(edge_src), _lib._ptr(edge_dst), _lib._ptr(shift) if has_shift else None,
                 _lib._ptr(w0), _lib._ptr(grad_h.contiguous()), _lib._ptr(grad_vec.contiguous()) if grad_vec is not None else None,
-                E, N, nb, hidden, r_max, w_scale, act_scale, act, _lib._ptr(grad_pos), _lib._ptr(status), _lib.stream_ptr())
+                E, N, nb, hidden, *spec, w_scale, act_scale, act, _lib._ptr(grad_pos), _lib._ptr(status), _lib.stream_ptr())
         _lib.check(rc, "e3b_radial_embed_bwd")
         return grad_pos, None, None, None, None, None, None, None, None
 
 
 def edge_embed(pos: torch.Tensor, edge_src: torch.Tensor, edge_dst: torch.Tensor, shift: Optional[torch.Tensor],
                w0: torch.Tensor, r_max: float, w_scale: float, act_scale: float, act: Optional[str],
-               check_indices: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
-    """``(edge_vec [E,3], h [E,hidden])`` with ``h = act_scale * act(w_scale * bessel(|edge_vec|) @ w0)``.
+               check_indices: bool = False, basis: str = "bessel", cutoff: bool = True, start: float = 0.0,
+               basis_scale: float = 1.0, envelope: Optional[str] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``(edge_vec [E,3], h [E,hidden])`` with ``h = env(r) * act_scale * act(w_scale * B(r) @ w0)``, ``r = |edge_vec|``.
+
+    ``basis="bessel"``: ``B = e3nn.math.bessel(r, num_basis, r_max)``; ``"gaussian" | "cosine" | "smooth_finite" |
+    "fourier" | "soft_bessel"``: ``B = basis_scale * soft_one_hot_linspace(r, start, r_max, num_basis, basis, cutoff)``
+    (``e3nn/math/_soft_one_hot_linspace.py``; ``"soft_bessel"`` is its ``basis="bessel"``).  ``envelope="smooth_cutoff"``
+    multiplies ``h`` by ``smooth_cutoff(r / r_max)`` (``gate_points_2101.py:136-141``).
 
     ``w0`` is ``[num_basis <= 16, hidden in {32, 64, 96, 128}]``.  With ``check_indices`` the device status word
     is read back (a synchronisation) and an index outside the node range raises ``IndexError``.
@@ -74,13 +83,18 @@ def edge_embed(pos: torch.Tensor, edge_src: torch.Tensor, edge_dst: torch.Tensor
         raise NotImplementedError("edge_embed computes in float32")
     if edge_src.dtype != torch.int64 or edge_dst.dtype != torch.int64:
         raise TypeError("edge_src and edge_dst must be int64")
+    if basis not in _BASIS:
+        raise ValueError(f'basis="{basis}" is not a valid entry')
+    if envelope not in _ENVELOPE:
+        raise ValueError(f"unknown envelope {envelope!r}")
     nb, hidden = w0.shape
     if nb > 16 or hidden not in (32, 64, 96, 128):
         raise NotImplementedError("edge_embed: num_basis <= 16 and hidden in {32, 64, 96, 128}")
+    spec = (_BASIS[basis], int(bool(cutoff)), _ENVELOPE[envelope], float(start), float(r_max), float(basis_scale))
     shift_c = shift.contiguous().float() if shift is not None else None
     vec, h = _EdgeEmbedFunction.apply(pos.contiguous(), edge_src.contiguous(), edge_dst.contiguous(), shift_c,
                                       w0.detach().contiguous() if not w0.requires_grad else w0.contiguous(),
-                                      float(r_max), float(w_scale), float(act_scale), _ACT[act])
+                                      spec, float(w_scale), float(act_scale), _ACT[act])
     if check_indices:
         if int(_EdgeEmbedFunction.last_status.item()) == 2:
             raise IndexError("edge_embed: an edge index lies outside the node range")

@@ -122,10 +122,15 @@ int e3b_neighbor_fill(const float* pos, int64_t num_atoms, double box, double cu
 /*
  * Edge embedding of an interaction block, one kernel per direction:
  *   edge_vec[e] = pos[src[e]] - pos[dst[e]] + shift[e]        (e3nn/nn/models/gate_points_2101.py:328)
- *   B[e,k]      = sqrt(2/r_max) sin(k pi r / r_max) / r, k = 1..num_basis, r = |edge_vec[e]|
- *                                                             (e3nn/math/_bessel.py:6-37)
- *   h[e,:]      = act_scale * act(w_scale * B[e,:] @ w0)      (first layer of FullyConnectedNet,
- *                                                              e3nn/nn/_fc.py:38-48 and :70-88)
+ *   B[e,k]      = basis_scale * basis_k(r), r = |edge_vec[e]|, k = 1..num_basis, with
+ *                 basis 0: e3nn.math.bessel(r, num_basis, end)            (e3nn/math/_bessel.py:6-37; start = 0)
+ *                 basis 1..5: soft_one_hot_linspace(r, start, end, num_basis, 'gaussian' | 'cosine' |
+ *                             'smooth_finite' | 'fourier' | 'bessel', cutoff)
+ *                                                             (e3nn/math/_soft_one_hot_linspace.py:100-140)
+ *   h[e,:]      = env(r) * act_scale * act(w_scale * B[e,:] @ w0)   (first layer of FullyConnectedNet,
+ *                 e3nn/nn/_fc.py:38-48 and :70-88); envelope 0: env = 1, envelope 1: env = smooth_cutoff(r / end)
+ *                 (e3nn/nn/models/gate_points_2101.py:136-141; scaling h scales the network's linear output,
+ *                 i.e. the per-edge weights, which is where those models apply it through the edge attributes)
  * pos [num_nodes,3]; edge_src, edge_dst [num_edges] int64; shift [num_edges,3] or NULL; w0 row-major
  * [num_basis, hidden]; num_basis <= 16; hidden in {32, 64, 96, 128}; act: 0 silu, 1 tanh, 2 relu, 3 identity.
  * Outputs edge_vec [num_edges,3] and h [num_edges,hidden].  An index outside [0, num_nodes) sets *status = 2
@@ -136,12 +141,14 @@ int e3b_neighbor_fill(const float* pos, int64_t num_atoms, double box, double cu
  * zeroes it).  Replaces autograd through the same reference lines.
  */
 int e3b_radial_embed_fwd(const float* pos, const int64_t* edge_src, const int64_t* edge_dst, const float* shift,
-                         const float* w0, int64_t num_edges, int64_t num_nodes, int num_basis, int hidden, float r_max,
-                         float w_scale, float act_scale, int act, float* edge_vec, float* h, int32_t* status, void* stream);
+                         const float* w0, int64_t num_edges, int64_t num_nodes, int num_basis, int hidden, int basis,
+                         int cutoff, int envelope, float start, float end, float basis_scale, float w_scale,
+                         float act_scale, int act, float* edge_vec, float* h, int32_t* status, void* stream);
 int e3b_radial_embed_bwd(const float* pos, const int64_t* edge_src, const int64_t* edge_dst, const float* shift,
                          const float* w0, const float* grad_h, const float* grad_edge_vec, int64_t num_edges,
-                         int64_t num_nodes, int num_basis, int hidden, float r_max, float w_scale, float act_scale, int act,
-                         float* grad_pos, int32_t* status, void* stream);
+                         int64_t num_nodes, int num_basis, int hidden, int basis, int cutoff, int envelope, float start,
+                         float end, float basis_scale, float w_scale, float act_scale, int act, float* grad_pos,
+                         int32_t* status, void* stream);
 
 /*
  * Gate non-linearity on rows (e3nn/nn/_gate.py:127-144: Extract, two Activations of

@@ -7,6 +7,7 @@ is replaced by an identity stand-in before ``import e3nn``.
 
     python tests/golden/make_golden.py              (everything)
     python tests/golden/make_golden.py --only-gate  (only the Gate cases, leaving the other files untouched)
+    python tests/golden/make_golden.py --only-radial-bases
 
 Every case stores its fp32 inputs and the reference's fp64 output on those inputs
 (inputs upcast to fp64), plus the reference's own fp32 output for context.  The files
@@ -85,7 +86,31 @@ def gate_cases(meta):
                                "irreps_gated": gd, "irreps_in": str(g.irreps_in), "irreps_out": str(g.irreps_out)}
 
 
+def radial_basis_cases(meta):
+    """soft_one_hot_linspace for every basis / cutoff flag and smooth_cutoff, on seeded radii in (0, 6)."""
+    from e3nn.math import soft_one_hot_linspace
+    from e3nn.nn.models.gate_points_2101 import smooth_cutoff
+
+    gen = torch.Generator().manual_seed(4321)
+    r = torch.rand(64, generator=gen, dtype=torch.float64) * 6.0 + 1e-3
+    out = {"r": _np(r), "smooth_cutoff": _np(smooth_cutoff(r / 5.0))}
+    for basis in ("gaussian", "cosine", "smooth_finite", "fourier", "bessel"):
+        for cutoff in (False, True):
+            out[f"{basis}_{int(cutoff)}"] = _np(soft_one_hot_linspace(r, 0.5, 5.0, 8, basis=basis, cutoff=cutoff))
+    np.savez_compressed(os.path.join(HERE, "radial_bases.npz"), **out)
+    meta["cases"]["radial_bases"] = {"start": 0.5, "end": 5.0, "number": 8}
+
+
 def main():
+    if "--only-radial-bases" in sys.argv:
+        _import_reference()
+        with open(os.path.join(HERE, "meta.json")) as f:
+            meta = json.load(f)
+        radial_basis_cases(meta)
+        with open(os.path.join(HERE, "meta.json"), "w") as f:
+            json.dump(meta, f, indent=1)
+        print("radial basis golden vectors written to", HERE)
+        return
     if "--only-gate" in sys.argv:
         _import_reference()
         with open(os.path.join(HERE, "meta.json")) as f:
@@ -275,6 +300,7 @@ def main():
     }
 
     gate_cases(meta)
+    radial_basis_cases(meta)
 
     with open(os.path.join(HERE, "meta.json"), "w") as f:
         json.dump(meta, f, indent=1)

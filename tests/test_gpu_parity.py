@@ -608,6 +608,41 @@ def test_edge_embed_matches_fp64_chain(act, hidden, nb, with_shift):
     assert v0.shape == (0, 3) and h0.shape == (0, hidden)
 
 
+@pytest.mark.parametrize("basis,cutoff,envelope", [("gaussian", True, None), ("gaussian", False, "smooth_cutoff"),
+                                                   ("cosine", True, None), ("smooth_finite", True, "smooth_cutoff"),
+                                                   ("smooth_finite", False, None), ("fourier", True, None),
+                                                   ("fourier", False, None), ("soft_bessel", True, "smooth_cutoff"),
+                                                   ("soft_bessel", False, None)])
+def test_edge_embed_basis_families(basis, cutoff, envelope):
+    """The soft_one_hot_linspace families and the smooth_cutoff envelope in the fused edge embedding against the
+    oracle's restatement of e3nn/math/_soft_one_hot_linspace.py:100-140 / gate_points_2101.py:136-141 in fp64,
+    values and position gradient (radii span both sides of the cutoff)."""
+    from e3nn_b200 import nn as bnn
+
+    torch.manual_seed(17)
+    N, E, nb, hidden, start, end = 200, 3000, 8, 64, 0.5, 5.0
+    pos = torch.rand(N, 3) * 5.5
+    src, dst = torch.randint(0, N, (E,)), torch.randint(0, N, (E,))
+    dst = torch.where(dst == src, (dst + 1) % N, dst)          # no zero-length edges: soft bessel is 0/0 there
+    w0 = torch.randn(nb, hidden)
+    w_scale, act_scale, bscale = nb ** -0.5, bnn.normalize2mom_constant("silu"), nb ** 0.5
+    gh, gv = torch.randn(E, hidden), torch.randn(E, 3)
+    p64 = pos.double().requires_grad_(True)
+    vec64 = p64[src] - p64[dst]
+    r = vec64.norm(dim=-1)
+    B = bscale * orc.soft_one_hot_linspace(r, start, end, nb, "bessel" if basis == "soft_bessel" else basis, cutoff)
+    h64 = act_scale * torch.nn.functional.silu(B @ (w0.double() * w_scale))
+    if envelope is not None:
+        h64 = h64 * orc.smooth_cutoff(r / end)[:, None]
+    ((h64 * gh.double()).sum() + (vec64 * gv.double()).sum()).backward()
+    p = pos.clone().to(DEV).requires_grad_(True)
+    vec, h = bnn.edge_embed(p, src.to(DEV), dst.to(DEV), None, w0.to(DEV), end, w_scale, act_scale, "silu", basis=basis,
+                            cutoff=cutoff, start=start, basis_scale=bscale, envelope=envelope)
+    ((h * gh.to(DEV)).sum() + (vec * gv.to(DEV)).sum()).backward()
+    assert rel_err(h.detach().cpu(), h64.detach()) < TOL
+    assert rel_err(p.grad.cpu(), p64.grad) < 2e-5
+
+
 # ----------------------------------------------------------------------------- tensor-core contractions with split operands
 TOL_TF32X3 = 1e-4   # hi/lo-split tf32 operands: measured 1e-5 .. 4e-5 x RMS on these layouts
 

@@ -122,3 +122,14 @@ def test_gate(golden, golden_meta, name):
     x = torch.from_numpy(g["x"]).double()
     out = orc.gate(m["irreps_scalars"], m["act_scalars"], m["irreps_gates"], m["act_gates"], m["irreps_gated"], x)
     assert rel_err(out, torch.from_numpy(g["out_f64"])) < 1e-12
+
+
+def test_radial_bases(golden, golden_meta):
+    """soft_one_hot_linspace (all bases, both cutoff flags) and smooth_cutoff against the reference's values."""
+    g, m = golden("radial_bases"), golden_meta["cases"]["radial_bases"]
+    r = torch.from_numpy(g["r"])
+    assert rel_err(orc.smooth_cutoff(r / 5.0), torch.from_numpy(g["smooth_cutoff"])) < 1e-13
+    for basis in ("gaussian", "cosine", "smooth_finite", "fourier", "bessel"):
+        for cutoff in (False, True):
+            out = orc.soft_one_hot_linspace(r, m["start"], m["end"], m["number"], basis, cutoff)
+            assert rel_err(out, torch.from_numpy(g[f"{basis}_{int(cutoff)}"])) < 1e-12, (basis, cutoff)
