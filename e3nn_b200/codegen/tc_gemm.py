@@ -278,11 +278,11 @@ def matmul_gemm_spec(k: int, n: int, transpose: bool, scale: float, key: str) ->
     for g in groups:
         g.has_y = False
         g.aligned_out = d_out % 4 == 0 and g.out_off % 4 == 0
-        g.plain = d_in % 4 == 0
-    if any(g.nstage() < 2 for g in groups):
+        g.plain = d_in % 4 == 0     # rows can be moved 16 bytes at a time (and described by a tensor map)
+    if any(g.nstage() < 2 for g in groups) or not all(g.plain for g in groups):
         return None
     return GemmSpec(d_in, 0, d_out, groups, key, f"matmul{'^T' if transpose else ''} [{k} x {n}] scale {scale!r}",
-                    producer_warps=16 if transpose else 8, tma_a=all(g.plain for g in groups))
+                    producer_warps=16 if transpose else 8, tma_a=True)
 
 
 # ------------------------------------------------------------------------------------------- emission
@@ -479,77 +479,6 @@ for (int q = 0; q < {qn}; ++q) {{{{
                 __syncwarp();
                 if (lane == 0) tc::mbar_arrive(&bar_full[s]);
             }}
-        }}
-"""
-        elif g.plain:
-            assert g.dim == 1 and g.zt == 128 and 128 % (4 * PRODUCER_WARPS) == 0 and not has_y
-            RPW = 128 // PRODUCER_WARPS      # rows of the tile per producer warp
-            NJ = RPW // 4                    # 16-byte loads per lane and chunk
-            B = 2 if (nch % 2 == 0 and g.nstage() >= 4) else 1     # chunks per step (loaded together, one step ahead)
-            ld = lambda dst, ptr, c: "\n".join(
-                f"{dst}[{j}] = *reinterpret_cast<const float4*>({ptr}[{j}] + kXOff{gi}[{c}]);" for j in range(NJ))
-            loads_first = "\n".join(ld(f"cur{b}", "xp", f"{b}") for b in range(B))
-            loads_same = "\n".join(ld(f"nxt{b}", "xp", f"c + {B + b}") for b in range(B))
-            loads_next = "\n".join(ld(f"nxt{b}", "xq", f"{b}") for b in range(B))
-            steps = []
-            for b in range(B):
-                steps.append(f"""{{
-    const int s = (it + {b}) % NSTAGE;
-    uint8_t* stage = sS + s * STAGE_BYTES;
-{_indent(issue_b('stage', '&bar_full[s]', f'(c + {b})'), 4)}
-#pragma unroll
-    for (int j = 0; j < {NJ}; ++j) tc::split_store4<A_TILE>(cur{b}[j], stage + po[j], pieces);
-    tc::fence_proxy_async_smem();
-    __syncwarp();
-    if (lane == 0) tc::mbar_arrive(&bar_full[s]);
-}}""")
-            waits = "\n".join(
-                f"if (!tc::mbar_wait(&bar_empty[(it + {b}) % NSTAGE], (((it + {b}) / NSTAGE) & 1) ^ 1u, abort_flag)) {{ ok = false; break; }}"
-                for b in range(B))
-            rotate = "\n".join(f"for (int j = 0; j < {NJ}; ++j) cur{b}[j] = nxt{b}[j];" for b in range(B))
-            decl = ", ".join(f"cur{b}[{NJ}], nxt{b}[{NJ}]" for b in range(B))
-            PRODUCER_BLOCK = f"""        // rows of A are the input rows: a lane moves 16 bytes (4 consecutive K) of one row, 8 lanes one 128-byte
-        // row segment; a warp owns {RPW} consecutive rows of the tile.  The loads of the next step (next chunks of
-        // this tile or the first chunks of the CTA's next tile) are in flight while this step is converted.
-        uint32_t po[{NJ}];
-        const int pc4 = lane & 7;
-#pragma unroll
-        for (int j = 0; j < {NJ}; ++j) {{
-            const int r = pw * {RPW} + 4 * j + (lane >> 3);
-            po[j] = (r >> 3) * 1024 + (r & 7) * 128 + ((pc4 ^ (r & 7)) << 4);
-        }}
-        auto row_ptrs = [&](int64_t t, const float* (&xp)[{NJ}]) {{
-#pragma unroll
-            for (int j = 0; j < {NJ}; ++j) {{
-                int64_t z = t * ZT + pw * {RPW} + 4 * j + (lane >> 3);
-                if (z >= Z) z = Z - 1;            // rows past the end read the last row (their output is not stored)
-                xp[j] = x1 + z * {d1} + 4 * pc4;
-            }}
-        }};
-        float4 {decl};
-        const float* xp[{NJ}];
-        const float* xq[{NJ}];
-        if (cta < tiles) {{
-            row_ptrs(cta, xp);
-{_indent(loads_first, 12)}
-        }}
-        for (int64_t t = cta; t < tiles && ok; t += nctas) {{
-            const bool more = t + nctas < tiles;
-            if (more) row_ptrs(t + nctas, xq);
-            for (int c = 0; c < NCHUNK; c += {B}, it += {B}) {{
-                if (c + {B} < NCHUNK) {{
-{_indent(loads_same, 20)}
-                }} else if (more) {{
-{_indent(loads_next, 20)}
-                }}
-                asm volatile("" ::: "memory");   // the next step's loads are issued before anything below
-{_indent(waits, 16)}
-{_indent(chr(10).join(steps), 16)}
-#pragma unroll
-{_indent(rotate, 16)}
-            }}
-#pragma unroll
-            for (int j = 0; j < {NJ}; ++j) xp[j] = xq[j];
         }}
 """
         else:

@@ -158,26 +158,6 @@ __device__ __forceinline__ float to_tf32(float x) {
     return __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xFFFFE000u);
 }
 
-// Four consecutive K of one operand row -> tf32 pieces, stored as one 16-byte chunk per piece (the second
-// piece's tile lies TILE bytes after the first).  One piece: round to nearest.  Two pieces: hi = the value
-// with the low 13 mantissa bits cleared (one operation; x - hi is exact), lo = x - hi rounded to tf32, so
-// hi + lo carries 21 mantissa bits of x.
-template <uint32_t TILE>
-__device__ __forceinline__ void split_store4(float4 v, uint8_t* dst, int pieces) {
-    if (pieces == 1) {
-        *reinterpret_cast<float4*>(dst) = make_float4(to_tf32(v.x), to_tf32(v.y), to_tf32(v.z), to_tf32(v.w));
-    } else {
-        float4 hi;
-        hi.x = __uint_as_float(__float_as_uint(v.x) & 0xFFFFE000u);
-        hi.y = __uint_as_float(__float_as_uint(v.y) & 0xFFFFE000u);
-        hi.z = __uint_as_float(__float_as_uint(v.z) & 0xFFFFE000u);
-        hi.w = __uint_as_float(__float_as_uint(v.w) & 0xFFFFE000u);
-        *reinterpret_cast<float4*>(dst) = hi;
-        *reinterpret_cast<float4*>(dst + TILE) =
-            make_float4(to_tf32(v.x - hi.x), to_tf32(v.y - hi.y), to_tf32(v.z - hi.z), to_tf32(v.w - hi.w));
-    }
-}
-
 // lo pieces of four raw fp32 values whose hi pieces are the values themselves (the tensor core reads only
 // sign, exponent and the top 10 mantissa bits of a tf32 operand): lo = x - trunc(x), rounded to tf32
 __device__ __forceinline__ float4 lo_piece4(float4 v) {

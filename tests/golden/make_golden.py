@@ -1,7 +1,7 @@
 """Generate the golden vectors in this folder by running the reference e3nn itself.
 
-Run where the e3nn 0.6.0 sources are importable (``E3NN_REFERENCE`` environment
-variable, default ``/root/reference``).  The only missing dependency of the reference,
+Run where the e3nn 0.6.0 sources are available: the ``E3NN_REFERENCE`` environment variable
+names the directory that contains the ``e3nn`` package.  The only missing dependency of the reference,
 ``opt_einsum_fx`` (a contraction-order optimiser that does not change the mathematics),
 is replaced by an identity stand-in before ``import e3nn``.
 
@@ -29,7 +29,10 @@ def _import_reference():
     stub.optimize_einsums_full = lambda model, example_inputs, **kw: model
     stub.jitable = lambda gm: gm
     sys.modules["opt_einsum_fx"] = stub
-    sys.path.insert(0, os.environ.get("E3NN_REFERENCE", "/root/reference"))
+    ref = os.environ.get("E3NN_REFERENCE")
+    if not ref:
+        raise SystemExit("set E3NN_REFERENCE to the directory that contains the e3nn package")
+    sys.path.insert(0, ref)
     import e3nn  # noqa: F401
     from e3nn import o3
 

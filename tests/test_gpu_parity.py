@@ -486,6 +486,56 @@ def test_interaction_block_forward_and_position_gradient(irreps, lmax):
     assert rel_err(p2.grad.cpu(), p64.grad) < 1e-4
 
 
+# ----------------------------------------------------------------------------- two interaction blocks with a Gate between them
+@pytest.mark.parametrize("mode", ["fp32", "tf32x3"])
+def test_two_layer_network_forward_and_gradients(mode):
+    """block -> Gate -> block, the composition of gate_points_2101.py:275-334: output, gradient w.r.t. the positions
+    (through both blocks) and w.r.t. the input features (through the convolution's node-feature gradient, the Gate
+    and both Linears) against the same chain evaluated by the oracle in fp64."""
+    from e3nn_b200 import nn as bnn
+
+    torch.manual_seed(23)
+    n_atoms = 400
+    box = (n_atoms / 0.05) ** (1 / 3)
+    pos = torch.rand(n_atoms, 3) * box
+    src, dst, shift, rowptr = bnn.neighbor_list_pbc(pos.to(DEV), box, 5.0)
+    nn_avg = src.numel() / n_atoms
+    node, gate_in = "16x0e+16x1o+16x2e", "48x0e+16x1o+16x2e"
+    kw = dict(num_basis=8, hidden=64, r_max=5.0, num_neighbors=nn_avg, linear_math_mode=mode, radial_math_mode=mode)
+    b1 = bnn.InteractionBlock(node, 2, irreps_out=gate_in, **kw).to(DEV)
+    gate = bnn.Gate("16x0e", [torch.nn.functional.silu], "32x0e", [torch.sigmoid], "16x1o+16x2e").to(DEV)
+    b2 = bnn.InteractionBlock(node, 2, **kw).to(DEV)
+    assert str(gate.irreps_in) == gate_in and str(gate.irreps_out) == node
+    for m in (b1, b2):
+        for prm in m.parameters():
+            prm.requires_grad_(False)
+    x = torch.randn(n_atoms, b1.irreps_node.dim)
+    G = torch.randn(n_atoms, b2.irreps_out.dim)
+    p = pos.clone().to(DEV).requires_grad_(True)
+    xg = x.clone().to(DEV).requires_grad_(True)
+    h = gate(b1(p, xg, src, dst, rowptr, shift))
+    out = b2(p, h, src, dst, rowptr, shift)
+    (out * G.to(DEV)).sum().backward()
+
+    p64, x64 = pos.double().requires_grad_(True), x.double().requires_grad_(True)
+    srcc, dstc, shiftc = src.cpu(), dst.cpu(), shift.cpu().double()
+
+    def oracle_block(b, feats):
+        tp = b.tp
+        return orc.interaction_block(
+            str(tp.irreps_in1), str(tp.irreps_in2), str(tp.irreps_out), _ins(tp), str(b.irreps_out), p64, feats, srcc, dstc,
+            shiftc, [b.fc.layer0.weight.detach().cpu().double(), b.fc.layer1.weight.detach().cpu().double()],
+            b.lin.weight.detach().cpu().double(), 8, 5.0, nn_avg, [0, 1, 2], chunk=4096)
+
+    h64 = orc.gate("16x0e", ["silu"], "32x0e", ["sigmoid"], "16x1o+16x2e", oracle_block(b1, x64))
+    ref = oracle_block(b2, h64)
+    (ref * G.double()).sum().backward()
+    tol = 3e-5 if mode == "fp32" else 2e-4      # two blocks deep: twice the single-block budget
+    assert rel_err(out.detach().cpu(), ref.detach()) < tol
+    assert rel_err(xg.grad.cpu(), x64.grad) < tol
+    assert rel_err(p.grad.cpu(), p64.grad) < 2 * tol
+
+
 # ----------------------------------------------------------------------------- device neighbour list (cell list)
 @pytest.mark.parametrize("n_atoms,inside", [(2000, True), (5000, False), (40, True)])
 def test_neighbor_list_matches_kdtree(n_atoms, inside):
