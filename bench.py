@@ -512,20 +512,20 @@ def run_interaction(args, rank, world, device):
     del gw, gvec, gout, out_mid, w
     torch.cuda.empty_cache()
 
-    # ---- end to end: positions, features and graph from pinned host memory, gradient back to the host
+    # ---- end to end: positions and features from pinned host memory, neighbour list built on the device from the
+    # uploaded positions every step (as a simulation whose atoms move would), gradient back to the host.  The rank's
+    # row and edge ranges are those of the set-up partition (the positions do not change between steps).
     e2e = None
     if not args.skip_e2e:
-        host = {"pos": pos_host.pin_memory(), "x": node_x_host[n0:n1].contiguous().pin_memory(),
-                "src": src[e0:e1].contiguous().pin_memory(), "dst": dst[e0:e1].contiguous().pin_memory(),
-                "shift": shift[e0:e1].contiguous().pin_memory(), "rowptr": rowptr_local.pin_memory()}
+        host = {"pos": pos_host.pin_memory(), "x": node_x_host[n0:n1].contiguous().pin_memory()}
         grad_host = torch.empty(n_atoms, 3).pin_memory()
 
         copy_stream = torch.cuda.Stream(device=device)
         x_dev = torch.empty(n1 - n0, 1024, device=device)
 
         def e2e_step():
-            # the graph and the positions are needed first: main stream.  The feature rows (the bulk of the bytes) are
-            # not read before the convolution: their upload (and, sharded, the all-gather that follows it) runs on a
+            # the positions are needed first (neighbour list, edge embedding): main stream.  The feature rows (the bulk
+            # of the bytes) are not read before the convolution: their upload (and, sharded, the all-gather that follows it) runs on a
             # second stream under the edge embedding and the radial layer
             main = torch.cuda.current_stream()
             copy_stream.wait_stream(main)            # x_dev's previous reader (last step's kernels) is done
@@ -538,15 +538,18 @@ def run_interaction(args, rank, world, device):
                     xs = x_full
                 uploaded = torch.cuda.Event()
                 uploaded.record(copy_stream)
-            d = {k: v.to(device, non_blocking=True) for k, v in host.items() if k != "x"}
+            pos_up = host["pos"].to(device, non_blocking=True)
+            s_all, d_all, sh_all, rp_all = bnn.neighbor_list_pbc(pos_up, box, 5.0)
+            s_loc, d_loc, sh_loc = s_all[e0:e1], d_all[e0:e1], sh_all[e0:e1]
+            rp_loc = rp_all[n0:n1 + 1] - rp_all[n0:n0 + 1]
 
             def wait():
                 torch.cuda.current_stream().wait_event(uploaded)
                 if gather_wait is not None:
                     gather_wait()
 
-            p = d["pos"].requires_grad_(True)
-            (block(p, xs, d["src"], d["dst"], d["rowptr"], d["shift"], before_conv=wait) * G).sum().backward()
+            p = pos_up.requires_grad_(True)
+            (block(p, xs, s_loc, d_loc, rp_loc, sh_loc, before_conv=wait) * G).sum().backward()
             if world > 1:
                 torch.distributed.all_reduce(p.grad)
             grad_host.copy_(p.grad, non_blocking=True)
