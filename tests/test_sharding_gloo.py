@@ -47,6 +47,12 @@ def _worker(rank, world, port, out_dir):
     n0, n1, e0, e1, rp = sharding.local_shard(g["rowptr"], bounds, rank)
     x_full = sharding.all_gather_rows(g["x"][n0:n1].clone(), bounds)   # each rank owns only its rows
     assert torch.equal(x_full, g["x"])
+    # asynchronous form: work may be enqueued between the call and wait(); the result is complete after wait()
+    out = torch.full_like(g["x"], float("nan"))
+    same, wait = sharding.all_gather_rows(g["x"][n0:n1].clone(), bounds, out=out, async_op=True)
+    assert same is out
+    wait()
+    assert torch.equal(out, g["x"])
     local = _conv(g, x_full, g["src"][e0:e1], g["dst"][e0:e1] - n0, g["vec"][e0:e1], g["w"][e0:e1], n1 - n0)
     torch.save((bounds, n0, n1, e0, e1, rp, local), os.path.join(out_dir, f"r{rank}.pt"))
     dist.barrier()
