@@ -268,7 +268,18 @@ __global__ void __launch_bounds__(kEmbedWarps * 32) radial_embed_bwd_kernel(
         }
         __syncwarp();
         const int count = static_cast<int>(num_edges - b * 32 < 32 ? num_edges - b * 32 : 32);
+        // cotangent rows are read one edge ahead of their use: the load of edge i + 1 is in flight during edge i
+        float gh_next[H2];
+#pragma unroll
+        for (int j = 0; j < H2; ++j) gh_next[j] = count > 0 ? grad_h[(b * 32) * H + lane + 32 * j] : 0.0f;
         for (int i = 0; i < count; ++i) {
+            float gh_cur[H2];
+#pragma unroll
+            for (int j = 0; j < H2; ++j) gh_cur[j] = gh_next[j];
+            if (i + 1 < count) {
+#pragma unroll
+                for (int j = 0; j < H2; ++j) gh_next[j] = grad_h[(b * 32 + i + 1) * H + lane + 32 * j];
+            }
             float pre[H2];
 #pragma unroll
             for (int j = 0; j < H2; ++j) pre[j] = 0.0f;
@@ -280,7 +291,6 @@ __global__ void __launch_bounds__(kEmbedWarps * 32) radial_embed_bwd_kernel(
                     for (int j = 0; j < H2; ++j) pre[j] = fmaf(bk, w[k][j], pre[j]);
                 }
             }
-            const float* grow = grad_h + (b * 32 + i) * H;
             float cot[NB];
 #pragma unroll
             for (int k = 0; k < NB; ++k) cot[k] = 0.0f;
@@ -288,7 +298,7 @@ __global__ void __launch_bounds__(kEmbedWarps * 32) radial_embed_bwd_kernel(
             float genv = 0.0f;
 #pragma unroll
             for (int j = 0; j < H2; ++j) {
-                const float gh = grow[lane + 32 * j];
+                const float gh = gh_cur[j];
                 if (sp.envelope) genv = fmaf(gh * act_scale, act_fwd(act, pre[j]), genv);
                 const float dpre = gh * (envi * act_scale) * act_grad(act, pre[j]);
 #pragma unroll
