@@ -105,7 +105,10 @@ class Group:
         return self.resident_bytes() + self.nstage() * self.stage_bytes() + self.extra_bytes() + 1024 + 1024
 
     def work(self) -> int:
+        # per 128-row tile: the producers' chunks plus the epilogue (tensor-memory loads and stores of N columns per
+        # row; the dominant term of short-K groups)
         per_tile = sum(40 + self.case_cost[c.case] * max(1, -(-self.zt // PRODUCER_WARPS)) for c in self.chunks)
+        per_tile += 4 * self.n
         return max(1, int(1000 * per_tile / self.zt))
 
 
