@@ -486,6 +486,21 @@ def test_interaction_block_forward_and_position_gradient(irreps, lmax):
     assert rel_err(p2.grad.cpu(), p64.grad) < 1e-4
 
 
+# ----------------------------------------------------------------------------- self-connection with node attributes
+@pytest.mark.parametrize("mode", ["fp32", "tf32x3"])
+def test_self_connection_with_node_attributes(mode):
+    """FullyConnectedTensorProduct(node, node_attr, node) with a multi-channel scalar second operand: the
+    self-connection / lin1 / lin2 of e3nn/nn/models/v2106/points_convolution.py:56-58,89-92 ('uvw', in2 = 4x0e)."""
+    torch.manual_seed(4)
+    node, attr = "32x0e+32x1o+16x2e", "4x0e"
+    tp = o3.FullyConnectedTensorProduct(node, attr, node, math_mode=mode).to(DEV)
+    x = torch.randn(333, tp.irreps_in1.dim)
+    a = torch.nn.functional.one_hot(torch.randint(0, 4, (333,)), 4).float()
+    out = tp(x.to(DEV), a.to(DEV))
+    ref = _oracle_tp(tp, x.double(), a.double(), tp.weight.detach().cpu().double())
+    assert rel_err(out.detach().cpu(), ref) < (TOL if mode == "fp32" else TOL_TF32X3)
+
+
 # ----------------------------------------------------------------------------- two interaction blocks with a Gate between them
 @pytest.mark.parametrize("mode", ["fp32", "tf32x3"])
 def test_two_layer_network_forward_and_gradients(mode):
