@@ -170,6 +170,8 @@ def run_ours(args):
         return run_uvw(args, rank, world, device)
     if args.workload == "interaction_l3":
         return run_interaction(args, rank, world, device)
+    if args.workload == "conv_train_l3_23":
+        return run_conv_train(args, rank, world, device)
     layout, nodes, degree = WORKLOADS[args.workload]
     if args.nodes > 0:
         nodes = args.nodes
@@ -366,6 +368,92 @@ def run_gate(args, rank, world, device):
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": None, "peak_kind": f"of {peak_kind}", "kernel": "gate_fwd_kernel"},
         "gpu_launches": args.steps,
+    }), flush=True)
+
+
+# DRAM bytes per edge of conv_bwd_x_tma_kernel (layout l3_23), ncu capture of this workload (65,536 nodes x 32 edges)
+NCU_CONV_BWD_X_L3_TRAFFIC_PER_EDGE = 13727
+
+
+def run_conv_train(args, rank, world, device):
+    """Fused convolution of a hidden layer in training: forward, then the gradients w.r.t. the per-edge weights,
+    the edge vectors and the node features (layout l3_23, 65,536 nodes x 32 incoming edges; one GPU, or N
+    independent replicas).  `roofline` is reported on the node-feature gradient kernel, timed alone."""
+    import e3nn_b200
+    from e3nn_b200 import _lib
+
+    layout, nodes, degree = WORKLOADS["conv_l3_23"]
+    if args.nodes > 0:
+        nodes = args.nodes
+    d = make_graph(layout, nodes, degree, 0, 1, device)
+    tp, E = d["tp"], nodes * degree
+    x = d["node_x_local"].requires_grad_(True)
+    w = d["w"].requires_grad_(True)
+    vec = d["vec"].requires_grad_(True)
+    g = torch.randn(nodes, tp.irreps_out.dim, device=device)
+    scale = degree ** -0.5
+
+    def step():
+        x.grad = w.grad = vec.grad = None
+        out = e3nn_b200.conv_uvu(tp, x, vec, d["src"], d["rowptr"], w, scale=scale, edge_attr_is_vector=True)
+        out.backward(g)
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", "0")))
+    if rank == 0:
+        sampler.start()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(args.steps):
+        step()
+    stop.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([start.elapsed_time(stop)], device=device)
+    clocks = sampler.stop() if rank == 0 else None
+    if world > 1:
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+    ms_step = t.item() / args.steps
+    # the node-feature gradient kernel alone, through the C ABI (the table is zeroed outside the events)
+    x.grad = w.grad = vec.grad = None
+    torch.cuda.empty_cache()
+    mod = tp._uvu_module()
+    gx = torch.empty(nodes, tp.irreps_in1.dim, device=device)
+    status = torch.zeros(1, dtype=torch.int32, device=device)
+    P = _lib._ptr
+    kernel_ms = []
+    for _ in range(max(3, min(args.steps, 10))):
+        gx.zero_()
+        start.record()
+        rc = mod.lib.e3b_conv_bwd_x(P(vec), 1, P(d["src"]), P(d["rowptr"]), None, P(w), P(g), P(gx), nodes, nodes, E, scale,
+                                    P(status), _lib.stream_ptr())
+        stop.record()
+        torch.cuda.synchronize()
+        if rc != 0 or int(status.item()) != 0:
+            raise RuntimeError("conv_bwd_x failed: rc %d status %d" % (rc, int(status.item())))
+        kernel_ms.append(start.elapsed_time(stop))
+    if rank != 0:
+        return
+    kernel_ms.sort()
+    k_ms = kernel_ms[len(kernel_ms) // 2]
+    peak, peak_kind = measured_peaks()
+    # per edge: the weight row, the vector, the source index, read + write of one gradient row; per node its cotangent
+    per_edge = 4 * tp.weight_numel + 12 + 8 + 8 * tp.irreps_in1.dim + 4 * tp.irreps_out.dim / degree
+    achieved = per_edge * E / (k_ms * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": "TP edges/sec (fused SH + uvu + scatter, forward + all gradients, fp32)",
+        "value": world * E / (ms_step * 1e-3), "unit": "edges/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "conv_train_l3_23", "nodes": nodes, "edges": E, "in_degree": degree,
+                   "layout": f"{tp.irreps_in1} x {tp.irreps_in2} -> {len(tp.instructions)} uvu paths",
+                   "parallelism": "replicas only" if world > 1 else "single GPU",
+                   "l2": "per-edge weights (%.1f GB) far larger than the 126 MB L2" % (4e-9 * tp.weight_numel * E)},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": NCU_CONV_BWD_X_L3_TRAFFIC_PER_EDGE * E, "peak_kind": f"of {peak_kind}",
+                     "kernel": "conv_bwd_x_tma_kernel", "kernel_ms": k_ms, "algorithmic_bytes_per_edge": per_edge},
+        "gpu_launches": args.steps * 3, "clocks": clocks,
     }), flush=True)
 
 
@@ -776,7 +864,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS) + ["sh_l3", "uvw_fctp", "interaction_l3", "gate"])
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS) + ["sh_l3", "uvw_fctp", "interaction_l3", "gate", "conv_train_l3_23"])
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--nodes", type=int, default=0, help="override the node count (smaller graphs for profiling)")
     ap.add_argument("--skip-e2e", action="store_true", help="profiling runs: skip the host-buffer leg")

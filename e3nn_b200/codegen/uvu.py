@@ -33,7 +33,7 @@ import numpy as np
 
 from ..o3._spec import TPSpec
 from ..o3._wigner import wigner_3j_numpy
-from . import uvu_tma, uvu_tma_bwd
+from . import uvu_tma, uvu_tma_bwd, uvu_tma_bwdx
 
 
 def _f(v: float) -> str:
@@ -336,6 +336,10 @@ def emit_module(spec: TPSpec) -> str:
     if b2:
         v2_kernel += b2["kernel"]
     b2_launch = b2["launch"] if b2 else ""
+    x2k = uvu_tma_bwdx.emit(L) if b2 else None
+    if x2k:
+        v2_kernel += x2k["kernel"]
+    x2_launch = x2k["launch"] if x2k else ""
 
     src = f"""// Generated by e3nn_b200/codegen/uvu.py -- do not edit.
 // layout: {spec.irreps_in1} (x) {spec.irreps_in2} -> {spec.irreps_out}, {len(L.paths)} 'uvu' paths, key {spec.key()}
@@ -677,6 +681,7 @@ extern "C" int e3b_conv_bwd_x(const float* x2, int in2_mode, const int64_t* edge
     if (num_nodes == 0 || num_edges == 0) return 0;
     if (!rowptr || !grad_out || !status || !x2 || !edge_src || (kWn > 0 && !w)) return e3b_layout_fail(-1, "conv_bwd_x: null pointer");
     if (in2_mode == 1 && kShLmax < 0) return e3b_layout_fail(-3, "conv_bwd_x: irreps_in2 is not Y^0..Y^L, pass rows instead");
+{x2_launch}
     const int64_t blocks = (num_nodes + kRowsPerBlock - 1) / kRowsPerBlock;
     const unsigned grid = static_cast<unsigned>(blocks < 148LL * 64 ? blocks : 148LL * 64);
     if (in2_mode == 1)

@@ -42,9 +42,10 @@ def eligible(layout) -> bool:
     return uvu_tma.eligible(layout) and layout.d2 <= 16
 
 
-def split_slots(layout) -> List[List]:
+def split_slots(layout, per_warp: int = 0) -> List[List]:
+    """Paths grouped by output slot into the fewest warps that hold ``per_warp`` cotangent registers each."""
     total = 2 * sum(layout.spec.irreps_out[io].ir.dim for io in layout.out_used)
-    T = max(1, -(-total // G_FLOATS_PER_WARP))
+    T = max(1, -(-total // (per_warp or G_FLOATS_PER_WARP)))
     if T == 1:
         return [list(layout.paths)]
     slots: Dict[int, List] = {}

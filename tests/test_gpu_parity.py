@@ -409,14 +409,25 @@ def test_conv_pipelined_kernel(layout):
     # gradients w.r.t. the per-edge weights and the edge vectors: pipelined kernel vs oracle autograd
     vg = vec.clone().to(DEV).requires_grad_(True)
     wg = w.clone().to(DEV).requires_grad_(True)
-    out_g = e3nn_b200.conv_uvu(tp, node_x.to(DEV), vg, src.to(DEV), rowptr.to(DEV), wg, scale=0.7, edge_attr_is_vector=True)
+    xg = node_x.clone().to(DEV).requires_grad_(True)
+    out_g = e3nn_b200.conv_uvu(tp, xg, vg, src.to(DEV), rowptr.to(DEV), wg, scale=0.7, edge_attr_is_vector=True)
     go = torch.randn(N, tp.irreps_out.dim)
     out_g.backward(go.to(DEV))
-    v64, w64 = vec.double().requires_grad_(True), w.double().requires_grad_(True)
-    ref_g = orc.conv_uvu(str(tp.irreps_in1), str(tp.irreps_in2), str(tp.irreps_out), _ins(tp), node_x.double(), v64, src, dst,
+    v64, w64, x64 = vec.double().requires_grad_(True), w.double().requires_grad_(True), node_x.double().requires_grad_(True)
+    ref_g = orc.conv_uvu(str(tp.irreps_in1), str(tp.irreps_in2), str(tp.irreps_out), _ins(tp), x64, v64, src, dst,
                          w64, N, list(range(lmax + 1)), scale=0.7, chunk=2048)
     ref_g.backward(go.double())
     assert rel_err(wg.grad.cpu(), w64.grad) < TOL
+    # node-feature gradient: pipelined kernel vs oracle, and vs the direct-load kernel (atomics: not bitwise)
+    assert rel_err(xg.grad.cpu(), x64.grad) < TOL
+    mod.lib.e3b_conv_select(1)
+    try:
+        xs = node_x.clone().to(DEV).requires_grad_(True)
+        e3nn_b200.conv_uvu(tp, xs, vec.to(DEV), src.to(DEV), rowptr.to(DEV), w.to(DEV), scale=0.7,
+                           edge_attr_is_vector=True).backward(go.to(DEV))
+    finally:
+        mod.lib.e3b_conv_select(0)
+    assert rel_err(xg.grad.cpu(), xs.grad.cpu()) < TOL
     gv, gv_ref = vg.grad.cpu(), v64.grad.clone()
     gv[3] = 0.0      # the zero vector has an unbounded derivative under normalisation
     gv_ref[3] = 0.0
