@@ -66,6 +66,7 @@ def core() -> ctypes.CDLL:
         lib.e3b_csr_scratch_bytes.restype = c_int64
         lib.e3b_csr_from_dst.argtypes = [c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p]
         lib.e3b_dense_fwd.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int, c_void_p]
+        lib.e3b_dense_bwd_w.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p]
         lib.e3b_fill_columns.argtypes = [c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_int, c_void_p]
         spec = [c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_float, c_float, c_int]
         lib.e3b_radial_embed_fwd.argtypes = [c_void_p] * 5 + [c_int64, c_int64] + spec + [c_void_p, c_void_p, c_void_p, c_void_p]
@@ -77,7 +78,7 @@ def core() -> ctypes.CDLL:
                                           c_void_p, c_void_p, c_void_p]
         lib.e3b_gate_fwd.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]
         lib.e3b_gate_bwd.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]
-        for name in ("e3b_sh_fwd", "e3b_sh_bwd", "e3b_csr_from_dst", "e3b_dense_fwd", "e3b_fill_columns",
+        for name in ("e3b_sh_fwd", "e3b_sh_bwd", "e3b_csr_from_dst", "e3b_dense_fwd", "e3b_dense_bwd_w", "e3b_fill_columns",
                      "e3b_radial_embed_fwd", "e3b_radial_embed_bwd", "e3b_neighbor_count", "e3b_neighbor_fill",
                      "e3b_gate_fwd", "e3b_gate_bwd"):
             getattr(lib, name).restype = c_int

@@ -102,7 +102,8 @@ def uvw_plan(spec, instruction_ids: Optional[Sequence[int]] = None) -> Tuple[np.
 
 def linear_plan(irreps_in: Irreps, irreps_out: Irreps, instructions, transpose: bool = False) -> Tuple[np.ndarray, List[int]]:
     """Plan of a Linear (weight instructions only).  ``transpose``: the map from output
-    cotangents back to input cotangents (same weights, read with a stride)."""
+    cotangents back to input cotangents (same weights, read with a stride); a transposed plan may hold
+    several groups for one target and must be run with ``accumulate`` on zeroed rows."""
     oi, oo = irreps_in.offsets(), irreps_out.offsets()
     woff, offs = 0, []
     for ins in instructions:
@@ -119,7 +120,9 @@ def linear_plan(irreps_in: Irreps, irreps_out: Irreps, instructions, transpose: 
     targets = sorted({(ins.i_in if transpose else ins.i_out) for _, ins in live})
     for t in targets:
         mul_t, ir = dst[t]
-        kents = []
+        # a group reads W with one stride: forward 1; transposed the output multiplicity of the path, so the
+        # paths out of one input irrep are grouped by it (the caller accumulates the groups of a target)
+        by_stride = {}
         for n, ins in live:
             if (ins.i_in if transpose else ins.i_out) != t:
                 continue
@@ -127,14 +130,11 @@ def linear_plan(irreps_in: Irreps, irreps_out: Irreps, instructions, transpose: 
             mul_s = src[s].mul
             pid = b.add_path([[(k, 0, float(ins.path_weight))] for k in range(ir.dim)])
             mul_in, mul_out = ins.path_shape
+            kents = by_stride.setdefault(mul_out if transpose else 1, [])
             for q in range(mul_s):
                 # forward: W[u=q, w] contiguous in w; transpose: W[u, w=q] strided by mul_out in u
                 wbase = offs[n] + (q if transpose else q * mul_out)
                 kents.append((pid, so[s] + q * ir.dim, -1, wbase))
-        strides = {ins.path_shape[1] for n, ins in live if (ins.i_in if transpose else ins.i_out) == t}
-        # a transposed group reads W with one stride: all paths out of this input irrep must
-        # share the output multiplicity
-        if transpose and len(strides) > 1:
-            raise NotImplementedError("transposed Linear with differing output multiplicities per input irrep")
-        b.add_group(do[t], mul_t, ir.dim, kents, (strides.pop() if transpose else 1))
+        for stride, kents in by_stride.items():
+            b.add_group(do[t], mul_t, ir.dim, kents, stride)
     return b.finish(), targets

@@ -2,8 +2,9 @@
 
 Same constructor, attributes (``weight``, ``bias``, ``weight_numel``, ``bias_numel``,
 ``output_mask``, ``instructions``), weight layout and error types as the reference.  The
-contraction runs in ``e3b_dense_fwd`` (fp32); the gradient w.r.t. the features reuses the same
-kernel with a transposed plan.  ``f_in`` / ``f_out`` and per-row weights are not implemented.
+contraction runs in ``e3b_dense_fwd`` (fp32) or the tensor-core module; the gradient w.r.t. the features
+reuses the same kernels with a transposed plan, the gradient w.r.t. the weights is ``e3b_dense_bwd_w`` (fp32),
+the gradient w.r.t. the biases a column sum.  ``f_in`` / ``f_out`` and per-row weights are not implemented.
 """
 from __future__ import annotations
 
@@ -52,30 +53,43 @@ class _LinearFunction(torch.autograd.Function):
                                            bias.data_ptr() + 4 * boff, int(written), s)
                 _lib.check(rc, "e3b_fill_columns")
                 boff += n
-        ctx.save_for_backward(w)
+        ctx.save_for_backward(x, w)
         ctx.lin = lin
         return out
 
     @staticmethod
     def backward(ctx, grad_out):
-        (w,) = ctx.saved_tensors
+        x, w = ctx.saved_tensors
         lin = ctx.lin
-        if ctx.needs_input_grad[1] or ctx.needs_input_grad[2]:
-            raise NotImplementedError("gradients w.r.t. Linear weights / biases are not implemented in e3nn_b200")
         grad_out = grad_out.contiguous()
         Z, dev = grad_out.shape[0], grad_out.device
+        gx = gw = gb = None
+        if ctx.needs_input_grad[1]:
+            # dW[u, w] = pw * sum_{z, i} x[z, u, i] g[z, w, i]: the forward plan read the other way round (fp32)
+            gw = torch.zeros_like(w)
+            if lin.weight_numel > 0:
+                with torch.cuda.device(dev):
+                    rc = _lib.core().e3b_dense_bwd_w(lin._plan_host.ctypes.data, _lib._ptr(lin._plan_on(dev, False)),
+                                                     _lib._ptr(x), None, _lib._ptr(grad_out), _lib._ptr(gw), Z,
+                                                     _lib.stream_ptr())
+                _lib.check(rc, "e3b_dense_bwd_w")
+        if ctx.needs_input_grad[2]:
+            parts = [grad_out[:, off : off + n].sum(0) for off, n, _ in lin._bias_ranges]
+            gb = torch.cat(parts) if parts else torch.zeros(1, dtype=torch.float32, device=dev)
+        if not ctx.needs_input_grad[0]:
+            return None, gw, gb, None
         if lin.weight_numel > 0 and lin._tc_bwd is not None and lin._precision > 0:
             gx = torch.empty(Z, lin.irreps_in.dim, dtype=torch.float32, device=dev)
             _lib.tc_gemm_module(lin._tc_bwd).run(grad_out, None, w, gx, lin._precision)
-            return gx, None, None, None
+            return gx, gw, gb, None
         gx = torch.zeros(Z, lin.irreps_in.dim, dtype=torch.float32, device=dev)
         if lin.weight_numel > 0:
             with torch.cuda.device(dev):
                 rc = _lib.core().e3b_dense_fwd(lin._plan_t_host.ctypes.data, _lib._ptr(lin._plan_on(dev, True)),
-                                               _lib._ptr(grad_out), None, _lib._ptr(w), 0, _lib._ptr(gx), Z, 0,
+                                               _lib._ptr(grad_out), None, _lib._ptr(w), 0, _lib._ptr(gx), Z, 1,
                                                _lib.stream_ptr())
             _lib.check(rc, "e3b_dense_fwd (transposed)")
-        return gx, None, None, None
+        return gx, gw, gb, None
 
 
 class Linear(torch.nn.Module):
@@ -123,10 +137,7 @@ class Linear(torch.nn.Module):
         # the flat weight vector skips empty instructions, exactly as the reference's code generator does
         packed = [ins if 0 not in ins.path_shape else ins._replace(path_shape=(0, 0)) for ins in self.instructions]
         self._plan_host, written = linear_plan(irreps_in, irreps_out, packed, transpose=False)
-        try:
-            self._plan_t_host, _ = linear_plan(irreps_in, irreps_out, packed, transpose=True)
-        except NotImplementedError:
-            self._plan_t_host = None
+        self._plan_t_host, _ = linear_plan(irreps_in, irreps_out, packed, transpose=True)
         self._plan_dev = {}
         # tensor-core modules (None when the multiplicities do not fit the 32-wide K chunks / 16-wide N)
         tag = hashlib.sha1(repr((str(irreps_in), str(irreps_out), [(i.i_in, i.i_out, i.path_shape, repr(i.path_weight))
@@ -175,8 +186,6 @@ class Linear(torch.nn.Module):
         key = (str(device), transposed)
         if key not in self._plan_dev:
             host = self._plan_t_host if transposed else self._plan_host
-            if host is None:
-                raise NotImplementedError("gradient of this Linear layout w.r.t. its input is not implemented")
             self._plan_dev[key] = torch.from_numpy(host).to(device)
         return self._plan_dev[key]
 

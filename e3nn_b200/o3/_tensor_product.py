@@ -16,6 +16,8 @@ from math import prod
 from typing import Iterator, List, Optional, Union
 
 import numpy as np
+import warnings
+
 import torch
 
 from .. import _lib
@@ -50,23 +52,40 @@ class _UvuFunction(torch.autograd.Function):
         return g1, g2, gw, None, None
 
 
-class _DenseFunction(torch.autograd.Function):
-    """Forward of the weight-shared 'uvw' paths (no gradient kernels yet)."""
+class _UvwFunction(torch.autograd.Function):
+    """Weight-shared or per-row 'uvw' paths: forward on the engine the module's ``math_mode`` selects; gradients
+    w.r.t. the two operands as two derived 'uvw' products of the cotangent (``TensorProduct._vjp_module``), w.r.t.
+    shared weights by ``e3b_dense_bwd_w``."""
 
     @staticmethod
-    def forward(ctx, x1, x2, w, plan_host, plan_dev, out, accumulate: bool):
-        w_row_stride = w.shape[1] if w.dim() == 2 else 0
-        with torch.cuda.device(x1.device):
-            rc = _lib.core().e3b_dense_fwd(plan_host.ctypes.data, _lib._ptr(plan_dev), _lib._ptr(x1), _lib._ptr(x2),
-                                           _lib._ptr(w), w_row_stride, _lib._ptr(out), x1.shape[0], int(accumulate),
-                                           _lib.stream_ptr())
-        _lib.check(rc, "e3b_dense_fwd")
+    def forward(ctx, x1, x2, w, out, tp, accumulate: bool):
+        tp._uvw_run(x1, x2, w, out, accumulate)
         ctx.mark_dirty(out)
+        ctx.save_for_backward(x1, x2, w)
+        ctx.tp, ctx.accumulate = tp, accumulate
         return out
 
     @staticmethod
     def backward(ctx, grad_out):
-        raise NotImplementedError("gradients of 'uvw' tensor products are not implemented in e3nn_b200")
+        x1, x2, w = ctx.saved_tensors
+        tp = ctx.tp
+        need1, need2, needw = ctx.needs_input_grad[:3]
+        if (need1 or need2 or needw) and not tp.shared_weights:
+            raise NotImplementedError("gradients of 'uvw' tensor products with per-row weights are not implemented in e3nn_b200")
+        g = grad_out.contiguous()
+        g1 = g2 = gw = None
+        with torch.no_grad():
+            if need1:
+                g1 = tp._vjp_module(0)(g, x2, tp._vjp_weights(0, w))
+            if need2:
+                g2 = tp._vjp_module(1)(x1, g, tp._vjp_weights(1, w))
+            if needw:
+                gw = torch.zeros_like(w)
+                with torch.cuda.device(g.device):
+                    rc = _lib.core().e3b_dense_bwd_w(tp._plan_host.ctypes.data, _lib._ptr(tp._plan_on(g.device)), _lib._ptr(x1),
+                                                     _lib._ptr(x2), _lib._ptr(g), _lib._ptr(gw), x1.shape[0], _lib.stream_ptr())
+                _lib.check(rc, "e3b_dense_bwd_w")
+        return g1, g2, gw, (grad_out if ctx.accumulate else None), None, None
 
 
 class TensorProduct(torch.nn.Module):
@@ -286,12 +305,21 @@ class TensorProduct(torch.nn.Module):
                 _lib.check(rc, "e3b_fill_columns")
 
     def _uvw_forward(self, x2d, y2d, w, out, accumulate: bool):
-        if self.math_mode == "tf32":
-            from ._uvw_tc import uvw_tc_forward
+        if torch.is_grad_enabled() and (x2d.requires_grad or y2d.requires_grad or w.requires_grad or out.requires_grad):
+            return _UvwFunction.apply(x2d, y2d, w, out, self, accumulate)
+        return self._uvw_run(x2d, y2d, w, out, accumulate)
 
-            return uvw_tc_forward(self, x2d, y2d, w, out, accumulate)
-        if self.math_mode == "tf32x3" and self.shared_weights and not accumulate and not (
-                torch.is_grad_enabled() and (x2d.requires_grad or y2d.requires_grad or w.requires_grad)):
+    def _uvw_run(self, x2d, y2d, w, out, accumulate: bool):
+        """The 'uvw' paths on the engine of ``math_mode`` (no autograd bookkeeping)."""
+        if self.math_mode == "tf32":
+            from ._uvw_tc import tc_eligible, uvw_tc_forward
+
+            if tc_eligible(self):
+                return uvw_tc_forward(self, x2d, y2d, w, out, accumulate)
+            if not getattr(self, "_warned_tc", False):
+                warnings.warn(f"{self}: layout not eligible for the tensor-core kernel, using the fp32 kernel")
+                self._warned_tc = True
+        if self.math_mode == "tf32x3" and self.shared_weights and not accumulate:
             # tensor cores with hi/lo-split tf32 operands when the layout fits the kernel
             if not hasattr(self, "_tcg_spec"):
                 from ..codegen import tc_gemm
@@ -302,7 +330,53 @@ class TensorProduct(torch.nn.Module):
                 mod.run(x2d, y2d, w, out, 2)
                 self._last_tc_status = mod.last_status
                 return out
-        return _DenseFunction.apply(x2d, y2d, w, self._plan_host, self._plan_on(x2d.device), out, accumulate)
+        w_row_stride = w.shape[1] if w.dim() == 2 else 0
+        with torch.cuda.device(x2d.device):
+            rc = _lib.core().e3b_dense_fwd(self._plan_host.ctypes.data, _lib._ptr(self._plan_on(x2d.device)), _lib._ptr(x2d),
+                                           _lib._ptr(y2d), _lib._ptr(w), w_row_stride, _lib._ptr(out), x2d.shape[0],
+                                           int(accumulate), _lib.stream_ptr())
+        _lib.check(rc, "e3b_dense_fwd")
+        return out
+
+    # ---- gradients of the 'uvw' paths w.r.t. the operands -----------------------------------------------
+    # The product is trilinear, so its transpose in one operand is again a 'uvw' product: of the cotangent and
+    # the other operand, with each path's weights permuted and the same coefficient (the real 3j symbols of a
+    # permuted triple are equal up to a sign, which goes into the weights).
+    def _vjp_module(self, which: int) -> "TensorProduct":
+        if not hasattr(self, "_vjp"):
+            self._vjp = {}
+        if which not in self._vjp:
+            from ._wigner import wigner_3j_numpy
+
+            instr, signs = [], []
+            for n in self._uvw_ids:
+                ins = self.instructions[n]
+                l1, l2, l3 = (self.irreps_in1[ins.i_in1].ir.l, self.irreps_in2[ins.i_in2].ir.l, self.irreps_out[ins.i_out].ir.l)
+                c = wigner_3j_numpy(l1, l2, l3)
+                if which == 0:    # d/dx1: (cotangent, x2) -> x1 slots
+                    instr.append((ins.i_out, ins.i_in2, ins.i_in1, "uvw", True, ins.path_weight ** 2))
+                    signs.append(float(np.sum(wigner_3j_numpy(l3, l2, l1) * c.transpose(2, 1, 0))))
+                else:             # d/dx2: (x1, cotangent) -> x2 slots
+                    instr.append((ins.i_in1, ins.i_out, ins.i_in2, "uvw", True, ins.path_weight ** 2))
+                    signs.append(float(np.sum(wigner_3j_numpy(l1, l3, l2) * c.transpose(0, 2, 1))))
+            ins_ = (self.irreps_out, self.irreps_in2, self.irreps_in1) if which == 0 else (self.irreps_in1, self.irreps_out, self.irreps_in2)
+            mod = TensorProduct(*ins_, instr, irrep_normalization="none", path_normalization="none", internal_weights=False,
+                                shared_weights=True, math_mode=self.math_mode)
+            mod._vjp_signs = [1.0 if s > 0 else -1.0 for s in signs]
+            self._vjp[which] = mod
+        return self._vjp[which]
+
+    def _vjp_weights(self, which: int, w: torch.Tensor) -> torch.Tensor:
+        """Flat weights of `_vjp_module(which)`: per 'uvw' path [u, v, w] -> [w, v, u] (which = 0) or [u, w, v]."""
+        signs = self._vjp_module(which)._vjp_signs
+        offs = self._spec.weight_offsets()
+        parts = []
+        for n, sgn in zip(self._uvw_ids, signs):
+            ins = self.instructions[n]
+            view = w[offs[n] : offs[n] + prod(ins.path_shape)].view(ins.path_shape)
+            view = view.permute(2, 1, 0) if which == 0 else view.permute(0, 2, 1)
+            parts.append((view * sgn).reshape(-1))
+        return torch.cat(parts) if parts else w.new_zeros(0)
 
 
 class _UvuView(TPSpec):

@@ -1,8 +1,6 @@
 """Host side of the tensor-core ('tf32') mode of fully-connected tensor products."""
 from __future__ import annotations
 
-import warnings
-
 import torch
 
 from .. import _lib
@@ -15,16 +13,6 @@ def tc_eligible(tp) -> bool:
 
 def uvw_tc_forward(tp, x2d: torch.Tensor, y2d: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool):
     """out[:, written columns] (+)= uvw(x, y; w) on the tcgen05 tensor cores (tf32 operands, fp32 accumulate)."""
-    if not tc_eligible(tp):
-        if not getattr(tp, "_warned_tc", False):
-            warnings.warn(f"{tp}: layout not eligible for the tensor-core kernel, using the fp32 kernel")
-            tp._warned_tc = True
-        from ._tensor_product import _DenseFunction
-
-        return _DenseFunction.apply(x2d, y2d, w, tp._plan_host, tp._plan_on(x2d.device), out, accumulate)
-    if x2d.requires_grad or y2d.requires_grad or w.requires_grad:
-        if torch.is_grad_enabled():
-            raise NotImplementedError("gradients of 'uvw' tensor products are not implemented in e3nn_b200")
     mod = _lib.uvw_tc_module(tp._spec)
     target = torch.empty_like(out) if accumulate else out
     status = torch.zeros(1, dtype=torch.int32, device=out.device)

@@ -186,6 +186,16 @@ int e3b_dense_fwd(const int32_t* plan_host, const int32_t* plan_dev, const float
                   void* stream);
 
 /*
+ * Gradient of e3b_dense_fwd w.r.t. its SHARED weights (what autograd derives from the einsums of
+ * e3nn/o3/_tensor_product/_codegen.py:148-165 and e3nn/o3/_linear.py:420-469 for `weight`):
+ *   grad_weight[wbase(K) + w * wstride] += sum_{z,k} A[z,k,K] * grad_out[z, out_off + w * dim3 + k]
+ * with the same plan as the forward call.  grad_weight [weight_numel] must be zeroed by the caller
+ * (the kernel adds with float atomics; summation order is not fixed).  x2 may be NULL for Linear plans.
+ */
+int e3b_dense_bwd_w(const int32_t* plan_host, const int32_t* plan_dev, const float* x1, const float* x2,
+                    const float* grad_out, float* grad_weight, int64_t num_rows, void* stream);
+
+/*
  * out[z, col0 + c] = (add ? out[z, col0 + c] : 0) + (bias ? bias[c] : 0) for c < ncol: zero fill of
  * outputs no path writes (e3nn/o3/_tensor_product/_codegen.py:15-21) and the scalar biases of
  * Linear (e3nn/o3/_linear.py:423-427).

@@ -761,3 +761,97 @@ def test_linear_math_modes_forward_and_transpose(irreps):
         out.backward(go.float().to(DEV))
         e_fwd, e_bwd = rel_err(out.detach().cpu(), ref.detach()), rel_err(xg.grad.cpu(), x64.grad)
         assert lo <= e_fwd < hi and e_bwd < hi, (mode, e_fwd, e_bwd)
+
+
+# ----------------------------------------------------------------------------- gradients of the weight-shared paths
+@pytest.mark.parametrize("layout,mode,tol", [
+    (("8x0e+8x1o+4x2e", "1x0e+1x1o+1x2e", "8x0e+6x1o+4x2e+2x1e"), "fp32", TOL),
+    (("5x0e+3x1o+2x2e+1x3o", "2x0e+3x1o+1x2e", "4x0e+2x0o+3x1o+2x1e+1x2e"), "fp32", TOL),   # multiplicities > 1 on both sides
+    (("32x0e+32x1o+32x2e", "1x0e+1x1o+1x2e", "32x0e+32x1o+32x2e"), "fp32", TOL),              # BASELINE config 1
+    (("32x0e+32x1o+32x2e", "1x0e+1x1o+1x2e", "32x0e+32x1o+32x2e"), "tf32x3", 1e-4),
+    (("128x0e+64x1o+32x2e", "0e+1o+2e+3o", "128x0e+64x1o+32x2e"), "tf32", TOL_TF32),         # BASELINE config 4
+])
+def test_uvw_gradients(layout, mode, tol):
+    """Cotangents of a fully connected product w.r.t. both operands and the shared weights against autograd
+    through the fp64 oracle (the reference obtains them from autograd through its einsums)."""
+    torch.manual_seed(11)
+    tp = o3.FullyConnectedTensorProduct(*layout, math_mode=mode).to(DEV)
+    with torch.no_grad():
+        for view in tp.weight_views():
+            view.div_((view.shape[0] * view.shape[1]) ** 0.5)
+    Z = 777
+    x, y = torch.randn(Z, tp.irreps_in1.dim), torch.randn(Z, tp.irreps_in2.dim)
+    go = torch.randn(Z, tp.irreps_out.dim)
+    xg, yg = x.to(DEV).requires_grad_(True), y.to(DEV).requires_grad_(True)
+    out = tp(xg, yg)
+    out.backward(go.to(DEV))
+    x64, y64 = x.double().requires_grad_(True), y.double().requires_grad_(True)
+    w64 = tp.weight.detach().cpu().double().requires_grad_(True)
+    ref = _oracle_tp(tp, x64, y64, w64)
+    ref.backward(go.double())
+    assert rel_err(out.detach().cpu(), ref.detach()) < tol
+    assert rel_err(xg.grad.cpu(), x64.grad) < tol
+    assert rel_err(yg.grad.cpu(), y64.grad) < tol
+    assert rel_err(tp.weight.grad.cpu(), w64.grad) < max(tol, TOL)
+    # external weights, only the weights require a gradient
+    tp2 = o3.FullyConnectedTensorProduct(*layout, internal_weights=False, math_mode=mode).to(DEV)
+    wg = tp.weight.detach().clone().requires_grad_(True)
+    tp2(x.to(DEV), y.to(DEV), wg).backward(go.to(DEV))
+    assert rel_err(wg.grad.cpu(), w64.grad) < max(tol, TOL)
+
+
+def test_uvw_weight_gradient_many_rows():
+    """The weight gradient sums over the rows: 200,000 rows through several row tiles per block."""
+    torch.manual_seed(12)
+    tp = o3.FullyConnectedTensorProduct("16x0e+8x1o", "1x0e+1x1o", "8x0e+8x1o").to(DEV)
+    Z = 200_000
+    x, y, go = torch.randn(Z, tp.irreps_in1.dim), torch.randn(Z, tp.irreps_in2.dim), torch.randn(Z, tp.irreps_out.dim)
+    tp(x.to(DEV), y.to(DEV)).backward(go.to(DEV))
+    w64 = tp.weight.detach().cpu().double().requires_grad_(True)
+    _oracle_tp(tp, x.double(), y.double(), w64).backward(go.double())
+    assert rel_err(tp.weight.grad.cpu(), w64.grad) < TOL
+
+
+def test_mixed_uvu_uvw_gradients():
+    """A product with both kinds of paths: the two autograd nodes share the output rows."""
+    torch.manual_seed(13)
+    ir1, ir2, iro = o3.Irreps("4x0e+4x1o"), o3.Irreps("1x0e+1x1o"), o3.Irreps("4x0e+4x1o+3x1o")
+    instr = [(0, 0, 0, "uvu", True), (1, 1, 0, "uvu", True), (1, 0, 1, "uvu", True), (0, 1, 2, "uvw", True),
+             (1, 0, 2, "uvw", True), (1, 1, 0, "uvw", True)]
+    tp = o3.TensorProduct(ir1, ir2, iro, instr).to(DEV)
+    Z = 100
+    x, y, go = torch.randn(Z, ir1.dim), torch.randn(Z, ir2.dim), torch.randn(Z, iro.dim)
+    xg, yg = x.to(DEV).requires_grad_(True), y.to(DEV).requires_grad_(True)
+    out = tp(xg, yg)
+    out.backward(go.to(DEV))
+    x64, y64 = x.double().requires_grad_(True), y.double().requires_grad_(True)
+    w64 = tp.weight.detach().cpu().double().requires_grad_(True)
+    ref = _oracle_tp(tp, x64, y64, w64)
+    ref.backward(go.double())
+    assert rel_err(out.detach().cpu(), ref.detach()) < TOL
+    assert rel_err(xg.grad.cpu(), x64.grad) < TOL
+    assert rel_err(yg.grad.cpu(), y64.grad) < TOL
+    assert rel_err(tp.weight.grad.cpu(), w64.grad) < TOL
+
+
+@pytest.mark.parametrize("mode,tol", [("fp32", TOL), ("tf32x3", 1e-4)])
+def test_linear_weight_and_bias_gradients(mode, tol):
+    torch.manual_seed(14)
+    lin = o3.Linear("64x0e+64x1o+32x2e+3x3o", "64x0e+32x1o+32x2e+5x0e", biases=[True, False, False, True], math_mode=mode).to(DEV)
+    with torch.no_grad():
+        lin.bias.normal_()
+    Z = 5000
+    x = torch.randn(Z, lin.irreps_in.dim)
+    go = torch.randn(Z, lin.irreps_out.dim)
+    xg = x.to(DEV).requires_grad_(True)
+    out = lin(xg)
+    out.backward(go.to(DEV))
+    x64 = x.double().requires_grad_(True)
+    w64 = lin.weight.detach().cpu().double().requires_grad_(True)
+    b64 = lin.bias.detach().cpu().double().requires_grad_(True)
+    ref = orc.linear(str(lin.irreps_in), str(lin.irreps_out), x64, w64, b64, biases=[True, False, False, True])
+    ref.backward(go.double())
+    assert rel_err(out.detach().cpu(), ref.detach()) < tol
+    assert rel_err(xg.grad.cpu(), x64.grad) < tol
+    assert rel_err(lin.weight.grad.cpu(), w64.grad) < TOL
+    assert rel_err(lin.bias.grad.cpu(), b64.grad) < TOL
