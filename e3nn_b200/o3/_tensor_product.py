@@ -6,9 +6,11 @@ broadcasting rules and error types follow ``e3nn/o3/_tensor_product/_tensor_prod
 and ``_sub.py:10-68``.  The arithmetic runs in CUDA kernels only:
 
 * 'uvu' paths: a per-layout generated module (``e3nn_b200/codegen/uvu.py``);
-* 'uvw' paths: ``e3b_dense_fwd`` (fp32) or the tcgen05 tensor-core kernel (``math_mode='tf32'``).
+* 'uvw' paths: ``e3b_dense_fwd`` (fp32) or the tcgen05 tensor-core kernels (``math_mode='tf32'`` / ``'tf32x3'``);
+* 'uuu' paths (``_codegen.py:245-280``): every (row, channel) pair becomes a row of a multiplicity-one 'uvu' product
+  of the two irreps, evaluated by that product's generated module (the slices are copied out and back by torch).
 
-Connection modes other than 'uvu' and 'uvw' raise ``NotImplementedError``.
+Other connection modes raise ``NotImplementedError``.
 """
 from __future__ import annotations
 
@@ -135,12 +137,14 @@ class TensorProduct(torch.nn.Module):
         for ins in self.instructions:
             if ins.connection_mode not in SUPPORTED_MODES:
                 raise NotImplementedError(
-                    f"connection mode '{ins.connection_mode}' is not implemented by e3nn_b200 (only 'uvu' and 'uvw')"
+                    f"connection mode '{ins.connection_mode}' is not implemented by e3nn_b200 (only 'uvu', 'uvw' and 'uuu')"
                 )
             if ins.connection_mode == "uvu":
                 assert self.irreps_in1[ins.i_in1].mul == self.irreps_out[ins.i_out].mul
             if ins.connection_mode == "uvw":
                 assert ins.has_weight
+            if ins.connection_mode == "uuu":
+                assert self.irreps_in1[ins.i_in1].mul == self.irreps_in2[ins.i_in2].mul == self.irreps_out[ins.i_out].mul
 
         self._in1_dim, self._in2_dim = self.irreps_in1.dim, self.irreps_in2.dim
 
@@ -180,6 +184,8 @@ class TensorProduct(torch.nn.Module):
         self._spec = TPSpec(self.irreps_in1, self.irreps_in2, self.irreps_out, tuple(self.instructions), shared_weights)
         self._uvw_ids = [n for n, ins in self._spec.live_instructions() if ins.connection_mode == "uvw"]
         self._has_uvu = any(ins.connection_mode == "uvu" for _, ins in self._spec.live_instructions())
+        self._uuu_ids = [n for n, ins in self._spec.live_instructions() if ins.connection_mode == "uuu"]
+        self._uuu_mods = {}
         self._plan_host = None
         self._plan_dev = {}
         if self._uvw_ids:
@@ -286,14 +292,45 @@ class TensorProduct(torch.nn.Module):
 
         if self._has_uvu:
             out = _UvuFunction.apply(x2d, y2d, w2d, self._uvu_module(), self.shared_weights)
-        elif self._uvw_ids:
+        elif self._uvw_ids and not self._uuu_ids:
             out = torch.empty(Z, out_dim, dtype=torch.float32, device=x.device)
             self._zero_unwritten(out)
         else:
             out = x2d.new_zeros(Z, out_dim)
         if self._uvw_ids:
             out = self._uvw_forward(x2d, y2d, w2d, out, accumulate=self._has_uvu)
+        if self._uuu_ids:
+            out = self._uuu_forward(x2d, y2d, w2d, out)
         return out.reshape(*lead, out_dim)
+
+    def _uuu_sub(self, n: int) -> "TensorProduct":
+        """The multiplicity-one 'uvu' product that evaluates 'uuu' instruction ``n`` on (row, channel) pairs."""
+        ins = self.instructions[n]
+        ir1, ir2, ir3 = self.irreps_in1[ins.i_in1].ir, self.irreps_in2[ins.i_in2].ir, self.irreps_out[ins.i_out].ir
+        key = (str(ir1), str(ir2), str(ir3), float(ins.path_weight))
+        if key not in self._uuu_mods:
+            # 'none' normalisations: the final coefficient is sqrt(path_weight argument)
+            self._uuu_mods[key] = TensorProduct(f"1x{ir1}", f"1x{ir2}", f"1x{ir3}", [(0, 0, 0, "uvu", False, ins.path_weight ** 2)],
+                                                irrep_normalization="none", path_normalization="none")
+        return self._uuu_mods[key]
+
+    def _uuu_forward(self, x2d, y2d, w, out):
+        """'uuu' paths: out[z, u, :] += pw * w[u] * (x1[z, u, :] (x) x2[z, u, :]) with the (z, u) pairs as rows."""
+        Z = x2d.shape[0]
+        o1, o2, oo = self.irreps_in1.offsets(), self.irreps_in2.offsets(), self.irreps_out.offsets()
+        woffs = self._spec.weight_offsets()
+        for n in self._uuu_ids:
+            ins = self.instructions[n]
+            (mul, ir1), (_, ir2), (_, ir3) = self.irreps_in1[ins.i_in1], self.irreps_in2[ins.i_in2], self.irreps_out[ins.i_out]
+            a = x2d[:, o1[ins.i_in1] : o1[ins.i_in1] + mul * ir1.dim].reshape(Z * mul, ir1.dim)
+            b = y2d[:, o2[ins.i_in2] : o2[ins.i_in2] + mul * ir2.dim].reshape(Z * mul, ir2.dim)
+            r = self._uuu_sub(n)(a, b).view(Z, mul, ir3.dim)
+            if ins.has_weight:
+                wv = w[woffs[n] : woffs[n] + mul].view(1, mul, 1) if self.shared_weights else w[:, woffs[n] : woffs[n] + mul].unsqueeze(-1)
+                r = r * wv
+            sl = slice(oo[ins.i_out], oo[ins.i_out] + mul * ir3.dim)
+            out[:, sl] += r.reshape(Z, mul * ir3.dim)
+        return out
 
     def _zero_unwritten(self, out: torch.Tensor) -> None:
         offs = self.irreps_out.offsets()
@@ -408,3 +445,47 @@ class FullyConnectedTensorProduct(TensorProduct):
         ]
         super().__init__(irreps_in1, irreps_in2, irreps_out, instr, irrep_normalization=irrep_normalization,
                          path_normalization=path_normalization, **kwargs)
+
+
+class ElementwiseTensorProduct(TensorProduct):
+    """Channel-by-channel product ``z_u = x_u (x) y_u`` without weights (``_sub.py:69-133``).
+
+    The two layouts are cut into blocks of equal multiplicity; every block pair contributes one 'uuu' path per
+    irrep of its product (optionally filtered by ``filter_ir_out``)."""
+
+    def __init__(self, irreps_in1, irreps_in2, filter_ir_out=None, irrep_normalization: str = None, **kwargs) -> None:
+        from ._irreps import Irrep
+
+        a, b = Irreps(irreps_in1).simplify(), Irreps(irreps_in2).simplify()
+        if filter_ir_out is not None:
+            try:
+                filter_ir_out = [Irrep(ir) for ir in filter_ir_out]
+            except ValueError:
+                raise ValueError(f"filter_ir_out (={filter_ir_out}) must be an iterable of e3nn.o3.Irrep")
+        assert a.num_irreps == b.num_irreps
+        # walk both layouts with one cursor each, emitting the common part of the two current blocks
+        blocks1, blocks2 = [], []
+        ia = ib = 0
+        left_a = a[0].mul if len(a) else 0
+        left_b = b[0].mul if len(b) else 0
+        while ia < len(a) and ib < len(b):
+            m = min(left_a, left_b)
+            if m > 0:
+                blocks1.append((m, a[ia].ir))
+                blocks2.append((m, b[ib].ir))
+            left_a -= m
+            left_b -= m
+            if left_a == 0:
+                ia += 1
+                left_a = a[ia].mul if ia < len(a) else 0
+            if left_b == 0:
+                ib += 1
+                left_b = b[ib].mul if ib < len(b) else 0
+        out, instr = [], []
+        for n, ((mul, ir1), (_, ir2)) in enumerate(zip(blocks1, blocks2)):
+            for ir in ir1 * ir2:
+                if filter_ir_out is not None and ir not in filter_ir_out:
+                    continue
+                instr.append((n, n, len(out), "uuu", False))
+                out.append((mul, ir))
+        super().__init__(Irreps(blocks1), Irreps(blocks2), Irreps(out), instr, irrep_normalization=irrep_normalization, **kwargs)

@@ -22,6 +22,8 @@ def _build_tp(tp: TensorProduct) -> str:
     paths = []
     if tp._has_uvu:
         paths.append(tp._uvu_module().path)
+    for n in tp._uuu_ids:
+        paths.append(tp._uuu_sub(n)._uvu_module().path)
     if tp._uvw_ids and not tp._has_uvu:
         if uvw_tc.plan_groups(tp._spec) is not None:
             paths.append(_lib.uvw_tc_module(tp._spec).path)
@@ -68,6 +70,8 @@ def tps_from_cases(path: str) -> Iterable[TensorProduct]:
         # exotic cases.  The golden cases only use default weights except where noted there.
         if name == "tp_mixed_shared":
             ins[4] = ins[4] + (2.5,)
+        if name == "tp_uuu_mixed_shared":
+            ins[6] = ins[6] + (0.5,)
         yield TensorProduct(m["irreps_in1"], m["irreps_in2"], m["irreps_out"], ins, internal_weights=False,
                             shared_weights=m["shared_weights"], **m.get("norm_kwargs", {}))
 

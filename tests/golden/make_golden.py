@@ -8,6 +8,7 @@ is replaced by an identity stand-in before ``import e3nn``.
     python tests/golden/make_golden.py              (everything)
     python tests/golden/make_golden.py --only-gate  (only the Gate cases, leaving the other files untouched)
     python tests/golden/make_golden.py --only-radial-bases
+    python tests/golden/make_golden.py --only-uuu
 
 Every case stores its fp32 inputs and the reference's fp64 output on those inputs
 (inputs upcast to fp64), plus the reference's own fp32 output for context.  The files
@@ -104,7 +105,74 @@ def radial_basis_cases(meta):
     meta["cases"]["radial_bases"] = {"start": 0.5, "end": 5.0, "number": 8}
 
 
+def _tp_case(meta, name, tp_factory, Z, shared, weight_scale=None, norm_kwargs=None):
+    tp32 = tp_factory()
+    x1 = torch.randn(Z, tp32.irreps_in1.dim)
+    x2 = torch.randn(Z, tp32.irreps_in2.dim)
+    w = torch.randn(tp32.weight_numel) if shared else torch.randn(Z, tp32.weight_numel)
+    if weight_scale is not None:
+        w = w * weight_scale(tp32)
+    torch.set_default_dtype(torch.float64)
+    tp64 = tp_factory()
+    torch.set_default_dtype(torch.float32)
+    out64 = tp64(x1.double(), x2.double(), w.double())
+    out32 = tp32(x1, x2, w)
+    np.savez_compressed(
+        os.path.join(HERE, f"{name}.npz"), x1=_np(x1), x2=_np(x2), w=_np(w), out_f64=_np(out64), out_f32=_np(out32)
+    )
+    meta["cases"][name] = {
+        "irreps_in1": str(tp32.irreps_in1),
+        "irreps_in2": str(tp32.irreps_in2),
+        "irreps_out": str(tp32.irreps_out),
+        "instructions": [
+            [i.i_in1, i.i_in2, i.i_out, i.connection_mode, bool(i.has_weight), float(i.path_weight)]
+            for i in tp32.instructions
+        ],
+        "weight_numel": tp32.weight_numel,
+        "shared_weights": shared,
+        "output_mask": _np(tp32.output_mask).astype(int).tolist(),
+        "norm_kwargs": norm_kwargs or {},
+    }
+
+
+
+def uuu_cases(meta):
+    """'uuu' paths: the reference's ElementwiseTensorProduct (no weights) and a weighted mix with 'uvu' / 'uvw'."""
+    from e3nn import o3
+
+    torch.manual_seed(7)
+    _tp_case(meta, "tp_elementwise", lambda: o3.ElementwiseTensorProduct("4x0e+3x1o+2x2e+5x1e", "4x0e+3x1o+2x1o+5x2e"), 16, True)
+
+    def mixed():
+        return o3.TensorProduct(
+            "4x0e+3x1o+2x2e", "4x0e+3x1o+1x1o+3x0e", "4x0e+3x1o+3x1e+2x2e",
+            [(0, 0, 0, "uuu", True), (1, 3, 1, "uuu", True), (1, 1, 2, "uuu", False), (1, 1, 2, "uuu", True),
+             (2, 0, 3, "uvu", True), (1, 2, 0, "uvw", True), (1, 1, 3, "uvw", True, 0.5)],
+            internal_weights=False, shared_weights=True,
+        )
+
+    _tp_case(meta, "tp_uuu_mixed_shared", mixed, 16, True)
+
+    def unshared():
+        return o3.TensorProduct(
+            "3x0e+3x1o", "3x1o+3x2e", "3x1o+3x1e+3x0e",
+            [(0, 0, 0, "uuu", True), (1, 0, 1, "uuu", True), (1, 0, 2, "uuu", True), (1, 1, 0, "uuu", True)],
+            internal_weights=False, shared_weights=False,
+        )
+
+    _tp_case(meta, "tp_uuu_unshared", unshared, 16, False)
+
+
 def main():
+    if "--only-uuu" in sys.argv:
+        _import_reference()
+        with open(os.path.join(HERE, "meta.json")) as f:
+            meta = json.load(f)
+        uuu_cases(meta)
+        with open(os.path.join(HERE, "meta.json"), "w") as f:
+            json.dump(meta, f, indent=1)
+        print("'uuu' golden vectors written to", HERE)
+        return
     if "--only-radial-bases" in sys.argv:
         _import_reference()
         with open(os.path.join(HERE, "meta.json")) as f:
@@ -164,33 +232,7 @@ def main():
 
     # ---- tensor products --------------------------------------------------------------
     def tp_case(name, tp_factory, Z, shared, weight_scale=None, norm_kwargs=None):
-        tp32 = tp_factory()
-        x1 = torch.randn(Z, tp32.irreps_in1.dim)
-        x2 = torch.randn(Z, tp32.irreps_in2.dim)
-        w = torch.randn(tp32.weight_numel) if shared else torch.randn(Z, tp32.weight_numel)
-        if weight_scale is not None:
-            w = w * weight_scale(tp32)
-        torch.set_default_dtype(torch.float64)
-        tp64 = tp_factory()
-        torch.set_default_dtype(torch.float32)
-        out64 = tp64(x1.double(), x2.double(), w.double())
-        out32 = tp32(x1, x2, w)
-        np.savez_compressed(
-            os.path.join(HERE, f"{name}.npz"), x1=_np(x1), x2=_np(x2), w=_np(w), out_f64=_np(out64), out_f32=_np(out32)
-        )
-        meta["cases"][name] = {
-            "irreps_in1": str(tp32.irreps_in1),
-            "irreps_in2": str(tp32.irreps_in2),
-            "irreps_out": str(tp32.irreps_out),
-            "instructions": [
-                [i.i_in1, i.i_in2, i.i_out, i.connection_mode, bool(i.has_weight), float(i.path_weight)]
-                for i in tp32.instructions
-            ],
-            "weight_numel": tp32.weight_numel,
-            "shared_weights": shared,
-            "output_mask": _np(tp32.output_mask).astype(int).tolist(),
-            "norm_kwargs": norm_kwargs or {},
-        }
+        _tp_case(meta, name, tp_factory, Z, shared, weight_scale, norm_kwargs)
 
     def fctp(a, b, c):
         return lambda: o3.FullyConnectedTensorProduct(a, b, c, internal_weights=False, shared_weights=True)

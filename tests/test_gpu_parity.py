@@ -98,7 +98,7 @@ def test_sh_equivariance():
 # ----------------------------------------------------------------------------- tensor products
 TP_CASES = [
     "tp_cfg1_uvw", "tp_cfg4_uvw", "tp_small_uvw", "tp_cfg3_uvu_15", "tp_cfg3_uvu_11", "tp_cfg5_uvu_23",
-    "tp_small_uvu", "tp_mixed_shared", "tp_mixed_unshared",
+    "tp_small_uvu", "tp_mixed_shared", "tp_mixed_unshared", "tp_elementwise", "tp_uuu_mixed_shared", "tp_uuu_unshared",
 ]
 
 
@@ -106,6 +106,8 @@ def _tp_from_meta(name, m):
     ins = [tuple(i[:5]) for i in m["instructions"]]
     if name == "tp_mixed_shared":
         ins[4] = ins[4] + (2.5,)
+    if name == "tp_uuu_mixed_shared":
+        ins[6] = ins[6] + (0.5,)
     return o3.TensorProduct(m["irreps_in1"], m["irreps_in2"], m["irreps_out"], ins, internal_weights=False,
                             shared_weights=m["shared_weights"], **m["norm_kwargs"])
 
@@ -855,3 +857,43 @@ def test_linear_weight_and_bias_gradients(mode, tol):
     assert rel_err(xg.grad.cpu(), x64.grad) < tol
     assert rel_err(lin.weight.grad.cpu(), w64.grad) < TOL
     assert rel_err(lin.bias.grad.cpu(), b64.grad) < TOL
+
+
+@pytest.mark.parametrize("name", ["tp_elementwise", "tp_uuu_mixed_shared", "tp_uuu_unshared"])
+def test_uuu_gradients(golden, golden_meta, name):
+    """'uuu' paths (alone, and mixed with 'uvu' / 'uvw'): all cotangents against autograd through the fp64 oracle."""
+    g, m = golden(name), golden_meta["cases"][name]
+    tp = _tp_from_meta(name, m)
+    x1, x2, w = (torch.from_numpy(g[k]) for k in ("x1", "x2", "w"))
+    torch.manual_seed(3)
+    go = torch.randn(x1.shape[0], tp.irreps_out.dim)
+    d = [t.to(DEV).requires_grad_(True) for t in (x1, x2, w)]
+    out = tp(d[0], d[1], d[2] if w.numel() > 0 else None)
+    out.backward(go.to(DEV))
+    r = [t.double().requires_grad_(True) for t in (x1, x2, w)]
+    ref = _oracle_tp(tp, *r)
+    ref.backward(go.double())
+    assert rel_err(out.detach().cpu(), ref.detach()) < TOL
+    assert rel_err(d[0].grad.cpu(), r[0].grad) < TOL
+    assert rel_err(d[1].grad.cpu(), r[1].grad) < TOL
+    if w.numel() > 0:
+        assert rel_err(d[2].grad.cpu(), r[2].grad) < TOL
+
+
+def test_elementwise_tensor_product_module():
+    """`ElementwiseTensorProduct` end to end (layout splitting + kernels) against the reference's output."""
+    etp = o3.ElementwiseTensorProduct("4x0e+3x1o+2x2e+5x1e", "4x0e+3x1o+2x1o+5x2e")
+    torch.manual_seed(4)
+    x1, x2 = torch.randn(50, etp.irreps_in1.dim), torch.randn(50, etp.irreps_in2.dim)
+    out = etp(x1.to(DEV), x2.to(DEV))
+    ref = _oracle_tp(etp, x1.double(), x2.double(), torch.zeros(0, dtype=torch.float64))
+    assert rel_err(out.cpu(), ref) < TOL
+    assert etp.weight_numel == 0
+    # filter: the scalar products only
+    dot = o3.ElementwiseTensorProduct("5x1o+5x1e", "10x1e", ["0e", "0o"])
+    assert str(dot.irreps_out) == "5x0o+5x0e"
+    a, b = torch.randn(9, 30), torch.randn(9, 30)
+    o = dot(a.to(DEV), b.to(DEV)).cpu()
+    assert rel_err(o, _oracle_tp(dot, a.double(), b.double(), torch.zeros(0, dtype=torch.float64))) < TOL
+    # component normalisation of a scalar output: w3j = delta / sqrt(3), coefficient 1 -> dot product / sqrt(3)
+    assert rel_err(o, ((a.view(9, 10, 3) * b.view(9, 10, 3)).sum(-1) / 3 ** 0.5).double()) < TOL

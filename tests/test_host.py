@@ -50,6 +50,8 @@ def test_tp_normalisation_matches_reference(golden_meta):
         ins = [tuple(i[:5]) for i in m["instructions"]]
         if name == "tp_mixed_shared":
             ins[4] = ins[4] + (2.5,)
+        if name == "tp_uuu_mixed_shared":
+            ins[6] = ins[6] + (0.5,)
         tp = o3.TensorProduct(m["irreps_in1"], m["irreps_in2"], m["irreps_out"], ins, internal_weights=False,
                               shared_weights=m["shared_weights"], **m["norm_kwargs"])
         assert tp.weight_numel == m["weight_numel"], name
@@ -92,7 +94,7 @@ def test_error_behaviour_without_gpu():
     with pytest.raises(AssertionError):
         tp(torch.randn(3, 4), torch.randn(3, 4))           # wrong last dimension
     with pytest.raises(NotImplementedError):
-        o3.TensorProduct("2x0e", "2x0e", "2x0e", [(0, 0, 0, "uuu", False)])
+        o3.TensorProduct("2x0e", "2x0e", "4x0e", [(0, 0, 0, "uvuv", False)])
     tp = o3.TensorProduct("2x0e", "0e", "2x0e", [(0, 0, 0, "uvu", True)], shared_weights=False)
     assert not tp.internal_weights
     with pytest.raises(RuntimeError):
@@ -207,3 +209,18 @@ def test_gate_module_bookkeeping_matches_reference(golden_meta):
         bnn.Gate("4x0o", [torch.nn.functional.silu], "", [], "")              # odd scalar, activation without parity
     with pytest.raises(NotImplementedError):
         bnn.Gate("4x0e", [torch.tanh], "4x0e", [torch.tanh], "4x1o")(torch.zeros(2, 20))   # CPU tensor
+
+
+def test_elementwise_tensor_product_layout(golden_meta):
+    """Block splitting and instruction list of `ElementwiseTensorProduct` against the reference's (golden meta)."""
+    m = golden_meta["cases"]["tp_elementwise"]
+    etp = o3.ElementwiseTensorProduct("4x0e+3x1o+2x2e+5x1e", "4x0e+3x1o+2x1o+5x2e")
+    assert (str(etp.irreps_in1), str(etp.irreps_in2), str(etp.irreps_out)) == (m["irreps_in1"], m["irreps_in2"], m["irreps_out"])
+    got = [(i.i_in1, i.i_in2, i.i_out, i.connection_mode, i.has_weight) for i in etp.instructions]
+    assert got == [tuple(i[:5]) for i in m["instructions"]]
+    assert np.allclose([i.path_weight for i in etp.instructions], [i[5] for i in m["instructions"]], rtol=1e-14)
+    assert etp.weight_numel == 0
+    dot = o3.ElementwiseTensorProduct("5x1o + 5x1e", "10x1e", ["0e", "0o"])   # the reference's doctest
+    assert str(dot.irreps_out) == "5x0o+5x0e" and len(dot.instructions) == 2
+    with pytest.raises(AssertionError):
+        o3.ElementwiseTensorProduct("3x0e", "4x0e")

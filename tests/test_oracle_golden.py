@@ -8,7 +8,7 @@ from oracle import e3nn_oracle as orc
 
 TP_CASES = [
     "tp_cfg1_uvw", "tp_cfg4_uvw", "tp_small_uvw", "tp_cfg3_uvu_15", "tp_cfg3_uvu_11", "tp_cfg5_uvu_23",
-    "tp_small_uvu", "tp_mixed_shared", "tp_mixed_unshared",
+    "tp_small_uvu", "tp_mixed_shared", "tp_mixed_unshared", "tp_elementwise", "tp_uuu_mixed_shared", "tp_uuu_unshared",
 ]
 
 
@@ -57,6 +57,9 @@ def _raw_instructions(name, m):
     if name == "tp_mixed_shared":
         return [(0, 0, 0, "uvu", True), (1, 1, 0, "uvw", True), (1, 0, 1, "uvu", True), (1, 1, 2, "uvu", False),
                 (2, 1, 1, "uvw", True, 2.5), (2, 0, 3, "uvu", True), (1, 1, 3, "uvw", True)]
+    if name == "tp_uuu_mixed_shared":
+        return [(0, 0, 0, "uuu", True), (1, 3, 1, "uuu", True), (1, 1, 2, "uuu", False), (1, 1, 2, "uuu", True),
+                (2, 0, 3, "uvu", True), (1, 2, 0, "uvw", True), (1, 1, 3, "uvw", True, 0.5)]
     return [tuple(i[:5]) for i in m["instructions"]]
 
 
