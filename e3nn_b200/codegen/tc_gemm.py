@@ -79,6 +79,9 @@ class Group:
     has_y: bool = True
     aligned_out: bool = True   # output rows allow 16-byte stores
     plain: bool = False        # A is the input rows themselves (dense layer): 16-byte loads and stores
+    # two MMAs per k-step in the split mode (a_hi x [b_hi | b_lo], a_lo x b_hi) instead of three; needs N <= 128
+    # and twice the accumulator columns, pays for long contractions (the epilogue reads twice the columns)
+    wide_b: bool = False
 
     def resident_bytes(self) -> int:
         """Bytes of the prepared B operand when all of it stays in shared memory for the life of the CTA:
@@ -260,6 +263,7 @@ def matmul_gemm_spec(k: int, n: int, transpose: bool, scale: float, key: str) ->
         g.case_d1.append(1)
         for n0 in range(0, n, 32):
             g.chunks.append(Chunk(0, n0, n0, 1, n, scale))
+        g.wide_b = k <= 128 and n >= 8 * k and PIECES == 2
         groups = [g]
         d_in, d_out = n, k
     else:
@@ -523,17 +527,17 @@ for (int q = 0; q < {qn}; ++q) {{{{
                 for (int h = 0; h < 2; ++h) {{{{
                     uint32_t r0[16], r1[16];
                     tc::tmem_ld16(tbase + wb + 32 * h, r0); tc::tmem_ld16(tbase + wb + 32 * h + 16, r1);
-                    if (NACC == 2) {{{{   // second partial accumulator (odd k-steps): summed here in fp32
+                    if (nparts == 1) tc::tmem_ld_wait();
+                    for (int p = 1; p < nparts; ++p) {{{{   // further partial accumulators: summed here in fp32
                         uint32_t q0[16], q1[16];
-                        tc::tmem_ld16(tbase + N + wb + 32 * h, q0); tc::tmem_ld16(tbase + N + wb + 32 * h + 16, q1);
+                        const uint32_t po = part_off(p);
+                        tc::tmem_ld16(tbase + po + wb + 32 * h, q0); tc::tmem_ld16(tbase + po + wb + 32 * h + 16, q1);
                         tc::tmem_ld_wait();
 #pragma unroll
                         for (int j = 0; j < 16; ++j) {{{{
                             r0[j] = __float_as_uint(__uint_as_float(r0[j]) + __uint_as_float(q0[j]));
                             r1[j] = __float_as_uint(__uint_as_float(r1[j]) + __uint_as_float(q1[j]));
                         }}}}
-                    }}}} else {{{{
-                        tc::tmem_ld_wait();
                     }}}}
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {{{{
@@ -563,9 +567,10 @@ for (int q = 0; q < {qn}; ++q) {{{{
             uint32_t ra[16], rb[16];
             for (int w0 = 0; w0 < N; w0 += 16) {{{{
                 tc::tmem_ld16(tbase + w0, ra);
-                if (NACC == 2) tc::tmem_ld16(tbase + N + w0, rb);
-                tc::tmem_ld_wait();
-                if (NACC == 2) {{{{
+                if (nparts == 1) tc::tmem_ld_wait();
+                for (int p = 1; p < nparts; ++p) {{{{
+                    tc::tmem_ld16(tbase + part_off(p) + w0, rb);
+                    tc::tmem_ld_wait();
 #pragma unroll
                     for (int j = 0; j < 16; ++j) ra[j] = __float_as_uint(__uint_as_float(ra[j]) + __uint_as_float(rb[j]));
                 }}}}
@@ -598,11 +603,20 @@ __device__ __forceinline__ void run_group_{gi}(const float* __restrict__ x1, con
     constexpr int N = {g.n}, DIM = {g.dim}, ZT = {g.zt}, NCHUNK = {nch}, NSTAGE = {g.nstage()}, NBUF = 2;
     // partial accumulators per buffer: even / odd k-steps accumulate in different TMEM columns, which halves
     // the length of each dependent MMA chain (and of the fp32 accumulation error); summed in the epilogue
-    constexpr int NACC = {2 if 4 * g.n <= 512 else 1};
+    constexpr bool WIDE = {'true' if g.wide_b else 'false'};   // split mode with two MMAs per k-step (issue_chunk_wide)
+    constexpr int ACCW = WIDE ? 2 * N : N;          // columns of one partial accumulator
+    constexpr int NACC = {(2 if 8 * g.n <= 512 else 1) if g.wide_b else (2 if 4 * g.n <= 512 else 1)};
+    static_assert(NBUF * NACC * ACCW <= 512, "accumulators exceed tensor memory");
     constexpr int OUT_OFF = {g.out_off};
     constexpr uint32_t A_TILE = {A_TILE}, B_HALF = N * 128, STAGE_BYTES = {g.stage_bytes()};
     constexpr uint32_t RESIDENT_BYTES = {g.resident_bytes()};   // > 0: the whole prepared B stays in shared memory
     constexpr uint32_t IDESC = tc::idesc_tf32_m128(N);
+    constexpr uint32_t IDESC_WIDE = tc::idesc_tf32_m128(WIDE ? 2 * N : N);
+    // the epilogue sums `nparts` column blocks of width N: the partial accumulators, and in the two-MMA split
+    // mode the two halves of each
+    const int nsub = (WIDE && pieces == 2) ? 2 : 1;
+    const int nparts = NACC * nsub;
+    auto part_off = [&](int p) {{ return (p / nsub) * ACCW + (p % nsub) * N; }};
     uint8_t* sB = smem;
     uint8_t* sS = smem + RESIDENT_BYTES;
     uint64_t* bar_full = reinterpret_cast<uint64_t*>(sS + NSTAGE * STAGE_BYTES);
@@ -646,7 +660,7 @@ __device__ __forceinline__ void run_group_{gi}(const float* __restrict__ x1, con
             const int64_t z = t * ZT + zq;
             const bool valid = zq < ZT && z < Z;
             float* orow = out + z * {dout} + OUT_OFF;
-            const uint32_t tbase = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + b * (NACC * N);
+            const uint32_t tbase = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + b * (NACC * ACCW);
 {EPILOGUE}
             tc::tc_fence_before_sync();
             __syncwarp();
@@ -680,7 +694,7 @@ __device__ __forceinline__ void run_group_{gi}(const float* __restrict__ x1, con
             const uint32_t bph = (tile_i / NBUF) & 1;
             if (!tc::mbar_wait(&bar_acc_empty[b], bph ^ 1u, abort_flag)) break;
             tc::tc_fence_after_sync();
-            const uint32_t d_base = tmem_base + b * (NACC * N);
+            const uint32_t d_base = tmem_base + b * (NACC * ACCW);
             for (int c = 0; c < NCHUNK; ++c, ++it) {{
                 const int s = it % NSTAGE;
                 const uint32_t ph = (it / NSTAGE) & 1;
@@ -691,9 +705,10 @@ __device__ __forceinline__ void run_group_{gi}(const float* __restrict__ x1, con
                 const uint64_t adesc = tc::smem_desc_k_sw128(tc::smem_u32(sS + s * STAGE_BYTES));
                 const uint64_t bdesc = RESIDENT_BYTES > 0 ? bdesc_resident + static_cast<uint64_t>(c) * (({PIECES} * B_HALF) >> 4)
                                                           : adesc + (({PIECES} * A_TILE) >> 4);
-                if (pieces == 1) tc::issue_chunk<1, N, NACC, A_TILE, B_HALF>(d_base, adesc, bdesc, IDESC, c > 0);
-                else if (pieces == 2) tc::issue_chunk<2, N, NACC, A_TILE, B_HALF>(d_base, adesc, bdesc, IDESC, c > 0);
-                else tc::issue_chunk<3, N, NACC, A_TILE, B_HALF>(d_base, adesc, bdesc, IDESC, c > 0);
+                if (pieces == 1) tc::issue_chunk<1, N, NACC, A_TILE, B_HALF, ACCW>(d_base, adesc, bdesc, IDESC, c > 0);
+                else if (WIDE && pieces == 2) tc::issue_chunk_wide<N, NACC, A_TILE, B_HALF>(d_base, adesc, bdesc, IDESC, IDESC_WIDE, c > 0);
+                else if (pieces == 2) tc::issue_chunk<2, N, NACC, A_TILE, B_HALF, ACCW>(d_base, adesc, bdesc, IDESC, c > 0);
+                else tc::issue_chunk<3, N, NACC, A_TILE, B_HALF, ACCW>(d_base, adesc, bdesc, IDESC, c > 0);
                 tc::mma_commit(&bar_empty[s]);
             }}
             if (ok) tc::mma_commit(&bar_acc_full[b]);

@@ -128,11 +128,12 @@ __device__ __forceinline__ void mma_tf32(uint32_t d_tmem, uint64_t a_desc, uint6
 // All MMAs of one 32-wide K chunk (4 k-steps of 8): operand pieces a_i * b_j with i + j < P, smallest
 // magnitudes first; even / odd k-steps go to different partial accumulators when NACC == 2.
 // adesc / bdesc: descriptors of piece 0 at k-step 0; other pieces / k-steps are constant address offsets.
-template <int P, int N, int NACC, uint32_t A_TILE, uint32_t B_HALF>
+// ACCW: columns between the partial accumulators of a buffer.
+template <int P, int N, int NACC, uint32_t A_TILE, uint32_t B_HALF, int ACCW = N>
 __device__ __forceinline__ void issue_chunk(uint32_t d_base, uint64_t adesc, uint64_t bdesc, uint32_t idesc, bool not_first_chunk) {
 #pragma unroll
     for (int ks = 0; ks < 4; ++ks) {
-        const uint32_t d_tmem = d_base + (NACC == 2 ? (ks & 1) * N : 0);
+        const uint32_t d_tmem = d_base + (NACC == 2 ? (ks & 1) * ACCW : 0);
         uint32_t acc = (not_first_chunk || ks >= NACC) ? 1u : 0u;
 #pragma unroll
         for (int deg = P - 1; deg >= 0; --deg) {
@@ -143,6 +144,22 @@ __device__ __forceinline__ void issue_chunk(uint32_t d_base, uint64_t adesc, uin
                 acc = 1u;
             }
         }
+    }
+}
+
+// Two-piece split with two MMAs per k-step instead of three (N <= 128): the hi and lo pieces of B lie next to
+// each other in the stage, so  a_hi x [b_hi | b_lo]  is ONE instruction of width 2N whose result columns
+// [0, N) hold hi*hi and [N, 2N) hold hi*lo;  a_lo x b_hi  (width N) is added to the first half and the epilogue
+// sums the halves.  Per k-step the tensor core reads A twice and B 1.5 times instead of three times each.
+template <int N, int NACC, uint32_t A_TILE, uint32_t B_HALF>
+__device__ __forceinline__ void issue_chunk_wide(uint32_t d_base, uint64_t adesc, uint64_t bdesc, uint32_t idesc_n,
+                                                 uint32_t idesc_2n, bool not_first_chunk) {
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks) {
+        const uint32_t d_tmem = d_base + (NACC == 2 ? (ks & 1) * 2 * N : 0);
+        const uint32_t acc = (not_first_chunk || ks >= NACC) ? 1u : 0u;
+        mma_tf32(d_tmem, adesc + ((ks * 32) >> 4), bdesc + ((ks * 32) >> 4), idesc_2n, acc);
+        mma_tf32(d_tmem, adesc + ((A_TILE + ks * 32) >> 4), bdesc + ((ks * 32) >> 4), idesc_n, 1u);
     }
 }
 

@@ -45,24 +45,29 @@ def bessel(x: torch.Tensor, n: int, x_max: float = 1.0) -> torch.Tensor:
 
 
 class _ScaledMatmul(torch.autograd.Function):
-    """``scale * x @ W`` on the tensor cores (hi/lo-split tf32 operands); gradient w.r.t. ``x`` only."""
+    """``scale * x @ W`` on the tensor cores (hi/lo-split tf32 operands).  The gradient w.r.t. ``x`` is the
+    transposed module; the gradient w.r.t. ``W`` (``scale * x^T g``, a plain [h_in, rows] x [rows, h_out] product
+    needed only in training) is a library fp32 GEMM."""
 
     @staticmethod
-    def forward(ctx, x, weight, fwd_spec, bwd_spec):
+    def forward(ctx, x, weight, fwd_spec, bwd_spec, scale):
         out = torch.empty(x.shape[0], weight.shape[1], dtype=torch.float32, device=x.device)
         _lib.tc_gemm_module(fwd_spec).run(x, None, weight, out, 2)
-        ctx.save_for_backward(weight)
-        ctx.bwd_spec = bwd_spec
+        ctx.save_for_backward(weight, x if weight.requires_grad else None)
+        ctx.bwd_spec, ctx.scale = bwd_spec, scale
         return out
 
     @staticmethod
     def backward(ctx, grad_out):
-        (weight,) = ctx.saved_tensors
+        weight, x = ctx.saved_tensors
+        grad_out = grad_out.contiguous()
+        gx = gw = None
+        if ctx.needs_input_grad[0]:
+            gx = torch.empty(grad_out.shape[0], weight.shape[0], dtype=torch.float32, device=grad_out.device)
+            _lib.tc_gemm_module(ctx.bwd_spec).run(grad_out, None, weight, gx, 2)
         if ctx.needs_input_grad[1]:
-            raise NotImplementedError("weight gradients of the tensor-core radial layer are not implemented")
-        gx = torch.empty(grad_out.shape[0], weight.shape[0], dtype=torch.float32, device=grad_out.device)
-        _lib.tc_gemm_module(ctx.bwd_spec).run(grad_out.contiguous(), None, weight, gx, 2)
-        return gx, None, None, None
+            gw = (x.t() @ grad_out) * ctx.scale
+        return gx, gw, None, None, None
 
 
 class _Layer(torch.nn.Module):
@@ -89,12 +94,11 @@ class _Layer(torch.nn.Module):
         return self._tc
 
     def _matmul(self, x: torch.Tensor) -> torch.Tensor:
-        use_tc = (self.math_mode == "tf32x3" and x.is_cuda and x.dtype == torch.float32 and x.dim() == 2
-                  and not (torch.is_grad_enabled() and self.weight.requires_grad))
+        use_tc = self.math_mode == "tf32x3" and x.is_cuda and x.dtype == torch.float32 and x.dim() == 2
         if use_tc:
             fwd, bwd = self._tc_specs()
             if fwd is not None and bwd is not None:
-                return _ScaledMatmul.apply(x.contiguous(), self.weight, fwd, bwd)
+                return _ScaledMatmul.apply(x.contiguous(), self.weight, fwd, bwd, self._scale())
         return x @ (self.weight * self._scale())
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:

@@ -897,3 +897,40 @@ def test_elementwise_tensor_product_module():
     assert rel_err(o, _oracle_tp(dot, a.double(), b.double(), torch.zeros(0, dtype=torch.float64))) < TOL
     # component normalisation of a scalar output: w3j = delta / sqrt(3), coefficient 1 -> dot product / sqrt(3)
     assert rel_err(o, ((a.view(9, 10, 3) * b.view(9, 10, 3)).sum(-1) / 3 ** 0.5).double()) < TOL
+
+
+@pytest.mark.parametrize("modes", [("fp32", "fp32"), ("tf32x3", "tf32x3")])
+def test_interaction_block_training_gradients(modes):
+    """One training step of the block: gradients w.r.t. every parameter (radial layers, Linear) and the node
+    features against autograd through the fp64 oracle."""
+    from e3nn_b200 import nn as bnn
+
+    torch.manual_seed(21)
+    n_atoms, irreps, lmax = 400, "16x0e+16x1o+16x2e", 2
+    box = (n_atoms / 0.05) ** (1 / 3)
+    pos = torch.rand(n_atoms, 3) * box
+    src, dst, shift = bnn.radius_graph_pbc(pos, box, 5.0)
+    nn_avg = src.numel() / n_atoms
+    block = bnn.InteractionBlock(irreps, lmax, num_basis=8, hidden=64, r_max=5.0, num_neighbors=nn_avg,
+                                 linear_math_mode=modes[0], radial_math_mode=modes[1]).to(DEV)
+    node_x = torch.randn(n_atoms, block.irreps_node.dim)
+    G = torch.randn(n_atoms, block.irreps_out.dim)
+    _, rowptr = e3nn_b200.csr_from_dst(dst.to(DEV), n_atoms)
+    xg = node_x.to(DEV).requires_grad_(True)
+    out = block(pos.to(DEV), xg, src.to(DEV), dst.to(DEV), rowptr, shift.to(DEV))
+    (out * G.to(DEV)).sum().backward()
+
+    tp = block.tp
+    w0, w1, wl = (t.detach().cpu().double().requires_grad_(True)
+                  for t in (block.fc.layer0.weight, block.fc.layer1.weight, block.lin.weight))
+    x64 = node_x.double().requires_grad_(True)
+    ref = orc.interaction_block(
+        str(tp.irreps_in1), str(tp.irreps_in2), str(tp.irreps_out), _ins(tp), str(block.irreps_out), pos.double(),
+        x64, src, dst, shift.double(), [w0, w1], wl, 8, 5.0, nn_avg, list(range(lmax + 1)), chunk=4096)
+    (ref * G.double()).sum().backward()
+    tol = 5e-5 if modes[0] == "fp32" else 2e-4
+    assert rel_err(out.detach().cpu(), ref.detach()) < tol
+    assert rel_err(xg.grad.cpu(), x64.grad) < tol
+    assert rel_err(block.lin.weight.grad.cpu(), wl.grad) < tol
+    assert rel_err(block.fc.layer1.weight.grad.cpu(), w1.grad) < tol
+    assert rel_err(block.fc.layer0.weight.grad.cpu(), w0.grad) < tol
