@@ -41,6 +41,11 @@ SMEM_LIMIT = 227 * 1024
 A_TILE = 128 * 128          # one 128 x 32 fp32 sub-tile
 Y_BYTES = 8192
 EPI_BYTES = 4 * 32 * 64 * 4   # 4 epilogue warps x (32 rows x 64 columns) fp32
+# Row-staged epilogue of the 2l+1 > 1 groups (see Group.staged_rows): correct, but measured slower than the direct
+# strided stores on the l <= 3 Linear of 262,144 rows (transposed 8.0 instead of 4.4 ms, forward 3.16 instead of
+# 3.08 ms): two block barriers per 32 channels serialise the four epilogue warps, and its 32 KB of staging leave
+# the N = 256 groups two pipeline stages.  Off.
+STAGED_ROWS = False
 PRODUCER_WARPS = 8          # default; GemmSpec.producer_warps selects 8 or 16 per module
 PIECES = 2                  # tf32 pieces the stages have room for (hi, lo); 3 is supported by the code below
 
@@ -98,8 +103,13 @@ class Group:
         """dim == 1 groups transpose their output through shared memory for fully coalesced stores."""
         return self.dim == 1 and self.n % 64 == 0 and self.aligned_out
 
+    def staged_rows(self) -> bool:
+        """dim > 1 groups: the tile's columns go through shared memory in blocks of 16 or 32 channels so that every
+        row z is written as one contiguous run of channels x (2l+1) floats instead of strided single floats."""
+        return self.dim > 1 and self.n % 16 == 0 and STAGED_ROWS
+
     def extra_bytes(self) -> int:
-        return (Y_BYTES if self.has_y else 0) + (EPI_BYTES if self.staged_epilogue() else 0)
+        return (Y_BYTES if self.has_y else 0) + (EPI_BYTES if (self.staged_epilogue() or self.staged_rows()) else 0)
 
     def nstage(self) -> int:
         return int(max(0, min(6, (SMEM_LIMIT - 3072 - self.extra_bytes() - self.resident_bytes()) // self.stage_bytes())))
@@ -556,6 +566,38 @@ for (int q = 0; q < {qn}; ++q) {{{{
                 }}}}
                 __syncwarp();
             }}}}""".replace("{{", "{").replace("}}", "}")
+        elif g.staged_rows():
+            CW = 32 if g.n % 32 == 0 else 16
+            EPILOGUE = f"""            // {CW} channels at a time: a thread (row = (z, k)) puts its values at [z][channel * DIM + k] of a tile shared by
+            // the four epilogue warps (row stride (CW + 1) * DIM floats: consecutive lanes hit consecutive banks), then
+            // the 128 threads copy the tile out: per z one contiguous run of CW * DIM floats, whole lines per instruction
+            constexpr int CW = {CW}, RUN = CW * DIM, RSTRIDE = (CW + 1) * DIM;
+            const int etid = warp * 32 + lane;
+            for (int wc0 = 0; wc0 < N; wc0 += CW) {{{{
+#pragma unroll
+                for (int h = 0; h < CW / 16; ++h) {{{{
+                    uint32_t ra[16], rb[16];
+                    tc::tmem_ld16(tbase + wc0 + 16 * h, ra);
+                    if (nparts == 1) tc::tmem_ld_wait();
+                    for (int p = 1; p < nparts; ++p) {{{{
+                        tc::tmem_ld16(tbase + part_off(p) + wc0 + 16 * h, rb);
+                        tc::tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) ra[j] = __float_as_uint(__uint_as_float(ra[j]) + __uint_as_float(rb[j]));
+                    }}}}
+                    if (zq < ZT) {{{{
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) sE[zq * RSTRIDE + (16 * h + j) * DIM + kq] = __uint_as_float(ra[j]);
+                    }}}}
+                }}}}
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                for (int i = etid; i < ZT * RUN; i += 128) {{{{
+                    const int zl = i / RUN, cc = i - zl * RUN;
+                    const int64_t zr = t * ZT + zl;
+                    if (zr < Z) out[zr * {dout} + OUT_OFF + wc0 * DIM + cc] = sE[zl * RSTRIDE + cc];
+                }}}}
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+            }}}}""".replace("{{", "{").replace("}}", "}")
         else:
             EPILOGUE = f"""            // 16 columns per tcgen05.ld; the next load is in flight while the previous block is stored
             // (a register block is only read after the wait that follows its load)
@@ -576,6 +618,12 @@ for (int q = 0; q < {qn}; ++q) {{{{
                 }}}}
                 store16(ra, w0);
             }}}}""".replace("{{", "{").replace("}}", "}")
+        if g.staged_rows():
+            # the four epilogue warps meet at a named barrier inside the tile: they must agree on leaving the loop, so
+            # the outcome of the bounded wait is AND-reduced over the 128 threads (itself a barrier all of them reach)
+            ACC_WAIT = ("            if (!tc::named_barrier_and<1, 128>(tc::mbar_wait(&bar_acc_full[b], bph, abort_flag))) break;")
+        else:
+            ACC_WAIT = "            if (!tc::mbar_wait(&bar_acc_full[b], bph, abort_flag)) break;"
         if g.plain and gs.tma_a:
             TMA_ROLE = f"""    if (warp == kMmaWarp + 1 && lane == 0) {{
         // ================= TMA issue (single thread): raw A tiles (and the streamed B chunks) as far ahead as the
@@ -655,7 +703,7 @@ __device__ __forceinline__ void run_group_{gi}(const float* __restrict__ x1, con
         for (int64_t t = cta; t < tiles; t += nctas, ++tile_i) {{
             const int b = tile_i % NBUF;
             const uint32_t bph = (tile_i / NBUF) & 1;
-            if (!tc::mbar_wait(&bar_acc_full[b], bph, abort_flag)) break;
+{ACC_WAIT}
             tc::tc_fence_after_sync();
             const int64_t z = t * ZT + zq;
             const bool valid = zq < ZT && z < Z;
