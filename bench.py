@@ -168,6 +168,8 @@ def run_ours(args):
         return run_gate(args, rank, world, device)
     if args.workload == "uvw_fctp":
         return run_uvw(args, rank, world, device)
+    if args.workload == "uvw_cfg1":
+        return run_uvw_cfg1(args, rank, world, device)
     if args.workload == "interaction_l3":
         return run_interaction(args, rank, world, device)
     if args.workload == "conv_train_l3_23":
@@ -784,6 +786,72 @@ def run_uvw(args, rank, world, device):
     }), flush=True)
 
 
+def run_uvw_cfg1(args, rank, world, device):
+    """BASELINE config 1 (the reference's own CPU-runnable case): 10,000 rows of a 32-channel l <= 2 fully connected
+    product.  23 MB of data and 0.7 GFLOP: the call is bound by launch latency, so the line reports the time of one
+    call per arithmetic mode, and of a CUDA-graph replay of the fp32 call."""
+    from e3nn_b200 import o3
+
+    layout = ("32x0e+32x1o+32x2e", "1x0e+1x1o+1x2e", "32x0e+32x1o+32x2e")
+    rows = args.nodes if args.nodes > 0 else 10_000
+    gen = torch.Generator(device=device).manual_seed(rank)
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    times = {}
+    with torch.no_grad():
+        base = o3.FullyConnectedTensorProduct(*layout).to(device)
+        x = torch.randn(rows, base.irreps_in1.dim, device=device, generator=gen)
+        y = torch.randn(rows, base.irreps_in2.dim, device=device, generator=gen)
+        for mode in ("fp32", "tf32x3", "tf32"):
+            tp = o3.FullyConnectedTensorProduct(*layout, math_mode=mode).to(device)
+            tp.load_state_dict(base.state_dict())
+            for _ in range(max(3, args.warmup)):
+                tp(x, y)
+            torch.cuda.synchronize()
+            ts = []
+            for _ in range(max(20, args.steps)):
+                start.record()
+                tp(x, y)
+                stop.record()
+                torch.cuda.synchronize()
+                ts.append(start.elapsed_time(stop))
+            ts.sort()
+            times[mode] = ts[len(ts) // 2]
+        # the fp32 call captured in a CUDA graph (what a caller with a fixed batch would replay)
+        graph = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream(device=device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            base(x, y)
+        torch.cuda.current_stream().wait_stream(side)
+        with torch.cuda.graph(graph):
+            out = base(x, y)
+        graph.replay()
+        torch.cuda.synchronize()
+        n = 50
+        start.record()
+        for _ in range(n):
+            graph.replay()
+        stop.record()
+        torch.cuda.synchronize()
+        times["fp32_graph_replay"] = start.elapsed_time(stop) / n
+    if rank != 0:
+        return
+    peak, peak_kind = measured_peaks()
+    ms = times["fp32"]
+    nbytes = 4.0 * rows * (base.irreps_in1.dim + base.irreps_in2.dim + base.irreps_out.dim)
+    print(json.dumps({
+        "metric": "uvw TP rows/sec (config 1, fp32)", "value": world * rows / (ms * 1e-3), "unit": "rows/s", "n_gpus": world,
+        "steps": max(20, args.steps), "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "uvw_cfg1", "rows": rows, "ms_per_call": times, "parallelism": f"replicas x{world}",
+                   "l2": "23 MB of operands, L2 resident: a latency measurement, not a bandwidth one"},
+        "roofline": {"bound": "hbm", "achieved": nbytes / (ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+                     "frac": nbytes / (ms * 1e-3) / 1e9 / peak, "traffic": None, "peak_kind": f"of {peak_kind}",
+                     "kernel": "dense_fwd_kernel", "note": "launch bound (3 launches, one per output irrep)"},
+        "gpu_launches": max(20, args.steps) * 3,
+    }), flush=True)
+
+
 # ------------------------------------------------------------------------------------------- CPU arm
 def cpu_conv_sample(workload: str, sample_edges: int, threads: int):
     """One pass of the oracle over a sample of the workload: returns seconds."""
@@ -864,7 +932,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS) + ["sh_l3", "uvw_fctp", "interaction_l3", "gate", "conv_train_l3_23"])
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS) + ["sh_l3", "uvw_fctp", "interaction_l3", "gate", "conv_train_l3_23", "uvw_cfg1"])
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--nodes", type=int, default=0, help="override the node count (smaller graphs for profiling)")
     ap.add_argument("--skip-e2e", action="store_true", help="profiling runs: skip the host-buffer leg")
