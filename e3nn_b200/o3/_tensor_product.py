@@ -400,6 +400,7 @@ class TensorProduct(torch.nn.Module):
             mod = TensorProduct(*ins_, instr, irrep_normalization="none", path_normalization="none", internal_weights=False,
                                 shared_weights=True, math_mode=self.math_mode)
             mod._vjp_signs = [1.0 if s > 0 else -1.0 for s in signs]
+            mod._warned_tc = True     # a derived layout that misses the tensor-core kernel falls back to fp32 silently
             self._vjp[which] = mod
         return self._vjp[which]
 
