@@ -85,7 +85,8 @@ class Group:
     aligned_out: bool = True   # output rows allow 16-byte stores
     plain: bool = False        # A is the input rows themselves (dense layer): 16-byte loads and stores
     # two MMAs per k-step in the split mode (a_hi x [b_hi | b_lo], a_lo x b_hi) instead of three; needs N <= 128
-    # and twice the accumulator columns, pays for long contractions (the epilogue reads twice the columns)
+    # and twice the accumulator columns, pays for long contractions (the epilogue reads twice the columns); measured
+    # neutral on the Linear groups (N = 64, K = 256-448: 3.05 against 3.07 ms), so only the transposed dense layer uses it
     wide_b: bool = False
 
     def resident_bytes(self) -> int:
