@@ -163,20 +163,6 @@ __device__ __forceinline__ void issue_chunk_wide(uint32_t d_base, uint64_t adesc
     }
 }
 
-// Named barrier ID over THREADS threads that also returns the AND of their predicates: warps that meet at a
-// barrier inside a loop use it to agree on leaving the loop (e.g. after a bounded wait gave up in one of them).
-template <int ID, int THREADS>
-__device__ __forceinline__ bool named_barrier_and(bool pred) {
-    uint32_t out;
-    asm volatile(
-        "{\n\t.reg .pred p, q;\n\t"
-        "setp.ne.u32 p, %1, 0;\n\t"
-        "bar.red.and.pred q, %2, %3, p;\n\t"
-        "selp.u32 %0, 1, 0, q;\n\t}"
-        : "=r"(out) : "r"(pred ? 1u : 0u), "n"(ID), "n"(THREADS) : "memory");
-    return out != 0;
-}
-
 // mbarrier arrive once every MMA issued so far by this thread has completed
 __device__ __forceinline__ void mma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
