@@ -7,8 +7,9 @@ and ``_sub.py:10-68``.  The arithmetic runs in CUDA kernels only:
 
 * 'uvu' paths: a per-layout generated module (``e3nn_b200/codegen/uvu.py``);
 * 'uvw' paths: ``e3b_dense_fwd`` (fp32) or the tcgen05 tensor-core kernels (``math_mode='tf32'`` / ``'tf32x3'``);
-* 'uuu' paths (``_codegen.py:245-280``): every (row, channel) pair becomes a row of a multiplicity-one 'uvu' product
-  of the two irreps, evaluated by that product's generated module (the slices are copied out and back by torch).
+* 'uuu' and 'uvuv' paths (``_codegen.py:245-287``): every (row, channel) pair -- for 'uvuv' every (row, u, v) triple --
+  becomes a row of a multiplicity-one 'uvu' product of the two irreps, evaluated by that product's generated module
+  (the slices are copied out and back by torch).
 
 Other connection modes raise ``NotImplementedError``.
 """
@@ -137,7 +138,7 @@ class TensorProduct(torch.nn.Module):
         for ins in self.instructions:
             if ins.connection_mode not in SUPPORTED_MODES:
                 raise NotImplementedError(
-                    f"connection mode '{ins.connection_mode}' is not implemented by e3nn_b200 (only 'uvu', 'uvw' and 'uuu')"
+                    f"connection mode '{ins.connection_mode}' is not implemented by e3nn_b200 (only 'uvu', 'uvw', 'uuu' and 'uvuv')"
                 )
             if ins.connection_mode == "uvu":
                 assert self.irreps_in1[ins.i_in1].mul == self.irreps_out[ins.i_out].mul
@@ -145,6 +146,8 @@ class TensorProduct(torch.nn.Module):
                 assert ins.has_weight
             if ins.connection_mode == "uuu":
                 assert self.irreps_in1[ins.i_in1].mul == self.irreps_in2[ins.i_in2].mul == self.irreps_out[ins.i_out].mul
+            if ins.connection_mode == "uvuv":
+                assert self.irreps_in1[ins.i_in1].mul * self.irreps_in2[ins.i_in2].mul == self.irreps_out[ins.i_out].mul
 
         self._in1_dim, self._in2_dim = self.irreps_in1.dim, self.irreps_in2.dim
 
@@ -184,7 +187,7 @@ class TensorProduct(torch.nn.Module):
         self._spec = TPSpec(self.irreps_in1, self.irreps_in2, self.irreps_out, tuple(self.instructions), shared_weights)
         self._uvw_ids = [n for n, ins in self._spec.live_instructions() if ins.connection_mode == "uvw"]
         self._has_uvu = any(ins.connection_mode == "uvu" for _, ins in self._spec.live_instructions())
-        self._uuu_ids = [n for n, ins in self._spec.live_instructions() if ins.connection_mode == "uuu"]
+        self._uuu_ids = [n for n, ins in self._spec.live_instructions() if ins.connection_mode in ("uuu", "uvuv")]
         self._uuu_mods = {}
         self._plan_host = None
         self._plan_dev = {}
@@ -315,15 +318,23 @@ class TensorProduct(torch.nn.Module):
         return self._uuu_mods[key]
 
     def _uuu_forward(self, x2d, y2d, w, out):
-        """'uuu' paths: out[z, u, :] += pw * w[u] * (x1[z, u, :] (x) x2[z, u, :]) with the (z, u) pairs as rows."""
+        """'uuu' paths: out[z, u, :] += pw * w[u] * (x1[z, u, :] (x) x2[z, u, :]) with the (z, u) pairs as rows;
+        'uvuv' paths: out[z, (u, v), :] += pw * w[u, v] * (x1[z, u, :] (x) x2[z, v, :]) with the (z, u, v) triples as rows."""
         Z = x2d.shape[0]
         o1, o2, oo = self.irreps_in1.offsets(), self.irreps_in2.offsets(), self.irreps_out.offsets()
         woffs = self._spec.weight_offsets()
         for n in self._uuu_ids:
             ins = self.instructions[n]
             (mul, ir1), (_, ir2), (_, ir3) = self.irreps_in1[ins.i_in1], self.irreps_in2[ins.i_in2], self.irreps_out[ins.i_out]
-            a = x2d[:, o1[ins.i_in1] : o1[ins.i_in1] + mul * ir1.dim].reshape(Z * mul, ir1.dim)
-            b = y2d[:, o2[ins.i_in2] : o2[ins.i_in2] + mul * ir2.dim].reshape(Z * mul, ir2.dim)
+            if ins.connection_mode == "uvuv":
+                m1, m2 = mul, self.irreps_in2[ins.i_in2].mul
+                a = x2d[:, o1[ins.i_in1] : o1[ins.i_in1] + m1 * ir1.dim].reshape(Z, m1, 1, ir1.dim).expand(Z, m1, m2, ir1.dim)
+                b = y2d[:, o2[ins.i_in2] : o2[ins.i_in2] + m2 * ir2.dim].reshape(Z, 1, m2, ir2.dim).expand(Z, m1, m2, ir2.dim)
+                mul = m1 * m2            # output channel (u, v) = u * m2 + v, as is the weight index
+                a, b = a.reshape(Z * mul, ir1.dim), b.reshape(Z * mul, ir2.dim)
+            else:
+                a = x2d[:, o1[ins.i_in1] : o1[ins.i_in1] + mul * ir1.dim].reshape(Z * mul, ir1.dim)
+                b = y2d[:, o2[ins.i_in2] : o2[ins.i_in2] + mul * ir2.dim].reshape(Z * mul, ir2.dim)
             r = self._uuu_sub(n)(a, b).view(Z, mul, ir3.dim)
             if ins.has_weight:
                 wv = w[woffs[n] : woffs[n] + mul].view(1, mul, 1) if self.shared_weights else w[:, woffs[n] : woffs[n] + mul].unsqueeze(-1)
@@ -490,3 +501,23 @@ class ElementwiseTensorProduct(TensorProduct):
                 instr.append((n, n, len(out), "uuu", False))
                 out.append((mul, ir))
         super().__init__(Irreps(blocks1), Irreps(blocks2), Irreps(out), instr, irrep_normalization=irrep_normalization, **kwargs)
+
+
+class FullTensorProduct(TensorProduct):
+    """Every pair of channels, ``z_uv = x_u (x) y_v``, without weights (``_sub.py:136-205``): one 'uvuv' path per
+    pair of input irreps and irrep of their product, the output layout sorted by (l, p)."""
+
+    def __init__(self, irreps_in1, irreps_in2, filter_ir_out=None, irrep_normalization: str = None, **kwargs) -> None:
+        from ._irreps import Irrep
+
+        a, b = Irreps(irreps_in1).simplify(), Irreps(irreps_in2).simplify()
+        if filter_ir_out is not None:
+            try:
+                filter_ir_out = [Irrep(ir) for ir in filter_ir_out]
+            except ValueError:
+                raise ValueError(f"filter_ir_out (={filter_ir_out}) must be an iterable of e3nn.o3.Irrep")
+        pairs = [(n1, n2, m1 * m2, ir) for n1, (m1, ir1) in enumerate(a) for n2, (m2, ir2) in enumerate(b) for ir in ir1 * ir2
+                 if filter_ir_out is None or ir in filter_ir_out]
+        out, position, _ = Irreps([(m, ir) for _, _, m, ir in pairs]).sort()
+        instr = [(n1, n2, position[n], "uvuv", False) for n, (n1, n2, _, _) in enumerate(pairs)]
+        super().__init__(a, b, out, instr, irrep_normalization=irrep_normalization, **kwargs)

@@ -72,6 +72,8 @@ def tps_from_cases(path: str) -> Iterable[TensorProduct]:
             ins[4] = ins[4] + (2.5,)
         if name == "tp_uuu_mixed_shared":
             ins[6] = ins[6] + (0.5,)
+        if name == "tp_uvuv_mixed_unshared":
+            ins[3] = ins[3] + (2.0,)
         yield TensorProduct(m["irreps_in1"], m["irreps_in2"], m["irreps_out"], ins, internal_weights=False,
                             shared_weights=m["shared_weights"], **m.get("norm_kwargs", {}))
 

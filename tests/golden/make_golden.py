@@ -161,6 +161,18 @@ def uuu_cases(meta):
         )
 
     _tp_case(meta, "tp_uuu_unshared", unshared, 16, False)
+    # 'uvuv' paths: the reference's FullTensorProduct (no weights, sorted output) and a weighted mix
+    _tp_case(meta, "tp_full", lambda: o3.FullTensorProduct("2x0e+3x1o+1x2e", "2x0e+2x1o+1x1e"), 16, True)
+
+    def uvuv_mixed():
+        return o3.TensorProduct(
+            "2x0e+3x1o", "2x1o+4x0e", "6x0e+6x1e+3x1o+8x0e",
+            [(1, 0, 0, "uvuv", True), (1, 0, 1, "uvuv", False), (1, 1, 2, "uvu", True), (0, 1, 3, "uvuv", True, 2.0),
+             (1, 0, 3, "uvw", True)],
+            internal_weights=False, shared_weights=False,
+        )
+
+    _tp_case(meta, "tp_uvuv_mixed_unshared", uvuv_mixed, 16, False)
 
 
 def main():

@@ -99,6 +99,7 @@ def test_sh_equivariance():
 TP_CASES = [
     "tp_cfg1_uvw", "tp_cfg4_uvw", "tp_small_uvw", "tp_cfg3_uvu_15", "tp_cfg3_uvu_11", "tp_cfg5_uvu_23",
     "tp_small_uvu", "tp_mixed_shared", "tp_mixed_unshared", "tp_elementwise", "tp_uuu_mixed_shared", "tp_uuu_unshared",
+    "tp_full", "tp_uvuv_mixed_unshared",
 ]
 
 
@@ -108,6 +109,8 @@ def _tp_from_meta(name, m):
         ins[4] = ins[4] + (2.5,)
     if name == "tp_uuu_mixed_shared":
         ins[6] = ins[6] + (0.5,)
+    if name == "tp_uvuv_mixed_unshared":
+        ins[3] = ins[3] + (2.0,)
     return o3.TensorProduct(m["irreps_in1"], m["irreps_in2"], m["irreps_out"], ins, internal_weights=False,
                             shared_weights=m["shared_weights"], **m["norm_kwargs"])
 
@@ -859,9 +862,10 @@ def test_linear_weight_and_bias_gradients(mode, tol):
     assert rel_err(lin.bias.grad.cpu(), b64.grad) < TOL
 
 
-@pytest.mark.parametrize("name", ["tp_elementwise", "tp_uuu_mixed_shared", "tp_uuu_unshared"])
+@pytest.mark.parametrize("name", ["tp_elementwise", "tp_uuu_mixed_shared", "tp_uuu_unshared", "tp_full"])
 def test_uuu_gradients(golden, golden_meta, name):
-    """'uuu' paths (alone, and mixed with 'uvu' / 'uvw'): all cotangents against autograd through the fp64 oracle."""
+    """'uuu' and 'uvuv' paths (alone, and mixed with 'uvu' / 'uvw'): all cotangents against autograd through the fp64
+    oracle."""
     g, m = golden(name), golden_meta["cases"][name]
     tp = _tp_from_meta(name, m)
     x1, x2, w = (torch.from_numpy(g[k]) for k in ("x1", "x2", "w"))
@@ -934,3 +938,24 @@ def test_interaction_block_training_gradients(modes):
     assert rel_err(block.lin.weight.grad.cpu(), wl.grad) < tol
     assert rel_err(block.fc.layer1.weight.grad.cpu(), w1.grad) < tol
     assert rel_err(block.fc.layer0.weight.grad.cpu(), w0.grad) < tol
+
+
+def test_uvuv_weighted_gradients():
+    """Weighted 'uvuv' paths next to 'uvu' and 'uvw' ones, shared weights: all cotangents vs the fp64 oracle."""
+    torch.manual_seed(31)
+    tp = o3.TensorProduct("2x0e+3x1o", "2x1o+4x0e", "6x0e+6x1e+3x1o+8x0e",
+                          [(1, 0, 0, "uvuv", True), (1, 0, 1, "uvuv", False), (1, 1, 2, "uvu", True), (0, 1, 3, "uvuv", True, 2.0),
+                           (1, 0, 3, "uvw", True)]).to(DEV)
+    Z = 40
+    x, y, go = torch.randn(Z, tp.irreps_in1.dim), torch.randn(Z, tp.irreps_in2.dim), torch.randn(Z, tp.irreps_out.dim)
+    xg, yg = x.to(DEV).requires_grad_(True), y.to(DEV).requires_grad_(True)
+    out = tp(xg, yg)
+    out.backward(go.to(DEV))
+    x64, y64 = x.double().requires_grad_(True), y.double().requires_grad_(True)
+    w64 = tp.weight.detach().cpu().double().requires_grad_(True)
+    ref = _oracle_tp(tp, x64, y64, w64)
+    ref.backward(go.double())
+    assert rel_err(out.detach().cpu(), ref.detach()) < TOL
+    assert rel_err(xg.grad.cpu(), x64.grad) < TOL
+    assert rel_err(yg.grad.cpu(), y64.grad) < TOL
+    assert rel_err(tp.weight.grad.cpu(), w64.grad) < TOL

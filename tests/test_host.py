@@ -52,6 +52,8 @@ def test_tp_normalisation_matches_reference(golden_meta):
             ins[4] = ins[4] + (2.5,)
         if name == "tp_uuu_mixed_shared":
             ins[6] = ins[6] + (0.5,)
+        if name == "tp_uvuv_mixed_unshared":
+            ins[3] = ins[3] + (2.0,)
         tp = o3.TensorProduct(m["irreps_in1"], m["irreps_in2"], m["irreps_out"], ins, internal_weights=False,
                               shared_weights=m["shared_weights"], **m["norm_kwargs"])
         assert tp.weight_numel == m["weight_numel"], name
@@ -94,7 +96,7 @@ def test_error_behaviour_without_gpu():
     with pytest.raises(AssertionError):
         tp(torch.randn(3, 4), torch.randn(3, 4))           # wrong last dimension
     with pytest.raises(NotImplementedError):
-        o3.TensorProduct("2x0e", "2x0e", "4x0e", [(0, 0, 0, "uvuv", False)])
+        o3.TensorProduct("2x0e", "2x0e", "2x0e", [(0, 0, 0, "uvv", False)])
     tp = o3.TensorProduct("2x0e", "0e", "2x0e", [(0, 0, 0, "uvu", True)], shared_weights=False)
     assert not tp.internal_weights
     with pytest.raises(RuntimeError):
@@ -224,3 +226,15 @@ def test_elementwise_tensor_product_layout(golden_meta):
     assert str(dot.irreps_out) == "5x0o+5x0e" and len(dot.instructions) == 2
     with pytest.raises(AssertionError):
         o3.ElementwiseTensorProduct("3x0e", "4x0e")
+
+
+def test_full_tensor_product_layout(golden_meta):
+    """Output layout (sorted by (l, p)) and instruction list of `FullTensorProduct` against the reference's."""
+    m = golden_meta["cases"]["tp_full"]
+    ftp = o3.FullTensorProduct("2x0e+3x1o+1x2e", "2x0e+2x1o+1x1e")
+    assert (str(ftp.irreps_in1), str(ftp.irreps_in2), str(ftp.irreps_out)) == (m["irreps_in1"], m["irreps_in2"], m["irreps_out"])
+    got = [(i.i_in1, i.i_in2, i.i_out, i.connection_mode, i.has_weight) for i in ftp.instructions]
+    assert got == [tuple(i[:5]) for i in m["instructions"]]
+    assert np.allclose([i.path_weight for i in ftp.instructions], [i[5] for i in m["instructions"]], rtol=1e-14)
+    only = o3.FullTensorProduct("2x1o", "3x1o", ["0e"])
+    assert str(only.irreps_out) == "6x0e"
