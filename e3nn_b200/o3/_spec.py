@@ -15,8 +15,8 @@ from typing import List, NamedTuple, Optional, Sequence, Tuple
 
 from ._irreps import Irreps
 
-SUPPORTED_MODES = ("uvw", "uvu", "uuu", "uvuv")
 ALL_MODES = ("uvw", "uvu", "uvv", "uuw", "uuu", "uvuv", "uvu<v", "u<vw")
+SUPPORTED_MODES = ALL_MODES
 
 
 class Instruction(NamedTuple):

@@ -7,11 +7,10 @@ and ``_sub.py:10-68``.  The arithmetic runs in CUDA kernels only:
 
 * 'uvu' paths: a per-layout generated module (``e3nn_b200/codegen/uvu.py``);
 * 'uvw' paths: ``e3b_dense_fwd`` (fp32) or the tcgen05 tensor-core kernels (``math_mode='tf32'`` / ``'tf32x3'``);
-* 'uuu' and 'uvuv' paths (``_codegen.py:245-287``): every (row, channel) pair -- for 'uvuv' every (row, u, v) triple --
-  becomes a row of a multiplicity-one 'uvu' product of the two irreps, evaluated by that product's generated module
-  (the slices are copied out and back by torch).
-
-Other connection modes raise ``NotImplementedError``.
+* the other six modes (``_codegen.py:188-311``: 'uuu', 'uvuv', 'uvv', 'uuw', 'uvu<v', 'u<vw'): the channel pairs the mode
+  couples become rows of a multiplicity-one 'uvu' product of the two irreps, evaluated by that product's generated
+  module; the mode's weights follow (per pair, a sum over u, or a channel-mixing contraction on the Linear kernels).
+  The slices and index selections around the kernels are torch operations.
 """
 from __future__ import annotations
 
@@ -138,7 +137,7 @@ class TensorProduct(torch.nn.Module):
         for ins in self.instructions:
             if ins.connection_mode not in SUPPORTED_MODES:
                 raise NotImplementedError(
-                    f"connection mode '{ins.connection_mode}' is not implemented by e3nn_b200 (only 'uvu', 'uvw', 'uuu' and 'uvuv')"
+                    f"connection mode '{ins.connection_mode}' is not implemented by e3nn_b200 "
                 )
             if ins.connection_mode == "uvu":
                 assert self.irreps_in1[ins.i_in1].mul == self.irreps_out[ins.i_out].mul
@@ -148,6 +147,17 @@ class TensorProduct(torch.nn.Module):
                 assert self.irreps_in1[ins.i_in1].mul == self.irreps_in2[ins.i_in2].mul == self.irreps_out[ins.i_out].mul
             if ins.connection_mode == "uvuv":
                 assert self.irreps_in1[ins.i_in1].mul * self.irreps_in2[ins.i_in2].mul == self.irreps_out[ins.i_out].mul
+            if ins.connection_mode == "uvv":
+                assert self.irreps_in2[ins.i_in2].mul == self.irreps_out[ins.i_out].mul
+            if ins.connection_mode in ("uuw", "uvu<v", "u<vw"):
+                assert self.irreps_in1[ins.i_in1].mul == self.irreps_in2[ins.i_in2].mul
+            if ins.connection_mode == "uuw" and not ins.has_weight:
+                assert self.irreps_out[ins.i_out].mul == 1
+            if ins.connection_mode == "uvu<v":
+                m = self.irreps_in1[ins.i_in1].mul
+                assert m * (m - 1) // 2 == self.irreps_out[ins.i_out].mul
+            if ins.connection_mode == "u<vw":
+                assert ins.has_weight
 
         self._in1_dim, self._in2_dim = self.irreps_in1.dim, self.irreps_in2.dim
 
@@ -187,7 +197,7 @@ class TensorProduct(torch.nn.Module):
         self._spec = TPSpec(self.irreps_in1, self.irreps_in2, self.irreps_out, tuple(self.instructions), shared_weights)
         self._uvw_ids = [n for n, ins in self._spec.live_instructions() if ins.connection_mode == "uvw"]
         self._has_uvu = any(ins.connection_mode == "uvu" for _, ins in self._spec.live_instructions())
-        self._uuu_ids = [n for n, ins in self._spec.live_instructions() if ins.connection_mode in ("uuu", "uvuv")]
+        self._uuu_ids = [n for n, ins in self._spec.live_instructions() if ins.connection_mode not in ("uvu", "uvw")]
         self._uuu_mods = {}
         self._plan_host = None
         self._plan_dev = {}
@@ -318,29 +328,53 @@ class TensorProduct(torch.nn.Module):
         return self._uuu_mods[key]
 
     def _uuu_forward(self, x2d, y2d, w, out):
-        """'uuu' paths: out[z, u, :] += pw * w[u] * (x1[z, u, :] (x) x2[z, u, :]) with the (z, u) pairs as rows;
-        'uvuv' paths: out[z, (u, v), :] += pw * w[u, v] * (x1[z, u, :] (x) x2[z, v, :]) with the (z, u, v) triples as rows."""
+        """Paths whose channels pair up one to one before any weight is applied ('uuu', 'uvuv', 'uvv', 'uuw', 'uvu<v',
+        'u<vw'): t[z, q, :] = pw * x1[z, u(q), :] (x) x2[z, v(q), :] with the (z, q) pairs as rows of a multiplicity-one
+        product, then the mode's weights: per pair ('uuu', 'uvuv', 'uvu<v'), summed over u ('uvv'), or a channel-mixing
+        contraction over q on the Linear kernels ('uuw', 'u<vw')."""
         Z = x2d.shape[0]
         o1, o2, oo = self.irreps_in1.offsets(), self.irreps_in2.offsets(), self.irreps_out.offsets()
         woffs = self._spec.weight_offsets()
         for n in self._uuu_ids:
             ins = self.instructions[n]
-            (mul, ir1), (_, ir2), (_, ir3) = self.irreps_in1[ins.i_in1], self.irreps_in2[ins.i_in2], self.irreps_out[ins.i_out]
-            if ins.connection_mode == "uvuv":
-                m1, m2 = mul, self.irreps_in2[ins.i_in2].mul
-                a = x2d[:, o1[ins.i_in1] : o1[ins.i_in1] + m1 * ir1.dim].reshape(Z, m1, 1, ir1.dim).expand(Z, m1, m2, ir1.dim)
-                b = y2d[:, o2[ins.i_in2] : o2[ins.i_in2] + m2 * ir2.dim].reshape(Z, 1, m2, ir2.dim).expand(Z, m1, m2, ir2.dim)
-                mul = m1 * m2            # output channel (u, v) = u * m2 + v, as is the weight index
-                a, b = a.reshape(Z * mul, ir1.dim), b.reshape(Z * mul, ir2.dim)
-            else:
-                a = x2d[:, o1[ins.i_in1] : o1[ins.i_in1] + mul * ir1.dim].reshape(Z * mul, ir1.dim)
-                b = y2d[:, o2[ins.i_in2] : o2[ins.i_in2] + mul * ir2.dim].reshape(Z * mul, ir2.dim)
-            r = self._uuu_sub(n)(a, b).view(Z, mul, ir3.dim)
+            (m1, ir1), (m2, ir2), (mo, ir3) = self.irreps_in1[ins.i_in1], self.irreps_in2[ins.i_in2], self.irreps_out[ins.i_out]
+            mode = ins.connection_mode
+            xa = x2d[:, o1[ins.i_in1] : o1[ins.i_in1] + m1 * ir1.dim].reshape(Z, m1, ir1.dim)
+            xb = y2d[:, o2[ins.i_in2] : o2[ins.i_in2] + m2 * ir2.dim].reshape(Z, m2, ir2.dim)
+            if mode in ("uuu", "uuw"):
+                a, b, P = xa, xb, m1
+            elif mode in ("uvuv", "uvv"):       # all pairs, q = u * m2 + v
+                P = m1 * m2
+                a = xa.unsqueeze(2).expand(Z, m1, m2, ir1.dim)
+                b = xb.unsqueeze(1).expand(Z, m1, m2, ir2.dim)
+            else:                                # 'uvu<v', 'u<vw': the pairs u < v in row-major order
+                iu, iv = torch.triu_indices(m1, m1, 1, device=x2d.device)
+                a, b, P = xa[:, iu], xb[:, iv], iu.numel()
+            t = self._uuu_sub(n)(a.reshape(Z * P, ir1.dim), b.reshape(Z * P, ir2.dim)).view(Z, P, ir3.dim)
+            wn = prod(ins.path_shape) if ins.has_weight else 0
+            wp = None
             if ins.has_weight:
-                wv = w[woffs[n] : woffs[n] + mul].view(1, mul, 1) if self.shared_weights else w[:, woffs[n] : woffs[n] + mul].unsqueeze(-1)
-                r = r * wv
-            sl = slice(oo[ins.i_out], oo[ins.i_out] + mul * ir3.dim)
-            out[:, sl] += r.reshape(Z, mul * ir3.dim)
+                wp = w[woffs[n] : woffs[n] + wn] if self.shared_weights else w[:, woffs[n] : woffs[n] + wn]
+            if mode in ("uuu", "uvuv", "uvu<v"):
+                r = t * (wp.view(1, P, 1) if self.shared_weights else wp.unsqueeze(-1)) if ins.has_weight else t
+            elif mode == "uvv":
+                t4 = t.view(Z, m1, m2, ir3.dim)
+                if ins.has_weight:
+                    t4 = t4 * (wp.view(1, m1, m2, 1) if self.shared_weights else wp.view(Z, m1, m2, 1))
+                r = t4.sum(1)
+            elif not ins.has_weight:             # 'uuw' without weights: the sum over u (one output channel)
+                r = t.sum(1, keepdim=True)
+            elif self.shared_weights:            # out[z, w, :] = sum_q W[q, w] t[z, q, :] on the Linear kernels
+                key = ("mix", P, mo, str(ir3))
+                if key not in self._uuu_mods:
+                    from ._linear import Linear
+
+                    self._uuu_mods[key] = Linear(f"{P}x{ir3}", f"{mo}x{ir3}", internal_weights=False, shared_weights=True)
+                r = self._uuu_mods[key](t.reshape(Z, P * ir3.dim), wp * P ** 0.5)     # (undoes its fan-in factor)
+            else:
+                r = torch.einsum("zqw,zqk->zwk", wp.view(Z, P, mo), t)
+            sl = slice(oo[ins.i_out], oo[ins.i_out] + mo * ir3.dim)
+            out[:, sl] += r.reshape(Z, mo * ir3.dim)
         return out
 
     def _zero_unwritten(self, out: torch.Tensor) -> None:

@@ -74,6 +74,8 @@ def tps_from_cases(path: str) -> Iterable[TensorProduct]:
             ins[6] = ins[6] + (0.5,)
         if name == "tp_uvuv_mixed_unshared":
             ins[3] = ins[3] + (2.0,)
+        if name in ("tp_rest_shared", "tp_rest_unshared"):
+            ins[3] = ins[3] + (0.7,)
         yield TensorProduct(m["irreps_in1"], m["irreps_in2"], m["irreps_out"], ins, internal_weights=False,
                             shared_weights=m["shared_weights"], **m.get("norm_kwargs", {}))
 

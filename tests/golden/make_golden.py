@@ -174,6 +174,18 @@ def uuu_cases(meta):
 
     _tp_case(meta, "tp_uvuv_mixed_unshared", uvuv_mixed, 16, False)
 
+    # the remaining connection modes: 'uvv', 'uuw', 'uvu<v', 'u<vw' (weighted and not), shared and per-row weights
+    def rest(shared):
+        return lambda: o3.TensorProduct(
+            "4x0e+4x1o+1x1o", "4x1o+4x0e+3x1e", "4x1o+5x0e+6x1e+1x2e+3x1o+6x0e",
+            [(0, 0, 0, "uvv", True), (1, 0, 1, "uuw", True), (1, 0, 2, "uvu<v", True), (1, 0, 1, "u<vw", True, 0.7),
+             (1, 0, 3, "uuw", False), (4 - 2, 2, 4, "uvv", False), (0, 1, 5, "uvu<v", False)],
+            internal_weights=False, shared_weights=shared,
+        )
+
+    _tp_case(meta, "tp_rest_shared", rest(True), 16, True)
+    _tp_case(meta, "tp_rest_unshared", rest(False), 16, False)
+
 
 def main():
     if "--only-uuu" in sys.argv:

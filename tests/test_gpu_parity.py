@@ -99,7 +99,7 @@ def test_sh_equivariance():
 TP_CASES = [
     "tp_cfg1_uvw", "tp_cfg4_uvw", "tp_small_uvw", "tp_cfg3_uvu_15", "tp_cfg3_uvu_11", "tp_cfg5_uvu_23",
     "tp_small_uvu", "tp_mixed_shared", "tp_mixed_unshared", "tp_elementwise", "tp_uuu_mixed_shared", "tp_uuu_unshared",
-    "tp_full", "tp_uvuv_mixed_unshared",
+    "tp_full", "tp_uvuv_mixed_unshared", "tp_rest_shared", "tp_rest_unshared",
 ]
 
 
@@ -111,6 +111,8 @@ def _tp_from_meta(name, m):
         ins[6] = ins[6] + (0.5,)
     if name == "tp_uvuv_mixed_unshared":
         ins[3] = ins[3] + (2.0,)
+    if name in ("tp_rest_shared", "tp_rest_unshared"):
+        ins[3] = ins[3] + (0.7,)
     return o3.TensorProduct(m["irreps_in1"], m["irreps_in2"], m["irreps_out"], ins, internal_weights=False,
                             shared_weights=m["shared_weights"], **m["norm_kwargs"])
 
@@ -862,7 +864,7 @@ def test_linear_weight_and_bias_gradients(mode, tol):
     assert rel_err(lin.bias.grad.cpu(), b64.grad) < TOL
 
 
-@pytest.mark.parametrize("name", ["tp_elementwise", "tp_uuu_mixed_shared", "tp_uuu_unshared", "tp_full"])
+@pytest.mark.parametrize("name", ["tp_elementwise", "tp_uuu_mixed_shared", "tp_uuu_unshared", "tp_full", "tp_rest_shared", "tp_rest_unshared"])
 def test_uuu_gradients(golden, golden_meta, name):
     """'uuu' and 'uvuv' paths (alone, and mixed with 'uvu' / 'uvw'): all cotangents against autograd through the fp64
     oracle."""

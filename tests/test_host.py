@@ -54,6 +54,8 @@ def test_tp_normalisation_matches_reference(golden_meta):
             ins[6] = ins[6] + (0.5,)
         if name == "tp_uvuv_mixed_unshared":
             ins[3] = ins[3] + (2.0,)
+        if name in ("tp_rest_shared", "tp_rest_unshared"):
+            ins[3] = ins[3] + (0.7,)
         tp = o3.TensorProduct(m["irreps_in1"], m["irreps_in2"], m["irreps_out"], ins, internal_weights=False,
                               shared_weights=m["shared_weights"], **m["norm_kwargs"])
         assert tp.weight_numel == m["weight_numel"], name
@@ -95,8 +97,10 @@ def test_error_behaviour_without_gpu():
         tp(torch.randn(3, 5), torch.randn(3, 4))           # CPU tensors: no fallback
     with pytest.raises(AssertionError):
         tp(torch.randn(3, 4), torch.randn(3, 4))           # wrong last dimension
-    with pytest.raises(NotImplementedError):
-        o3.TensorProduct("2x0e", "2x0e", "2x0e", [(0, 0, 0, "uvv", False)])
+    with pytest.raises(KeyError):
+        o3.TensorProduct("2x0e", "2x0e", "2x0e", [(0, 0, 0, "vuv", False)])      # not a connection mode (the reference: KeyError too)
+    with pytest.raises(AssertionError):
+        o3.TensorProduct("3x0e", "3x0e", "2x0e", [(0, 0, 0, "uvu<v", False)])    # 3 pairs u < v, not 2
     tp = o3.TensorProduct("2x0e", "0e", "2x0e", [(0, 0, 0, "uvu", True)], shared_weights=False)
     assert not tp.internal_weights
     with pytest.raises(RuntimeError):

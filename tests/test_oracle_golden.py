@@ -9,7 +9,7 @@ from oracle import e3nn_oracle as orc
 TP_CASES = [
     "tp_cfg1_uvw", "tp_cfg4_uvw", "tp_small_uvw", "tp_cfg3_uvu_15", "tp_cfg3_uvu_11", "tp_cfg5_uvu_23",
     "tp_small_uvu", "tp_mixed_shared", "tp_mixed_unshared", "tp_elementwise", "tp_uuu_mixed_shared", "tp_uuu_unshared",
-    "tp_full", "tp_uvuv_mixed_unshared",
+    "tp_full", "tp_uvuv_mixed_unshared", "tp_rest_shared", "tp_rest_unshared",
 ]
 
 
@@ -61,6 +61,9 @@ def _raw_instructions(name, m):
     if name == "tp_uuu_mixed_shared":
         return [(0, 0, 0, "uuu", True), (1, 3, 1, "uuu", True), (1, 1, 2, "uuu", False), (1, 1, 2, "uuu", True),
                 (2, 0, 3, "uvu", True), (1, 2, 0, "uvw", True), (1, 1, 3, "uvw", True, 0.5)]
+    if name in ("tp_rest_shared", "tp_rest_unshared"):
+        return [(0, 0, 0, "uvv", True), (1, 0, 1, "uuw", True), (1, 0, 2, "uvu<v", True), (1, 0, 1, "u<vw", True, 0.7),
+                (1, 0, 3, "uuw", False), (2, 2, 4, "uvv", False), (0, 1, 5, "uvu<v", False)]
     if name == "tp_uvuv_mixed_unshared":
         return [(1, 0, 0, "uvuv", True), (1, 0, 1, "uvuv", False), (1, 1, 2, "uvu", True), (0, 1, 3, "uvuv", True, 2.0),
                 (1, 0, 3, "uvw", True)]
