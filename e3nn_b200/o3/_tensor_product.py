@@ -555,3 +555,89 @@ class FullTensorProduct(TensorProduct):
         out, position, _ = Irreps([(m, ir) for _, _, m, ir in pairs]).sort()
         instr = [(n1, n2, position[n], "uvuv", False) for n, (n1, n2, _, _) in enumerate(pairs)]
         super().__init__(a, b, out, instr, irrep_normalization=irrep_normalization, **kwargs)
+
+
+def _square_alpha(ir_in, ir_out, normalization: str, diagonal: bool) -> float:
+    """Variance factor of one path of a tensor square (``_sub.py:238-275``).  ``diagonal``: the u == v part, whose
+    symmetric product has a different second moment than a product of independent channels."""
+    if normalization == "none":
+        return 1.0
+    if not diagonal:
+        return float(ir_out.dim) if normalization == "component" else float(ir_in[0].dim * ir_in[1].dim)
+    d = ir_in[0].dim
+    if normalization == "component":
+        return ir_out.dim / (d + 2) if ir_out.l == 0 else ir_out.dim / 2
+    return float(ir_out.dim * d) if ir_out.l == 0 else d * (d + 2) / 2
+
+
+class TensorSquare(TensorProduct):
+    """``x (x) x`` reduced into irreps (``_sub.py:208-420``).  A pair of different input blocks contributes once; within a
+    block the pairs u < v and, for even l, the diagonal u == v.  Without ``irreps_out`` nothing is weighted and the
+    output lists every product ('uvuv', 'uvu<v', 'uuu' paths, sorted by (l, p)); with ``irreps_out`` the same three
+    kinds of pairs are mixed into the given channels by weights ('uvw', 'u<vw', 'uuw')."""
+
+    def __init__(self, irreps_in, irreps_out=None, filter_ir_out=None, irrep_normalization: str = None, **kwargs) -> None:
+        from ._irreps import Irrep
+
+        if irrep_normalization is None:
+            irrep_normalization = "component"
+        assert irrep_normalization in ["component", "norm", "none"]
+        irreps_in = Irreps(irreps_in).simplify()
+        if filter_ir_out is not None:
+            try:
+                filter_ir_out = [Irrep(ir) for ir in filter_ir_out]
+            except ValueError as exc:
+                raise ValueError(f"Error constructing filter_ir_out irrep: {exc}") from exc
+        if irreps_out is not None and filter_ir_out is not None:
+            raise ValueError("Both `irreps_out` and `filter_ir_out` are not None, this is ambiguous.")
+        connected = irreps_out is not None
+        if connected:
+            irreps_out = Irreps(irreps_out).simplify()
+        instr = []
+        if connected:
+            # the reference walks the output slots inside each block pair: (pairs, diag) alternate per slot
+            for n1, (m1, ir1) in enumerate(irreps_in):
+                for n2 in range(n1, len(irreps_in)):
+                    ir2 = irreps_in[n2].ir
+                    for n_out, (_, ir_o) in enumerate(irreps_out):
+                        if ir_o not in ir1 * ir2:
+                            continue
+                        if n1 < n2:
+                            instr.append((n1, n2, n_out, "uvw", True, _square_alpha((ir1, ir2), ir_o, irrep_normalization, False)))
+                            continue
+                        if m1 > 1:
+                            instr.append((n1, n1, n_out, "u<vw", True, _square_alpha((ir1, ir1), ir_o, irrep_normalization, False)))
+                        if ir_o.l % 2 == 0:
+                            instr.append((n1, n1, n_out, "uuw", True, _square_alpha((ir1, ir1), ir_o, irrep_normalization, True)))
+        else:
+            produced = []     # (mul, ir) of every product, in the order of the instructions
+
+            def emit(n1, n2, ir, mode, mul, diagonal=False):
+                alpha = _square_alpha((irreps_in[n1].ir, irreps_in[n2].ir), ir, irrep_normalization, diagonal)
+                instr.append((n1, n2, len(produced), mode, False, alpha))
+                produced.append((mul, ir))
+
+            for n1, (m1, ir1) in enumerate(irreps_in):
+                for n2 in range(n1, len(irreps_in)):
+                    m2, ir2 = irreps_in[n2]
+                    for ir in ir1 * ir2:
+                        if filter_ir_out is not None and ir not in filter_ir_out:
+                            continue
+                        if n1 < n2:
+                            emit(n1, n2, ir, "uvuv", m1 * m2)
+                            continue
+                        if m1 > 1:
+                            emit(n1, n1, ir, "uvu<v", m1 * (m1 - 1) // 2)
+                        if ir.l % 2 == 0:
+                            emit(n1, n1, ir, "uuu", m1, diagonal=True)
+            irreps_out, position, _ = Irreps(produced).sort()
+            instr = [(a, b, position[c], mode, hw, alpha) for a, b, c, mode, hw, alpha in instr]
+        self.irreps_in = irreps_in
+        super().__init__(irreps_in, irreps_in, irreps_out, instr, irrep_normalization="none", **kwargs)
+
+    def __repr__(self) -> str:
+        npath = sum(prod(i.path_shape) for i in self.instructions)
+        return f"{self.__class__.__name__}({self.irreps_in} -> {self.irreps_out.simplify()} | {npath} paths | {self.weight_numel} weights)"
+
+    def forward(self, x, weight: Optional[torch.Tensor] = None):
+        return super().forward(x, x, weight)

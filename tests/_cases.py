@@ -41,3 +41,5 @@ def prebuild():
     pb._build_tp(o3.ElementwiseTensorProduct("4x0e+3x1o+2x2e+5x1e", "4x0e+3x1o+2x1o+5x2e"))
     pb._build_tp(o3.ElementwiseTensorProduct("5x1o+5x1e", "10x1e", ["0e", "0o"]))
     pb._build_tp(o3.FullTensorProduct("2x0e+3x1o+1x2e", "2x0e+2x1o+1x1e"))
+    pb._build_tp(o3.TensorSquare("2x0e+3x1o+2x2e"))
+    pb._build_tp(o3.TensorSquare("2x0e+3x1o+2x2e", "4x0e+3x1o+2x2e+1x1e"))

@@ -186,6 +186,22 @@ def uuu_cases(meta):
     _tp_case(meta, "tp_rest_shared", rest(True), 16, True)
     _tp_case(meta, "tp_rest_unshared", rest(False), 16, False)
 
+    # TensorSquare: one input, unweighted (full) and weighted (fully connected) forms
+    for name, args in (("square_full", ("2x0e+3x1o+2x2e",)), ("square_connected", ("2x0e+3x1o+2x2e", "4x0e+3x1o+2x2e+1x1e"))):
+        sq32 = o3.TensorSquare(*args, internal_weights=False) if len(args) > 1 else o3.TensorSquare(*args)
+        x = torch.randn(16, sq32.irreps_in.dim)
+        w = torch.randn(sq32.weight_numel)
+        torch.set_default_dtype(torch.float64)
+        sq64 = o3.TensorSquare(*args, internal_weights=False) if len(args) > 1 else o3.TensorSquare(*args)
+        torch.set_default_dtype(torch.float32)
+        np.savez_compressed(os.path.join(HERE, f"{name}.npz"), x=_np(x), w=_np(w), out_f64=_np(sq64(x.double(), w.double())),
+                            out_f32=_np(sq32(x, w)))
+        meta["cases"][name] = {
+            "args": list(args), "irreps_out": str(sq32.irreps_out), "weight_numel": sq32.weight_numel,
+            "instructions": [[i.i_in1, i.i_in2, i.i_out, i.connection_mode, bool(i.has_weight), float(i.path_weight)]
+                             for i in sq32.instructions],
+        }
+
 
 def main():
     if "--only-uuu" in sys.argv:

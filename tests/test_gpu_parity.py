@@ -961,3 +961,23 @@ def test_uvuv_weighted_gradients():
     assert rel_err(xg.grad.cpu(), x64.grad) < TOL
     assert rel_err(yg.grad.cpu(), y64.grad) < TOL
     assert rel_err(tp.weight.grad.cpu(), w64.grad) < TOL
+
+
+@pytest.mark.parametrize("name", ["square_full", "square_connected"])
+def test_tensor_square(golden, golden_meta, name):
+    """`TensorSquare` (unweighted and weighted forms) against the reference's outputs; gradients vs the fp64 oracle."""
+    g, m = golden(name), golden_meta["cases"][name]
+    sq = o3.TensorSquare(*m["args"], internal_weights=False) if len(m["args"]) > 1 else o3.TensorSquare(*m["args"])
+    x, w = torch.from_numpy(g["x"]), torch.from_numpy(g["w"])
+    xg, wg = x.to(DEV).requires_grad_(True), w.to(DEV).requires_grad_(True)
+    out = sq(xg, wg if w.numel() > 0 else None)
+    assert rel_err(out.detach().cpu(), torch.from_numpy(g["out_f64"])) < TOL
+    torch.manual_seed(5)
+    go = torch.randn(x.shape[0], sq.irreps_out.dim)
+    out.backward(go.to(DEV))
+    x64, w64 = x.double().requires_grad_(True), w.double().requires_grad_(True)
+    ref = _oracle_tp(sq, x64, x64, w64)
+    ref.backward(go.double())
+    assert rel_err(xg.grad.cpu(), x64.grad) < TOL
+    if w.numel() > 0:
+        assert rel_err(wg.grad.cpu(), w64.grad) < TOL

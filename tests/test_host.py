@@ -242,3 +242,16 @@ def test_full_tensor_product_layout(golden_meta):
     assert np.allclose([i.path_weight for i in ftp.instructions], [i[5] for i in m["instructions"]], rtol=1e-14)
     only = o3.FullTensorProduct("2x1o", "3x1o", ["0e"])
     assert str(only.irreps_out) == "6x0e"
+
+
+@pytest.mark.parametrize("name", ["square_full", "square_connected"])
+def test_tensor_square_layout(golden_meta, name):
+    """Paths, coefficients and output layout of `TensorSquare` against the reference's (golden meta)."""
+    m = golden_meta["cases"][name]
+    sq = o3.TensorSquare(*m["args"])
+    assert str(sq.irreps_out) == m["irreps_out"] and sq.weight_numel == m["weight_numel"]
+    got = [(i.i_in1, i.i_in2, i.i_out, i.connection_mode, i.has_weight) for i in sq.instructions]
+    assert got == [tuple(i[:5]) for i in m["instructions"]]
+    assert np.allclose([i.path_weight for i in sq.instructions], [i[5] for i in m["instructions"]], rtol=1e-14)
+    with pytest.raises(ValueError):
+        o3.TensorSquare("2x1o", "3x0e", filter_ir_out=["0e"])

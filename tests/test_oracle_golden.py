@@ -143,3 +143,15 @@ def test_radial_bases(golden, golden_meta):
         for cutoff in (False, True):
             out = orc.soft_one_hot_linspace(r, m["start"], m["end"], m["number"], basis, cutoff)
             assert rel_err(out, torch.from_numpy(g[f"{basis}_{int(cutoff)}"])) < 1e-12, (basis, cutoff)
+
+
+@pytest.mark.parametrize("name", ["square_full", "square_connected"])
+def test_tensor_square(golden, golden_meta, name):
+    """The oracle's 'uvuv' / 'uvu<v' / 'uuu' / 'uvw' / 'u<vw' / 'uuw' paths on the reference's TensorSquare outputs."""
+    g, m = golden(name), golden_meta["cases"][name]
+    ins = [tuple(i[:5]) for i in m["instructions"]]
+    x, w = torch.from_numpy(g["x"]).double(), torch.from_numpy(g["w"]).double()
+    irreps_in = m["args"][0]
+    out = orc.tensor_product(irreps_in, irreps_in, m["irreps_out"], ins, x, x, w, shared_weights=True,
+                             path_weights=[i[5] for i in m["instructions"]])
+    assert rel_err(out, torch.from_numpy(g["out_f64"])) < 1e-12
