@@ -1,5 +1,6 @@
 from ._irreps import Irrep, Irreps
 from ._linear import Linear
+from ._norm import Norm
 from ._rotation import angles_to_matrix, matrix_to_angles, rand_angles, rand_matrix
 from ._spec import Instruction
 from ._spherical_harmonics import SphericalHarmonics, spherical_harmonics
@@ -7,7 +8,7 @@ from ._tensor_product import ElementwiseTensorProduct, FullTensorProduct, FullyC
 from ._wigner import wigner_3j, wigner_D
 
 __all__ = [
-    "Irrep", "Irreps", "Linear", "Instruction", "SphericalHarmonics", "spherical_harmonics",
+    "Irrep", "Irreps", "Linear", "Norm", "Instruction", "SphericalHarmonics", "spherical_harmonics",
     "ElementwiseTensorProduct", "FullTensorProduct", "FullyConnectedTensorProduct", "TensorProduct", "TensorSquare", "wigner_3j", "wigner_D",
     "rand_matrix", "rand_angles", "angles_to_matrix", "matrix_to_angles",
 ]

@@ -43,3 +43,4 @@ def prebuild():
     pb._build_tp(o3.FullTensorProduct("2x0e+3x1o+1x2e", "2x0e+2x1o+1x1e"))
     pb._build_tp(o3.TensorSquare("2x0e+3x1o+2x2e"))
     pb._build_tp(o3.TensorSquare("2x0e+3x1o+2x2e", "4x0e+3x1o+2x2e+1x1e"))
+    pb._build_tp(o3.Norm("5x0e+4x1o+3x2e+2x3o").tp)

@@ -981,3 +981,30 @@ def test_tensor_square(golden, golden_meta, name):
     assert rel_err(xg.grad.cpu(), x64.grad) < TOL
     if w.numel() > 0:
         assert rel_err(wg.grad.cpu(), w64.grad) < TOL
+
+
+def test_norm_module():
+    """`o3.Norm` (e3nn/o3/_norm.py): per-channel Euclidean norms, the reference's doctest shape, squared form."""
+    torch.manual_seed(8)
+    norm = o3.Norm("17x1o")
+    assert norm(torch.randn(17 * 3, device=DEV)).shape == (17,)
+    irreps = o3.Irreps("5x0e+4x1o+3x2e+2x3o")
+    x = torch.randn(200, irreps.dim)
+    want, off = [], 0
+    for mul, ir in irreps:
+        want.append(x[:, off : off + mul * ir.dim].double().view(200, mul, ir.dim).norm(dim=-1))
+        off += mul * ir.dim
+    want = torch.cat(want, dim=1)
+    got = o3.Norm(irreps)(x.to(DEV)).cpu()
+    assert str(o3.Norm(irreps).irreps_out) == "14x0e"
+    assert rel_err(got, want) < TOL
+    assert rel_err(o3.Norm(irreps, squared=True)(x.to(DEV)).cpu(), want ** 2) < TOL
+    xg = x.to(DEV).requires_grad_(True)
+    o3.Norm(irreps)(xg).sum().backward()
+    x64 = x.double().requires_grad_(True)
+    off, total = 0, 0.0
+    for mul, ir in irreps:
+        total = total + x64[:, off : off + mul * ir.dim].view(200, mul, ir.dim).norm(dim=-1).sum()
+        off += mul * ir.dim
+    total.backward()
+    assert rel_err(xg.grad.cpu(), x64.grad) < TOL
