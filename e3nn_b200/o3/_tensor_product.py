@@ -30,7 +30,7 @@ from ._spec import SUPPORTED_MODES, Instruction, TPSpec, normalize_tp_instructio
 
 class _UvuFunction(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x1, x2, w, mod, w_shared: bool):
+    def forward(ctx, x1, x2, w, mod, w_shared: bool, other_weights: bool = False):
         Z = x1.shape[0]
         out = torch.empty(Z, mod.dout, dtype=torch.float32, device=x1.device)
         with torch.cuda.device(x1.device):
@@ -38,7 +38,7 @@ class _UvuFunction(torch.autograd.Function):
                                      _lib.stream_ptr())
         mod.check(rc, "e3b_uvu_fwd")
         ctx.save_for_backward(x1, x2, w)
-        ctx.mod, ctx.w_shared = mod, w_shared
+        ctx.mod, ctx.w_shared, ctx.other_weights = mod, w_shared, other_weights
         return out
 
     @staticmethod
@@ -46,18 +46,21 @@ class _UvuFunction(torch.autograd.Function):
         x1, x2, w = ctx.saved_tensors
         mod = ctx.mod
         grad_out = grad_out.contiguous()
-        g1, g2, gw = torch.empty_like(x1), torch.empty_like(x2), torch.empty_like(w)
+        # per-row weights: the kernel stores only the entries of its own paths; the entries of paths other engines
+        # handle must read zero (shared weights are zeroed by the entry point itself)
+        g1, g2 = torch.empty_like(x1), torch.empty_like(x2)
+        gw = torch.zeros_like(w) if (ctx.other_weights and not ctx.w_shared) else torch.empty_like(w)
         with torch.cuda.device(x1.device):
             rc = mod.lib.e3b_uvu_bwd(_lib._ptr(x1), _lib._ptr(x2), _lib._ptr(w), _lib._ptr(grad_out), _lib._ptr(g1),
                                      _lib._ptr(g2), _lib._ptr(gw), x1.shape[0], int(ctx.w_shared), _lib.stream_ptr())
         mod.check(rc, "e3b_uvu_bwd")
-        return g1, g2, gw, None, None
+        return g1, g2, gw, None, None, None
 
 
 class _UvwFunction(torch.autograd.Function):
     """Weight-shared or per-row 'uvw' paths: forward on the engine the module's ``math_mode`` selects; gradients
     w.r.t. the two operands as two derived 'uvw' products of the cotangent (``TensorProduct._vjp_module``), w.r.t.
-    shared weights by ``e3b_dense_bwd_w``."""
+    shared weights by ``e3b_dense_bwd_w``, w.r.t. per-row weights by ``TensorProduct._uvw_row_weight_grad``."""
 
     @staticmethod
     def forward(ctx, x1, x2, w, out, tp, accumulate: bool):
@@ -72,8 +75,6 @@ class _UvwFunction(torch.autograd.Function):
         x1, x2, w = ctx.saved_tensors
         tp = ctx.tp
         need1, need2, needw = ctx.needs_input_grad[:3]
-        if (need1 or need2 or needw) and not tp.shared_weights:
-            raise NotImplementedError("gradients of 'uvw' tensor products with per-row weights are not implemented in e3nn_b200")
         g = grad_out.contiguous()
         g1 = g2 = gw = None
         with torch.no_grad():
@@ -81,7 +82,9 @@ class _UvwFunction(torch.autograd.Function):
                 g1 = tp._vjp_module(0)(g, x2, tp._vjp_weights(0, w))
             if need2:
                 g2 = tp._vjp_module(1)(x1, g, tp._vjp_weights(1, w))
-            if needw:
+            if needw and not tp.shared_weights:
+                gw = tp._uvw_row_weight_grad(x1, x2, g, w)
+            elif needw:
                 gw = torch.zeros_like(w)
                 with torch.cuda.device(g.device):
                     rc = _lib.core().e3b_dense_bwd_w(tp._plan_host.ctypes.data, _lib._ptr(tp._plan_on(g.device)), _lib._ptr(x1),
@@ -304,7 +307,7 @@ class TensorProduct(torch.nn.Module):
             w2d = x2d.new_zeros(1)
 
         if self._has_uvu:
-            out = _UvuFunction.apply(x2d, y2d, w2d, self._uvu_module(), self.shared_weights)
+            out = _UvuFunction.apply(x2d, y2d, w2d, self._uvu_module(), self.shared_weights, bool(self._uvw_ids or self._uuu_ids))
         elif self._uvw_ids and not self._uuu_ids:
             out = torch.empty(Z, out_dim, dtype=torch.float32, device=x.device)
             self._zero_unwritten(out)
@@ -427,7 +430,7 @@ class TensorProduct(torch.nn.Module):
     def _vjp_module(self, which: int) -> "TensorProduct":
         if not hasattr(self, "_vjp"):
             self._vjp = {}
-        if which not in self._vjp:
+        if which not in self._vjp:   # (the derived module shares weights exactly when this one does)
             from ._wigner import wigner_3j_numpy
 
             instr, signs = [], []
@@ -443,11 +446,29 @@ class TensorProduct(torch.nn.Module):
                     signs.append(float(np.sum(wigner_3j_numpy(l1, l3, l2) * c.transpose(0, 2, 1))))
             ins_ = (self.irreps_out, self.irreps_in2, self.irreps_in1) if which == 0 else (self.irreps_in1, self.irreps_out, self.irreps_in2)
             mod = TensorProduct(*ins_, instr, irrep_normalization="none", path_normalization="none", internal_weights=False,
-                                shared_weights=True, math_mode=self.math_mode)
+                                shared_weights=self.shared_weights, math_mode=self.math_mode)
             mod._vjp_signs = [1.0 if s > 0 else -1.0 for s in signs]
             mod._warned_tc = True     # a derived layout that misses the tensor-core kernel falls back to fp32 silently
             self._vjp[which] = mod
         return self._vjp[which]
+
+    def _uvw_row_weight_grad(self, x1, x2, g, w) -> torch.Tensor:
+        """Cotangent of per-row 'uvw' weights: grad[z, u, v, w] = sum_k t[z, (u, v), k] g[z, w, k], where t is the
+        coupled pair product of the path (coefficient included), formed on the (z, u, v) rows of a multiplicity-one
+        'uvu' module; the sum over k is one batched product."""
+        Z = x1.shape[0]
+        o1, o2, oo = self.irreps_in1.offsets(), self.irreps_in2.offsets(), self.irreps_out.offsets()
+        offs = self._spec.weight_offsets()
+        gw = torch.zeros_like(w)
+        for n in self._uvw_ids:
+            ins = self.instructions[n]
+            (m1, ir1), (m2, ir2), (mo, ir3) = self.irreps_in1[ins.i_in1], self.irreps_in2[ins.i_in2], self.irreps_out[ins.i_out]
+            a = x1[:, o1[ins.i_in1] : o1[ins.i_in1] + m1 * ir1.dim].reshape(Z, m1, 1, ir1.dim).expand(Z, m1, m2, ir1.dim)
+            b = x2[:, o2[ins.i_in2] : o2[ins.i_in2] + m2 * ir2.dim].reshape(Z, 1, m2, ir2.dim).expand(Z, m1, m2, ir2.dim)
+            t = self._uuu_sub(n)(a.reshape(Z * m1 * m2, ir1.dim), b.reshape(Z * m1 * m2, ir2.dim)).view(Z, m1 * m2, ir3.dim)
+            gk = g[:, oo[ins.i_out] : oo[ins.i_out] + mo * ir3.dim].reshape(Z, mo, ir3.dim)
+            gw[:, offs[n] : offs[n] + m1 * m2 * mo] = torch.bmm(t, gk.transpose(1, 2)).reshape(Z, -1)
+        return gw
 
     def _vjp_weights(self, which: int, w: torch.Tensor) -> torch.Tensor:
         """Flat weights of `_vjp_module(which)`: per 'uvw' path [u, v, w] -> [w, v, u] (which = 0) or [u, w, v]."""
@@ -456,10 +477,11 @@ class TensorProduct(torch.nn.Module):
         parts = []
         for n, sgn in zip(self._uvw_ids, signs):
             ins = self.instructions[n]
-            view = w[offs[n] : offs[n] + prod(ins.path_shape)].view(ins.path_shape)
-            view = view.permute(2, 1, 0) if which == 0 else view.permute(0, 2, 1)
-            parts.append((view * sgn).reshape(-1))
-        return torch.cat(parts) if parts else w.new_zeros(0)
+            block = w[..., offs[n] : offs[n] + prod(ins.path_shape)]
+            view = block.reshape(block.shape[:-1] + tuple(ins.path_shape))
+            view = view.transpose(-1, -3) if which == 0 else view.transpose(-1, -2)
+            parts.append((view * sgn).reshape(block.shape[:-1] + (-1,)))
+        return torch.cat(parts, dim=-1) if parts else w.new_zeros(0)
 
 
 class _UvuView(TPSpec):

@@ -864,7 +864,8 @@ def test_linear_weight_and_bias_gradients(mode, tol):
     assert rel_err(lin.bias.grad.cpu(), b64.grad) < TOL
 
 
-@pytest.mark.parametrize("name", ["tp_elementwise", "tp_uuu_mixed_shared", "tp_uuu_unshared", "tp_full", "tp_rest_shared", "tp_rest_unshared"])
+@pytest.mark.parametrize("name", ["tp_elementwise", "tp_uuu_mixed_shared", "tp_uuu_unshared", "tp_full", "tp_rest_shared", "tp_rest_unshared",
+                                  "tp_uvuv_mixed_unshared", "tp_mixed_unshared"])
 def test_uuu_gradients(golden, golden_meta, name):
     """'uuu' and 'uvuv' paths (alone, and mixed with 'uvu' / 'uvw'): all cotangents against autograd through the fp64
     oracle."""
