@@ -290,7 +290,7 @@ def finish(args, rank, world, d, tp, nodes, degree, edges_total, ms_step, kernel
         "clocks": clocks,
     }
     if world == 1 and not args.skip_cpu:
-        line["cpu_baseline"] = cpu_baseline(args.workload, budget_s=12.0)
+        line["cpu_baseline"] = cpu_baseline(args.workload)
     print(json.dumps(line), flush=True)
     if world > 1:
         torch.distributed.destroy_process_group()
@@ -693,15 +693,95 @@ def run_interaction(args, rank, world, device):
         "clocks": clocks,
     }
     if world == 1 and not args.skip_cpu:
-        line["cpu_baseline"] = cpu_interaction_baseline(budget_s=15.0)
+        line["cpu_baseline"] = cpu_interaction_baseline()
     print(json.dumps(line), flush=True)
     if world > 1:
         torch.distributed.destroy_process_group()
 
 
+def import_reference():
+    """The unmodified e3nn installed in ``baseline/_ref`` (by ``baseline/install_reference.py``, which
+    ``__graft_entry__.build()`` runs where the sources exist), or None.  It travels to the GPU box with the repository."""
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    if not (os.path.isfile(os.path.join(ref, "e3nn", "__init__.py")) and os.path.isdir(os.path.join(ref, "opt_einsum_fx"))):
+        return None
+    if ref not in sys.path:
+        sys.path.insert(0, ref)
+    try:
+        import e3nn
+    except Exception:   # a dependency of the reference (sympy, scipy) is missing on this machine
+        return None
+    return e3nn
+
+
+def _reference_dce(module):
+    """Remove the dead outer-product nodes the reference's generated graph keeps when opt_einsum_fx is absent
+    (that package would have removed them; outputs are bit-identical)."""
+    gm = getattr(module, "_compiled_main_left_right", None)
+    if gm is not None and hasattr(gm, "graph"):
+        gm.graph.eliminate_dead_code()
+        gm.recompile()
+    return module
+
+
+_REF_CACHE = {}
+
+
+def reference_interaction_model():
+    """The block of the default workload assembled from the reference's own modules (recipe of its ``Convolution``)."""
+    if "interaction" in _REF_CACHE:
+        return _REF_CACHE["interaction"]
+    e3nn = import_reference()
+    from e3nn import o3
+    from e3nn.nn import FullyConnectedNet
+
+    torch.manual_seed(0)
+    node, sh = o3.Irreps("64x0e+64x1o+64x2e+64x3o"), o3.Irreps.spherical_harmonics(3)
+    mid, ins = [], []
+    for i, (mul, ir_in) in enumerate(node):
+        for j, (_, ir_edge) in enumerate(sh):
+            for ir_out in ir_in * ir_edge:
+                if ir_out in node:
+                    ins.append((i, j, len(mid), "uvu", True))
+                    mid.append((mul, ir_out))
+    mid, perm, _ = o3.Irreps(mid).sort()
+    ins = [(a, b, perm[c], m, t) for a, b, c, m, t in ins]
+    tp = _reference_dce(o3.TensorProduct(node, sh, mid, ins, internal_weights=False, shared_weights=False))
+    fc = FullyConnectedNet([8, 64, tp.weight_numel], torch.nn.functional.silu)
+    lin = o3.Linear(mid, node)
+    for m in (fc, lin):
+        for prm in m.parameters():
+            prm.requires_grad_(False)
+    _REF_CACHE["interaction"] = (e3nn, o3, sh, tp, fc, lin)
+    return _REF_CACHE["interaction"]
+
+
+def reference_interaction_sample(n_atoms: int, threads: int):
+    """The reference itself (eager fp32, torch CPU, `threads` intra-op threads): forward + position gradient of the
+    block on a smaller box of the same density.  Returns (edges, seconds)."""
+    e3nn, o3, sh, tp, fc, lin = reference_interaction_model()
+    from e3nn.math import bessel
+
+    torch.set_num_threads(threads)
+    box, pos, src, dst, shift, _ = interaction_problem(n_atoms, seed=3)
+    gen = torch.Generator().manual_seed(0)
+    x = torch.randn(n_atoms, 1024, generator=gen)
+    G = torch.randn(n_atoms, 1024, generator=gen)
+    nn = src.numel() / n_atoms
+    t0 = time.perf_counter()
+    p = pos.clone().requires_grad_(True)
+    vec = p[src] - p[dst] + shift
+    w = fc(bessel(vec.norm(dim=1), 8, 5.0))
+    msg = tp(x[src], o3.spherical_harmonics(sh, vec, True, "component"), w)
+    mid = torch.zeros(n_atoms, msg.shape[1]).index_add_(0, dst, msg) / nn ** 0.5
+    (lin(mid) * G).sum().backward()
+    assert p.grad is not None
+    return src.numel(), time.perf_counter() - t0
+
+
 def cpu_interaction_sample(n_atoms: int, threads: int):
     """Oracle (fp32, torch CPU) forward + position gradient of the same block on a smaller box of the
-    same density: returns (edges, seconds)."""
+    same density: returns (edges, seconds).  Only used when the reference is not installed."""
     from oracle import e3nn_oracle as orc
 
     torch.set_num_threads(threads)
@@ -721,13 +801,28 @@ def cpu_interaction_sample(n_atoms: int, threads: int):
     return src.numel(), time.perf_counter() - t0
 
 
-def cpu_interaction_baseline(budget_s: float):
+CPU_SAMPLE_ATOMS = 512     # the CPU arms (cpu_baseline of the default line and --impl reference) time the same sample
+
+
+def cpu_interaction_arm(steps: int, warmup: int):
+    """(value edges/s, seconds per step, steps, cpu_baseline dict) of the CPU arm on CPU_SAMPLE_ATOMS atoms."""
     threads = os.cpu_count() or 1
-    edges, t = cpu_interaction_sample(512, threads)
-    n = int(min(8192, max(512, 512 * budget_s / max(t, 1e-3)))) // 256 * 256
-    edges, t = cpu_interaction_sample(n, threads)
-    return {"value": edges / t, "unit": "edges/s", "cores": threads, "kind": "port",
-            "sample": f"{n} atoms / {edges} edges at the same density (fp32 torch-CPU oracle, forward + position gradient), {t:.1f} s"}
+    ref = import_reference()
+    fn, kind = (reference_interaction_sample, "reference") if ref is not None else (cpu_interaction_sample, "port")
+    for _ in range(warmup):
+        fn(256, threads)
+    runs = [fn(CPU_SAMPLE_ATOMS, threads) for _ in range(max(1, steps))]
+    edges, t = runs[0][0], sum(r[1] for r in runs) / len(runs)
+    what = ("e3nn 0.6.0 itself (eager fp32 torch-CPU, identity opt_einsum_fx stand-in, dead FX nodes removed)"
+            if kind == "reference" else "fp32 torch-CPU oracle port (the reference is not installed in baseline/_ref)")
+    base = {"value": edges / t, "unit": "edges/s", "cores": threads, "kind": kind,
+            "sample": f"{CPU_SAMPLE_ATOMS} atoms / {edges} edges at the same density, forward + position gradient, "
+                      f"{what}, {t:.1f} s per step"}
+    return edges / t, t, len(runs), base
+
+
+def cpu_interaction_baseline():
+    return cpu_interaction_arm(steps=1, warmup=1)[3]
 
 
 def run_uvw(args, rank, world, device):
@@ -879,50 +974,93 @@ def cpu_conv_sample(workload: str, sample_edges: int, threads: int):
     return time.perf_counter() - t0
 
 
-def cpu_baseline(workload: str, budget_s: float):
+def reference_conv_sample(workload: str, sample_edges: int, threads: int):
+    """The reference itself on a sample of a fused-convolution workload: gather, spherical harmonics, its
+    ``TensorProduct`` ('uvu', per-edge weights) and the scatter sum, in chunks of 16,384 edges.  Returns seconds."""
+    layout, nodes, degree = WORKLOADS[workload]
+    key = "conv_" + layout
+    if key not in _REF_CACHE:
+        import_reference()
+        from e3nn import o3
+        from e3nn_b200 import layouts
+
+        node, edge, keep = layouts.BENCH_CONV_LAYOUTS[layout]
+        node, edge, keep = o3.Irreps(node), o3.Irreps(edge), o3.Irreps(keep)
+        mid, ins = [], []
+        for i, (mul, ir_in) in enumerate(node):
+            for j, (_, ir_edge) in enumerate(edge):
+                for ir_out in ir_in * ir_edge:
+                    if ir_out in keep or ir_out == o3.Irrep(0, 1):
+                        ins.append((i, j, len(mid), "uvu", True))
+                        mid.append((mul, ir_out))
+        mid, perm, _ = o3.Irreps(mid).sort()
+        ins = [(a, b, perm[c], m, t) for a, b, c, m, t in ins]
+        tp = _reference_dce(o3.TensorProduct(node, edge, mid, ins, internal_weights=False, shared_weights=False))
+        _REF_CACHE[key] = (o3, node, edge, tp)
+    o3, node, edge, tp = _REF_CACHE[key]
+    torch.set_num_threads(threads)
+    gen = torch.Generator().manual_seed(0)
+    n_dst = sample_edges // degree
+    node_x = torch.randn(nodes, node.dim, generator=gen)
+    vec = torch.randn(sample_edges, 3, generator=gen)
+    src = torch.randint(0, nodes, (sample_edges,), generator=gen)
+    dst = torch.arange(sample_edges) // degree
+    w = torch.randn(sample_edges, tp.weight_numel, generator=gen)
+    t0 = time.perf_counter()
+    out = torch.zeros(n_dst, tp.irreps_out.dim)
+    with torch.no_grad():
+        for c0 in range(0, sample_edges, 16384):
+            c1 = min(c0 + 16384, sample_edges)
+            y = o3.spherical_harmonics(edge, vec[c0:c1], True, "component")
+            out.index_add_(0, dst[c0:c1], tp(node_x[src[c0:c1]], y, w[c0:c1]))
+        out *= degree ** -0.5
+    return time.perf_counter() - t0
+
+
+CPU_SAMPLE_EDGES = 262144
+
+
+def cpu_conv_arm(workload: str, steps: int, warmup: int):
     threads = os.cpu_count() or 1
-    sample = 16384
-    t = cpu_conv_sample(workload, sample, threads)  # warm-up and rate estimate
-    sample = int(min(1 << 20, max(16384, sample * budget_s / max(t, 1e-3)))) // 16384 * 16384
-    t = cpu_conv_sample(workload, sample, threads)
-    return {"value": sample / t, "unit": "edges/s", "cores": threads, "kind": "port",
-            "sample": f"{sample} edges of the same graph (fp32 torch-CPU oracle, chunks of 16384 edges), {t:.1f} s"}
+    fn, kind = (reference_conv_sample, "reference") if import_reference() is not None else (cpu_conv_sample, "port")
+    for _ in range(warmup):
+        fn(workload, 16384, threads)
+    times = [fn(workload, CPU_SAMPLE_EDGES, threads) for _ in range(max(1, steps))]
+    t = sum(times) / len(times)
+    what = ("e3nn 0.6.0 itself (eager fp32 torch-CPU, identity opt_einsum_fx stand-in, dead FX nodes removed)"
+            if kind == "reference" else "fp32 torch-CPU oracle port (the reference is not installed in baseline/_ref)")
+    base = {"value": CPU_SAMPLE_EDGES / t, "unit": "edges/s", "cores": threads, "kind": kind,
+            "sample": f"{CPU_SAMPLE_EDGES} edges of the same graph in chunks of 16384, {what}, {t:.1f} s per step"}
+    return CPU_SAMPLE_EDGES / t, t, len(times), base
+
+
+def cpu_baseline(workload: str):
+    return cpu_conv_arm(workload, steps=1, warmup=1)[3]
 
 
 def run_reference(args):
+    """CPU arm: the reference's own implementation of the workload on the host cores, a bounded sample per step.
+    Under torchrun only rank 0 works."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    threads = os.cpu_count() or 1
+    steps, warmup = max(1, min(args.steps, 3)), min(args.warmup, 1)
     if args.workload == "interaction_l3":
-        n = 1024
-        for _ in range(min(args.warmup, 1)):
-            cpu_interaction_sample(256, threads)
-        runs = [cpu_interaction_sample(n, threads) for _ in range(max(1, min(args.steps, 3)))]
-        edges, t = runs[0][0], sum(r[1] for r in runs) / len(runs)
-        value = edges / t
-        sample = f"{n} atoms / {edges} edges per step at the same density (fp32 torch-CPU oracle, forward + position gradient)"
+        value, t, steps, base = cpu_interaction_arm(steps, warmup)
         metric = "TP edges/sec (uvu l<=3, fp32): interaction block forward + gradient w.r.t. positions"
-        config = {"workload": "interaction_l3", "atoms": 262144, "cutoff": 5.0, "sample_atoms": n}
-        steps = len(runs)
+        config = {"workload": "interaction_l3", "atoms": 262144, "cutoff": 5.0, "sample_atoms": CPU_SAMPLE_ATOMS}
     else:
         workload = args.workload if args.workload in WORKLOADS else "conv_l2_15"
         layout, nodes, degree = WORKLOADS[workload]
-        sample_edges = 65536
-        for _ in range(min(args.warmup, 1)):
-            cpu_conv_sample(workload, 16384, threads)
-        times = [cpu_conv_sample(workload, sample_edges, threads) for _ in range(max(1, min(args.steps, 5)))]
-        t = sum(times) / len(times)
-        value = sample_edges / t
-        sample = f"{sample_edges} edges per step of the same graph (fp32 torch-CPU oracle)"
+        value, t, steps, base = cpu_conv_arm(workload, steps, warmup)
         metric = "TP edges/sec (fused SH + uvu + scatter, fp32)"
-        config = {"workload": workload, "nodes": nodes, "edges": nodes * degree, "in_degree": degree}
-        steps = len(times)
+        config = {"workload": workload, "nodes": nodes, "edges": nodes * degree, "in_degree": degree,
+                  "sample_edges": CPU_SAMPLE_EDGES}
     print(json.dumps({
         "impl": "reference", "metric": metric, "value": value, "unit": "edges/s", "n_gpus": args.gpus, "steps": steps,
-        "warmup": min(args.warmup, 1), "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "strong",
+        "warmup": warmup, "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config,
-        "cpu_baseline": {"value": value, "unit": "edges/s", "cores": threads, "kind": "port", "sample": sample},
+        "cpu_baseline": base,
         "e2e": {"value": value, "unit": "edges/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }), flush=True)
 
