@@ -46,9 +46,6 @@ WORKLOADS = {
     "conv_l3_23": ("cfg5_23", 65536, 32),
 }
 DEFAULT_WORKLOAD = "interaction_l3"
-# DRAM bytes (read + write) of one conv launch measured with ncu on a 1/8-size graph and scaled
-# linearly in the edge count (profiles/); None until a capture exists for the layout.
-NCU_TRAFFIC_BYTES = {}
 
 
 def measured_peaks():
@@ -160,7 +157,9 @@ def run_ours(args):
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
     if world > 1:
-        torch.distributed.init_process_group("nccl", device_id=device)
+        from e3nn_b200 import sharding
+
+        sharding.init_process_group("nccl", device, timeout_s=600.0)
 
     if args.workload == "sh_l3":
         return run_sh(args, rank, world, device)
@@ -267,7 +266,7 @@ def finish(args, rank, world, d, tp, nodes, degree, edges_total, ms_step, kernel
     k_ms = kernel_ms[len(kernel_ms) // 2]
     bytes_per_launch = algorithmic_bytes_per_edge(tp, nodes, edges_total) * d["e_local"]
     achieved = bytes_per_launch / (k_ms * 1e-3) / 1e9
-    traffic = NCU_TRAFFIC_BYTES.get(args.workload) if nodes == WORKLOADS[args.workload][1] else None
+    traffic = None
     line = {
         "metric": "TP edges/sec (fused SH + uvu + scatter, fp32)",
         "value": edges_total / (ms_step * 1e-3),
@@ -459,6 +458,145 @@ def run_conv_train(args, rank, world, device):
     }), flush=True)
 
 
+def measure_tf32_peak(device) -> float:
+    """Dense tf32 matmul throughput of this GPU in TFLOP/s: torch.matmul on 8192^3 with tf32 allowed, best of 10
+    (the burst figure, measured the way the bf16 figure of MEASURED_PEAKS.json was)."""
+    n = 8192
+    a = torch.randn(n, n, device=device)
+    b = torch.randn(n, n, device=device)
+    old = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = True
+    try:
+        for _ in range(3):
+            a @ b
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        best = float("inf")
+        for _ in range(10):
+            start.record()
+            a @ b
+            stop.record()
+            torch.cuda.synchronize()
+            best = min(best, start.elapsed_time(stop))
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = old
+    return 2.0 * n ** 3 / (best * 1e-3) / 1e12
+
+
+def _median_launch_ms(fn, launches: int, flush=None):
+    """Median CUDA-event time of one launch of `fn` (events on the current stream directly around the call)."""
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ts = []
+    for _ in range(launches):
+        if flush is not None:
+            flush.zero_()
+        start.record()
+        fn()
+        stop.record()
+        torch.cuda.synchronize()
+        ts.append(start.elapsed_time(stop))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def secondary_workloads(device, tf32_peak: float):
+    """The other configurations of the path, one compact record each, timed through the C ABI with outputs
+    allocated beforehand: spherical harmonics of 4,194,304 vectors, the fused convolution on the 15- and 11-path
+    l <= 2 layouts (65,536 nodes x 32 edges), the 1,048,576-row fully connected product + Linear, and the
+    10,000-row product.  Inputs are far larger than L2 except where `l2` says otherwise."""
+    from e3nn_b200 import _lib, layouts, o3
+
+    peak, peak_kind = measured_peaks()
+    P, core = _lib._ptr, _lib.core()
+    out = []
+    gen = torch.Generator(device=device).manual_seed(7)
+    status = torch.zeros(1, dtype=torch.int32, device=device)
+
+    # ---- spherical harmonics, lmax 3, normalize, 'component'
+    n = 4_194_304
+    vec = torch.randn(n, 3, device=device, generator=gen)
+    y = torch.empty(n, 16, device=device)
+    flush = torch.empty(64 * 1024 * 1024, device=device)   # 256 MB, written between launches
+
+    def sh():
+        rc = core.e3b_sh_fwd(P(vec), P(y), n, 3, 1, 0, _lib.stream_ptr())
+        assert rc == 0
+    for _ in range(3):
+        sh()
+    ms = _median_launch_ms(sh, 50, flush)
+    out.append({"workload": "sh_l3", "metric": "SH edges/sec (lmax 3, fp32)", "value": n / (ms * 1e-3), "unit": "edges/s",
+                "kernel": "sh_fwd_kernel<3>", "kernel_ms": ms, "launches": 50, "l2": "256 MB written between launches",
+                "roofline": {"bound": "hbm", "achieved": 76.0 * n / (ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+                             "frac": 76.0 * n / (ms * 1e-3) / 1e9 / peak, "peak_kind": f"of {peak_kind}"}})
+    del vec, y
+
+    # ---- fused convolution, l <= 2 layouts
+    for name in ("conv_l2_15", "conv_l2_11"):
+        layout, nodes, degree = WORKLOADS[name]
+        d = make_graph(layout, nodes, degree, 0, 1, device)
+        tp, E = d["tp"], nodes * degree
+        mod = tp._uvu_module()
+        res = torch.empty(nodes, tp.irreps_out.dim, device=device)
+
+        def conv():
+            rc = mod.lib.e3b_conv_fwd(P(d["node_x_local"]), P(d["vec"]), 1, P(d["src"]), P(d["rowptr"]), None, P(d["w"]),
+                                      P(res), nodes, nodes, E, degree ** -0.5, P(status), _lib.stream_ptr())
+            assert rc == 0
+        for _ in range(3):
+            conv()
+        ms = _median_launch_ms(conv, 20)
+        per_edge = algorithmic_bytes_per_edge(tp, nodes, E)
+        out.append({"workload": name, "metric": "TP edges/sec (fused SH + uvu + scatter, fp32)", "value": E / (ms * 1e-3),
+                    "unit": "edges/s", "kernel": "conv_fwd_tma_kernel", "kernel_ms": ms, "launches": 20,
+                    "paths": len(tp.instructions), "l2": "per-edge weights (%.1f GB) far larger than L2" % (4e-9 * tp.weight_numel * E),
+                    "roofline": {"bound": "hbm", "achieved": per_edge * E / (ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+                                 "frac": per_edge * E / (ms * 1e-3) / 1e9 / peak, "peak_kind": f"of {peak_kind}",
+                                 "algorithmic_bytes_per_edge": per_edge}})
+        del d, res
+    torch.cuda.empty_cache()
+
+    # ---- fully connected product + Linear, 1,048,576 rows (tensor cores, plain tf32)
+    rows = 1_048_576
+    tp = o3.FullyConnectedTensorProduct("128x0e+64x1o+32x2e", "0e+1o+2e+3o", "128x0e+64x1o+32x2e", math_mode="tf32").to(device)
+    lin = o3.Linear(tp.irreps_out, tp.irreps_out, math_mode="tf32").to(device)
+    with torch.no_grad():
+        for view in tp.weight_views():
+            view.div_((view.shape[0] * view.shape[1]) ** 0.5)
+        x = torch.randn(rows, tp.irreps_in1.dim, device=device, generator=gen)
+        y2 = torch.randn(rows, tp.irreps_in2.dim, device=device, generator=gen)
+        for _ in range(3):
+            lin(tp(x, y2))
+        ms_tp = _median_launch_ms(lambda: tp(x, y2), 10)
+        ms_both = _median_launch_ms(lambda: lin(tp(x, y2)), 10)
+    tf = 282_624.0 * rows / (ms_tp * 1e-3) / 1e12
+    tf_both = (282_624.0 + 67_584.0) * rows / (ms_both * 1e-3) / 1e12
+    out.append({"workload": "uvw_fctp", "metric": "uvw TP rows/sec (tf32 tensor cores) + Linear", "value": rows / (ms_both * 1e-3),
+                "unit": "rows/s", "kernel": "uvw_tc_kernel",
+                "kernel_ms": ms_tp, "tp_plus_linear_ms": ms_both, "launches": 10,
+                "roofline": {"bound": "tensor", "achieved": tf, "peak": tf32_peak, "unit": "TFLOP/s", "frac": tf / tf32_peak,
+                             "peak_kind": "tf32 matmul measured in this run", "tp_plus_linear_tflops": tf_both,
+                             "tp_plus_linear_frac": tf_both / tf32_peak,
+                             "hbm_frac_tp": 3904.0 * rows / (ms_tp * 1e-3) / 1e9 / peak,
+                             "hbm_frac_tp_plus_linear": 3904.0 * rows / (ms_both * 1e-3) / 1e9 / peak}})
+    del x, y2, tp, lin
+    torch.cuda.empty_cache()
+
+    # ---- the 10,000-row product (23 MB of operands: a latency figure)
+    tp = o3.FullyConnectedTensorProduct("32x0e+32x1o+32x2e", "1x0e+1x1o+1x2e", "32x0e+32x1o+32x2e").to(device)
+    with torch.no_grad():
+        x = torch.randn(10_000, tp.irreps_in1.dim, device=device, generator=gen)
+        y2 = torch.randn(10_000, tp.irreps_in2.dim, device=device, generator=gen)
+        for _ in range(3):
+            tp(x, y2)
+        ms = _median_launch_ms(lambda: tp(x, y2), 50)
+    out.append({"workload": "uvw_cfg1", "metric": "uvw TP rows/sec (10,000 rows, fp32)", "value": 10_000 / (ms * 1e-3),
+                "unit": "rows/s", "kernel": "dense_fwd_kernel", "kernel_ms": ms, "launches": 50,
+                "l2": "operands are L2 resident: launch latency, not bandwidth"})
+    del x, y2, tp, flush
+    torch.cuda.empty_cache()
+    return out
+
+
 def interaction_problem(n_atoms: int, seed: int = 0, device=None):
     """Positions and neighbour list of BASELINE config 5 at `n_atoms` (host tensors, edges sorted by destination).
 
@@ -498,6 +636,12 @@ def run_interaction(args, rank, world, device):
     from e3nn_b200 import sharding
 
     n_atoms = args.nodes if args.nodes > 0 else 262_144
+    secondary = tf32_peak = None
+    if world == 1 and not args.skip_secondary:
+        # the other configurations and the tf32 peak, measured before the large problem is resident
+        tf32_peak = measure_tf32_peak(device)
+        secondary = secondary_workloads(device, tf32_peak)
+        torch.cuda.empty_cache()
     box, pos_host, src, dst, shift, t_graph = interaction_problem(n_atoms, device=device)
     E = src.numel()
     rowptr_host = torch.zeros(n_atoms + 1, dtype=torch.int64)
@@ -521,20 +665,29 @@ def run_interaction(args, rank, world, device):
     x_full = torch.empty(n_atoms, 1024, device=device) if world > 1 else x_local
     tp = block.tp
 
-    def forward(p, xs, before_conv=None):
+    def forward(p, xs, before_conv=None, phase_mark=None):
         # the block's own forward: global indices into the (replicated) positions and the gathered features,
         # the rank's local CSR -> the rank's output rows
-        return block(p, xs, src_d, dst_glob, rowptr, shift_d, before_conv=before_conv)
+        return block(p, xs, src_d, dst_glob, rowptr, shift_d, before_conv=before_conv, phase_mark=phase_mark)
 
-    def step(p_in):
+    def step(p_in, phase_mark=None, keep=None):
+        mark = phase_mark if phase_mark is not None else (lambda name: None)
+        mark("start")
         wait = None
         if world > 1:
             # asynchronous: the transfer overlaps the edge embedding and the radial layers, which do not read features
             _, wait = sharding.all_gather_rows(x_local, bounds, out=x_full, async_op=True)
         p = p_in.detach().requires_grad_(True)
-        (forward(p, x_full, wait) * G).sum().backward()
+        out = forward(p, x_full, wait, phase_mark)
+        loss = (out * G).sum()
+        mark("loss")
+        loss.backward()
+        mark("bwd_embed")
         if world > 1:
             torch.distributed.all_reduce(p.grad)
+        mark("allreduce")
+        if keep is not None:
+            keep["out"] = out.detach()
         return p.grad
 
     def barrier():
@@ -560,6 +713,28 @@ def run_interaction(args, rank, world, device):
         torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
     ms_step = t.item() / args.steps
     clocks = sampler.stop() if rank == 0 else None
+
+    # ---- what the step computed, reduced over the ranks (the same numbers at every N), and the phases of one step
+    keep = {}
+    marks = []
+
+    def phase_mark(name):
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        marks.append((name, ev))
+
+    g = step(pos_d, phase_mark, keep)
+    torch.cuda.synchronize()
+    sums = torch.stack([keep["out"].double().pow(2).sum(), torch.tensor(float(keep["out"].numel()), device=device, dtype=torch.float64)])
+    if world > 1:
+        torch.distributed.all_reduce(sums)
+    check = {"out_rms": (sums[0] / sums[1]).sqrt().item(), "dpos_rms": g.double().pow(2).mean().sqrt().item(),
+             "dpos_abs_sum": g.double().abs().sum().item(), "dpos_sum": g.double().sum(0).abs().max().item()}
+    phase_ms = {}
+    for (_, e_prev), (name, e_now) in zip(marks, marks[1:]):
+        phase_ms[name] = phase_ms.get(name, 0.0) + e_prev.elapsed_time(e_now)
+    del keep, marks
+    status_word = e3nn_b200.last_status_code()
 
     # ---- dominant kernel alone (conv_bwd) and the forward convolution, events directly around the launches
     mod = tp._uvu_module()
@@ -691,7 +866,16 @@ def run_interaction(args, rank, world, device):
         "e2e": e2e,
         "gpu_launches": args.steps * 12,
         "clocks": clocks,
+        "check": check,
+        "phase_ms": phase_ms,
+        "kernel_status": status_word,
     }
+    if clocks and clocks.get("sm_mhz"):
+        line["ms_per_step_x_sm_ghz"] = ms_step * clocks["sm_mhz"] * 1e-3   # for comparing N against N at different clocks
+    if tf32_peak is not None:
+        line["tf32_peak_tflops"] = tf32_peak
+    if secondary is not None:
+        line["secondary"] = secondary
     if world == 1 and not args.skip_cpu:
         line["cpu_baseline"] = cpu_interaction_baseline()
     print(json.dumps(line), flush=True)
@@ -1075,6 +1259,7 @@ def main():
     ap.add_argument("--nodes", type=int, default=0, help="override the node count (smaller graphs for profiling)")
     ap.add_argument("--skip-e2e", action="store_true", help="profiling runs: skip the host-buffer leg")
     ap.add_argument("--skip-cpu", action="store_true", help="profiling runs: skip the CPU baseline leg")
+    ap.add_argument("--skip-secondary", action="store_true", help="profiling runs: skip the list of the other configurations")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -6,7 +6,8 @@
 CUDA only: there is no CPU implementation and no fallback to PyTorch operators.
 """
 from . import o3
+from ._lib import E3BError, check_status, last_status_code
 from .message_passing import conv_uvu, csr_from_dst
 
-__version__ = "0.1.0"
-__all__ = ["o3", "conv_uvu", "csr_from_dst"]
+__version__ = "0.2.0"
+__all__ = ["o3", "conv_uvu", "csr_from_dst", "check_status", "last_status_code", "E3BError"]

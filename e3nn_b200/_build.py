@@ -10,6 +10,8 @@ Two kinds of shared objects are produced:
 """
 from __future__ import annotations
 
+import contextlib
+import fcntl
 import os
 import shutil
 import subprocess
@@ -21,13 +23,40 @@ CSRC = os.path.join(PKG, "csrc")
 LIB_DIR = os.path.join(PKG, "lib")
 LAYOUT_DIR = os.path.join(PKG, "_layouts")
 CORE_LIB = os.path.join(LIB_DIR, "libe3nn_b200.so")
-CORE_SOURCES = ["abi.cu", "sh.cu", "csr.cu", "dense.cu", "radial.cu", "neighbor.cu", "gate.cu"]
+CORE_SOURCES = ["abi.cu", "sh.cu", "csr.cu", "dense.cu", "radial.cu", "neighbor.cu", "gate.cu", "selftest.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC",
 ]
 _lock = threading.Lock()
+
+
+_target_locks = {}
+
+
+@contextlib.contextmanager
+def _build_lock(name: str):
+    """One builder per target at a time, across threads (a lock per target) and across processes (an advisory lock
+    on a file beside the target): ranks started together that all miss the same module take turns, and the later
+    ones find the first one's result.  Different targets build in parallel."""
+    with _lock:
+        tl = _target_locks.setdefault(name, threading.Lock())
+    with tl:
+        os.makedirs(LAYOUT_DIR, exist_ok=True)
+        with open(os.path.join(LAYOUT_DIR, f".lock_{name}"), "w") as f:
+            fcntl.flock(f, fcntl.LOCK_EX)
+            try:
+                yield
+            finally:
+                fcntl.flock(f, fcntl.LOCK_UN)
+
+
+def _write_atomic(path: str, text: str) -> None:
+    tmp = f"{path}.tmp{os.getpid()}"
+    with open(tmp, "w") as f:
+        f.write(text)
+    os.replace(tmp, path)
 
 
 def nvcc_path() -> Optional[str]:
@@ -50,9 +79,9 @@ def generate_sh_header() -> str:
 
     path = os.path.join(CSRC, "sh_gen.cuh")
     text = sh.emit_header()
-    if not os.path.exists(path) or open(path).read() != text:
-        with open(path, "w") as f:
-            f.write(text)
+    with _build_lock("sh_gen"):
+        if not os.path.exists(path) or open(path).read() != text:
+            _write_atomic(path, text)
     return path
 
 
@@ -67,18 +96,20 @@ def build_core(force: bool = False, verbose: bool = False) -> str:
     nvcc = nvcc_path()
     if nvcc is None:
         raise RuntimeError("nvcc not found: cannot build libe3nn_b200.so")
-    with _lock:
+    header = generate_sh_header()
+    with _build_lock("core"):
         os.makedirs(LIB_DIR, exist_ok=True)
-        header = generate_sh_header()
         srcs = [os.path.join(CSRC, s) for s in CORE_SOURCES if os.path.exists(os.path.join(CSRC, s))]
         deps = srcs + [header, os.path.join(CSRC, "common.cuh"), os.path.join(PKG, "..", "include", "e3nn_b200.h")]
         deps += [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith(".cuh")]
         if not force and _newer(CORE_LIB, deps):
             return CORE_LIB
-        cmd = [nvcc] + _flags() + ["-shared", "-t", "0", "-o", CORE_LIB] + srcs
+        tmp = CORE_LIB + f".tmp{os.getpid()}"
+        cmd = [nvcc] + _flags() + ["-shared", "-t", "0", "-o", tmp] + srcs
         if verbose:
             cmd.insert(1, "-Xptxas=-v")
         _run(cmd, "libe3nn_b200.so")
+        os.replace(tmp, CORE_LIB)
     return CORE_LIB
 
 
@@ -87,7 +118,8 @@ def build_layout_module(kind: str, key: str, source: str, force: bool = False, e
     os.makedirs(LAYOUT_DIR, exist_ok=True)
     cu = os.path.join(LAYOUT_DIR, f"{kind}_{key}.cu")
     so = os.path.join(LAYOUT_DIR, f"{kind}_{key}.so")
-    with _lock:
+    generate_sh_header()
+    with _build_lock(f"{kind}_{key}"):
         same = os.path.exists(cu) and open(cu).read() == source
         if same and os.path.exists(so) and not force and _newer(so, [cu, os.path.join(CSRC, "layout_common.cuh")]):
             return so
@@ -97,10 +129,8 @@ def build_layout_module(kind: str, key: str, source: str, force: bool = False, e
                 f"layout module {kind}_{key} is not built and nvcc is not available to build it; "
                 "run __graft_entry__.build() (or e3nn_b200.prebuild) on a machine with the CUDA toolkit"
             )
-        generate_sh_header()
         if not same:
-            with open(cu, "w") as f:
-                f.write(source)
+            _write_atomic(cu, source)
         tmp = so + f".tmp{os.getpid()}"
         cmd = [nvcc] + _flags() + (extra_flags or []) + ["-I", CSRC, "-shared", "-o", tmp, cu]
         _run(cmd, os.path.basename(so))

@@ -5,6 +5,7 @@ error that says how to build it, and every op raises for tensors that are not on
 """
 from __future__ import annotations
 
+import contextlib
 import ctypes
 import os
 import threading
@@ -32,6 +33,22 @@ def stream_ptr() -> c_void_p:
     return c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
+NVTX_ENABLED = os.environ.get("E3NN_B200_NVTX", "0") not in ("", "0")
+
+
+@contextlib.contextmanager
+def nvtx_range(name: str):
+    """NVTX range around a kernel launch (visible in Nsight timelines) when E3NN_B200_NVTX=1; free otherwise."""
+    if not NVTX_ENABLED:
+        yield
+        return
+    torch.cuda.nvtx.range_push(name)
+    try:
+        yield
+    finally:
+        torch.cuda.nvtx.range_pop()
+
+
 def require_cuda(*tensors: torch.Tensor) -> None:
     for t in tensors:
         if t is not None and not t.is_cuda:
@@ -41,8 +58,122 @@ def require_cuda(*tensors: torch.Tensor) -> None:
             )
 
 
+# ------------------------------------------------------------------------------------------- kernel status
+# Kernels report conditions they cannot raise themselves through a status word in device memory: 1 = a destination
+# index out of range (CSR builder), 2 = a source / edge index out of range (the access was skipped), 3 = a bounded
+# wait on an mbarrier gave up (the kernel returned early, its output is incomplete).  One word per device lives for
+# the life of the process.  After every launch that can raise it, a 4-byte copy into pinned host memory is enqueued
+# behind the kernel; the next call of any op on that device looks at the copy if it has landed (no
+# synchronisation) and raises; `check_status` synchronises and raises.  A code stays until it is raised once.
+class _DeviceStatus:
+    def __init__(self, device: torch.device):
+        self.device = device
+        self.word = torch.zeros(1, dtype=torch.int32, device=device)
+        self.host = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self.event: Optional[torch.cuda.Event] = None
+
+    def clear(self) -> None:
+        self.word.zero_()
+        self.host.zero_()
+        self.event = None
+
+
+_status: Dict[int, _DeviceStatus] = {}
+
+
+def _device_status(device: torch.device) -> _DeviceStatus:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    st = _status.get(idx)
+    if st is None:
+        st = _status[idx] = _DeviceStatus(torch.device("cuda", idx))
+    return st
+
+
+def status_word(device: torch.device) -> torch.Tensor:
+    """The device's persistent int32 status word (pass its pointer to the kernels)."""
+    return _device_status(device).word
+
+
+def _raise_status(code: int, what: str) -> None:
+    if code == 2:
+        raise IndexError(f"{what}: an edge or source index was outside its range (the kernel skipped the access)")
+    if code == 1:
+        raise IndexError(f"{what}: a destination index was outside [0, num_nodes)")
+    if code == 3:
+        raise E3BError(f"{what}: a bounded wait inside a kernel gave up (status 3); the output of that launch is incomplete")
+    raise E3BError(f"{what}: kernel status {code}")
+
+
+def status_after_launch(device: torch.device) -> None:
+    """Enqueue the read-back of the status word behind the launches made so far on the current stream."""
+    if torch.cuda.is_current_stream_capturing():
+        return
+    st = _device_status(device)
+    with torch.cuda.device(st.device):
+        st.host.copy_(st.word, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+    st.event = ev
+
+
+def poll_status(device: torch.device, what: str = "an earlier e3nn_b200 kernel") -> None:
+    """Raise if an earlier launch on `device` has reported a condition and its read-back has landed.  Never waits."""
+    st = _status.get(device.index if device.index is not None else torch.cuda.current_device())
+    if st is None or st.event is None or torch.cuda.is_current_stream_capturing() or not st.event.query():
+        return
+    code = int(st.host[0])
+    st.event = None
+    if code != 0:
+        st.clear()
+        _raise_status(code, what)
+
+
+def last_status_code(device: Optional[torch.device] = None) -> int:
+    """Synchronise `device` (default: the current one) and return its status word without raising or clearing."""
+    dev = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+    st = _device_status(dev)
+    return int(st.word.item())
+
+
+def check_status(device: Optional[torch.device] = None, what: str = "e3nn_b200 kernels") -> None:
+    """Synchronise `device` and raise if any launch since the last check reported a condition."""
+    dev = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+    code = last_status_code(dev)
+    if code != 0:
+        _device_status(dev).clear()
+        _raise_status(code, what)
+
+
+def require_same_device(*tensors: Optional[torch.Tensor]) -> None:
+    """Every tensor whose pointer goes to a kernel must be on one CUDA device (a host pointer or another GPU's
+    memory would be dereferenced by the kernel)."""
+    first = None
+    for t in tensors:
+        if t is None:
+            continue
+        require_cuda(t)
+        if first is None:
+            first = t.device
+        elif t.device != first:
+            raise RuntimeError(f"expected all tensors on {first}, got one on {t.device}")
+
+
+def require_operand(t: torch.Tensor, like: torch.Tensor, name: str, numel: Optional[int] = None,
+                    dtype: torch.dtype = torch.float32) -> None:
+    """A tensor whose pointer a kernel dereferences: on the device of `like`, of `dtype`, with `numel` elements.
+    Raises the reference's error types (`RuntimeError` for device / dtype, `torch._assert` for the size) instead
+    of letting the kernel read a host pointer or run past the end of a buffer."""
+    if not t.is_cuda or t.device != like.device:
+        raise RuntimeError(f"Expected all tensors to be on the same device, but {name} is on {t.device} "
+                           f"and the features are on {like.device}")
+    if t.dtype != dtype:
+        raise RuntimeError(f"{name} must be {dtype}, got {t.dtype}")
+    if numel is not None:
+        torch._assert(t.numel() == numel, f"Invalid {name} shape: expected {numel} elements, got {t.numel()}")
+
+
 def core() -> ctypes.CDLL:
-    """The fixed-function library; built on first use when nvcc is present."""
+    """The fixed-function library; (re)built on first use when nvcc is present and a source is newer."""
     global _core
     if _core is not None:
         return _core
@@ -50,13 +181,13 @@ def core() -> ctypes.CDLL:
         if _core is not None:
             return _core
         path = _build.CORE_LIB
-        if not os.path.exists(path):
-            if _build.nvcc_path() is None:
-                raise E3BError(
-                    f"{path} is missing and nvcc is not available to build it. "
-                    "Build it with `python -c 'import __graft_entry__ as g; g.build()'` on a machine with CUDA 12.9."
-                )
-            _build.build_core()
+        if _build.nvcc_path() is not None:
+            _build.build_core()        # compares modification times: a no-op when the library is up to date
+        elif not os.path.exists(path):
+            raise E3BError(
+                f"{path} is missing and nvcc is not available to build it. "
+                "Build it with `python -c 'import __graft_entry__ as g; g.build()'` on a machine with CUDA 12.9."
+            )
         lib = ctypes.CDLL(path)
         lib.e3b_abi_version.restype = c_int
         lib.e3b_last_error.restype = c_char_p
@@ -78,6 +209,8 @@ def core() -> ctypes.CDLL:
                                           c_void_p, c_void_p, c_void_p]
         lib.e3b_gate_fwd.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]
         lib.e3b_gate_bwd.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]
+        lib.e3b_selftest_bounded_wait.argtypes = [c_void_p, ctypes.c_uint, c_void_p]
+        lib.e3b_selftest_bounded_wait.restype = c_int
         for name in ("e3b_sh_fwd", "e3b_sh_bwd", "e3b_csr_from_dst", "e3b_dense_fwd", "e3b_dense_bwd_w", "e3b_fill_columns",
                      "e3b_radial_embed_fwd", "e3b_radial_embed_bwd", "e3b_neighbor_count", "e3b_neighbor_fill",
                      "e3b_gate_fwd", "e3b_gate_bwd"):
@@ -200,7 +333,6 @@ class TcGemmModule:
         self.key = lib.e3b_layout_key().decode()
         self.scratch_bytes = int(lib.e3b_tc_gemm_scratch_bytes())
         self._scratch: Dict[str, torch.Tensor] = {}
-        self.last_status = None
 
     def check(self, rc: int, what: str) -> None:
         if rc != 0:
@@ -210,12 +342,12 @@ class TcGemmModule:
         dev = out.device
         # prepared weights live in a per-stream-ordered scratch tensor owned by the caller side (here)
         scratch = torch.empty(max(self.scratch_bytes, 16), dtype=torch.uint8, device=dev)
-        status = torch.zeros(1, dtype=torch.int32, device=dev)
-        with torch.cuda.device(dev):
+        poll_status(dev)
+        with torch.cuda.device(dev), nvtx_range("e3b_tc_gemm_fwd " + self.key):
             rc = self.lib.e3b_tc_gemm_fwd(_ptr(x1), _ptr(x2), _ptr(weight), _ptr(out), x1.shape[0], precision,
-                                          _ptr(scratch), None, _ptr(status), stream_ptr())
+                                          _ptr(scratch), None, _ptr(status_word(dev)), stream_ptr())
         self.check(rc, "e3b_tc_gemm_fwd")
-        self.last_status = status
+        status_after_launch(dev)
         return out
 
 

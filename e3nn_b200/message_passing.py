@@ -53,19 +53,19 @@ class _ConvFunction(torch.autograd.Function):
         N = rowptr.numel() - 1
         E = edge_src.numel()
         out = torch.empty(N, mod.dout, dtype=torch.float32, device=node_x.device)
-        status = torch.zeros(1, dtype=torch.int32, device=node_x.device)
-        with torch.cuda.device(node_x.device):
+        status = _lib.status_word(node_x.device)
+        with torch.cuda.device(node_x.device), _lib.nvtx_range("e3b_conv_fwd"):
             rc = mod.lib.e3b_conv_fwd(_lib._ptr(node_x), _lib._ptr(x2), in2_mode, _lib._ptr(edge_src), _lib._ptr(rowptr),
                                       _lib._ptr(perm), _lib._ptr(weight), _lib._ptr(out), N, node_x.shape[0], E,
                                       scale, _lib._ptr(status), _lib.stream_ptr())
         mod.check(rc, "e3b_conv_fwd")
+        _lib.status_after_launch(node_x.device)
         ctx.save_for_backward(node_x, x2, weight, edge_src, rowptr, perm if perm is not None else torch.empty(0))
         ctx.meta = (mod, in2_mode, scale, perm is not None)
-        ctx.status = status
-        mod.last_status = status
         return out
 
     @staticmethod
+    @torch.autograd.function.once_differentiable
     def backward(ctx, grad_out):
         node_x, x2, weight, edge_src, rowptr, perm = ctx.saved_tensors
         mod, in2_mode, scale, has_perm = ctx.meta
@@ -74,23 +74,25 @@ class _ConvFunction(torch.autograd.Function):
         gx = None
         if ctx.needs_input_grad[0]:
             gx = torch.empty_like(node_x)
-            st = torch.zeros(1, dtype=torch.int32, device=node_x.device)
-            with torch.cuda.device(node_x.device):
+            st = _lib.status_word(node_x.device)
+            with torch.cuda.device(node_x.device), _lib.nvtx_range("e3b_conv_bwd_x"):
                 rc = mod.lib.e3b_conv_bwd_x(_lib._ptr(x2), in2_mode, _lib._ptr(edge_src), _lib._ptr(rowptr),
                                             _lib._ptr(perm) if has_perm else None, _lib._ptr(weight), _lib._ptr(grad_out),
                                             _lib._ptr(gx), N, node_x.shape[0], E, scale, _lib._ptr(st), _lib.stream_ptr())
             mod.check(rc, "e3b_conv_bwd_x")
+            _lib.status_after_launch(node_x.device)
             if not (ctx.needs_input_grad[1] or ctx.needs_input_grad[2]):
                 return gx, None, None, None, None, None, None, None, None
         gw = torch.empty_like(weight)
         gx2 = torch.empty_like(x2)
-        status = torch.zeros(1, dtype=torch.int32, device=node_x.device)
-        with torch.cuda.device(node_x.device):
+        status = _lib.status_word(node_x.device)
+        with torch.cuda.device(node_x.device), _lib.nvtx_range("e3b_conv_bwd"):
             rc = mod.lib.e3b_conv_bwd(_lib._ptr(node_x), _lib._ptr(x2), in2_mode, _lib._ptr(edge_src), _lib._ptr(rowptr),
                                       _lib._ptr(perm) if has_perm else None, _lib._ptr(weight), _lib._ptr(grad_out),
                                       _lib._ptr(gw), _lib._ptr(gx2), N, node_x.shape[0], E, scale, _lib._ptr(status),
                                       _lib.stream_ptr())
         mod.check(rc, "e3b_conv_bwd")
+        _lib.status_after_launch(node_x.device)
         return gx, gx2, gw, None, None, None, None, None, None
 
 
@@ -115,12 +117,17 @@ def conv_uvu(
     already sorted by destination).  With ``edge_attr_is_vector=True`` ``edge_attr`` holds the edge
     vectors ``[E, 3]`` and the spherical harmonics (``normalize=True, normalization='component'``) are
     evaluated inside the kernel; ``tp.irreps_in2`` must then be ``Y^0..Y^L``.
-    ``check_indices=True`` reads back the kernel's status word (a device synchronisation) and raises
-    ``IndexError`` if a source index was out of range.
+    ``check_indices=True`` synchronises, reads the device's status word and raises ``IndexError`` if a source
+    index was out of range.  Without it a reported condition (bad index, a bounded wait that gave up) is raised
+    by the next e3nn_b200 call on the device after the kernel has finished, or by `e3nn_b200.check_status()`.
     """
     _lib.require_cuda(node_features, edge_attr, weight, edge_src, rowptr)
-    if tp._uvw_ids or tp.shared_weights:
+    if tp._uvw_ids or getattr(tp, "_uuu_ids", None) or tp.shared_weights:
         raise NotImplementedError("conv_uvu needs a TensorProduct made of 'uvu' paths with shared_weights=False")
+    _lib.require_same_device(node_features, edge_attr, weight, edge_src, rowptr, perm)
+    if edge_src.dtype != torch.int64 or rowptr.dtype != torch.int64 or (perm is not None and perm.dtype != torch.int64):
+        raise TypeError("edge_src, rowptr and perm must be int64")
+    _lib.poll_status(node_features.device)
     mod = tp._uvu_module()
     in2_mode = 1 if edge_attr_is_vector else 0
     E = edge_src.numel()
@@ -137,9 +144,5 @@ def conv_uvu(
         rowptr.contiguous(), None if perm is None else perm.contiguous(), mod, in2_mode, float(scale),
     )
     if check_indices:  # synchronises: reads the status word the kernel wrote
-        code = int(mod.last_status.item())
-        if code == 2:
-            raise IndexError("edge_src holds a value outside [0, num_nodes)")
-        if code != 0:
-            raise _lib.E3BError(f"fused convolution kernel reported status {code} (a bounded wait gave up)")
+        _lib.check_status(node_features.device, "conv_uvu")
     return out

@@ -20,27 +20,26 @@ _ENVELOPE = {None: 0, "smooth_cutoff": 1}
 
 
 class _EdgeEmbedFunction(torch.autograd.Function):
-    last_status = None   # device status word of the most recent forward launch
-
     @staticmethod
     def forward(ctx, pos, edge_src, edge_dst, shift, w0, spec, w_scale, act_scale, act):
         E, N = edge_src.numel(), pos.shape[0]
         nb, hidden = w0.shape
         edge_vec = torch.empty(E, 3, dtype=torch.float32, device=pos.device)
         h = torch.empty(E, hidden, dtype=torch.float32, device=pos.device)
-        status = torch.zeros(1, dtype=torch.int32, device=pos.device)
-        with torch.cuda.device(pos.device):
+        status = _lib.status_word(pos.device)
+        with torch.cuda.device(pos.device), _lib.nvtx_range("e3b_radial_embed_fwd"):
             rc = _lib.core().e3b_radial_embed_fwd(
                 _lib._ptr(pos), _lib._ptr(edge_src), _lib._ptr(edge_dst), _lib._ptr(shift) if shift is not None else None,
                 _lib._ptr(w0), E, N, nb, hidden, *spec, w_scale, act_scale, act, _lib._ptr(edge_vec), _lib._ptr(h),
                 _lib._ptr(status), _lib.stream_ptr())
         _lib.check(rc, "e3b_radial_embed_fwd")
+        _lib.status_after_launch(pos.device)
         ctx.save_for_backward(pos, edge_src, edge_dst, shift if shift is not None else torch.empty(0), w0)
         ctx.meta = (shift is not None, spec, w_scale, act_scale, act)
-        _EdgeEmbedFunction.last_status = status
         return edge_vec, h
 
     @staticmethod
+    @torch.autograd.function.once_differentiable
     def backward(ctx, grad_vec, grad_h):
         pos, edge_src, edge_dst, shift, w0 = ctx.saved_tensors
         has_shift, spec, w_scale, act_scale, act = ctx.meta
@@ -51,13 +50,14 @@ class _EdgeEmbedFunction(torch.autograd.Function):
         grad_pos = torch.zeros_like(pos)
         if grad_h is None:
             grad_h = torch.zeros(E, hidden, dtype=torch.float32, device=pos.device)
-        status = torch.zeros(1, dtype=torch.int32, device=pos.device)
-        with torch.cuda.device(pos.device):
+        status = _lib.status_word(pos.device)
+        with torch.cuda.device(pos.device), _lib.nvtx_range("e3b_radial_embed_bwd"):
             rc = _lib.core().e3b_radial_embed_bwd(
                 _lib._ptr(pos), _lib._ptr(edge_src), _lib._ptr(edge_dst), _lib._ptr(shift) if has_shift else None,
                 _lib._ptr(w0), _lib._ptr(grad_h.contiguous()), _lib._ptr(grad_vec.contiguous()) if grad_vec is not None else None,
                 E, N, nb, hidden, *spec, w_scale, act_scale, act, _lib._ptr(grad_pos), _lib._ptr(status), _lib.stream_ptr())
         _lib.check(rc, "e3b_radial_embed_bwd")
+        _lib.status_after_launch(pos.device)
         return grad_pos, None, None, None, None, None, None, None, None
 
 
@@ -77,6 +77,8 @@ def edge_embed(pos: torch.Tensor, edge_src: torch.Tensor, edge_dst: torch.Tensor
     """
     if not pos.is_cuda:
         raise NotImplementedError("edge_embed runs on CUDA tensors only")
+    _lib.require_same_device(pos, edge_src, edge_dst, shift, w0)
+    _lib.poll_status(pos.device)
     if act not in _ACT:
         raise NotImplementedError(f"edge_embed: unsupported activation {act!r}")
     if pos.dtype != torch.float32 or w0.dtype != torch.float32:
@@ -96,6 +98,5 @@ def edge_embed(pos: torch.Tensor, edge_src: torch.Tensor, edge_dst: torch.Tensor
                                       w0.detach().contiguous() if not w0.requires_grad else w0.contiguous(),
                                       spec, float(w_scale), float(act_scale), _ACT[act])
     if check_indices:
-        if int(_EdgeEmbedFunction.last_status.item()) == 2:
-            raise IndexError("edge_embed: an edge index lies outside the node range")
+        _lib.check_status(pos.device, "edge_embed")
     return vec, h

@@ -58,6 +58,7 @@ class _ScaledMatmul(torch.autograd.Function):
         return out
 
     @staticmethod
+    @torch.autograd.function.once_differentiable
     def backward(ctx, grad_out):
         weight, x = ctx.saved_tensors
         grad_out = grad_out.contiguous()
@@ -98,6 +99,8 @@ class _Layer(torch.nn.Module):
         if use_tc:
             fwd, bwd = self._tc_specs()
             if fwd is not None and bwd is not None:
+                _lib.require_operand(self.weight, x, "layer weight", self.h_in * self.h_out)
+                torch._assert(x.shape[1] == self.h_in, "Incorrect last dimension for the layer input")
                 return _ScaledMatmul.apply(x.contiguous(), self.weight, fwd, bwd, self._scale())
         return x @ (self.weight * self._scale())
 

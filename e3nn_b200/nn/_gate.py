@@ -64,6 +64,7 @@ class _GateFunction(torch.autograd.Function):
         return out
 
     @staticmethod
+    @torch.autograd.function.once_differentiable
     def backward(ctx, grad_out):
         x, in_tbl, in_cst = ctx.saved_tensors
         rows, din = x.shape
@@ -155,5 +156,9 @@ class Gate(torch.nn.Module):
         torch._assert(features.shape[-1] == self.irreps_in.dim, "Incorrect last dimension for features")
         lead = features.shape[:-1]
         x = features.reshape(-1, self.irreps_in.dim).to(torch.float32).contiguous()
+        for name in ("_out_tbl", "_in_tbl"):
+            _lib.require_operand(getattr(self, name), x, f"Gate.{name} (move the module with .to(device))", None, torch.int32)
+        for name in ("_out_cst", "_in_cst"):
+            _lib.require_operand(getattr(self, name), x, f"Gate.{name} (move the module with .to(device))")
         out = _GateFunction.apply(x, self._out_tbl, self._out_cst, self._in_tbl, self._in_cst, self.irreps_out.dim)
         return out.reshape(*lead, self.irreps_out.dim)

@@ -110,12 +110,17 @@ class InteractionBlock(torch.nn.Module):
         return self.fc(basis)
 
     def forward(self, pos: torch.Tensor, node_features: torch.Tensor, edge_src: torch.Tensor, edge_dst: torch.Tensor,
-                rowptr: torch.Tensor, shift: Optional[torch.Tensor] = None, before_conv=None) -> torch.Tensor:
+                rowptr: torch.Tensor, shift: Optional[torch.Tensor] = None, before_conv=None,
+                phase_mark=None) -> torch.Tensor:
         """``edge_*`` must be sorted by destination and ``rowptr`` their CSR (`e3nn_b200.csr_from_dst`).
 
         ``before_conv``: optional callable run right before the convolution, the first step that reads
         ``node_features`` (a sharded caller passes the ``wait`` of its asynchronous feature all-gather, which then
-        overlaps the edge embedding and the radial network)."""
+        overlaps the edge embedding and the radial network).
+        ``phase_mark``: optional callable ``phase_mark(name)`` called on the launching stream at the phase
+        boundaries of the step (forward: after the radial network, after ``before_conv``, after the convolution,
+        after the Linear; backward, through tensor hooks: after the transposed Linear, after the convolution
+        gradient, after the transposed radial layer), e.g. to record CUDA events."""
         layer0 = self.fc.layer0
         fused = (pos.is_cuda and pos.dtype == torch.float32 and len(self.fc.hs) == 3 and self.num_basis <= 16
                  and self.fc.hs[1] in (32, 64, 96, 128) and not (torch.is_grad_enabled() and layer0.weight.requires_grad))
@@ -130,8 +135,20 @@ class InteractionBlock(torch.nn.Module):
             if shift is not None:
                 edge_vec = edge_vec + shift
             w = self.edge_weights(edge_vec)
+        mark = phase_mark if phase_mark is not None else (lambda name: None)
+        if phase_mark is not None and w.requires_grad:
+            w.register_hook(lambda g: mark("bwd_conv"))
+            if fused and h.requires_grad:
+                h.register_hook(lambda g: mark("bwd_radial"))
+        mark("radial")
         if before_conv is not None:
             before_conv()
+        mark("gather_wait")
         mid = conv_uvu(self.tp, node_features, edge_vec, edge_src, rowptr, w, scale=self.num_neighbors ** -0.5,
                        edge_attr_is_vector=True)
-        return self.lin(mid)
+        if phase_mark is not None and mid.requires_grad:
+            mid.register_hook(lambda g: mark("bwd_linear"))
+        mark("conv")
+        out = self.lin(mid)
+        mark("linear")
+        return out

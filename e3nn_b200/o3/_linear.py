@@ -58,6 +58,7 @@ class _LinearFunction(torch.autograd.Function):
         return out
 
     @staticmethod
+    @torch.autograd.function.once_differentiable
     def backward(ctx, grad_out):
         x, w = ctx.saved_tensors
         lin = ctx.lin
@@ -206,8 +207,13 @@ class Linear(torch.nn.Module):
         x = features.reshape(-1, self.irreps_in.dim).contiguous()
         if x.shape[0] == 0 or self.irreps_out.dim == 0:
             return features.new_zeros(*lead, self.irreps_out.dim)
-        w = weight.reshape(-1).contiguous() if weight.numel() > 0 else x.new_zeros(1)
-        b = bias.reshape(-1).contiguous() if bias.numel() > 0 else x.new_zeros(1)
+        if self.weight_numel > 0:
+            _lib.require_operand(weight, x, "weight", self.weight_numel)
+        if self.bias_numel > 0:
+            _lib.require_operand(bias, x, "bias", self.bias_numel)
+        _lib.poll_status(x.device)
+        w = weight.reshape(-1).contiguous() if self.weight_numel > 0 else x.new_zeros(1)
+        b = bias.reshape(-1).contiguous() if self.bias_numel > 0 else x.new_zeros(1)
         out = _LinearFunction.apply(x, w, b, self)
         return out.reshape(*lead, self.irreps_out.dim)
 

@@ -21,7 +21,7 @@ class _SHFunction(torch.autograd.Function):
     def forward(ctx, x: torch.Tensor, lmax: int, normalize: bool, code: int):
         n = x.shape[0]
         out = torch.empty(n, (lmax + 1) ** 2, dtype=torch.float32, device=x.device)
-        with torch.cuda.device(x.device):
+        with torch.cuda.device(x.device), _lib.nvtx_range("e3b_sh_fwd"):
             rc = _lib.core().e3b_sh_fwd(_lib._ptr(x), _lib._ptr(out), n, lmax, int(normalize), code, _lib.stream_ptr())
         _lib.check(rc, "e3b_sh_fwd")
         ctx.save_for_backward(x)
@@ -29,6 +29,7 @@ class _SHFunction(torch.autograd.Function):
         return out
 
     @staticmethod
+    @torch.autograd.function.once_differentiable
     def backward(ctx, grad_out: torch.Tensor):
         (x,) = ctx.saved_tensors
         lmax, normalize, code = ctx.args

@@ -42,6 +42,7 @@ class _UvuFunction(torch.autograd.Function):
         return out
 
     @staticmethod
+    @torch.autograd.function.once_differentiable
     def backward(ctx, grad_out):
         x1, x2, w = ctx.saved_tensors
         mod = ctx.mod
@@ -71,6 +72,7 @@ class _UvwFunction(torch.autograd.Function):
         return out
 
     @staticmethod
+    @torch.autograd.function.once_differentiable
     def backward(ctx, grad_out):
         x1, x2, w = ctx.saved_tensors
         tp = ctx.tp
@@ -283,7 +285,8 @@ class TensorProduct(torch.nn.Module):
         torch._assert(x.shape[-1] == self._in1_dim, "Incorrect last dimension for x")
         torch._assert(y.shape[-1] == self._in2_dim, "Incorrect last dimension for y")
         w = self._get_weights(weight)
-        _lib.require_cuda(x, y, w if w.numel() > 0 else None)
+        _lib.require_same_device(x, y, w if w.numel() > 0 else None)
+        _lib.poll_status(x.device)
         for t in (x, y, w):
             if t.numel() > 0 and t.dtype != torch.float32:
                 raise TypeError(f"e3nn_b200 tensor products are fp32 only, got {t.dtype}")
@@ -413,7 +416,6 @@ class TensorProduct(torch.nn.Module):
             if self._tcg_spec is not None:
                 mod = _lib.tc_gemm_module(self._tcg_spec)
                 mod.run(x2d, y2d, w, out, 2)
-                self._last_tc_status = mod.last_status
                 return out
         w_row_stride = w.shape[1] if w.dim() == 2 else 0
         with torch.cuda.device(x2d.device):

@@ -47,6 +47,7 @@ def prebuild_linears() -> List[str]:
     lins = [
         Linear("128x0e+64x1o+32x2e", "128x0e+64x1o+32x2e"),
         Linear(bench_conv_tp("cfg5_23").irreps_out, "64x0e+64x1o+64x2e+64x3o"),
+        Linear(bench_conv_tp("cfg3_15").irreps_out, "64x0e+64x1o+64x2e", math_mode="tf32x3"),
     ]
     with ThreadPoolExecutor(max_workers=4) as pool:
         return list(pool.map(_build_linear, lins))

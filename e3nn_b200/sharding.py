@@ -10,10 +10,25 @@ are single-device edge lists).
 """
 from __future__ import annotations
 
+import datetime
+import os
 from typing import List, Optional, Tuple
 
 import torch
 import torch.distributed as dist
+
+
+def init_process_group(backend: str, device: Optional[torch.device] = None, timeout_s: float = 120.0, **kwargs) -> None:
+    """``torch.distributed.init_process_group`` with the failure behaviour this package relies on: every collective
+    carries a timeout (`timeout_s`), and with NCCL a collective that times out or fails asynchronously (a peer that
+    died between steps) is turned into an exception in the waiting rank instead of a hang: the communicator's
+    watchdog polls for asynchronous errors and aborts the communicator (``TORCH_NCCL_ASYNC_ERROR_HANDLING``, set
+    here unless the caller chose a value).  Rendezvous settings come from the environment as usual."""
+    if backend == "nccl":
+        os.environ.setdefault("TORCH_NCCL_ASYNC_ERROR_HANDLING", "1")
+        if device is not None:
+            kwargs.setdefault("device_id", device)
+    dist.init_process_group(backend, timeout=datetime.timedelta(seconds=timeout_s), **kwargs)
 
 
 def partition_rows_by_edges(rowptr: torch.Tensor, world: int) -> List[int]:

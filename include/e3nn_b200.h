@@ -203,6 +203,14 @@ int e3b_dense_bwd_w(const int32_t* plan_host, const int32_t* plan_dev, const flo
 int e3b_fill_columns(float* out, int64_t num_rows, int row_stride, int col0, int ncol, const float* bias, int add,
                      void* stream);
 
+/*
+ * Self-test of the bounded-wait convention of the pipelined kernels (no counterpart in the reference, which has
+ * no device code): one small block waits on an mbarrier that nothing arrives at, gives up after `limit` polls
+ * (1 .. 100000, each a try_wait with a short back-off), stores 3 in *status and returns.  The host reads the
+ * word like that of any other kernel; the device context stays usable.
+ */
+int e3b_selftest_bounded_wait(int32_t* status, unsigned limit, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

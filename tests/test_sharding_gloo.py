@@ -85,3 +85,30 @@ def test_partition_edge_cases():
         b = sharding.partition_rows_by_edges(rowptr, world)
         assert len(b) == world + 1 and b[0] == 0 and b[-1] == 5 and b == sorted(b)
     assert sharding.partition_rows_by_edges(torch.tensor([0]), 4) == [0, 0, 0, 0, 0]
+
+
+def _timeout_worker(rank, world, port, out_dir):
+    """Rank 1 leaves between steps (it never joins the second collective); rank 0's collective must end with an
+    error after the process-group timeout instead of waiting for ever."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    sharding.init_process_group("gloo", timeout_s=3.0)
+    x = torch.ones(4) * (rank + 1)
+    dist.all_reduce(x)                     # step 1: both ranks
+    assert float(x[0]) == 3.0
+    if rank == 1:
+        torch.save("left", os.path.join(out_dir, "r1.pt"))
+        os._exit(0)                        # leaves with nothing in flight
+    try:
+        dist.all_reduce(x)                 # step 2: the peer is gone
+        outcome = "no error"
+    except Exception as exc:               # gloo: a RuntimeError naming the timeout or the closed connection
+        outcome = f"error: {type(exc).__name__}"
+    torch.save(outcome, os.path.join(out_dir, "r0.pt"))
+    os._exit(0)
+
+
+def test_collective_with_a_missing_rank_times_out(tmp_path):
+    world = 2
+    mp.spawn(_timeout_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    assert torch.load(os.path.join(tmp_path, "r1.pt")) == "left"
+    assert torch.load(os.path.join(tmp_path, "r0.pt")).startswith("error")
