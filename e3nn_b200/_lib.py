@@ -305,11 +305,13 @@ def uvw_tc_module(spec) -> TcModule:
     mod = _tc_cache.get(key)
     if mod is not None:
         return mod
-    from .codegen import uvw_tc
+    from .codegen import uvw_post, uvw_tc
 
-    so = os.path.join(_build.LAYOUT_DIR, f"uvwtc_{key}.so")
+    # the kernel that applies the Clebsch-Gordan coupling after the matrix product, when the layout fits it
+    kind, gen = ("uvwpost", uvw_post) if uvw_post.plan_groups(spec) is not None else ("uvwtc", uvw_tc)
+    so = os.path.join(_build.LAYOUT_DIR, f"{kind}_{key}.so")
     if not os.path.exists(so) or _build.nvcc_path() is not None:
-        so = _build.build_layout_module("uvwtc", key, uvw_tc.emit_module(spec))
+        so = _build.build_layout_module(kind, key, gen.emit_module(spec))
     mod = TcModule(so)
     if mod.key != key:
         raise E3BError(f"layout module {so} was built for another layout ({mod.key} != {key})")

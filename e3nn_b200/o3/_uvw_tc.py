@@ -4,11 +4,11 @@ from __future__ import annotations
 import torch
 
 from .. import _lib
-from ..codegen import uvw_tc
+from ..codegen import uvw_post, uvw_tc
 
 
 def tc_eligible(tp) -> bool:
-    return uvw_tc.plan_groups(tp._spec) is not None
+    return uvw_post.plan_groups(tp._spec) is not None or uvw_tc.plan_groups(tp._spec) is not None
 
 
 def uvw_tc_forward(tp, x2d: torch.Tensor, y2d: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool):

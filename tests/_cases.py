@@ -36,6 +36,9 @@ def prebuild():
     for layout in [("32x0e+32x1o+32x2e", "1x0e+1x1o+1x2e", "32x0e+32x1o+32x2e"),
                    ("128x0e+64x1o+32x2e", "0e+1o+2e+3o", "128x0e+64x1o+32x2e")]:
         pb._build_tp(o3.FullyConnectedTensorProduct(*layout, math_mode="tf32x3"))
+        # the derived product that gives the gradient w.r.t. the first operand in the tensor-core modes
+        for mode in ("tf32", "tf32x3"):
+            pb._build_tp(o3.FullyConnectedTensorProduct(*layout, math_mode=mode)._vjp_module(0))
     pb._build_linear(o3.Linear("16x0e+8x1o+4x2e", "8x0e+8x1o+4x2e"))
     pb._build_linear(o3.Linear("64x0e+32x1o+32x2e", "32x0e+64x1o+32x2e"))
     pb._build_tp(o3.ElementwiseTensorProduct("4x0e+3x1o+2x2e+5x1e", "4x0e+3x1o+2x1o+5x2e"))

@@ -1010,3 +1010,43 @@ def test_norm_module():
         off += mul * ir.dim
     total.backward()
     assert rel_err(xg.grad.cpu(), x64.grad) < TOL
+
+
+# ----------------------------------------------------------------------------- product + Linear as one product
+@pytest.mark.parametrize("layout,mode,tol", [
+    (("32x0e+32x1o+32x2e", "1x0e+1x1o+1x2e", "32x0e+32x1o+32x2e"), "fp32", TOL),
+    (("8x0e+8x1o+4x2e", "1x0e+1x1o+1x2e", "8x0e+6x1o+4x2e+2x1e"), "fp32", TOL),
+    (("128x0e+64x1o+32x2e", "0e+1o+2e+3o", "128x0e+64x1o+32x2e"), "tf32", TOL_TF32),      # BASELINE config 4
+])
+def test_tensor_product_linear_fused(layout, mode, tol):
+    """``TensorProductLinear(tp, lin)(x, y)`` against ``lin(tp(x, y))`` evaluated by the fp64 oracle, forward and the
+    gradients w.r.t. both operands and both modules' weights."""
+    torch.manual_seed(21)
+    tp = o3.FullyConnectedTensorProduct(*layout, math_mode=mode).to(DEV)
+    with torch.no_grad():
+        for view in tp.weight_views():
+            view.div_((view.shape[0] * view.shape[1]) ** 0.5)
+    lin = o3.Linear(tp.irreps_out, tp.irreps_out).to(DEV)
+    fused = o3.TensorProductLinear(tp, lin)
+    Z = 515
+    x, y = torch.randn(Z, tp.irreps_in1.dim), torch.randn(Z, tp.irreps_in2.dim)
+    go = torch.randn(Z, lin.irreps_out.dim)
+    xg, yg = x.to(DEV).requires_grad_(True), y.to(DEV).requires_grad_(True)
+    out = fused(xg, yg)
+    out.backward(go.to(DEV))
+    e3nn_b200.check_status()
+    x64, y64 = x.double().requires_grad_(True), y.double().requires_grad_(True)
+    w64 = tp.weight.detach().cpu().double().requires_grad_(True)
+    l64 = lin.weight.detach().cpu().double().requires_grad_(True)
+    ref = orc.linear(str(tp.irreps_out), str(lin.irreps_out), _oracle_tp(tp, x64, y64, w64), l64)
+    ref.backward(go.double())
+    assert rel_err(out.detach().cpu(), ref.detach()) < tol
+    assert rel_err(xg.grad.cpu(), x64.grad) < tol
+    assert rel_err(yg.grad.cpu(), y64.grad) < tol
+    wtol = max(tol, 5e-5)     # weight gradients: float atomics over all rows
+    assert rel_err(tp.weight.grad.cpu(), w64.grad) < wtol
+    assert rel_err(lin.weight.grad.cpu(), l64.grad) < wtol
+    # the two modules side by side give the same result
+    with torch.no_grad():
+        two_step = lin(tp(x.to(DEV), y.to(DEV)))
+    assert rel_err(out.detach().cpu(), two_step.cpu().double()) < max(tol, 2e-6)
