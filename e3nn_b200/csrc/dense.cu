@@ -18,6 +18,7 @@
 //   pathk   : per path, per k (path base in word [off_pathk + path]) -> (cg_start, cg_count) pairs
 //   cg      : triples (i, j, coef)
 #include "common.cuh"
+#include "gate_act.cuh"
 
 namespace e3b {
 
@@ -31,12 +32,25 @@ constexpr int kKBlock = 32;                               // summation block of 
 
 struct DenseGroup { int out_off, mul_out, dim3, K, kent_start, w_stride; };
 
+// Gate applied where the contraction's result is still in registers (Linear followed by Gate).  Column c of the
+// contraction's output row is described by tbl[4 c ..] = {kind, destination column, activation, gate slot} and
+// cst[c]: kind 0 = scalar: final[z, dst] = cst * act(v); kind 2 = gate: gates[z, slot] = cst * act(v);
+// kind 1 = gated component: final[z, dst] = v * gates[z, slot] (its gate's launch ran before); kind 3 = unused.
+struct DenseGateEpilogue {
+    const int32_t* tbl;
+    const float* cst;
+    float* gates;       // [rows, n_slots] activated gates
+    float* final_out;   // [rows, dout_final]
+    int n_slots, dout_final;
+};
+
 template <bool VEC4>
 __global__ void __launch_bounds__(kDenseThreads) dense_fwd_kernel(const int32_t* __restrict__ plan,
         const float* __restrict__ x1, const float* __restrict__ x2, const float* __restrict__ W,
         float* __restrict__ out, int64_t Z, int group, int rows_z /* z per tile */, int accumulate,
         int64_t w_row_stride /* 0: shared weights, else floats between the weight rows of consecutive z */,
-        int k_chunk /* entries of the contraction staged at a time (= K when the whole A tile fits) */) {
+        int k_chunk /* entries of the contraction staged at a time (= K when the whole A tile fits) */,
+        DenseGateEpilogue ep /* tbl == nullptr: plain store */) {
     extern __shared__ float smem[];
     const int d1 = plan[1], d2 = plan[2], dout = plan[3];
     const int32_t* gp = plan + plan[7] + 6 * group;
@@ -160,6 +174,19 @@ __global__ void __launch_bounds__(kDenseThreads) dense_fwd_kernel(const int32_t*
             }
             }
             if (r0 < RT && w0 < g.mul_out) {
+                // gated epilogue: one table entry per channel (the components of a channel are consecutive columns
+                // with consecutive destinations and share the gate), fetched once per pass
+                int e_kind[kTN], e_dst[kTN], e_act[kTN], e_slot[kTN];
+                float e_cst[kTN];
+                if (ep.tbl != nullptr) {
+#pragma unroll
+                    for (int j = 0; j < kTN; ++j) {
+                        const int c = g.out_off + (w0 + j < g.mul_out ? w0 + j : 0) * g.dim3;
+                        const int4 t = *reinterpret_cast<const int4*>(ep.tbl + 4 * c);
+                        e_kind[j] = t.x; e_dst[j] = t.y; e_act[j] = t.z; e_slot[j] = t.w;
+                        e_cst[j] = ep.cst[c];
+                    }
+                }
 #pragma unroll
                 for (int i = 0; i < kTM; ++i) {
                     const int r = r0 + i;
@@ -170,9 +197,16 @@ __global__ void __launch_bounds__(kDenseThreads) dense_fwd_kernel(const int32_t*
                     float* orow = out + z * dout + g.out_off;
 #pragma unroll
                     for (int j = 0; j < kTN; ++j) {
-                        if (w0 + j < g.mul_out) {
+                        if (w0 + j >= g.mul_out) continue;
+                        if (ep.tbl == nullptr) {
                             float* p = orow + (w0 + j) * g.dim3 + k;
                             *p = accumulate ? *p + acc[i][j] : acc[i][j];
+                        } else if (e_kind[j] == 0) {
+                            ep.final_out[z * ep.dout_final + e_dst[j]] = e_cst[j] * gate_act(e_act[j], acc[i][j]);
+                        } else if (e_kind[j] == 2) {
+                            ep.gates[z * ep.n_slots + e_slot[j]] = e_cst[j] * gate_act(e_act[j], acc[i][j]);
+                        } else if (e_kind[j] == 1) {
+                            ep.final_out[z * ep.dout_final + e_dst[j] + k] = acc[i][j] * __ldg(ep.gates + z * ep.n_slots + e_slot[j]);
                         }
                     }
                 }
@@ -300,15 +334,13 @@ __global__ void dense_fill_kernel(float* __restrict__ out, int64_t Z, int dout, 
 
 }  // namespace e3b
 
-extern "C" int e3b_dense_fwd(const int32_t* plan_host, const int32_t* plan_dev, const float* x1, const float* x2,
-                             const float* weight, int64_t weight_row_stride, float* out, int64_t num_rows,
-                             int accumulate, void* stream) {
-    using namespace e3b;
-    if (!plan_host || plan_host[0] != kDenseMagic) return fail(E3B_ERR_ARG, "dense_fwd: bad plan");
-    if (num_rows < 0) return fail(E3B_ERR_ARG, "dense_fwd: negative row count");
-    if (num_rows == 0) return E3B_OK;
-    if (!plan_dev || !x1 || !out || !weight) return fail(E3B_ERR_ARG, "dense_fwd: null pointer");
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
+namespace e3b {
+namespace {
+
+// Launches of the groups of a plan; pass 0 = every group, 1 = groups of scalars (2l+1 == 1), 2 = the others.
+int launch_dense_groups(const int32_t* plan_host, const int32_t* plan_dev, const float* x1, const float* x2,
+                        const float* weight, int64_t weight_row_stride, float* out, int64_t num_rows, int accumulate,
+                        const DenseGateEpilogue& ep, int pass, cudaStream_t s) {
     const int n_groups = plan_host[4];
     const int32_t* groups = plan_host + plan_host[7];
     const int32_t* kent_all = plan_host + plan_host[8];
@@ -316,6 +348,7 @@ extern "C" int e3b_dense_fwd(const int32_t* plan_host, const int32_t* plan_dev, 
         const int mul_out = groups[6 * g + 1], dim3 = groups[6 * g + 2], K = groups[6 * g + 3];
         const int kent_start = groups[6 * g + 4], w_stride = groups[6 * g + 5];
         if (K == 0 || mul_out == 0) continue;
+        if ((pass == 1 && dim3 != 1) || (pass == 2 && dim3 == 1)) continue;
         if (dim3 > kRowsPerPass) return fail(E3B_ERR_UNSUPPORTED, "dense_fwd: irrep dimension %d too large", dim3);
         const int rows_z = kRowsPerPass / dim3;
         // the A tile of the whole contraction when it fits (K <= 768), else chunks of 512 entries
@@ -328,15 +361,47 @@ extern "C" int e3b_dense_fwd(const int32_t* plan_host, const int32_t* plan_dev, 
         const unsigned grid = static_cast<unsigned>(std::min<int64_t>(tiles, kNumSMs * 4));
         if (vec4) {
             E3B_CUDA_TRY(cudaFuncSetAttribute(dense_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            dense_fwd_kernel<true><<<grid, kDenseThreads, smem, s>>>(plan_dev, x1, x2, weight, out, num_rows, g, rows_z, accumulate, weight_row_stride, k_chunk);
+            dense_fwd_kernel<true><<<grid, kDenseThreads, smem, s>>>(plan_dev, x1, x2, weight, out, num_rows, g, rows_z, accumulate, weight_row_stride, k_chunk, ep);
         } else {
             E3B_CUDA_TRY(cudaFuncSetAttribute(dense_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            dense_fwd_kernel<false><<<grid, kDenseThreads, smem, s>>>(plan_dev, x1, x2, weight, out, num_rows, g, rows_z, accumulate, weight_row_stride, k_chunk);
+            dense_fwd_kernel<false><<<grid, kDenseThreads, smem, s>>>(plan_dev, x1, x2, weight, out, num_rows, g, rows_z, accumulate, weight_row_stride, k_chunk, ep);
         }
         int rc = check_launch("e3b_dense_fwd");
         if (rc != E3B_OK) return rc;
     }
     return E3B_OK;
+}
+
+}  // namespace
+}  // namespace e3b
+
+extern "C" int e3b_dense_fwd(const int32_t* plan_host, const int32_t* plan_dev, const float* x1, const float* x2,
+                             const float* weight, int64_t weight_row_stride, float* out, int64_t num_rows,
+                             int accumulate, void* stream) {
+    using namespace e3b;
+    if (!plan_host || plan_host[0] != kDenseMagic) return fail(E3B_ERR_ARG, "dense_fwd: bad plan");
+    if (num_rows < 0) return fail(E3B_ERR_ARG, "dense_fwd: negative row count");
+    if (num_rows == 0) return E3B_OK;
+    if (!plan_dev || !x1 || !out || !weight) return fail(E3B_ERR_ARG, "dense_fwd: null pointer");
+    const DenseGateEpilogue none{nullptr, nullptr, nullptr, nullptr, 0, 0};
+    return launch_dense_groups(plan_host, plan_dev, x1, x2, weight, weight_row_stride, out, num_rows, accumulate, none, 0,
+                               static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int e3b_dense_fwd_gate(const int32_t* plan_host, const int32_t* plan_dev, const float* x, const float* weight,
+                                  const int32_t* gate_table, const float* gate_const, float* gates, int n_slots,
+                                  float* out, int dout, int64_t num_rows, void* stream) {
+    using namespace e3b;
+    if (!plan_host || plan_host[0] != kDenseMagic) return fail(E3B_ERR_ARG, "dense_fwd_gate: bad plan");
+    if (num_rows < 0 || n_slots < 0 || dout < 0) return fail(E3B_ERR_ARG, "dense_fwd_gate: negative size");
+    if (num_rows == 0) return E3B_OK;
+    if (!plan_dev || !x || !weight || !gate_table || !gate_const || !out || (n_slots > 0 && !gates))
+        return fail(E3B_ERR_ARG, "dense_fwd_gate: null pointer");
+    const DenseGateEpilogue ep{gate_table, gate_const, gates, out, n_slots, dout};
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // scalars and gates first: the launches of the gated irreps read the activated gates of the same rows
+    if (int rc = launch_dense_groups(plan_host, plan_dev, x, nullptr, weight, 0, out, num_rows, 0, ep, 1, s)) return rc;
+    return launch_dense_groups(plan_host, plan_dev, x, nullptr, weight, 0, out, num_rows, 0, ep, 2, s);
 }
 
 extern "C" int e3b_dense_bwd_w(const int32_t* plan_host, const int32_t* plan_dev, const float* x1, const float* x2,

@@ -10,41 +10,10 @@
 // The irreps bookkeeping lives on the host: per OUTPUT column {input column, gate column or -1,
 // activation code, constant}, per INPUT column {kind, first output column, count, partner column}.
 #include "common.cuh"
+#include "gate_act.cuh"
 
 namespace e3b {
 namespace {
-
-enum GateAct { kGSilu = 0, kGTanh = 1, kGRelu = 2, kGIdentity = 3, kGSigmoid = 4, kGAbs = 5 };
-
-__device__ __forceinline__ float gate_act(int kind, float x) {
-    switch (kind) {
-        case kGSilu: return x / (1.0f + expf(-x));
-        case kGTanh: return tanhf(x);
-        case kGRelu: return fmaxf(x, 0.0f);
-        case kGSigmoid: return 1.0f / (1.0f + expf(-x));
-        case kGAbs: return fabsf(x);
-        default: return x;
-    }
-}
-__device__ __forceinline__ float gate_act_grad(int kind, float x) {
-    switch (kind) {
-        case kGSilu: {
-            const float s = 1.0f / (1.0f + expf(-x));
-            return s * (1.0f + x * (1.0f - s));
-        }
-        case kGTanh: {
-            const float t = tanhf(x);
-            return 1.0f - t * t;
-        }
-        case kGRelu: return x > 0.0f ? 1.0f : 0.0f;
-        case kGSigmoid: {
-            const float s = 1.0f / (1.0f + expf(-x));
-            return s * (1.0f - s);
-        }
-        case kGAbs: return x > 0.0f ? 1.0f : (x < 0.0f ? -1.0f : 0.0f);
-        default: return 1.0f;
-    }
-}
 
 // A thread owns one column (its table entry stays in registers) and walks the rows: consecutive threads touch
 // consecutive addresses, no per-element index arithmetic beyond one multiply-add per row.

@@ -81,23 +81,24 @@ __global__ void cell_scatter_kernel(const int32_t* __restrict__ cell_of, int64_t
     cell_atoms[cell_start[cell] + slot] = static_cast<int32_t>(i);
 }
 
-// One thread per destination atom i.  FILL == false: deg[i] = number of neighbours.  FILL == true: writes the
-// row's edges at rowptr[i] and sorts them by source.
+// One thread per destination atom i of the rows [row0, row0 + nrows).  FILL == false: deg[i - row0] = number of
+// neighbours.  FILL == true: writes the row's edges at rowptr[i - row0] and sorts them by source.
 template <bool FILL>
 __global__ void neighbor_walk_kernel(const float* __restrict__ pos, const double* __restrict__ p, const int32_t* __restrict__ cell_of,
-                                     const int64_t* __restrict__ cell_start, const int32_t* __restrict__ cell_atoms, int64_t n,
-                                     double box, double cutoff2, int nc, int32_t* __restrict__ deg,
+                                     const int64_t* __restrict__ cell_start, const int32_t* __restrict__ cell_atoms, int64_t row0,
+                                     int64_t nrows, double box, double cutoff2, int nc, int32_t* __restrict__ deg,
                                      const int64_t* __restrict__ rowptr, int64_t* __restrict__ edge_src,
                                      int64_t* __restrict__ edge_dst, float* __restrict__ shift) {
-    const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (i >= n) return;
+    const int64_t local = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (local >= nrows) return;
+    const int64_t i = row0 + local;
     const double pix = p[i * 3], piy = p[i * 3 + 1], piz = p[i * 3 + 2];
     const int cell = cell_of[i];
     const int cz = cell % nc, cy = (cell / nc) % nc, cx = cell / (nc * nc);
     // offset between the caller's coordinates and the wrapped ones (0 for atoms inside the box)
     const double oix = pix - static_cast<double>(pos[i * 3]), oiy = piy - static_cast<double>(pos[i * 3 + 1]),
                  oiz = piz - static_cast<double>(pos[i * 3 + 2]);
-    const int64_t base = FILL ? rowptr[i] : 0;
+    const int64_t base = FILL ? rowptr[local] : 0;
     int count = 0;
     for (int dx = -1; dx <= 1; ++dx) {
         int nx = cx + dx;
@@ -134,7 +135,7 @@ __global__ void neighbor_walk_kernel(const float* __restrict__ pos, const double
         }
     }
     if (!FILL) {
-        deg[i] = count;
+        deg[local] = count;
         return;
     }
     // insertion sort of this row by source index (rows are short; the row is private to this thread)
@@ -158,6 +159,12 @@ int cells_per_side(double box, double cutoff) {
     return q > 1024.0 ? 1024 : static_cast<int>(q);   // more cells than that only lengthens the scan
 }
 
+int check_rows(int64_t n, int64_t row0, int64_t row1) {
+    if (row0 < 0 || row1 < row0 || row1 > n) return fail(E3B_ERR_ARG, "neighbor list: rows [%lld, %lld) outside [0, %lld)",
+                                                          static_cast<long long>(row0), static_cast<long long>(row1), static_cast<long long>(n));
+    return E3B_OK;
+}
+
 int check_neighbor_args(int64_t n, double box, double cutoff) {
     if (n < 0) return fail(E3B_ERR_ARG, "neighbor list: negative atom count");
     if (n > 2147483647LL) return fail(E3B_ERR_ARG, "neighbor list: more than 2^31 - 1 atoms");
@@ -179,11 +186,18 @@ extern "C" int64_t e3b_neighbor_scratch_bytes(int64_t num_atoms, double box, dou
 
 extern "C" int e3b_neighbor_count(const float* pos, int64_t num_atoms, double box, double cutoff, void* scratch,
                                   int64_t scratch_bytes, int64_t* rowptr, void* stream) {
+    return e3b_neighbor_count_rows(pos, num_atoms, box, cutoff, scratch, scratch_bytes, 0, num_atoms, rowptr, stream);
+}
+
+extern "C" int e3b_neighbor_count_rows(const float* pos, int64_t num_atoms, double box, double cutoff, void* scratch,
+                                       int64_t scratch_bytes, int64_t row0, int64_t row1, int64_t* rowptr, void* stream) {
     using namespace e3b;
     if (int rc = check_neighbor_args(num_atoms, box, cutoff)) return rc;
+    if (int rc = check_rows(num_atoms, row0, row1)) return rc;
     if (!rowptr) return fail(E3B_ERR_ARG, "neighbor_count: null pointer");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (num_atoms == 0) {
+    const int64_t nrows = row1 - row0;
+    if (num_atoms == 0 || nrows == 0) {
         E3B_CUDA_TRY(cudaMemsetAsync(rowptr, 0, sizeof(int64_t), s));
         return E3B_OK;
     }
@@ -200,18 +214,28 @@ extern "C" int e3b_neighbor_count(const float* pos, int64_t num_atoms, double bo
     wrap_bin_kernel<<<grid, threads, 0, s>>>(pos, num_atoms, box, nc, sc.p, sc.cell_of, sc.cell_count);
     exclusive_scan_i32_kernel<<<1, 1024, 0, s>>>(sc.cell_count, cells, sc.cell_start);
     cell_scatter_kernel<<<grid, threads, 0, s>>>(sc.cell_of, num_atoms, sc.cell_start, sc.cell_fill, sc.cell_atoms);
-    neighbor_walk_kernel<false><<<grid, threads, 0, s>>>(pos, sc.p, sc.cell_of, sc.cell_start, sc.cell_atoms, num_atoms, box,
-                                                         cutoff * cutoff, nc, sc.deg, nullptr, nullptr, nullptr, nullptr);
-    exclusive_scan_i32_kernel<<<1, 1024, 0, s>>>(sc.deg, num_atoms, rowptr);
+    const unsigned row_grid = static_cast<unsigned>(ceil_div(nrows, threads));
+    neighbor_walk_kernel<false><<<row_grid, threads, 0, s>>>(pos, sc.p, sc.cell_of, sc.cell_start, sc.cell_atoms, row0, nrows, box,
+                                                             cutoff * cutoff, nc, sc.deg, nullptr, nullptr, nullptr, nullptr);
+    exclusive_scan_i32_kernel<<<1, 1024, 0, s>>>(sc.deg, nrows, rowptr);
     return check_launch("neighbor_count");
 }
 
 extern "C" int e3b_neighbor_fill(const float* pos, int64_t num_atoms, double box, double cutoff, void* scratch,
                                  int64_t scratch_bytes, const int64_t* rowptr, int64_t* edge_src, int64_t* edge_dst,
                                  float* shift, void* stream) {
+    return e3b_neighbor_fill_rows(pos, num_atoms, box, cutoff, scratch, scratch_bytes, 0, num_atoms, rowptr, edge_src, edge_dst,
+                                  shift, stream);
+}
+
+extern "C" int e3b_neighbor_fill_rows(const float* pos, int64_t num_atoms, double box, double cutoff, void* scratch,
+                                      int64_t scratch_bytes, int64_t row0, int64_t row1, const int64_t* rowptr, int64_t* edge_src,
+                                      int64_t* edge_dst, float* shift, void* stream) {
     using namespace e3b;
     if (int rc = check_neighbor_args(num_atoms, box, cutoff)) return rc;
-    if (num_atoms == 0) return E3B_OK;
+    if (int rc = check_rows(num_atoms, row0, row1)) return rc;
+    const int64_t nrows = row1 - row0;
+    if (num_atoms == 0 || nrows == 0) return E3B_OK;
     const int nc = cells_per_side(box, cutoff);
     const int64_t cells = static_cast<int64_t>(nc) * nc * nc;
     if (!pos || !scratch || !rowptr || !edge_src || !edge_dst || !shift) return fail(E3B_ERR_ARG, "neighbor_fill: null pointer");
@@ -219,9 +243,9 @@ extern "C" int e3b_neighbor_fill(const float* pos, int64_t num_atoms, double box
         return fail(E3B_ERR_ARG, "neighbor_fill: scratch too small or not 256-byte aligned");
     NeighborScratch sc = carve(scratch, num_atoms, cells);
     const int threads = 256;
-    const unsigned grid = static_cast<unsigned>(ceil_div(num_atoms, threads));
+    const unsigned grid = static_cast<unsigned>(ceil_div(nrows, threads));
     neighbor_walk_kernel<true><<<grid, threads, 0, static_cast<cudaStream_t>(stream)>>>(
-        pos, sc.p, sc.cell_of, sc.cell_start, sc.cell_atoms, num_atoms, box, cutoff * cutoff, nc, sc.deg, rowptr, edge_src,
+        pos, sc.p, sc.cell_of, sc.cell_start, sc.cell_atoms, row0, nrows, box, cutoff * cutoff, nc, sc.deg, rowptr, edge_src,
         edge_dst, shift);
     return check_launch("neighbor_fill");
 }

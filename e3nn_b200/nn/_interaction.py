@@ -39,8 +39,12 @@ def radius_graph_pbc(pos: torch.Tensor, box: float, cutoff: float) -> Tuple[torc
     return _radius_graph_pbc_host(pos, box, cutoff)
 
 
-def neighbor_list_pbc(pos: torch.Tensor, box: float, cutoff: float):
-    """Device cell list: ``edge_src, edge_dst, shift, rowptr`` (edges sorted by destination, then source)."""
+def neighbor_list_pbc(pos: torch.Tensor, box: float, cutoff: float, rows: Optional[Tuple[int, int]] = None):
+    """Device cell list: ``edge_src, edge_dst, shift, rowptr`` (edges sorted by destination, then source).
+
+    ``rows=(n0, n1)``: only the edges whose destination lies in ``[n0, n1)`` (the shard of a rank that owns those
+    rows); ``rowptr`` is then the CSR of the range, starting at 0, while ``edge_src`` / ``edge_dst`` keep global atom
+    numbers.  All atoms are binned in either case; only the rows of the range are walked."""
     from .. import _lib
 
     if not pos.is_cuda:
@@ -52,19 +56,23 @@ def neighbor_list_pbc(pos: torch.Tensor, box: float, cutoff: float):
     core = _lib.core()
     nbytes = core.e3b_neighbor_scratch_bytes(n, float(box), float(cutoff))
     scratch = torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=dev)
-    rowptr = torch.empty(n + 1, dtype=torch.int64, device=dev)
+    n0, n1 = (0, n) if rows is None else (int(rows[0]), int(rows[1]))
+    if not (0 <= n0 <= n1 <= n):
+        raise IndexError(f"rows {rows} outside [0, {n}]")
+    rowptr = torch.empty(n1 - n0 + 1, dtype=torch.int64, device=dev)
     with torch.cuda.device(dev):
-        rc = core.e3b_neighbor_count(_lib._ptr(pos32), n, float(box), float(cutoff), _lib._ptr(scratch), scratch.numel(),
-                                     _lib._ptr(rowptr), _lib.stream_ptr())
-        _lib.check(rc, "e3b_neighbor_count")
-        num_edges = int(rowptr[n].item())       # the one synchronisation: the caller allocates the edge arrays
+        rc = core.e3b_neighbor_count_rows(_lib._ptr(pos32), n, float(box), float(cutoff), _lib._ptr(scratch), scratch.numel(),
+                                          n0, n1, _lib._ptr(rowptr), _lib.stream_ptr())
+        _lib.check(rc, "e3b_neighbor_count_rows")
+        num_edges = int(rowptr[n1 - n0].item())       # the one synchronisation: the caller allocates the edge arrays
         src = torch.empty(num_edges, dtype=torch.int64, device=dev)
         dst = torch.empty(num_edges, dtype=torch.int64, device=dev)
         shift = torch.empty(num_edges, 3, dtype=torch.float32, device=dev)
         if num_edges > 0:
-            rc = core.e3b_neighbor_fill(_lib._ptr(pos32), n, float(box), float(cutoff), _lib._ptr(scratch), scratch.numel(),
-                                        _lib._ptr(rowptr), _lib._ptr(src), _lib._ptr(dst), _lib._ptr(shift), _lib.stream_ptr())
-            _lib.check(rc, "e3b_neighbor_fill")
+            rc = core.e3b_neighbor_fill_rows(_lib._ptr(pos32), n, float(box), float(cutoff), _lib._ptr(scratch), scratch.numel(),
+                                             n0, n1, _lib._ptr(rowptr), _lib._ptr(src), _lib._ptr(dst), _lib._ptr(shift),
+                                             _lib.stream_ptr())
+            _lib.check(rc, "e3b_neighbor_fill_rows")
     return src, dst, shift.to(pos.dtype), rowptr
 
 

@@ -118,6 +118,17 @@ int e3b_neighbor_count(const float* pos, int64_t num_atoms, double box, double c
                        int64_t* rowptr, void* stream);
 int e3b_neighbor_fill(const float* pos, int64_t num_atoms, double box, double cutoff, void* scratch, int64_t scratch_bytes,
                       const int64_t* rowptr, int64_t* edge_src, int64_t* edge_dst, float* shift, void* stream);
+/*
+ * The same list restricted to the destination rows [row0, row1) (a rank's shard of a graph partitioned by
+ * destination ranges; the reference has no partitioned graphs): every atom is binned, only the rows of the range
+ * are walked.  rowptr [row1 - row0 + 1] is the CSR of the range starting at 0, edge_dst holds GLOBAL atom numbers.
+ * Concatenating the ranges of a partition gives exactly the edges of the full list, in the same order.
+ */
+int e3b_neighbor_count_rows(const float* pos, int64_t num_atoms, double box, double cutoff, void* scratch,
+                            int64_t scratch_bytes, int64_t row0, int64_t row1, int64_t* rowptr, void* stream);
+int e3b_neighbor_fill_rows(const float* pos, int64_t num_atoms, double box, double cutoff, void* scratch,
+                           int64_t scratch_bytes, int64_t row0, int64_t row1, const int64_t* rowptr, int64_t* edge_src,
+                           int64_t* edge_dst, float* shift, void* stream);
 
 /*
  * Edge embedding of an interaction block, one kernel per direction:
@@ -184,6 +195,21 @@ int e3b_gate_bwd(const float* x, const float* grad_out, const int32_t* in_table,
 int e3b_dense_fwd(const int32_t* plan_host, const int32_t* plan_dev, const float* x1, const float* x2,
                   const float* weight, int64_t weight_row_stride, float* out, int64_t num_rows, int accumulate,
                   void* stream);
+
+/*
+ * A per-irrep Linear (e3nn/o3/_linear.py:445-469) followed by Gate (e3nn/nn/_gate.py:127-144) without the
+ * intermediate row: the plan is the Linear's, whose output row would be the Gate's input row; the gate is applied
+ * where the Linear's result is still in registers.  gate_table [din_gate, 4] int32 = {kind, destination column,
+ * activation, gate slot} and gate_const [din_gate] float per column of that (never materialised) row:
+ *   kind 0 scalar:  out[z, dst]    = const * act(y)        kind 2 gate: gates[z, slot] = const * act(y)
+ *   kind 1 gated:   out[z, dst]    = y * gates[z, slot]    kind 3: no output depends on the column.
+ * gates [rows, n_slots] is written and read by this call (the only extra traffic: the gate scalars, once each way);
+ * out [rows, dout] is the Gate's output row.  Scalar irreps are launched before the gated ones on `stream`.
+ * Activation codes as in e3b_gate_fwd.
+ */
+int e3b_dense_fwd_gate(const int32_t* plan_host, const int32_t* plan_dev, const float* x, const float* weight,
+                       const int32_t* gate_table, const float* gate_const, float* gates, int n_slots, float* out,
+                       int dout, int64_t num_rows, void* stream);
 
 /*
  * Gradient of e3b_dense_fwd w.r.t. its SHARED weights (what autograd derives from the einsums of

@@ -7,6 +7,7 @@ is replaced by an identity stand-in before ``import e3nn``.
 
     python tests/golden/make_golden.py              (everything)
     python tests/golden/make_golden.py --only-gate  (only the Gate cases, leaving the other files untouched)
+    python tests/golden/make_golden.py --only-activation
     python tests/golden/make_golden.py --only-radial-bases
     python tests/golden/make_golden.py --only-uuu
 
@@ -88,6 +89,28 @@ def gate_cases(meta):
         np.savez_compressed(os.path.join(HERE, f"{name}.npz"), x=_np(x), out_f64=_np(out64))
         meta["cases"][name] = {"irreps_scalars": sc, "act_scalars": act_s, "irreps_gates": ga, "act_gates": act_g,
                                "irreps_gated": gd, "irreps_in": str(g.irreps_in), "irreps_out": str(g.irreps_out)}
+
+
+ACTIVATION_CASES = {
+    "activation_mixed": ("16x0e+8x0o+4x1e", ["silu", "tanh", None]),
+    "activation_abs": ("8x0o", ["abs"]),
+    "activation_identity": ("4x0e+4x1o", [None, None]),
+    "activation_relu_sigmoid": ("5x0e+3x0e+2x2e", ["relu", "sigmoid", None]),
+}
+
+
+def activation_cases(meta):
+    """Activation.forward of the reference on seeded rows (e3nn/nn/_activation.py:80-111)."""
+    from e3nn.nn import Activation
+
+    fn = {"silu": torch.nn.functional.silu, "tanh": torch.tanh, "sigmoid": torch.sigmoid, "abs": torch.abs,
+          "relu": torch.relu, None: None}
+    gen = torch.Generator().manual_seed(4242)
+    for name, (irreps, acts) in ACTIVATION_CASES.items():
+        a = Activation(irreps, [fn[n] for n in acts])
+        x = torch.randn(7, a.irreps_in.dim, generator=gen)
+        np.savez_compressed(os.path.join(HERE, f"{name}.npz"), x=_np(x), out_f64=_np(a(x.double())))
+        meta["cases"][name] = {"irreps_in": irreps, "acts": acts, "irreps_out": str(a.irreps_out)}
 
 
 def radial_basis_cases(meta):
@@ -221,6 +244,15 @@ def main():
         with open(os.path.join(HERE, "meta.json"), "w") as f:
             json.dump(meta, f, indent=1)
         print("radial basis golden vectors written to", HERE)
+        return
+    if "--only-activation" in sys.argv:
+        _import_reference()
+        with open(os.path.join(HERE, "meta.json")) as f:
+            meta = json.load(f)
+        activation_cases(meta)
+        with open(os.path.join(HERE, "meta.json"), "w") as f:
+            json.dump(meta, f, indent=1)
+        print("activation golden vectors written to", HERE)
         return
     if "--only-gate" in sys.argv:
         _import_reference()

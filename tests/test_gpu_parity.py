@@ -602,6 +602,27 @@ def test_neighbor_list_matches_kdtree(n_atoms, inside):
     assert torch.equal(s3, src) and torch.equal(d3, dst)
 
 
+def test_neighbor_list_row_ranges_concatenate_to_the_full_list():
+    """A rank's shard (destination rows [n0, n1)) is bit-identical to the matching slice of the full list; an empty
+    range and the whole range are valid."""
+    from e3nn_b200 import nn as bnn
+
+    torch.manual_seed(5)
+    n_atoms, box = 3000, (3000 / 0.05) ** (1 / 3)
+    pos = (torch.rand(n_atoms, 3) * box).to(DEV)
+    src, dst, shift, rowptr = bnn.neighbor_list_pbc(pos, box, 5.0)
+    bounds = [0, 0, 700, 701, 2222, n_atoms]
+    parts = [bnn.neighbor_list_pbc(pos, box, 5.0, rows=(a, b)) for a, b in zip(bounds, bounds[1:])]
+    assert torch.equal(torch.cat([p[0] for p in parts]), src)
+    assert torch.equal(torch.cat([p[1] for p in parts]), dst)
+    assert torch.equal(torch.cat([p[2] for p in parts]), shift)
+    for (a, b), (s_, d_, sh_, rp_) in zip(zip(bounds, bounds[1:]), parts):
+        assert rp_.numel() == b - a + 1 and torch.equal(rp_, rowptr[a:b + 1] - rowptr[a])
+        assert d_.numel() == 0 or (int(d_.min()) >= a and int(d_.max()) < b)
+    with pytest.raises(IndexError):
+        bnn.neighbor_list_pbc(pos, box, 5.0, rows=(10, n_atoms + 1))
+
+
 def test_neighbor_list_edge_cases():
     from e3nn_b200 import nn as bnn
 
@@ -645,6 +666,66 @@ def test_gate_golden_and_gradient(golden, golden_meta, name):
     o.backward(go.to(DEV))
     assert rel_err(xg.grad.cpu(), x64.grad) < TOL
     assert gate(torch.zeros(0, gate.irreps_in.dim, device=DEV)).shape == (0, gate.irreps_out.dim)
+
+
+@pytest.mark.parametrize("name", ["activation_mixed", "activation_abs", "activation_identity", "activation_relu_sigmoid"])
+def test_activation_golden_and_gradient(golden, golden_meta, name):
+    """Activation module against the reference's output on the golden rows (its irreps_out too), and its gradient
+    against autograd through the fp64 oracle."""
+    from e3nn_b200 import nn as bnn
+
+    fn = {"silu": torch.nn.functional.silu, "tanh": torch.tanh, "sigmoid": torch.sigmoid, "abs": torch.abs,
+          "relu": torch.relu, None: None}
+    g, m = golden(name), golden_meta["cases"][name]
+    act = bnn.Activation(m["irreps_in"], [fn[a] for a in m["acts"]]).to(DEV)
+    assert str(act.irreps_out) == m["irreps_out"]
+    out = act(torch.from_numpy(g["x"]).to(DEV))
+    assert rel_err(out.cpu(), torch.from_numpy(g["out_f64"])) < TOL
+    torch.manual_seed(8)
+    x = torch.randn(3, 257, act.irreps_in.dim)
+    go = torch.randn(3, 257, act.irreps_out.dim)
+    x64 = x.double().requires_grad_(True)
+    ref = orc.activation(m["irreps_in"], m["acts"], x64)
+    ref.backward(go.double())
+    xg = x.clone().to(DEV).requires_grad_(True)
+    o = act(xg)
+    o.backward(go.to(DEV))
+    assert rel_err(o.detach().cpu(), ref.detach()) < TOL and rel_err(xg.grad.cpu(), x64.grad) < TOL
+    assert act(torch.zeros(0, act.irreps_in.dim, device=DEV)).shape == (0, act.irreps_out.dim)
+
+
+@pytest.mark.parametrize("name", ["gate_mixed", "gate_l3", "gate_abs_identity"])
+def test_linear_gate_fused(golden_meta, name):
+    """Gate as the epilogue of the Linear that feeds it: equal to ``gate(linear(x))`` of the fp64 oracle within the fp32
+    bound, and to the two modules run one after the other; with a gradient required the two-module path runs."""
+    from e3nn_b200 import nn as bnn
+
+    fn = {"silu": torch.nn.functional.silu, "tanh": torch.tanh, "sigmoid": torch.sigmoid, "abs": torch.abs,
+          "relu": torch.relu, None: None}
+    m = golden_meta["cases"][name]
+    gate = bnn.Gate(m["irreps_scalars"], [fn[a] for a in m["act_scalars"]], m["irreps_gates"],
+                    [fn[a] for a in m["act_gates"]], m["irreps_gated"]).to(DEV)
+    irreps_x = "24x0e+8x0o+16x1o+8x1e+8x2e+4x2o+8x3o"
+    lin = o3.Linear(irreps_x, gate.irreps_in).to(DEV)
+    fused = bnn.LinearGate(lin, gate).to(DEV)
+    torch.manual_seed(17)
+    x = torch.randn(3, 211, lin.irreps_in.dim)
+    with torch.no_grad():
+        assert fused.fusable(x.to(DEV))
+        out = fused(x.to(DEV))
+        two = gate(lin(x.to(DEV)))
+    e3nn_b200.check_status()
+    y = orc.linear(irreps_x, str(gate.irreps_in), x.double().reshape(-1, x.shape[-1]), lin.weight.detach().cpu().double())
+    ref = orc.gate(m["irreps_scalars"], m["act_scalars"], m["irreps_gates"], m["act_gates"], m["irreps_gated"], y)
+    ref = ref.reshape(*x.shape[:-1], -1)
+    assert out.shape == ref.shape and rel_err(out.cpu(), ref) < TOL
+    assert rel_err(out.cpu(), two.cpu().double()) < 2e-6
+    # training: gradients through the pair of modules
+    xg = x.clone().to(DEV).requires_grad_(True)
+    assert not fused.fusable(xg)
+    o = fused(xg)
+    o.sum().backward()
+    assert xg.grad is not None and lin.weight.grad is not None
 
 
 # ----------------------------------------------------------------------------- fused edge embedding

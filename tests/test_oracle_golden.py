@@ -134,6 +134,14 @@ def test_gate(golden, golden_meta, name):
     assert rel_err(out, torch.from_numpy(g["out_f64"])) < 1e-12
 
 
+@pytest.mark.parametrize("name", ["activation_mixed", "activation_abs", "activation_identity", "activation_relu_sigmoid"])
+def test_activation(golden, golden_meta, name):
+    """Activation.forward of the reference (e3nn/nn/_activation.py:80-111)."""
+    g, m = golden(name), golden_meta["cases"][name]
+    out = orc.activation(m["irreps_in"], m["acts"], torch.from_numpy(g["x"]).double())
+    assert rel_err(out, torch.from_numpy(g["out_f64"])) < 1e-12
+
+
 def test_radial_bases(golden, golden_meta):
     """soft_one_hot_linspace (all bases, both cutoff flags) and smooth_cutoff against the reference's values."""
     g, m = golden("radial_bases"), golden_meta["cases"]["radial_bases"]
