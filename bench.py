@@ -2,7 +2,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference]
 
-Workloads (synthetic, seeded; shapes and distributions of the BASELINE configurations):
+Workloads (synthetic, seeded; shapes and distributions of the benchmark configurations):
   conv_l2_15   fused gather -> SH(lmax 2) -> 'uvu' (15 paths, 64 channels) -> per-destination sum;
                65,536 nodes, 2,097,152 edges, in-degree 32, uniform random sources, per-edge weights.
   conv_l2_11   same graph, the 11-path layout (outputs restricted to the node irreps).
@@ -611,7 +611,7 @@ def secondary_workloads(device, tf32_peak: float):
 
 
 def interaction_problem(n_atoms: int, seed: int = 0, device=None):
-    """Positions and neighbour list of BASELINE config 5 at `n_atoms` (host tensors, edges sorted by destination).
+    """Positions and neighbour list of benchmark case 5 (interaction block) at `n_atoms` (host tensors, edges sorted by destination).
 
     With `device` the list is built by the device cell list (timed with a synchronisation on both sides, after
     one untimed call); without it by the host k-d tree (the CPU arms)."""
@@ -639,7 +639,7 @@ NCU_CONV_BWD_L3_TRAFFIC_PER_EDGE = 15718
 
 
 def run_interaction(args, rank, world, device):
-    """BASELINE config 5: interaction block, forward + gradient w.r.t. positions.
+    """benchmark case 5 (interaction block): interaction block, forward + gradient w.r.t. positions.
 
     N GPUs: destination atoms are split into N contiguous ranges balanced by edge count; a rank owns the
     features of its atoms, all-gathers all source features every step (NCCL), evaluates its own output rows
@@ -1022,7 +1022,7 @@ def cpu_interaction_baseline():
 
 
 def run_uvw(args, rank, world, device):
-    """BASELINE config 4: rows are independent, so N GPUs run N replicas of rows/N each (no collective)."""
+    """benchmark case 4 (1,048,576-row fully connected product): rows are independent, so N GPUs run N replicas of rows/N each (no collective)."""
     from e3nn_b200 import o3
 
     rows_total = args.nodes if args.nodes > 0 else 1_048_576
@@ -1082,7 +1082,7 @@ def run_uvw(args, rank, world, device):
 
 
 def run_uvw_cfg1(args, rank, world, device):
-    """BASELINE config 1 (the reference's own CPU-runnable case): 10,000 rows of a 32-channel l <= 2 fully connected
+    """benchmark case 1 (10,000-row fully connected product) (the reference's own CPU-runnable case): 10,000 rows of a 32-channel l <= 2 fully connected
     product.  23 MB of data and 0.7 GFLOP: the call is bound by launch latency, so the line reports the time of one
     call per arithmetic mode, and of a CUDA-graph replay of the fp32 call."""
     from e3nn_b200 import o3

@@ -214,13 +214,14 @@ def core() -> ctypes.CDLL:
         lib.e3b_neighbor_fill_rows.argtypes = [c_void_p, c_int64, c_double, c_double, c_void_p, c_int64, c_int64, c_int64,
                                                c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]
         lib.e3b_gate_fwd.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]
+        lib.e3b_gate_fwd_channels.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p]
         lib.e3b_gate_bwd.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]
         lib.e3b_selftest_bounded_wait.argtypes = [c_void_p, ctypes.c_uint, c_void_p]
         lib.e3b_selftest_bounded_wait.restype = c_int
         for name in ("e3b_sh_fwd", "e3b_sh_bwd", "e3b_csr_from_dst", "e3b_dense_fwd", "e3b_dense_fwd_gate", "e3b_dense_bwd_w", "e3b_fill_columns",
                      "e3b_radial_embed_fwd", "e3b_radial_embed_bwd", "e3b_neighbor_count", "e3b_neighbor_fill",
                      "e3b_neighbor_count_rows", "e3b_neighbor_fill_rows",
-                     "e3b_gate_fwd", "e3b_gate_bwd"):
+                     "e3b_gate_fwd", "e3b_gate_fwd_channels", "e3b_gate_bwd"):
             getattr(lib, name).restype = c_int
         _core = lib
     return _core

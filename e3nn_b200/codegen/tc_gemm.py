@@ -41,11 +41,6 @@ SMEM_LIMIT = 227 * 1024
 A_TILE = 128 * 128          # one 128 x 32 fp32 sub-tile
 Y_BYTES = 8192
 EPI_BYTES = 4 * 32 * 64 * 4   # 4 epilogue warps x (32 rows x 64 columns) fp32
-# Staged epilogue of the 2l+1 > 1 groups (see Group.staged_rows).  Correct, but slower than the direct strided
-# stores on the transposed l <= 3 Linear of 262,144 rows (4.4 ms direct): 10.5 ms with this per-warp tile (about 700
-# instructions per 64 channels in each of the four epilogue warps, one warp per scheduler: latency bound), 8.0 ms
-# with one tile shared by the four warps and two block barriers per 32 channels.  Off.
-STAGED_ROWS = False
 PRODUCER_WARPS = 8          # default; GemmSpec.producer_warps selects 8 or 16 per module
 PIECES = 2                  # tf32 pieces the stages have room for (hi, lo); 3 is supported by the code below
 
@@ -104,13 +99,8 @@ class Group:
         """dim == 1 groups transpose their output through shared memory for fully coalesced stores."""
         return self.dim == 1 and self.n % 64 == 0 and self.aligned_out
 
-    def staged_rows(self) -> bool:
-        """dim > 1 groups: every epilogue warp passes its 32 rows through its own shared-memory tile so that the
-        components of a row z leave as contiguous runs of channels x (2l+1) floats instead of strided single floats."""
-        return self.dim > 1 and self.n % 16 == 0 and STAGED_ROWS
-
     def extra_bytes(self) -> int:
-        return (Y_BYTES if self.has_y else 0) + (EPI_BYTES if (self.staged_epilogue() or self.staged_rows()) else 0)
+        return (Y_BYTES if self.has_y else 0) + (EPI_BYTES if self.staged_epilogue() else 0)
 
     def nstage(self) -> int:
         return int(max(0, min(6, (SMEM_LIMIT - 3072 - self.extra_bytes() - self.resident_bytes()) // self.stage_bytes())))
@@ -241,7 +231,7 @@ def linear_gemm_spec(irreps_in: Irreps, irreps_out: Irreps, instructions, transp
         for g in out:
             m = merged[-1] if merged else None
             width = len(m.chunks[0].blocks) if (m and m.chunks[0].blocks) else 1
-            limit = 192 if (g.dim == 1 or STAGED_ROWS) else 256   # (32 KB of epilogue staging + a resident N = 256 operand: two stages)
+            limit = 192 if g.dim == 1 else 256   # (32 KB of epilogue staging + a resident N = 256 operand: two stages)
             if (m is not None and m.dim == g.dim and m.n // width == g.n and m.n + g.n <= limit
                     and g.out_off == m.out_off + m.n * m.dim and len(m.chunks) == len(g.chunks)
                     and all(a.xoff == b.xoff and a.sk == b.sk and a.sn == b.sn for a, b in zip(m.chunks, g.chunks))):
@@ -564,50 +554,6 @@ for (int q = 0; q < {qn}; ++q) {{{{
                     const float4 v = reinterpret_cast<const float4*>(se + rl * 64)[cc ^ (rl & 15)];
                     const int64_t zr = t * ZT + warp * 32 + rl;
                     if (zr < Z) reinterpret_cast<float4*>(out + zr * {dout} + OUT_OFF + wb)[cc] = v;
-                }}}}
-                __syncwarp();
-            }}}}""".replace("{{", "{").replace("}}", "}")
-        elif g.staged_rows():
-            CB = 64 if g.n % 64 == 0 else (32 if g.n % 32 == 0 else 16)
-            EPILOGUE = f"""            // {CB} channels at a time through this warp's own staging tile (32 rows x {CB} floats, 16-byte chunks XOR-swizzled
-            // by row).  A row is a (z, k) pair, so the values of one z are 2l+1 rows of the tile; they leave as the
-            // contiguous run out[z, (wb + w) * DIM + k], 32 consecutive floats per store instruction.  A z whose rows
-            // are split between two warps is written by both, each its own components.
-            constexpr int CB = {CB}, NCH = CB / 4;
-            float* se = sE + warp * (32 * 64);
-            const int r_base = warp * 32;
-            const int z_first = r_base / DIM;
-            const int z_last = (r_base + 31) / DIM < ZT - 1 ? (r_base + 31) / DIM : ZT - 1;
-            for (int wb = 0; wb < N; wb += CB) {{{{
-                float4* mine = reinterpret_cast<float4*>(se + lane * CB);
-#pragma unroll
-                for (int h = 0; h < CB / 16; ++h) {{{{
-                    uint32_t ra[16], rb[16];
-                    tc::tmem_ld16(tbase + wb + 16 * h, ra);
-                    if (nparts == 1) tc::tmem_ld_wait();
-                    for (int p = 1; p < nparts; ++p) {{{{
-                        tc::tmem_ld16(tbase + part_off(p) + wb + 16 * h, rb);
-                        tc::tmem_ld_wait();
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) ra[j] = __float_as_uint(__uint_as_float(ra[j]) + __uint_as_float(rb[j]));
-                    }}}}
-#pragma unroll
-                    for (int c = 0; c < 4; ++c)
-                        mine[(4 * h + c) ^ (lane & (NCH - 1))] = make_float4(__uint_as_float(ra[4 * c]), __uint_as_float(ra[4 * c + 1]),
-                                                                            __uint_as_float(ra[4 * c + 2]), __uint_as_float(ra[4 * c + 3]));
-                }}}}
-                __syncwarp();
-                for (int zl = z_first; zl <= z_last; ++zl) {{{{
-                    const int64_t zr = t * ZT + zl;
-                    if (zr >= Z) break;
-                    float* dstrow = out + zr * {dout} + OUT_OFF + wb * DIM;
-                    const int rz = zl * DIM - r_base;      // tile row of component 0 (outside [0, 32) at a split z)
-#pragma unroll 2
-                    for (int c = lane; c < CB * DIM; c += 32) {{{{
-                        const int w = c / DIM, k = c - w * DIM;
-                        const int rl = rz + k;
-                        if (rl >= 0 && rl < 32) dstrow[c] = se[rl * CB + ((((w >> 2) ^ rl) & (NCH - 1)) << 2) + (w & 3)];
-                    }}}}
                 }}}}
                 __syncwarp();
             }}}}""".replace("{{", "{").replace("}}", "}")

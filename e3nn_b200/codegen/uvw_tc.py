@@ -360,8 +360,7 @@ __device__ __forceinline__ void run_group_{gi}(const float* __restrict__ x1, con
         f"    const int cta_begin{gi} = {'0' if gi == 0 else f'cta_end{gi-1}'}, cta_end{gi} = cta_begin{gi} + split.n[{gi}];" for gi in range(ngroups)
     )
     work = [sum(_chunk_cost(g.paths[pi], g.dim) for pi, _ in g.chunks()) for g in groups]
-    # measured on 128x0e+64x1o+32x2e (x) 0e..3o: the scalar-output group (one sub-tile per stage, 128 rows per tile)
-    # needs about 1.35 x the CTAs this model gives it (4.32 -> 3.95 ms); sweeps of +-30 % around every group's share
+    # the scalar-output group (one sub-tile per stage, 128 rows per tile) needs about 1.35 x the CTAs this model gives it
     work = [int(w * 1.35) if g.dim == 1 else w for w, g in zip(work, groups)]
     return f"""// Generated by e3nn_b200/codegen/uvw_tc.py -- do not edit.
 // layout: {spec.irreps_in1} (x) {spec.irreps_in2} -> {spec.irreps_out}, {sum(len(g.paths) for g in groups)} 'uvw' paths, key {spec.key()}

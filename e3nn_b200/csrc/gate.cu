@@ -40,6 +40,34 @@ __global__ void __launch_bounds__(256) gate_fwd_kernel(const float* __restrict__
     }
 }
 
+// One thread per CHANNEL (a scalar, or the 2l+1 components of a gated channel): the gate's activation, the only
+// transcendental work of the row, is evaluated once per channel instead of once per output column.
+// ch_tbl[q] = {first input column, count (1 or 2l+1), gate column or -1, activation code, first output column},
+// ch_cst[q] = constant.  Lanes are consecutive channels, i.e. adjacent runs of 2l+1 floats: full lines are used.
+__global__ void __launch_bounds__(256) gate_fwd_channel_kernel(const float* __restrict__ x, const int32_t* __restrict__ ch_tbl,
+                                                               const float* __restrict__ ch_cst, float* __restrict__ out,
+                                                               int64_t rows, int din, int dout, int nch) {
+    const int q = blockIdx.y * blockDim.x + threadIdx.x;
+    if (q >= nch) return;
+    const int src = ch_tbl[5 * q], cnt = ch_tbl[5 * q + 1], gate = ch_tbl[5 * q + 2], act = ch_tbl[5 * q + 3], dst = ch_tbl[5 * q + 4];
+    const float cst = ch_cst[q];
+    for (int64_t z0 = static_cast<int64_t>(blockIdx.x) * 2; z0 < rows; z0 += static_cast<int64_t>(gridDim.x) * 2) {
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const int64_t z = z0 + r;
+            if (z >= rows) break;
+            const float* xr = x + z * din;
+            float* orow = out + z * dout + dst;
+            if (gate < 0) {
+                orow[0] = cst * gate_act(act, xr[src]);
+            } else {
+                const float gv = cst * gate_act(act, xr[gate]);
+                for (int m = 0; m < cnt; ++m) orow[m] = xr[src + m] * gv;
+            }
+        }
+    }
+}
+
 // in_tbl[c] = {kind, first output column, count, partner, activation code}, in_cst[c] = constant:
 // kind 0 = scalar, 1 = gated component (partner = its gate's input column, activation of that gate),
 // 2 = gate (count = 2l+1 components of its channel, partner = input column of the first component),
@@ -89,6 +117,17 @@ extern "C" int e3b_gate_fwd(const float* x, const int32_t* out_table, const floa
     if (!x || !out_table || !out_const || !out) return fail(E3B_ERR_ARG, "gate_fwd: null pointer");
     gate_fwd_kernel<<<gate_grid(rows, dout), 256, 0, static_cast<cudaStream_t>(stream)>>>(x, out_table, out_const, out, rows, din, dout);
     return check_launch("gate_fwd");
+}
+
+extern "C" int e3b_gate_fwd_channels(const float* x, const int32_t* channel_table, const float* channel_const, float* out,
+                                     int64_t rows, int din, int dout, int num_channels, void* stream) {
+    using namespace e3b;
+    if (rows < 0 || din < 0 || dout < 0 || num_channels < 0) return fail(E3B_ERR_ARG, "gate_fwd_channels: negative size");
+    if (rows == 0 || num_channels == 0) return E3B_OK;
+    if (!x || !channel_table || !channel_const || !out) return fail(E3B_ERR_ARG, "gate_fwd_channels: null pointer");
+    gate_fwd_channel_kernel<<<gate_grid(rows, num_channels), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        x, channel_table, channel_const, out, rows, din, dout, num_channels);
+    return check_launch("gate_fwd_channels");
 }
 
 extern "C" int e3b_gate_bwd(const float* x, const float* grad_out, const int32_t* in_table, const float* in_const,

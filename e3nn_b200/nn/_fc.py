@@ -7,8 +7,7 @@ mirrors ``e3nn/math/_bessel.py:6-37``.  With ``math_mode='tf32x3'`` the layers w
 (h_in % 32 == 0, h_out % 16 == 0: the 64 -> weight_numel layer) run on the tcgen05 kernel of
 ``codegen/tc_gemm.py`` with hi/lo-split tf32 operands, forward and input gradient; other layers and
 ``math_mode='fp32'`` are plain dense GEMMs left to cuBLAS through ``torch.matmul`` in fp32.  The
-elementwise parts are torch operators.  Fusing this network into the convolution kernel (so that the
-per-edge weights never reach HBM) is the next step for the full interaction block.
+elementwise parts are torch operators.
 """
 from __future__ import annotations
 

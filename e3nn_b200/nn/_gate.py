@@ -50,14 +50,37 @@ def _activation_irreps(irreps: Irreps, acts: Sequence[Optional[str]]) -> Irreps:
     return Irreps(out)
 
 
+def channel_tables(out_tbl: torch.Tensor, out_cst: torch.Tensor):
+    """Per-channel form of the per-output-column table: runs of output columns that read consecutive input columns
+    and share one gate column become one entry {first input column, count, gate column, activation, first output
+    column}; scalars are runs of one.  Returns ``(int32 [n, 5], float32 [n])`` host tensors."""
+    rows, csts = [], []
+    tbl, cst = out_tbl.reshape(-1, 3).tolist(), out_cst.tolist()
+    j = 0
+    while j < len(tbl):
+        src, gate, act = tbl[j]
+        n = 1
+        if gate >= 0:
+            while j + n < len(tbl) and tbl[j + n][1] == gate and tbl[j + n][0] == src + n:
+                n += 1
+        rows.append([src, n, gate, act, j])
+        csts.append(cst[j])
+        j += n
+    return torch.tensor(rows, dtype=torch.int32).reshape(-1, 5), torch.tensor(csts, dtype=torch.float32)
+
+
 class _GateFunction(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, out_tbl, out_cst, in_tbl, in_cst, dout):
+    def forward(ctx, x, out_tbl, out_cst, in_tbl, in_cst, dout, ch_tbl=None, ch_cst=None):
         rows, din = x.shape
         out = torch.empty(rows, dout, dtype=torch.float32, device=x.device)
         with torch.cuda.device(x.device):
-            rc = _lib.core().e3b_gate_fwd(_lib._ptr(x), _lib._ptr(out_tbl), _lib._ptr(out_cst), _lib._ptr(out), rows, din, dout,
-                                          _lib.stream_ptr())
+            if ch_tbl is not None:
+                rc = _lib.core().e3b_gate_fwd_channels(_lib._ptr(x), _lib._ptr(ch_tbl), _lib._ptr(ch_cst), _lib._ptr(out), rows,
+                                                       din, dout, ch_tbl.shape[0], _lib.stream_ptr())
+            else:
+                rc = _lib.core().e3b_gate_fwd(_lib._ptr(x), _lib._ptr(out_tbl), _lib._ptr(out_cst), _lib._ptr(out), rows, din,
+                                              dout, _lib.stream_ptr())
         _lib.check(rc, "e3b_gate_fwd")
         ctx.save_for_backward(x, in_tbl, in_cst)
         ctx.dout = dout
@@ -73,7 +96,7 @@ class _GateFunction(torch.autograd.Function):
             rc = _lib.core().e3b_gate_bwd(_lib._ptr(x), _lib._ptr(grad_out.contiguous()), _lib._ptr(in_tbl), _lib._ptr(in_cst),
                                           _lib._ptr(gx), rows, din, ctx.dout, _lib.stream_ptr())
         _lib.check(rc, "e3b_gate_bwd")
-        return gx, None, None, None, None, None
+        return gx, None, None, None, None, None, None, None
 
 
 class Gate(torch.nn.Module):
@@ -146,6 +169,9 @@ class Gate(torch.nn.Module):
         self.register_buffer("_out_cst", torch.tensor(out_cst, dtype=torch.float32), persistent=False)
         self.register_buffer("_in_tbl", torch.tensor(in_tbl, dtype=torch.int32).reshape(-1, 5), persistent=False)
         self.register_buffer("_in_cst", torch.tensor(in_cst, dtype=torch.float32), persistent=False)
+        ch_tbl, ch_cst = channel_tables(self._out_tbl, self._out_cst)
+        self.register_buffer("_ch_tbl", ch_tbl, persistent=False)
+        self.register_buffer("_ch_cst", ch_cst, persistent=False)
 
     def __repr__(self) -> str:
         return f"{self.__class__.__name__} ({self.irreps_in} -> {self.irreps_out})"
@@ -156,9 +182,10 @@ class Gate(torch.nn.Module):
         torch._assert(features.shape[-1] == self.irreps_in.dim, "Incorrect last dimension for features")
         lead = features.shape[:-1]
         x = features.reshape(-1, self.irreps_in.dim).to(torch.float32).contiguous()
-        for name in ("_out_tbl", "_in_tbl"):
+        for name in ("_out_tbl", "_in_tbl", "_ch_tbl"):
             _lib.require_operand(getattr(self, name), x, f"Gate.{name} (move the module with .to(device))", None, torch.int32)
-        for name in ("_out_cst", "_in_cst"):
+        for name in ("_out_cst", "_in_cst", "_ch_cst"):
             _lib.require_operand(getattr(self, name), x, f"Gate.{name} (move the module with .to(device))")
-        out = _GateFunction.apply(x, self._out_tbl, self._out_cst, self._in_tbl, self._in_cst, self.irreps_out.dim)
+        out = _GateFunction.apply(x, self._out_tbl, self._out_cst, self._in_tbl, self._in_cst, self.irreps_out.dim,
+                                  self._ch_tbl if self._ch_tbl.shape[0] > 0 else None, self._ch_cst)
         return out.reshape(*lead, self.irreps_out.dim)

@@ -176,6 +176,12 @@ int e3b_radial_embed_bwd(const float* pos, const int64_t* edge_src, const int64_
  */
 int e3b_gate_fwd(const float* x, const int32_t* out_table, const float* out_const, float* out, int64_t rows, int din,
                  int dout, void* stream);
+/* The same forward map driven by a per-CHANNEL table (a scalar, or the 2l+1 components of one gated channel):
+ * channel_table [num_channels,5] int32 = {first input column, count, gate column or -1, activation, first output
+ * column}, channel_const [num_channels]; every output column must belong to exactly one channel.  The activation of
+ * a gate is evaluated once per channel instead of once per gated component. */
+int e3b_gate_fwd_channels(const float* x, const int32_t* channel_table, const float* channel_const, float* out,
+                          int64_t rows, int din, int dout, int num_channels, void* stream);
 int e3b_gate_bwd(const float* x, const float* grad_out, const int32_t* in_table, const float* in_const, float* grad_x,
                  int64_t rows, int din, int dout, void* stream);
 

@@ -13,7 +13,7 @@ is replaced by an identity stand-in before ``import e3nn``.
 
 Every case stores its fp32 inputs and the reference's fp64 output on those inputs
 (inputs upcast to fp64), plus the reference's own fp32 output for context.  The files
-are small on purpose: the layouts are the BASELINE ones, the batch is a handful of rows.
+are small on purpose: the layouts are those of the benchmark configurations, the batch is a handful of rows.
 """
 import json
 import os
