@@ -343,8 +343,8 @@ def run_gate(args, rank, world, device):
     rows_total = args.nodes if args.nodes > 0 else 1_048_576
     rows = rows_total // world
     gate = bnn.Gate("64x0e", [torch.nn.functional.silu], "192x0e", [torch.sigmoid], "64x1o+64x2e+64x3o").to(device)
-    lin = o3.Linear("64x0e+64x1o+64x2e+64x3o", gate.irreps_in).to(device)
-    fused = bnn.LinearGate(lin, gate).to(device)
+    lin = o3.Linear("64x0e+64x1o+64x2e+64x3o", gate.irreps_in, math_mode="tf32x3").to(device)   # tensor cores, hi/lo-split tf32
+    fused = bnn.LinearGate(lin, gate, fuse=True).to(device)
     gen = torch.Generator(device=device).manual_seed(rank)
     x = torch.randn(rows, gate.irreps_in.dim, device=device, generator=gen)
     h = torch.randn(rows, lin.irreps_in.dim, device=device, generator=gen)

@@ -340,6 +340,9 @@ class TcGemmModule:
         lib.e3b_tc_gemm_fwd.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p, c_void_p,
                                         c_void_p, c_void_p]
         lib.e3b_tc_gemm_fwd.restype = c_int
+        lib.e3b_tc_gemm_fwd_gate.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int64,
+                                             c_int, c_void_p, c_void_p, c_void_p]
+        lib.e3b_tc_gemm_fwd_gate.restype = c_int
         self.key = lib.e3b_layout_key().decode()
         self.scratch_bytes = int(lib.e3b_tc_gemm_scratch_bytes())
         self._scratch: Dict[str, torch.Tensor] = {}
@@ -357,6 +360,20 @@ class TcGemmModule:
             rc = self.lib.e3b_tc_gemm_fwd(_ptr(x1), _ptr(x2), _ptr(weight), _ptr(out), x1.shape[0], precision,
                                           _ptr(scratch), None, _ptr(status_word(dev)), stream_ptr())
         self.check(rc, "e3b_tc_gemm_fwd")
+        status_after_launch(dev)
+        return out
+
+    def run_gate(self, x1: torch.Tensor, weight: torch.Tensor, gate_tbl: torch.Tensor, gate_cst: torch.Tensor,
+                 gates: torch.Tensor, out: torch.Tensor, precision: int = 2):
+        """The contraction (a Linear) with Gate as its epilogue: `out` receives the Gate's output rows."""
+        dev = out.device
+        scratch = torch.empty(max(self.scratch_bytes, 16), dtype=torch.uint8, device=dev)
+        poll_status(dev)
+        with torch.cuda.device(dev), nvtx_range("e3b_tc_gemm_fwd_gate " + self.key):
+            rc = self.lib.e3b_tc_gemm_fwd_gate(_ptr(x1), _ptr(weight), _ptr(gate_tbl), _ptr(gate_cst), _ptr(gates),
+                                               gates.shape[1], _ptr(out), out.shape[1], x1.shape[0], precision,
+                                               _ptr(scratch), _ptr(status_word(dev)), stream_ptr())
+        self.check(rc, "e3b_tc_gemm_fwd_gate")
         status_after_launch(dev)
         return out
 

@@ -509,14 +509,51 @@ for (int q = 0; q < {qn}; ++q) {{{{
             }}
         }}
 """
+        # gate applied to the 16 values a thread holds for row z (Linear followed by Gate): the table entry of a
+        # channel (column of its component 0) gives kind, destination, activation and gate slot
+        gated_store = """if (ep.tbl != nullptr) {
+                        const int4 e0 = __ldg(reinterpret_cast<const int4*>(ep.tbl) + OUT_OFF + w0 * DIM);
+                        const int4 e15 = __ldg(reinterpret_cast<const int4*>(ep.tbl) + OUT_OFF + (w0 + 15) * DIM);
+                        const float* grow = ep.gates + z * ep.n_slots + e0.w;
+                        if (e0.x == 1 && e15.x == 1 && e15.y == e0.y + 15 * DIM && e15.w == e0.w + 15 &&
+                            (reinterpret_cast<uintptr_t>(grow) & 15u) == 0) {
+                            // 16 consecutive gated channels with consecutive gates and destinations (the layout a Gate
+                            // produces inside one irreps block): four 16-byte gate loads, no per-channel table reads
+                            float4 gq[4];
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) gq[q] = __ldg(reinterpret_cast<const float4*>(grow) + q);
+                            float* dstp = ep.final_out + z * ep.dout_final + e0.y + kq;
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                dstp[(4 * q) * DIM] = __uint_as_float(r[4 * q]) * gq[q].x;
+                                dstp[(4 * q + 1) * DIM] = __uint_as_float(r[4 * q + 1]) * gq[q].y;
+                                dstp[(4 * q + 2) * DIM] = __uint_as_float(r[4 * q + 2]) * gq[q].z;
+                                dstp[(4 * q + 3) * DIM] = __uint_as_float(r[4 * q + 3]) * gq[q].w;
+                            }
+                        } else {
+#pragma unroll 1
+                            for (int j = 0; j < 16; ++j) {
+                                const int c = OUT_OFF + (w0 + j) * DIM;
+                                const int4 e = __ldg(reinterpret_cast<const int4*>(ep.tbl) + c);
+                                const float v = __uint_as_float(r[j]);
+                                if (e.x == 1) ep.final_out[z * ep.dout_final + e.y + kq] = v * __ldg(ep.gates + z * ep.n_slots + e.w);
+                                else if (e.x == 0) ep.final_out[z * ep.dout_final + e.y] = __ldg(ep.cst + c) * tc::gate_act(e.z, v);
+                                else if (e.x == 2) ep.gates[z * ep.n_slots + e.w] = __ldg(ep.cst + c) * tc::gate_act(e.z, v);
+                            }
+                        }
+                    } else """
         if g.dim == 1 and dout % 4 == 0 and g.out_off % 4 == 0:
-            store = """#pragma unroll
+            store = gated_store + """{
+#pragma unroll
                     for (int q = 0; q < 4; ++q)
                         reinterpret_cast<float4*>(orow + w0)[q] = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
-                                                                             __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));"""
+                                                                             __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
+                    }"""
         else:
-            store = """#pragma unroll
-                    for (int j = 0; j < 16; ++j) orow[(w0 + j) * DIM + kq] = __uint_as_float(r[j]);"""
+            store = gated_store + """{
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) orow[(w0 + j) * DIM + kq] = __uint_as_float(r[j]);
+                    }"""
         if g.staged_epilogue():
             EPILOGUE = f"""            // 64 columns at a time: registers -> this warp's staging tile (16-byte chunks XOR-swizzled by row,
             // conflict free) -> read back two rows per instruction -> fully coalesced 256-byte row segments
@@ -548,12 +585,53 @@ for (int q = 0; q < {qn}; ++q) {{{{
                 }}}}
                 __syncwarp();
                 const int half = lane >> 4, cc = lane & 15;
+                if (ep.tbl != nullptr) {{{{
+                    // Gate on the scalar irreps: this lane's four columns keep their table entries for the 32 rows
+                    int4 e[4];
+                    float ec[4];
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {{{{
+                        const int c = OUT_OFF + wb + 4 * cc + q;
+                        e[q] = __ldg(reinterpret_cast<const int4*>(ep.tbl) + c);
+                        ec[q] = __ldg(ep.cst + c);
+                    }}}}
+                    // four columns of one kind with consecutive, 16-byte aligned destinations leave as one store
+                    const bool same = e[0].x == e[1].x && e[0].x == e[2].x && e[0].x == e[3].x && e[0].z == e[1].z &&
+                                      e[0].z == e[2].z && e[0].z == e[3].z;
+                    const bool vec_s = same && e[0].x == 0 && e[1].y == e[0].y + 1 && e[2].y == e[0].y + 2 && e[3].y == e[0].y + 3 &&
+                                       (e[0].y & 3) == 0 && (ep.dout_final & 3) == 0;
+                    const bool vec_g = same && e[0].x == 2 && e[1].w == e[0].w + 1 && e[2].w == e[0].w + 2 && e[3].w == e[0].w + 3 &&
+                                       (e[0].w & 3) == 0 && (ep.n_slots & 3) == 0;
+#pragma unroll 4
+                    for (int rr = 0; rr < 32; rr += 2) {{{{
+                        const int rl = rr + half;
+                        const float4 v = reinterpret_cast<const float4*>(se + rl * 64)[cc ^ (rl & 15)];
+                        const int64_t zr = t * ZT + warp * 32 + rl;
+                        if (zr >= Z) continue;
+                        const float vv[4] = {{{{v.x, v.y, v.z, v.w}}}};
+                        float a[4];
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) a[q] = ec[q] * tc::gate_act(e[q].z, vv[q]);
+                        if (vec_s) {{{{
+                            *reinterpret_cast<float4*>(ep.final_out + zr * ep.dout_final + e[0].y) = make_float4(a[0], a[1], a[2], a[3]);
+                        }}}} else if (vec_g) {{{{
+                            *reinterpret_cast<float4*>(ep.gates + zr * ep.n_slots + e[0].w) = make_float4(a[0], a[1], a[2], a[3]);
+                        }}}} else {{{{
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {{{{
+                                if (e[q].x == 0) ep.final_out[zr * ep.dout_final + e[q].y] = a[q];
+                                else if (e[q].x == 2) ep.gates[zr * ep.n_slots + e[q].w] = a[q];
+                            }}}}
+                        }}}}
+                    }}}}
+                }}}} else {{{{
 #pragma unroll 4
                 for (int rr = 0; rr < 32; rr += 2) {{{{
                     const int rl = rr + half;
                     const float4 v = reinterpret_cast<const float4*>(se + rl * 64)[cc ^ (rl & 15)];
                     const int64_t zr = t * ZT + warp * 32 + rl;
                     if (zr < Z) reinterpret_cast<float4*>(out + zr * {dout} + OUT_OFF + wb)[cc] = v;
+                }}}}
                 }}}}
                 __syncwarp();
             }}}}""".replace("{{", "{").replace("}}", "}")
@@ -601,7 +679,7 @@ for (int q = 0; q < {qn}; ++q) {{{{
 // ---------------------------------------------------------------- group {gi}: N = {g.n}, 2l+1 = {g.dim}, K = {32 * nch}
 __device__ __forceinline__ void run_group_{gi}(const float* __restrict__ x1, const float* __restrict__ x2,
         const uint8_t* __restrict__ bprep, float* __restrict__ out, int64_t Z, int cta, int nctas, uint8_t* smem,
-        int* status, int pieces, const CUtensorMap* tmap) {{
+        int* status, int pieces, const CUtensorMap* tmap, const GateEpilogue& ep) {{
     constexpr int N = {g.n}, DIM = {g.dim}, ZT = {g.zt}, NCHUNK = {nch}, NSTAGE = {g.nstage()}, NBUF = 2;
     // partial accumulators per buffer: even / odd k-steps accumulate in different TMEM columns, which halves
     // the length of each dependent MMA chain (and of the fp32 accumulation error); summed in the epilogue
@@ -744,7 +822,7 @@ __device__ __forceinline__ void prep_group_{gi}(const float* __restrict__ W, uin
 
     ng = len(gs.groups)
     dispatch = "\n".join(
-        f"    {'else ' if gi else ''}if (blockIdx.x < cta_end{gi}) run_group_{gi}(x1, x2, bprep, out, Z, blockIdx.x - cta_begin{gi}, cta_end{gi} - cta_begin{gi}, smem, status, pieces, &tmap_a);"
+        f"    {'else ' if gi else ''}if (blockIdx.x < cta_end{gi}) run_group_{gi}(x1, x2, bprep, out, Z, blockIdx.x - cta_begin{gi}, cta_end{gi} - cta_begin{gi}, smem, status, pieces, &tmap_a, ep);"
         for gi in range(ng))
     bounds = "\n".join(
         f"    const int cta_begin{gi} = {'0' if gi == 0 else f'cta_end{gi-1}'}, cta_end{gi} = cta_begin{gi} + split.n[{gi}];" for gi in range(ng))
@@ -776,12 +854,24 @@ constexpr long long kPrepBytes = {prep_off};
 
 struct CtaSplit {{ int n[kGroups]; }};
 
+// Gate applied in the epilogue (a Linear followed by Gate, e3nn/nn/_gate.py:127-144).  tbl[4 c ..] = {{kind,
+// destination column, activation, gate slot}} and cst[c] per column c of the Linear's output row: kind 0 scalar:
+// final[z, dst] = cst * act(v); kind 2 gate: gates[z, slot] = cst * act(v); kind 1 gated component k of a channel
+// whose component 0 is column c: final[z, dst + k] = v * gates[z, slot]; kind 3: unused.  tbl == nullptr: plain store.
+struct GateEpilogue {{
+    const int32_t* tbl;
+    const float* cst;
+    float* gates;
+    float* final_out;
+    int n_slots, dout_final;
+}};
+
 {chr(10).join(consts)}
 {''.join(funcs)}
 
 __global__ void __launch_bounds__(kThreads, 1) tc_gemm_kernel(const float* __restrict__ x1, const float* __restrict__ x2,
         const uint8_t* __restrict__ bprep, float* __restrict__ out, int64_t Z, CtaSplit split, int* status, int pieces,
-        const __grid_constant__ CUtensorMap tmap_a) {{
+        const __grid_constant__ CUtensorMap tmap_a, const GateEpilogue ep) {{
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
 {bounds}
@@ -804,45 +894,44 @@ extern "C" const char* e3b_layout_last_error(void) {{ return e3b_layout_error_bu
 extern "C" long long e3b_tc_gemm_scratch_bytes(void) {{ return kPrepBytes; }}
 
 static const int kGroupWork[kGroups] = {{{', '.join(str(g.work()) for g in gs.groups)}}};
+static const int kGroupDim[kGroups] = {{{', '.join(str(g.dim) for g in gs.groups)}}};   // 2l+1 of each output group
 
-// precision = number of tf32 pieces per operand: 1 = plain tf32 (1 MMA per step, ~1e-3 relative),
-// 2 = hi/lo split (3 MMAs, 22-bit operands, ~2e-5 x RMS); 3 (hi/mid/lo, 6 MMAs) only if the module was
-// generated with room for three pieces.
-// scratch: e3b_tc_gemm_scratch_bytes() bytes of device memory, 16-byte aligned (prepared weights).
-// cta_split: optional host array of kGroups CTA counts (NULL: proportional to the estimated work).
-extern "C" int e3b_tc_gemm_fwd(const float* x1, const float* x2, const float* weight, float* out, int64_t Z,
-                               int precision, void* scratch, const int* cta_split, int32_t* status, void* stream) {{
-    if (Z < 0) return e3b_layout_fail(-1, "tc_gemm: negative row count");
-    if (Z == 0) return 0;
-    if (!x1 || !weight || !out || !status || !scratch || ({d2} > 0 && !x2)) return e3b_layout_fail(-1, "tc_gemm: null pointer");
-    if (reinterpret_cast<uintptr_t>(out) % 16 != 0 || reinterpret_cast<uintptr_t>(scratch) % 16 != 0)
-        return e3b_layout_fail(-1, "tc_gemm: out and scratch must be 16-byte aligned");
-    if (precision < 1 || precision > {PIECES}) return e3b_layout_fail(-1, "tc_gemm: precision must be between 1 and {PIECES}");
-    if ({'true' if any(g.plain for g in gs.groups) else 'false'} && reinterpret_cast<uintptr_t>(x1) % 16 != 0)
-        return e3b_layout_fail(-1, "tc_gemm: x1 must be 16-byte aligned");
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
-{zero_fill}
+static int tc_gemm_launch(const float* x1, const float* x2, const float* weight, float* out, int64_t Z, int precision,
+                          void* scratch, const int* cta_split, int32_t* status, cudaStream_t s, const GateEpilogue& ep,
+                          int pass /* 0: every group; 1: groups of scalars only; 2: the other groups */, bool prepare) {{
     CtaSplit split;
     int used = 0;
+    bool any = false;
+    for (int g = 0; g < kGroups; ++g) any = any || pass == 0 || (pass == 1) == (kGroupDim[g] == 1);
+    if (!any) return 0;
     if (cta_split) {{
         for (int g = 0; g < kGroups; ++g) {{ split.n[g] = cta_split[g] < 1 ? 1 : cta_split[g]; used += split.n[g]; }}
     }} else {{
         const int num_ctas = 148 < kGroups ? kGroups : 148;
         long total = 0;
-        for (int g = 0; g < kGroups; ++g) total += kGroupWork[g];
         for (int g = 0; g < kGroups; ++g) {{
-            int n = static_cast<int>((static_cast<long>(num_ctas) * kGroupWork[g]) / total);
-            split.n[g] = n < 1 ? 1 : n;
-            used += split.n[g];
+            const bool on = pass == 0 || (pass == 1) == (kGroupDim[g] == 1);
+            total += on ? kGroupWork[g] : 0;
         }}
-        for (int g = kGroups - 1; used < num_ctas; g = (g + kGroups - 1) % kGroups) {{ split.n[g]++; used++; }}
-        while (used > num_ctas) {{
+        int on_groups = 0;
+        for (int g = 0; g < kGroups; ++g) {{
+            const bool on = pass == 0 || (pass == 1) == (kGroupDim[g] == 1);
+            int n = on ? static_cast<int>((static_cast<long>(num_ctas) * kGroupWork[g]) / total) : 0;
+            if (on && n < 1) n = 1;
+            split.n[g] = n;
+            used += n;
+            on_groups += on ? 1 : 0;
+        }}
+        for (int g = kGroups - 1; used < num_ctas; g = (g + kGroups - 1) % kGroups)
+            if (split.n[g] > 0) {{ split.n[g]++; used++; }}
+        while (used > num_ctas && used > on_groups) {{
             int big = 0;
             for (int g = 1; g < kGroups; ++g) if (split.n[g] > split.n[big]) big = g;
             split.n[big]--; used--;
         }}
     }}
-    tc_gemm_prep_kernel<<<dim3(({prep_max} + 255) / 256, kGroups), 256, 0, s>>>(weight, static_cast<uint8_t*>(scratch));
+    if (prepare)
+        tc_gemm_prep_kernel<<<dim3(({prep_max} + 255) / 256, kGroups), 256, 0, s>>>(weight, static_cast<uint8_t*>(scratch));
     cudaError_t err = cudaFuncSetAttribute(tc_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (err != cudaSuccess) return e3b_layout_fail(-2, "tc_gemm: smem attribute: %s", cudaGetErrorString(err));
     CUtensorMap tmap;
@@ -853,7 +942,54 @@ extern "C" int e3b_tc_gemm_fwd(const float* x1, const float* x2, const float* we
         if (rc != 0) return e3b_layout_fail(-2, "tc_gemm: cuTensorMapEncodeTiled failed (%d)", rc);
     }}
     tc_gemm_kernel<<<used, kThreads, kSmemBytes, s>>>(x1, x2, static_cast<const uint8_t*>(scratch), out, Z, split, status,
-                                                       precision, tmap);
+                                                       precision, tmap, ep);
     return e3b_layout_check("tc_gemm");
+}}
+
+static int tc_gemm_check_args(const float* x1, const float* x2, const float* weight, const float* out, int64_t Z,
+                              int precision, const void* scratch, const int32_t* status) {{
+    if (Z < 0) return e3b_layout_fail(-1, "tc_gemm: negative row count");
+    if (!x1 || !weight || !out || !status || !scratch || ({d2} > 0 && !x2)) return e3b_layout_fail(-1, "tc_gemm: null pointer");
+    if (reinterpret_cast<uintptr_t>(out) % 16 != 0 || reinterpret_cast<uintptr_t>(scratch) % 16 != 0)
+        return e3b_layout_fail(-1, "tc_gemm: out and scratch must be 16-byte aligned");
+    if (precision < 1 || precision > {PIECES}) return e3b_layout_fail(-1, "tc_gemm: precision must be between 1 and {PIECES}");
+    if ({'true' if any(g.plain for g in gs.groups) else 'false'} && reinterpret_cast<uintptr_t>(x1) % 16 != 0)
+        return e3b_layout_fail(-1, "tc_gemm: x1 must be 16-byte aligned");
+    return 0;
+}}
+
+// precision = number of tf32 pieces per operand: 1 = plain tf32 (1 MMA per step, ~1e-3 relative),
+// 2 = hi/lo split (3 MMAs, 22-bit operands, ~2e-5 x RMS); 3 (hi/mid/lo, 6 MMAs) only if the module was
+// generated with room for three pieces.
+// scratch: e3b_tc_gemm_scratch_bytes() bytes of device memory, 16-byte aligned (prepared weights).
+// cta_split: optional host array of kGroups CTA counts (NULL: proportional to the estimated work).
+extern "C" int e3b_tc_gemm_fwd(const float* x1, const float* x2, const float* weight, float* out, int64_t Z,
+                               int precision, void* scratch, const int* cta_split, int32_t* status, void* stream) {{
+    if (Z == 0) return 0;
+    if (int rc = tc_gemm_check_args(x1, x2, weight, out, Z, precision, scratch, status)) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+{zero_fill}
+    const GateEpilogue none{{nullptr, nullptr, nullptr, nullptr, 0, 0}};
+    return tc_gemm_launch(x1, x2, weight, out, Z, precision, scratch, cta_split, status, s, none, 0, true);
+}}
+
+// The same contraction with Gate as its epilogue (only meaningful for a Linear whose output row is a Gate's input
+// row): gate_table [dout, 4] int32 and gate_const [dout] describe the columns of that row as in GateEpilogue above,
+// gates [Z, n_slots] receives the activated gate scalars, out [Z, dout_final] the Gate's output row; the row of
+// {dout} columns itself is never written.  Two launches on `stream`: the scalar irreps (plain scalars and gates),
+// then the gated irreps, which read the gates of their rows.
+extern "C" int e3b_tc_gemm_fwd_gate(const float* x1, const float* weight, const int32_t* gate_table, const float* gate_const,
+                                    float* gates, int n_slots, float* out, int dout_final, int64_t Z, int precision,
+                                    void* scratch, int32_t* status, void* stream) {{
+    if (Z == 0) return 0;
+    if ({d2} > 0) return e3b_layout_fail(-3, "tc_gemm_fwd_gate: only layouts without a second operand (Linear)");
+    if (int rc = tc_gemm_check_args(x1, nullptr, weight, out, Z, precision, scratch, status)) return rc;
+    if (!gate_table || !gate_const || (n_slots > 0 && !gates) || n_slots < 0 || dout_final <= 0)
+        return e3b_layout_fail(-1, "tc_gemm_fwd_gate: bad gate arguments");
+    if (reinterpret_cast<uintptr_t>(gate_table) % 16 != 0) return e3b_layout_fail(-1, "tc_gemm_fwd_gate: gate_table must be 16-byte aligned");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const GateEpilogue ep{{gate_table, gate_const, gates, out, n_slots, dout_final}};
+    if (int rc = tc_gemm_launch(x1, nullptr, weight, out, Z, precision, scratch, nullptr, status, s, ep, 1, true)) return rc;
+    return tc_gemm_launch(x1, nullptr, weight, out, Z, precision, scratch, nullptr, status, s, ep, 2, false);
 }}
 """

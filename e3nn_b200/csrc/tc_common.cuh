@@ -5,7 +5,11 @@
 #include <cuda_runtime.h>
 #include <cstdint>
 
+#include "gate_act.cuh"
+
 namespace tc {
+
+using e3b::gate_act;    // activation codes of the Gate epilogue (csrc/gate_act.cuh)
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));

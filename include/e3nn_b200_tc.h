@@ -12,7 +12,9 @@
  *   - the per-irrep Linear and its transpose, e3nn/o3/_linear.py:445-469,
  *   - a dense layer x @ W * scale and its transpose, e3nn/nn/_fc.py:38-48
  *   as the layout it was generated for.  Operands are split into tf32 pieces in the kernel.
- * "uvwtc" modules (e3nn_b200/codegen/uvw_tc.py): the 'uvw' tensor product with plain tf32 operands.
+ * "uvwpost" / "uvwtc" modules (e3nn_b200/codegen/uvw_post.py, uvw_tc.py): the 'uvw' tensor product with plain tf32
+ *   operands; the first applies the Clebsch-Gordan coupling after the matrix product (raw input rows as the left
+ *   operand), the second before it, for layouts the first does not take.  Same entry point.
  */
 #ifndef E3NN_B200_TC_H
 #define E3NN_B200_TC_H
@@ -36,6 +38,18 @@ long long e3b_tc_gemm_scratch_bytes(void);
  */
 int e3b_tc_gemm_fwd(const float* x1, const float* x2, const float* weight, float* out, int64_t Z, int precision,
                     void* scratch, const int* cta_split, int32_t* status, void* stream);
+
+/*
+ * The contraction of a "tcg" Linear module with Gate (e3nn/nn/_gate.py:127-144) as its epilogue; the Linear's output
+ * row (the Gate's input row, `dout` columns) is never written.  gate_table [dout,4] int32 (16-byte aligned) =
+ * {kind, destination column, activation, gate slot} and gate_const [dout] per column of that row: kind 0 scalar:
+ * out[z, dst] = const * act(y); kind 2 gate: gates[z, slot] = const * act(y); kind 1 component k of a gated channel
+ * (entry of its component 0): out[z, dst + k] = y * gates[z, slot]; kind 3 unused.  gates [Z, n_slots], out
+ * [Z, dout_final] (the Gate's output row).  Activation codes of e3b_gate_fwd.  Two launches on `stream`.
+ */
+int e3b_tc_gemm_fwd_gate(const float* x1, const float* weight, const int32_t* gate_table, const float* gate_const,
+                         float* gates, int n_slots, float* out, int dout_final, int64_t Z, int precision, void* scratch,
+                         int32_t* status, void* stream);
 
 /*
  * 'uvw' tensor product with plain tf32 operands: x1 [Z, d1], x2 [Z, d2], weight [weight_numel] shared,

@@ -39,6 +39,7 @@ def prebuild():
         # the derived product that gives the gradient w.r.t. the first operand in the tensor-core modes
         for mode in ("tf32", "tf32x3"):
             pb._build_tp(o3.FullyConnectedTensorProduct(*layout, math_mode=mode)._vjp_module(0))
+    pb._build_linear(o3.Linear("64x0e+64x1o+64x2e+64x3o", "256x0e+64x1o+64x2e+64x3o", math_mode="tf32x3"))   # Linear -> Gate
     pb._build_linear(o3.Linear("16x0e+8x1o+4x2e", "8x0e+8x1o+4x2e"))
     pb._build_linear(o3.Linear("64x0e+32x1o+32x2e", "32x0e+64x1o+32x2e"))
     pb._build_tp(o3.ElementwiseTensorProduct("4x0e+3x1o+2x2e+5x1e", "4x0e+3x1o+2x1o+5x2e"))

@@ -699,6 +699,28 @@ def test_activation_golden_and_gradient(golden, golden_meta, name):
     assert act(torch.zeros(0, act.irreps_in.dim, device=DEV)).shape == (0, act.irreps_out.dim)
 
 
+def test_linear_gate_fused_tensor_cores():
+    """The same pair with the Linear on the tensor cores (hi/lo-split tf32 operands): Gate as the epilogue of the
+    tcgen05 kernel, against the fp64 oracle (1e-4, the bound of that Linear mode) and the two-module path."""
+    from e3nn_b200 import nn as bnn
+
+    gate = bnn.Gate("64x0e", [torch.nn.functional.silu], "192x0e", [torch.sigmoid], "64x1o+64x2e+64x3o").to(DEV)
+    lin = o3.Linear("64x0e+64x1o+64x2e+64x3o", gate.irreps_in, math_mode="tf32x3").to(DEV)
+    fused = bnn.LinearGate(lin, gate, fuse=True).to(DEV)
+    assert lin._tc_fwd is not None
+    torch.manual_seed(23)
+    x = torch.randn(777, lin.irreps_in.dim)
+    with torch.no_grad():
+        assert fused.fusable(x.to(DEV))
+        out = fused(x.to(DEV))
+        two = gate(lin(x.to(DEV)))
+    e3nn_b200.check_status()
+    y = orc.linear(str(lin.irreps_in), str(gate.irreps_in), x.double(), lin.weight.detach().cpu().double())
+    ref = orc.gate("64x0e", ["silu"], "192x0e", ["sigmoid"], "64x1o+64x2e+64x3o", y)
+    assert out.shape == ref.shape and rel_err(out.cpu(), ref) < TOL_TF32X3
+    assert rel_err(out.cpu(), two.cpu().double()) < 2e-6
+
+
 @pytest.mark.parametrize("name", ["gate_mixed", "gate_l3", "gate_abs_identity"])
 def test_linear_gate_fused(golden_meta, name):
     """Gate as the epilogue of the Linear that feeds it: equal to ``gate(linear(x))`` of the fp64 oracle within the fp32
@@ -712,7 +734,7 @@ def test_linear_gate_fused(golden_meta, name):
                     [fn[a] for a in m["act_gates"]], m["irreps_gated"]).to(DEV)
     irreps_x = "24x0e+8x0o+16x1o+8x1e+8x2e+4x2o+8x3o"
     lin = o3.Linear(irreps_x, gate.irreps_in).to(DEV)
-    fused = bnn.LinearGate(lin, gate).to(DEV)
+    fused = bnn.LinearGate(lin, gate, fuse=True).to(DEV)
     torch.manual_seed(17)
     x = torch.randn(3, 211, lin.irreps_in.dim)
     with torch.no_grad():

@@ -57,6 +57,8 @@ def test_provider_snippet_runs_the_reference_modules_on_these_kernels():
     torch.manual_seed(0)
     layout = ("8x0e+8x1o+4x2e", "0e+1o+2e", "8x0e+6x1o+4x2e")
     stock = o3.FullyConnectedTensorProduct(*layout)                       # the reference's own generated graph (CPU)
+    ins = [(0, 0, 0, "uvu", True), (1, 1, 0, "uvu", True), (1, 0, 1, "uvu", True), (0, 1, 1, "uvu", True)]
+    stock_u = o3.TensorProduct("4x0e+4x1o", "0e+1o", "4x0e+4x1o", ins, shared_weights=False, internal_weights=False)
     _tp._CODEGEN_PROVIDERS_LEFT_RIGHT.insert(0, b200_provider)
     try:
         patched = o3.FullyConnectedTensorProduct(*layout)                 # same class, main graph from the provider
@@ -66,8 +68,6 @@ def test_provider_snippet_runs_the_reference_modules_on_these_kernels():
         x, y = torch.randn(300, stock.irreps_in1.dim), torch.randn(300, stock.irreps_in2.dim)
         out = patched(x.to(dev), y.to(dev))
         # 'uvu' with per-row weights through the same seam
-        ins = [(0, 0, 0, "uvu", True), (1, 1, 0, "uvu", True), (1, 0, 1, "uvu", True), (0, 1, 1, "uvu", True)]
-        stock_u = o3.TensorProduct("4x0e+4x1o", "0e+1o", "4x0e+4x1o", ins, shared_weights=False, internal_weights=False)
         patched_u = o3.TensorProduct("4x0e+4x1o", "0e+1o", "4x0e+4x1o", ins, shared_weights=False, internal_weights=False).to(dev)
         xu, yu, wu = torch.randn(50, 16), torch.randn(50, 4), torch.randn(50, stock_u.weight_numel)
         out_u = patched_u(xu.to(dev), yu.to(dev), wu.to(dev))
