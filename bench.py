@@ -749,6 +749,32 @@ def run_interaction(args, rank, world, device):
     del keep, marks
     status_word = e3nn_b200.last_status_code()
 
+    # ---- the same step with every contraction in strict fp32 (CUDA-core Linear, library fp32 GEMM for the radial
+    # layer): the arithmetic mode whose error stays inside 1e-5 x RMS, reported beside the tensor-core default
+    fp32_ms = None
+    if world == 1 and not args.skip_secondary:
+        block32 = bnn.InteractionBlock("64x0e+64x1o+64x2e+64x3o", 3, num_basis=8, hidden=64, r_max=5.0, num_neighbors=E / n_atoms,
+                                       linear_math_mode="fp32", radial_math_mode="fp32").to(device)
+        block32.load_state_dict(block.state_dict())
+        for prm in block32.parameters():
+            prm.requires_grad_(False)
+
+        def step32():
+            p = pos_d.detach().requires_grad_(True)
+            (block32(p, x_full, src_d, dst_glob, rowptr, shift_d) * G).sum().backward()
+            return p.grad
+
+        step32()
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(2):
+            step32()
+        stop.record()
+        torch.cuda.synchronize()
+        fp32_ms = start.elapsed_time(stop) / 2
+        del block32
+        torch.cuda.empty_cache()
+
     # ---- dominant kernel alone (conv_bwd) and the forward convolution, events directly around the launches
     mod = tp._uvu_module()
     with torch.no_grad():
@@ -884,6 +910,8 @@ def run_interaction(args, rank, world, device):
     }
     if clocks and clocks.get("sm_mhz"):
         line["ms_per_step_x_sm_ghz"] = ms_step * clocks["sm_mhz"] * 1e-3   # for comparing N against N at different clocks
+    if fp32_ms is not None:
+        line["fp32_mode_ms_per_step"] = fp32_ms     # Linear and radial layer in strict fp32 instead of hi/lo-split tf32
     if tf32_peak is not None:
         line["tf32_peak_tflops"] = tf32_peak
     if secondary is not None:
@@ -997,23 +1025,29 @@ def cpu_interaction_sample(n_atoms: int, threads: int):
     return src.numel(), time.perf_counter() - t0
 
 
-CPU_SAMPLE_ATOMS = 512     # the CPU arms (cpu_baseline of the default line and --impl reference) time the same sample
+def cpu_sample_atoms(t_warm: float) -> int:
+    """Atoms of the CPU sample, the same rule in the `cpu_baseline` leg and in `--impl reference`: about 15 s of work
+    per step judged from the 256-atom warm-up (`t_warm` seconds), between 512 and 2,048 atoms in steps of 256."""
+    n = int(256 * 15.0 / max(t_warm, 1e-3)) // 256 * 256
+    return max(512, min(2048, n))
+
 
 
 def cpu_interaction_arm(steps: int, warmup: int):
-    """(value edges/s, seconds per step, steps, cpu_baseline dict) of the CPU arm on CPU_SAMPLE_ATOMS atoms."""
+    """(value edges/s, seconds per step, steps, cpu_baseline dict) of the CPU arm on the sample of `cpu_sample_atoms`."""
     threads = os.cpu_count() or 1
     ref = import_reference()
     fn, kind = (reference_interaction_sample, "reference") if ref is not None else (cpu_interaction_sample, "port")
-    for _ in range(warmup):
-        fn(256, threads)
-    runs = [fn(CPU_SAMPLE_ATOMS, threads) for _ in range(max(1, steps))]
+    fn(256, threads)                         # first call: graph construction, allocator warm-up
+    t_warm = fn(256, threads)[1]
+    n_atoms = cpu_sample_atoms(t_warm)
+    runs = [fn(n_atoms, threads) for _ in range(max(1, steps))]
     edges, t = runs[0][0], sum(r[1] for r in runs) / len(runs)
     what = ("e3nn 0.6.0 itself (eager fp32 torch-CPU, identity opt_einsum_fx stand-in, dead FX nodes removed)"
             if kind == "reference" else "fp32 torch-CPU oracle port (the reference is not installed in baseline/_ref)")
     base = {"value": edges / t, "unit": "edges/s", "cores": threads, "kind": kind,
-            "sample": f"{CPU_SAMPLE_ATOMS} atoms / {edges} edges at the same density, forward + position gradient, "
-                      f"{what}, {t:.1f} s per step"}
+            "sample": f"{n_atoms} atoms / {edges} edges at the same density, forward + position gradient, "
+                      f"{what}, {t:.1f} s per step", "sample_atoms": n_atoms}
     return edges / t, t, len(runs), base
 
 
@@ -1248,7 +1282,7 @@ def run_reference(args):
     if args.workload == "interaction_l3":
         value, t, steps, base = cpu_interaction_arm(steps, warmup)
         metric = "TP edges/sec (uvu l<=3, fp32): interaction block forward + gradient w.r.t. positions"
-        config = {"workload": "interaction_l3", "atoms": 262144, "cutoff": 5.0, "sample_atoms": CPU_SAMPLE_ATOMS}
+        config = {"workload": "interaction_l3", "atoms": 262144, "cutoff": 5.0, "sample_atoms": base["sample_atoms"]}
     else:
         workload = args.workload if args.workload in WORKLOADS else "conv_l2_15"
         layout, nodes, degree = WORKLOADS[workload]
