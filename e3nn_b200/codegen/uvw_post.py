@@ -16,25 +16,29 @@ coupling, and the coupling costs ``nnz(i, k)`` multiply-adds per accumulator val
 where ``t(z)`` is private to the thread (no work is repeated across lanes).  Both orders have the same
 matrix-product FLOPs.
 
-Kernel structure (persistent, one CTA per SM, a CTA serves one *group* = an output irrep restricted to a slab of
-S <= 64 of its channels):
-  * prologue: the group's weight slices W_p[:, slab] -> shared memory, rounded to tf32, K-major 128-byte swizzle;
-  * 4 producer warps de-interleave x1: one stage = the 128 x 32 tile ``x1[z0 + r, block(p), 32 kc + u, i]``
-    (fixed path p, component i, 32 channels); the 2 l1 + 1 component tiles of a chunk are filled together from
-    one contiguous run of each input row (16-byte loads in, 16-byte swizzled stores out); the same run of the
-    CTA's next row tile is requested into L2 at the same time;
-  * one thread issues ``tcgen05.mma.kind::tf32`` (M = 128, N = S, K = 8): per *job* (path) 2 l1 + 1 accumulators of
-    S columns each in one of two tensor-memory regions; jobs alternate between the regions so that the epilogue of
-    one job overlaps the matrix products of the next;
-  * 8 epilogue warps (two per lane quarter, each owning half of the slab's channels) compute t(z) from the x2 row,
-    read the accumulators with ``tcgen05.ld``, keep ``out[z, slab half, :]`` in registers across the jobs of the
-    tile and write it once, as one contiguous run per thread.
+Kernel structure (persistent, one CTA per SM, a CTA serves one *group* = one or more output irreps, or slabs of
+their channels, whose accumulators fit the registers of the epilogue threads together):
+  * prologue: for every input irrep ("block") of x1 the weight matrices of all paths that lead from it into the
+    group lie side by side as ONE right operand of N <= 256 columns -> shared memory, rounded to tf32, K-major
+    128-byte swizzle.  Paths that share an input block therefore share its left-operand tiles and its MMAs;
+  * left-operand tiles, one ring stage = the 128 x 32 tile ``x1[z0 + r, block, 32 kc + u, i]`` (component i, 32
+    channels).  Blocks of scalars need no de-interleaving: one thread issues a tensor-map TMA copy per stage.  For
+    the other blocks 4 producer warps fill the 2 l1 + 1 component tiles of a chunk together from one contiguous
+    run of each input row (16-byte streaming loads in, 16-byte swizzled stores out);
+  * one thread issues ``tcgen05.mma.kind::tf32`` (M = 128, N = the block's columns, K = 8).  A *job* is what the
+    epilogue receives as a whole: one component of a block when the block has a single 32-channel chunk (or a
+    single component), else all components of the block (the producers deliver chunk by chunk, so all component
+    accumulators are live).  Tensor memory is a ring of equal slots; the issuing thread runs ahead of the epilogue
+    by as many jobs as there are free slots, which also releases the ring stages of later jobs early;
+  * 8 epilogue warps (two per lane quarter, each owning half of every member's channels) compute t(z) from the x2
+    row, read the accumulators with ``tcgen05.ld``, keep their part of ``out[z, :]`` in registers across the jobs
+    of the tile and write it once through a per-warp staging tile, as 64-byte row segments with streaming stores.
 Register budget: the kernel is compiled for 128 registers per thread (512 threads); the epilogue and producer
 warpgroups raise their limit with ``setmaxnreg``, the issue warpgroup lowers its own.
 Every mbarrier wait is bounded; a wait that gives up sets the block's abort flag and status 3.
 
 Eligibility: every live path 'uvw' with shared weights, x2 multiplicities 1, x1 multiplicities multiples of 32,
-output multiplicities multiples of 16, output rows and group offsets multiples of four floats.
+output multiplicities multiples of 16, output rows, input rows and block offsets multiples of four floats.
 """
 from __future__ import annotations
 
@@ -48,8 +52,11 @@ from ..o3._wigner import wigner_3j_numpy
 
 SMEM_LIMIT = 227 * 1024
 TILE_BYTES = 128 * 128          # 128 rows x 32 tf32
-REGION_COLS = (320, 192)        # the two tensor-memory regions (columns)
-MAX_ACC_REGS = 96               # accumulator registers of an epilogue thread: (S / 2) * (2 l3 + 1)
+TMEM_COLS = 512
+STAGING_BYTES = 8 * 2048        # output staging tile of 32 rows x 16 floats per epilogue warp
+MAX_ACC_REGS = 96               # accumulator registers of an epilogue thread: sum over members of (width / 2) * (2 l3 + 1)
+MAX_N = 256                     # columns of one MMA instruction (M = 128)
+SLOT_POLICY = "ring"            # "ring": slots handed out round robin; "pingpong": two alternating regions
 
 
 def _f(v: float) -> str:
@@ -57,19 +64,47 @@ def _f(v: float) -> str:
 
 
 @dataclass
-class Job:
-    """One path of a group: 2 l1 + 1 accumulators of S columns."""
-    index: int          # instruction index
-    l1: int
-    l2: int
+class Member:
+    """An output irrep (or a slab of its channels) whose rows a group computes."""
+    i_out: int
     l3: int
-    mul1: int
-    off1: int           # x1 column of the path's input block
+    nfull: int          # output multiplicity
+    col0: int           # first channel of the slab
+    width: int          # channels of the slab
+    out_off: int        # output column of channel col0, component 0
+    acc_off: int = 0    # first accumulator register of an epilogue thread
+
+    @property
+    def d3(self) -> int:
+        return 2 * self.l3 + 1
+
+    @property
+    def half(self) -> int:
+        return self.width // 2
+
+
+@dataclass
+class Path:
+    index: int          # instruction index
+    l2: int
     off2: int           # x2 column of the path's second operand
-    woff: int           # weight offset of W_p[0, 0]
+    woff: int           # weight offset of W_p[0, col0]
     pw: float
-    region: int = 0
-    boff: int = 0       # byte offset of the path's weight tiles in the resident B area
+    member: int         # index into Group.members
+    coloff: int = 0     # first accumulator column of the path within its block's N columns
+
+
+@dataclass
+class Block:
+    """An input irrep of x1 with the paths that lead from it into the group's members.  All those paths share the
+    left operand, so their weight matrices lie side by side as ONE right operand of ``ncols`` columns."""
+    i_in1: int
+    l1: int
+    mul1: int
+    off1: int           # x1 column of the block
+    paths: List[Path] = field(default_factory=list)
+    ncols: int = 0
+    boff: int = 0       # byte offset of the block's weight tiles in the resident B area
 
     @property
     def d1(self) -> int:
@@ -79,48 +114,157 @@ class Job:
     def nchunk(self) -> int:
         return self.mul1 // 32
 
+    @property
+    def live(self) -> bool:
+        """True: the 2 l1 + 1 component accumulators are live together (one job); False: one job per component.
+        The producers emit the component tiles of a 32-channel chunk together, so components can only be separate
+        jobs when a block has a single chunk (or a single component)."""
+        return self.d1 > 1 and self.nchunk > 1
+
+
+@dataclass
+class Job:
+    """A run of ring stages accumulated into a range of tensor-memory slots and handed to the epilogue as a whole."""
+    block: int
+    comps: List[int]    # components of the block whose accumulators the job holds (ncols columns each)
+    nchunk: int
+    slot0: int = 0      # first slot; the job's barriers are those of this slot
+    nslot: int = 1
+    use_idx: int = 0    # this job is the use_idx-th job of a tile whose first slot is slot0
+    # completions of earlier jobs the issuing thread must have seen before it may overwrite the job's slots:
+    # (barrier = first slot of that job, its use_idx, True when that job belongs to the previous row tile)
+    waits: List[Tuple[int, int, bool]] = field(default_factory=list)
+
+    def cols(self, blocks: List[Block]) -> int:
+        return len(self.comps) * blocks[self.block].ncols
+
 
 @dataclass
 class Group:
-    i_out: int
-    l3: int
-    nfull: int          # output multiplicity
-    col0: int           # first channel of the slab
-    s: int              # slab width
-    out_off: int        # output column of channel col0, component 0
+    members: List[Member]
+    blocks: List[Block] = field(default_factory=list)
     jobs: List[Job] = field(default_factory=list)
+    slot_cols: int = 128        # tensor memory is handed out in slots of this many columns
+    nslots: int = 4
+    uses: List[int] = field(default_factory=list)   # per slot: jobs of a tile whose first slot it is
 
-    @property
-    def d3(self) -> int:
-        return 2 * self.l3 + 1
+    def nacc(self) -> int:
+        return sum(m.half * m.d3 for m in self.members)
 
     def b_bytes(self) -> int:
-        return sum(j.mul1 * self.s * 4 for j in self.jobs)
+        return sum(b.mul1 * b.ncols * 4 for b in self.blocks)
 
     def nstage(self) -> int:
-        return int(max(0, min(8, (SMEM_LIMIT - 4096 - self.b_bytes()) // TILE_BYTES)))
+        return int(max(0, min(8, (SMEM_LIMIT - 2048 - STAGING_BYTES - self.b_bytes()) // TILE_BYTES)))
 
     def smem_bytes(self) -> int:
-        return self.b_bytes() + self.nstage() * TILE_BYTES + 1024 + 1024
+        return self.b_bytes() + self.nstage() * TILE_BYTES + STAGING_BYTES + 1024 + 1024
 
     def tiles_per_row_tile(self) -> int:
-        return sum(j.d1 * j.nchunk for j in self.jobs)
+        return sum(b.d1 * b.nchunk for b in self.blocks)
+
+    def fma_per_row(self) -> int:
+        fma = 0
+        for b in self.blocks:
+            for p in b.paths:
+                m = self.members[p.member]
+                c = wigner_3j_numpy(b.l1, p.l2, m.l3)
+                fma += int((np.abs(c).sum(axis=1) != 0).sum()) * m.width
+        return fma
 
     def work(self) -> int:
         """Relative cost of one 128-row tile: producer instructions (tiles) plus epilogue multiply-adds."""
-        fma = 0
-        for j in self.jobs:
-            c = wigner_3j_numpy(j.l1, j.l2, j.l3)
-            nik = int((np.abs(c).sum(axis=1) != 0).sum())
-            fma += nik * self.s
-        return 100 * self.tiles_per_row_tile() + fma // 16
+        return 100 * self.tiles_per_row_tile() + self.fma_per_row() // 16
 
 
-def _slab_width(n: int, d1max: int, d3: int) -> Optional[int]:
-    for s in (64, 32, 16):
-        if n % s == 0 and d1max * s <= max(REGION_COLS) and (s // 2) * d3 <= MAX_ACC_REGS:
-            return s
-    return None
+def _plan_group(spec: TPSpec, members: List[Member]) -> Optional[Group]:
+    """Blocks, jobs and tensor-memory regions of a group, or None when it does not fit."""
+    live = spec.live_instructions()
+    o1, o2 = spec.irreps_in1.offsets(), spec.irreps_in2.offsets()
+    woffs = spec.weight_offsets()
+    g = Group(members=[Member(m.i_out, m.l3, m.nfull, m.col0, m.width, m.out_off) for m in members])
+    acc = 0
+    for m in g.members:
+        m.acc_off = acc
+        acc += m.half * m.d3
+        if m.out_off % 4 != 0 or (m.half * m.d3) % 4 != 0 or m.half % 8 != 0:
+            return None
+    if acc > MAX_ACC_REGS:
+        return None
+    by_block: Dict[int, Block] = {}
+    for n, ins in live:
+        for mi, m in enumerate(g.members):
+            if ins.i_out != m.i_out:
+                continue
+            (m1, ir1), (_, ir2) = spec.irreps_in1[ins.i_in1], spec.irreps_in2[ins.i_in2]
+            b = by_block.setdefault(ins.i_in1, Block(ins.i_in1, ir1.l, m1, o1[ins.i_in1]))
+            b.paths.append(Path(n, ir2.l, o2[ins.i_in2], woffs[n] + m.col0, float(ins.path_weight), mi))
+    if not by_block:
+        return None
+    boff = 0
+    for i_in1 in sorted(by_block):
+        b = by_block[i_in1]
+        col = 0
+        for p in b.paths:
+            p.coloff = col
+            col += g.members[p.member].width
+        b.ncols, b.boff = col, boff
+        boff += b.mul1 * b.ncols * 4
+        if b.ncols > MAX_N or b.ncols % 16 != 0:
+            return None
+        g.blocks.append(b)
+    jobs: List[Job] = []
+    for bi, b in enumerate(g.blocks):
+        if b.live or b.d1 == 1:
+            jobs.append(Job(bi, list(range(b.d1)), b.nchunk))
+        else:
+            jobs.extend(Job(bi, [i], 1) for i in range(b.d1))
+    # Tensor memory as a ring of equal slots: a single-component job takes one slot, a job that holds all components
+    # of a block takes as many as it needs.  The issuing thread runs ahead of the epilogue by as many jobs as there
+    # are free slots, so the ring stages of later jobs are consumed (and released to the producers) while the
+    # epilogue is still busy with an earlier, larger job.
+    single = [j.cols(g.blocks) for j in jobs if len(j.comps) == 1]
+    w = -(-max(single) // 32) * 32 if single else 128
+    nslots = min(8, TMEM_COLS // w)
+    pos = 0
+    uses = [0] * nslots
+    last_single = -1
+    for j in jobs:
+        k = -(-j.cols(g.blocks) // w)
+        if k > nslots:
+            return None
+        if SLOT_POLICY == "pingpong":
+            # two alternating regions: the last slot and everything before it
+            if k == 1 and nslots > 1 and last_single != nslots - 1:
+                pos = nslots - 1
+            else:
+                pos = 0
+            last_single = pos if k == 1 else -1
+        elif pos + k > nslots:
+            pos = 0
+        j.slot0, j.nslot = pos, k
+        j.use_idx = uses[pos]
+        uses[pos] += 1
+        pos += k
+    g.slot_cols, g.nslots, g.uses = w, nslots, uses
+    # who held a slot last, over two consecutive tiles (the schedule repeats per tile)
+    occupant: List[Optional[Tuple[int, int]]] = [None] * nslots       # (job index, tile)
+    seen = set()
+    for tile in (0, 1):
+        for ji, j in enumerate(jobs):
+            waits = []
+            for sl in range(j.slot0, j.slot0 + j.nslot):
+                o = occupant[sl]
+                if o is not None and o not in seen:
+                    seen.add(o)
+                    waits.append((jobs[o[0]].slot0, jobs[o[0]].use_idx, o[1] != tile))
+                occupant[sl] = (ji, tile)
+            if tile == 1:
+                j.waits = waits     # on a CTA's first tile the entries of the previous tile are skipped at run time
+    g.jobs = jobs
+    if g.nstage() < max(b.d1 for b in g.blocks) + 1:
+        return None
+    return g
 
 
 def plan_groups(spec: TPSpec) -> Optional[List[Group]]:
@@ -132,44 +276,35 @@ def plan_groups(spec: TPSpec) -> Optional[List[Group]]:
         return None
     if spec.irreps_in2.dim > 32 or spec.irreps_out.dim % 4 != 0 or spec.irreps_in1.dim % 4 != 0:
         return None
-    o1, o2, oo = spec.irreps_in1.offsets(), spec.irreps_in2.offsets(), spec.irreps_out.offsets()
-    woffs = spec.weight_offsets()
-    by_out: Dict[int, List[Job]] = {}
-    for n, ins in live:
-        (m1, ir1), (m2, ir2), (mo, iro) = spec.irreps_in1[ins.i_in1], spec.irreps_in2[ins.i_in2], spec.irreps_out[ins.i_out]
+    o1, oo = spec.irreps_in1.offsets(), spec.irreps_out.offsets()
+    for _, ins in live:
+        (m1, _), (m2, _), (mo, _) = spec.irreps_in1[ins.i_in1], spec.irreps_in2[ins.i_in2], spec.irreps_out[ins.i_out]
         if m2 != 1 or m1 % 32 != 0 or mo % 16 != 0 or o1[ins.i_in1] % 4 != 0:
             return None
-        by_out.setdefault(ins.i_out, []).append(
-            Job(n, ir1.l, ir2.l, iro.l, m1, o1[ins.i_in1], o2[ins.i_in2], woffs[n], float(ins.path_weight)))
     groups: List[Group] = []
-    for i_out in sorted(by_out):
-        jobs = by_out[i_out]
+    for i_out in sorted({ins.i_out for _, ins in live}):
         mo, iro = spec.irreps_out[i_out]
-        s = _slab_width(mo, max(j.d1 for j in jobs), iro.dim)
-        if s is None:
+        planned = None
+        for s in (mo, mo // 2, mo // 4, mo // 8):
+            if s < 16 or s % 16 != 0 or mo % s != 0:
+                continue
+            trial = [_plan_group(spec, [Member(i_out, iro.l, mo, col0, s, oo[i_out] + col0 * iro.dim)]) for col0 in range(0, mo, s)]
+            if all(t is not None for t in trial):
+                planned = trial
+                break
+        if planned is None:
             return None
-        for col0 in range(0, mo, s):
-            g = Group(i_out, iro.l, mo, col0, s, oo[i_out] + col0 * iro.dim)
-            # big jobs to the wide region, the others to the narrow one, alternating as long as both kinds last
-            wide = [j for j in jobs if j.d1 * s > REGION_COLS[1]]
-            narrow = [j for j in jobs if j.d1 * s <= REGION_COLS[1]]
-            if not wide:            # everything fits either region: split evenly
-                wide, narrow = narrow[1::2], narrow[0::2]
-            order: List[Tuple[Job, int]] = []
-            while wide or narrow:
-                if narrow:
-                    order.append((narrow.pop(0), 1))
-                if wide:
-                    order.append((wide.pop(0), 0))
-            boff = 0
-            for j, region in order:
-                g.jobs.append(Job(j.index, j.l1, j.l2, j.l3, j.mul1, j.off1, j.off2, j.woff, j.pw, region, boff))
-                boff += j.mul1 * s * 4
-            if any(j.d1 * s > REGION_COLS[j.region] for j in g.jobs):
-                return None
-            if g.out_off % 4 != 0 or ((s // 2) * iro.dim) % 4 != 0 or g.nstage() < max(j.d1 for j in g.jobs) + 1:
-                return None
-            groups.append(g)
+        groups.extend(planned)
+    # neighbouring groups whose accumulators fit one thread together share their left-operand tiles
+    merged = True
+    while merged:
+        merged = False
+        for a in range(len(groups) - 1):
+            both = _plan_group(spec, groups[a].members + groups[a + 1].members)
+            if both is not None:
+                groups[a:a + 2] = [both]
+                merged = True
+                break
     return groups
 
 
@@ -178,39 +313,50 @@ def _indent(text: str, n: int) -> str:
     return "\n".join(pad + line if line and not line.startswith("#pragma") else line for line in text.split("\n"))
 
 
-def _epilogue_job_code(g: Group, j: Job, d2_total: int) -> str:
-    """Straight-line epilogue of one job for the thread that owns row z: t(z), accumulator reads, multiply-adds.
-    In scope: x2r[] (the x2 row), acc[] (HALF * D3 floats), rbase (tensor-memory address of this thread's lane at
-    the thread's first column of region 0), valid."""
-    c = wigner_3j_numpy(j.l1, j.l2, j.l3) * j.pw
-    d1, d2, d3 = j.d1, 2 * j.l2 + 1, g.d3
-    half = g.s // 2
-    lines = [f"// path {j.index}: l={j.l1} (x) l={j.l2} -> l={j.l3}, {j.mul1} channels, region {j.region}"]
-    tnames: Dict[Tuple[int, int], str] = {}
-    for i in range(d1):
-        for k in range(d3):
-            terms = [(jj, c[i, jj, k]) for jj in range(d2) if c[i, jj, k] != 0.0]
-            if not terms:
-                continue
-            expr = " + ".join(f"{_f(v)} * x2r[{j.off2 + jj}]" for jj, v in terms)
-            tnames[(i, k)] = f"t{i}_{k}"
-            lines.append(f"const float t{i}_{k} = {expr};")
-    region_col = 0 if j.region == 0 else REGION_COLS[0]
-    step = 8
-    lines.append("#pragma unroll")
-    lines.append(f"for (int w0 = 0; w0 < {half}; w0 += {step}) {{")
-    for i in range(d1):
-        lines.append(f"    uint32_t v{i}[{step}];")
-        lines.append(f"    tc::tmem_ld8(rbase + {region_col + i * g.s} + w0, v{i});")
-    lines.append("    tc::tmem_ld_wait();")
-    lines.append("#pragma unroll")
-    lines.append(f"    for (int c = 0; c < {step}; ++c) {{")
-    for k in range(d3):
-        for i in range(d1):
-            if (i, k) in tnames:
-                lines.append(f"        acc[(w0 + c) * {d3} + {k}] = fmaf({tnames[(i, k)]}, __uint_as_float(v{i}[c]), acc[(w0 + c) * {d3} + {k}]);")
-    lines.append("    }")
-    lines.append("}")
+def _epilogue_job_code(g: Group, j: Job) -> str:
+    """Straight-line epilogue of one job for the thread that owns (row z, half h of every member's channels):
+    t(z) of the job's components, accumulator reads, multiply-adds.  In scope: x2r[] (the x2 row), acc[], lbase
+    (tensor-memory address of this thread's lane, column 0), h."""
+    b = g.blocks[j.block]
+    region_col = j.slot0 * g.slot_cols
+    lines = [f"// block {b.i_in1} (l = {b.l1}, {b.mul1} channels), components {j.comps}, slots [{j.slot0}, {j.slot0 + j.nslot})"]
+    for pi, p in enumerate(b.paths):
+        m = g.members[p.member]
+        c = wigner_3j_numpy(b.l1, p.l2, m.l3) * p.pw
+        d2, d3 = 2 * p.l2 + 1, m.d3
+        lines.append(f"{{   // path {p.index}: l={b.l1} (x) l={p.l2} -> l={m.l3}")
+        tn: Dict[Tuple[int, int], str] = {}
+        for i in j.comps:
+            for k in range(d3):
+                terms = [(jj, c[i, jj, k]) for jj in range(d2) if c[i, jj, k] != 0.0]
+                if not terms:
+                    continue
+                expr = " + ".join(f"{_f(v)} * x2r[{p.off2 + jj}]" for jj, v in terms)
+                tn[(i, k)] = f"t{i}_{k}"
+                lines.append(f"    const float t{i}_{k} = {expr};")
+        # a single-component job reads 16 columns per wait (two loads in flight), a job with all components 8 per component
+        step = 8
+        if len(j.comps) == 1:
+            step = 32 if m.half % 32 == 0 else (16 if m.half % 16 == 0 else 8)
+        lines.append(f"    const uint32_t cb = lbase + {region_col + p.coloff} + h * {m.half};")
+        lines.append("#pragma unroll")
+        lines.append(f"    for (int w0 = 0; w0 < {m.half}; w0 += {step}) {{")
+        for ci, i in enumerate(j.comps):
+            for part in range(step // 8):
+                lines.append(f"        uint32_t v{i}_{part}[8];")
+                lines.append(f"        tc::tmem_ld8(cb + {ci * b.ncols + part * 8} + w0, v{i}_{part});")
+        lines.append("        tc::tmem_ld_wait();")
+        for part in range(step // 8):
+            lines.append("#pragma unroll")
+            lines.append("        for (int c = 0; c < 8; ++c) {")
+            for k in range(d3):
+                for i in j.comps:
+                    if (i, k) in tn:
+                        a = f"acc[{m.acc_off} + (w0 + {part * 8} + c) * {d3} + {k}]"
+                        lines.append(f"            {a} = fmaf({tn[(i, k)]}, __uint_as_float(v{i}_{part}[c]), {a});")
+            lines.append("        }")
+        lines.append("    }")
+        lines.append("}")
     return "\n".join(lines)
 
 
@@ -223,68 +369,156 @@ def emit_module(spec: TPSpec) -> str:
 
     consts, funcs = [], []
     for gi, g in enumerate(groups):
-        nj = len(g.jobs)
-        arr = lambda name, vals: f"__constant__ int {name}{gi}[{nj}] = {{{', '.join(str(v) for v in vals)}}};"
+        nj, nb = len(g.jobs), len(g.blocks)
+        paths = [(b, p) for b in g.blocks for p in b.paths]
+        npth = len(paths)
+        arr = lambda name, vals: f"__constant__ int {name}{gi}[{len(vals)}] = {{{', '.join(str(v) for v in vals)}}};"
         consts.append("\n".join([
-            arr("kJWoff", [j.woff + g.col0 for j in g.jobs]),
-            arr("kJMul1", [j.mul1 for j in g.jobs]),
-            arr("kJBoff", [j.boff for j in g.jobs]),
-            arr("kJXoff", [j.off1 for j in g.jobs]),
-            arr("kJD1", [j.d1 for j in g.jobs]),
-            arr("kJRegion", [j.region for j in g.jobs]),
+            # per job
+            # per block (producers)
+            arr("kBXoff", [b.off1 for b in g.blocks]),
+            arr("kBD1", [b.d1 for b in g.blocks]),
+            arr("kBNchunk", [b.nchunk for b in g.blocks]),
+            # per path (weight prologue)
+            arr("kPWoff", [p.woff for b, p in paths]),
+            arr("kPMul1", [b.mul1 for b, p in paths]),
+            arr("kPBoff", [b.boff for b, p in paths]),
+            arr("kPNcols", [b.ncols for b, p in paths]),
+            arr("kPColoff", [p.coloff for b, p in paths]),
+            arr("kPWidth", [g.members[p.member].width for b, p in paths]),
+            arr("kPNfull", [g.members[p.member].nfull for b, p in paths]),
         ]))
-        half, d3 = g.s // 2, g.d3
-        nacc = half * d3
+        nacc = g.nacc()
         epi_jobs = []
         for ji, j in enumerate(g.jobs):
             epi_jobs.append(f"""{{
-    const int r = {j.region};
-    if (!tc::mbar_wait(&bar_reg_full[r], use{j.region} & 1u, abort_flag)) {{ ok = false; break; }}
+    constexpr int r = {j.slot0};
+    if (!tc::mbar_wait(&bar_reg_full[r], (tcount * {g.uses[j.slot0]}u + {j.use_idx}u) & 1u, abort_flag)) {{ ok = false; break; }}
     tc::tc_fence_after_sync();
-{_indent(_epilogue_job_code(g, j, d2t), 4)}
+{_indent(_epilogue_job_code(g, j), 4)}
     tc::tc_fence_before_sync();
     __syncwarp();
     if (lane == 0) tc::mbar_arrive(&bar_reg_empty[r]);
-    ++use{j.region};
 }}""")
         epi_code = "\n".join(epi_jobs)
+        mma_jobs = []
+        for ji, j in enumerate(g.jobs):
+            b = g.blocks[j.block]
+            waits = []
+            for bar, idx, prev in j.waits:
+                if prev:
+                    waits.append(f"    if (tcount > 0u && !tc::mbar_wait(&bar_reg_empty[{bar}], ((tcount - 1u) * {g.uses[bar]}u + {idx}u) & 1u, abort_flag)) {{ ok = false; break; }}")
+                else:
+                    waits.append(f"    if (!tc::mbar_wait(&bar_reg_empty[{bar}], (tcount * {g.uses[bar]}u + {idx}u) & 1u, abort_flag)) {{ ok = false; break; }}")
+            wait_code = "\n".join(waits)
+            mma_jobs.append(f"""{{   // job {ji}: block {b.i_in1}, components {j.comps}, slots [{j.slot0}, {j.slot0 + j.nslot})
+{wait_code}
+    tc::tc_fence_after_sync();
+    constexpr int ncomp = {len(j.comps)}, nchunk = {j.nchunk}, ncols = {b.ncols};
+    const uint32_t d0 = tmem_base + {j.slot0 * g.slot_cols}u;
+    constexpr uint32_t idesc = tc::idesc_tf32_m128({b.ncols}u);
+    const uint64_t bdesc0 = tc::smem_desc_k_sw128(tc::smem_u32(sB + {b.boff}));
+    for (int kc = 0; kc < nchunk && ok; ++kc) {{
+        const uint64_t bdesc = bdesc0 + static_cast<uint64_t>(kc) * ((ncols * 128) >> 4);
+        for (int c = 0; c < ncomp; ++c, ++it) {{
+            const int s = it % NSTAGE;
+            const uint32_t ph = (it / NSTAGE) & 1;
+            if (!tc::mbar_wait(&bar_full[s], ph, abort_flag)) {{ ok = false; break; }}
+            tc::tc_fence_after_sync();
+            const uint64_t adesc = tc::smem_desc_k_sw128(tc::smem_u32(sA + s * TILE));
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks)
+                tc::mma_tf32(d0 + c * ncols, adesc + ((ks * 32) >> 4), bdesc + ((ks * 32) >> 4), idesc, (kc > 0 || ks > 0) ? 1u : 0u);
+            tc::mma_commit(&bar_empty[s]);
+        }}
+    }}
+    if (!ok) break;
+    tc::mma_commit(&bar_reg_full[{j.slot0}]);
+}}""")
+        mma_code = "\n".join(mma_jobs)
+        # The thread that owns row z holds a contiguous run of each member's output row.  Stored directly, one
+        # instruction would touch 32 rows; the runs go through a per-warp staging tile of 32 rows x 16 floats instead
+        # (16-byte pieces, XOR-swizzled so that neither side has bank conflicts) and leave as 64-byte row segments,
+        # eight rows per instruction.
+        stores = []
+        for m in g.members:
+            n = m.half * m.d3
+            for c0 in range(0, n, 16):
+                wd = min(16, n - c0)
+                P = wd // 4
+                lines = [f"                {{   // member irrep {m.i_out}: floats [{c0}, {c0 + wd}) of the thread's run of {n}"]
+                for pc in range(P):
+                    a = m.acc_off + c0 + 4 * pc
+                    lines.append(f"                    *reinterpret_cast<float4*>(stg + lane * 16 + (({pc} ^ ((lane >> 1) & 3)) << 2)) = "
+                                 f"make_float4(acc[{a}], acc[{a + 1}], acc[{a + 2}], acc[{a + 3}]);")
+                lines.append("                    __syncwarp();")
+                lines.append("#pragma unroll")
+                lines.append(f"                    for (int it = 0; it < {P}; ++it) {{")
+                lines.append(f"                        const int idx = it * 32 + lane, rr = idx / {P}, pc = idx - rr * {P};")
+                lines.append("                        const float4 v = *reinterpret_cast<const float4*>(stg + rr * 16 + ((pc ^ ((rr >> 1) & 3)) << 2));")
+                lines.append(f"                        if (zw + rr < Z) __stcs(reinterpret_cast<float4*>(out + (zw + rr) * {dout} + {m.out_off + c0} + h * {n} + pc * 4), v);")
+                lines.append("                    }")
+                lines.append("                    __syncwarp();")
+                lines.append("                }")
+                stores.append("\n".join(lines))
+        store_code = "\n".join(stores)
         producer_cases = "\n".join(
             f"                    case {d}: ok = produce_group<{d}, NSTAGE>(src, z0, Z, sA, bar_full, bar_empty, it, abort_flag, pw, lane); break;"
-            for d in sorted({j.d1 for j in g.jobs}))
+            for d in sorted({b.d1 for b in g.blocks}) if d > 1)
+        if any(b.d1 == 1 for b in g.blocks):
+            # a block of scalars needs no de-interleaving: its 128 x 32 tile is one tensor-map copy (128-byte swizzle,
+            # rows past the end read as zero) issued by one thread, which also makes the arrivals of all producer warps
+            producer_cases += f"""
+                    case 1:
+                        if (pw == 0) {{
+                            if (lane == 0) {{
+                                const int s = it % NSTAGE;
+                                if (tc::mbar_wait(&bar_empty[s], ((it / NSTAGE) & 1u) ^ 1u, abort_flag))
+                                    tma_tile_to_stage(sA + s * TILE, tmap_x1, kBXoff{gi}[b] + kc * 32, static_cast<int32_t>(z0), &bar_full[s]);
+                                else
+                                    ok = false;
+                            }}
+                            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+                        }}
+                        ++it;
+                        break;"""
+        desc = ", ".join(f"irrep {m.i_out} (l = {m.l3}) channels [{m.col0}, {m.col0 + m.width}) of {m.nfull}" for m in g.members)
         funcs.append(f"""
-// ---------------------------------------------------------------- group {gi}: output irrep {g.i_out} (l = {g.l3}), channels [{g.col0}, {g.col0 + g.s}) of {g.nfull}
+// ---------------------------------------------------------------- group {gi}: {desc}
 __device__ __forceinline__ void run_group_{gi}(const float* __restrict__ x1, const float* __restrict__ x2,
-        const float* __restrict__ W, float* __restrict__ out, int64_t Z, int cta, int nctas, uint8_t* smem, int* status) {{
-    constexpr int S = {g.s}, HALF = {half}, NJOB = {nj}, NSTAGE = {g.nstage()}, NFULL = {g.nfull};
-    constexpr int OUT_OFF = {g.out_off};
+        const float* __restrict__ W, float* __restrict__ out, int64_t Z, int cta, int nctas, uint8_t* smem, int* status,
+        const CUtensorMap* tmap_x1) {{
+    constexpr int NBLOCK = {nb}, NPATH = {npth}, NSTAGE = {g.nstage()};
     constexpr uint32_t B_BYTES = {g.b_bytes()}, TILE = {TILE_BYTES};
-    constexpr uint32_t IDESC = tc::idesc_tf32_m128(S);
+    constexpr int NSLOT = {g.nslots};                      // tensor memory in slots of {g.slot_cols} columns
     uint8_t* sB = smem;
     uint8_t* sA = smem + B_BYTES;
-    uint64_t* bar_full = reinterpret_cast<uint64_t*>(sA + NSTAGE * TILE);
+    uint8_t* sStage = sA + NSTAGE * TILE;             // output staging: 2 KB per epilogue warp
+    uint64_t* bar_full = reinterpret_cast<uint64_t*>(sStage + kEpilogueWarps * 2048);
     uint64_t* bar_empty = bar_full + NSTAGE;
-    uint64_t* bar_reg_full = bar_empty + NSTAGE;      // [2] accumulators of a job complete
-    uint64_t* bar_reg_empty = bar_reg_full + 2;       // [2] the epilogue has read them
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_reg_empty + 2);
+    uint64_t* bar_reg_full = bar_empty + NSTAGE;      // [NSLOT] accumulators of the job whose first slot this is are complete
+    uint64_t* bar_reg_empty = bar_reg_full + NSLOT;   // [NSLOT] the epilogue has read them
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_reg_empty + NSLOT);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     volatile int* tile_progress = abort_flag + 1;     // row tiles the producers have started
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
-    // ---- prologue: the weight slices of the group's paths -> shared memory (tf32, K-major, 128-byte swizzle)
-    for (int j = 0; j < NJOB; ++j) {{
-        const int total = kJMul1{gi}[j] * S;
+    // ---- prologue: the weight matrices of the paths that leave one input block lie side by side as the block's
+    // right operand -> shared memory (tf32, K-major, 128-byte swizzle; row = accumulator column)
+    for (int p = 0; p < NPATH; ++p) {{
+        const int width = kPWidth{gi}[p], total = kPMul1{gi}[p] * width;
         for (int idx = tid; idx < total; idx += kThreads) {{
-            const int u = idx / S, w = idx - u * S;
-            const float v = W[kJWoff{gi}[j] + u * NFULL + w];
-            *reinterpret_cast<float*>(sB + kJBoff{gi}[j] + (u >> 5) * (S * 128) + tc::sw128_offset(w, u & 31)) = tc::to_tf32(v);
+            const int u = idx / width, w = idx - u * width;
+            const float v = W[kPWoff{gi}[p] + u * kPNfull{gi}[p] + w];
+            *reinterpret_cast<float*>(sB + kPBoff{gi}[p] + (u >> 5) * (kPNcols{gi}[p] * 128) + tc::sw128_offset(kPColoff{gi}[p] + w, u & 31)) = tc::to_tf32(v);
         }}
     }}
     if (tid == 0) {{
         *abort_flag = 0;
         *tile_progress = 0;
         for (int s = 0; s < NSTAGE; ++s) {{ tc::mbar_init(&bar_full[s], kProducerWarps); tc::mbar_init(&bar_empty[s], 1); }}
-        for (int r = 0; r < 2; ++r) {{ tc::mbar_init(&bar_reg_full[r], 1); tc::mbar_init(&bar_reg_empty[r], kEpilogueWarps); }}
+        for (int r = 0; r < NSLOT; ++r) {{ tc::mbar_init(&bar_reg_full[r], 1); tc::mbar_init(&bar_reg_empty[r], kEpilogueWarps); }}
         tc::mbar_init_fence();
     }}
     if (warp == kMmaWarp) tc::tmem_alloc(tmem_slot, kTmemCols);
@@ -298,11 +532,12 @@ __device__ __forceinline__ void run_group_{gi}(const float* __restrict__ x1, con
     if (warp < kEpilogueWarps) {{
         // ================= epilogue: t(z) from the x2 row, accumulators -> registers, coupling, one store per row
         asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kEpilogueRegs));
-        const int q = warp & 3, h = warp >> 2;          // lane quarter of tensor memory, half of the slab
-        const uint32_t rbase = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + h * HALF;
-        uint32_t use0 = 0u, use1 = 0u;          // jobs seen so far per tensor-memory region (barrier phase)
+        const int q = warp & 3, h = warp >> 2;          // lane quarter of tensor memory, half of every member's channels
+        const uint32_t lbase = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+        float* stg = reinterpret_cast<float*>(sStage + warp * 2048);
+        uint32_t tcount = 0u;                   // row tiles of this CTA so far (barrier phases follow from it)
         bool ok = true;
-        for (int64_t t = cta; t < tiles && ok; t += nctas) {{
+        for (int64_t t = cta; t < tiles && ok; t += nctas, ++tcount) {{
             const int64_t z = t * 128 + q * 32 + lane;
             const bool valid = z < Z;
             float x2r[{d2t}];
@@ -314,10 +549,9 @@ __device__ __forceinline__ void run_group_{gi}(const float* __restrict__ x1, con
             do {{
 {_indent(epi_code, 16)}
             }} while (false);
-            if (ok && valid) {{
-                float4* dst = reinterpret_cast<float4*>(out + z * {dout} + OUT_OFF + h * {nacc});
-#pragma unroll
-                for (int a = 0; a < {nacc // 4}; ++a) dst[a] = make_float4(acc[4 * a], acc[4 * a + 1], acc[4 * a + 2], acc[4 * a + 3]);
+            if (ok) {{
+                const int64_t zw = t * 128 + q * 32;        // first row of this warp
+{store_code}
             }}
         }}
     }} else if (warp < kEpilogueWarps + kProducerWarps) {{
@@ -331,10 +565,10 @@ __device__ __forceinline__ void run_group_{gi}(const float* __restrict__ x1, con
         for (int64_t t = cta; t < tiles && ok; t += nctas) {{
             const int64_t z0 = t * 128;
             if (pw == 0 && lane == 0) *tile_progress = ++tile_count;      // lets the prefetch warp run one row tile ahead
-            for (int j = 0; j < NJOB && ok; ++j) {{
-                const int d1 = kJD1{gi}[j], nchunk = kJMul1{gi}[j] >> 5;
+            for (int b = 0; b < NBLOCK && ok; ++b) {{
+                const int d1 = kBD1{gi}[b], nchunk = kBNchunk{gi}[b];
                 for (int kc = 0; kc < nchunk && ok; ++kc) {{
-                    const float* src = x1 + kJXoff{gi}[j] + kc * 32 * d1;
+                    const float* src = x1 + kBXoff{gi}[b] + kc * 32 * d1;
                     switch (d1) {{
 {producer_cases}
                     default: ok = false; break;
@@ -345,36 +579,15 @@ __device__ __forceinline__ void run_group_{gi}(const float* __restrict__ x1, con
     }} else {{
         asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kIssueRegs));
         if (warp == kMmaWarp && lane == 0) {{
-            // ================= MMA issue (single thread)
+            // ================= MMA issue (single thread): a job's stages arrive chunk by chunk, within a chunk
+            // component by component; component c of the job accumulates into columns [c N, (c + 1) N) of its slots
             uint32_t it = 0;
-            uint32_t use0 = 0u, use1 = 0u;
+            uint32_t tcount = 0u;
             bool ok = true;
-            for (int64_t t = cta; t < tiles && ok; t += nctas) {{
-                for (int j = 0; j < NJOB && ok; ++j) {{
-                    const int r = kJRegion{gi}[j], d1 = kJD1{gi}[j], nchunk = kJMul1{gi}[j] >> 5;
-                    const uint32_t use = r == 0 ? use0 : use1;
-                    if (!tc::mbar_wait(&bar_reg_empty[r], (use & 1u) ^ 1u, abort_flag)) {{ ok = false; break; }}
-                    tc::tc_fence_after_sync();
-                    const uint32_t d0 = tmem_base + (r == 0 ? 0u : {REGION_COLS[0]}u);
-                    const uint64_t bdesc0 = tc::smem_desc_k_sw128(tc::smem_u32(sB + kJBoff{gi}[j]));
-                    for (int kc = 0; kc < nchunk && ok; ++kc) {{
-                        const uint64_t bdesc = bdesc0 + static_cast<uint64_t>(kc) * ((S * 128) >> 4);
-                        for (int i = 0; i < d1; ++i, ++it) {{
-                            const int s = it % NSTAGE;
-                            const uint32_t ph = (it / NSTAGE) & 1;
-                            if (!tc::mbar_wait(&bar_full[s], ph, abort_flag)) {{ ok = false; break; }}
-                            tc::tc_fence_after_sync();
-                            const uint64_t adesc = tc::smem_desc_k_sw128(tc::smem_u32(sA + s * TILE));
-#pragma unroll
-                            for (int ks = 0; ks < 4; ++ks)
-                                tc::mma_tf32(d0 + i * S, adesc + ((ks * 32) >> 4), bdesc + ((ks * 32) >> 4), IDESC,
-                                             (kc > 0 || ks > 0) ? 1u : 0u);
-                            tc::mma_commit(&bar_empty[s]);
-                        }}
-                    }}
-                    if (ok) tc::mma_commit(&bar_reg_full[r]);
-                    if (r == 0) ++use0; else ++use1;
-                }}
+            for (int64_t t = cta; t < tiles && ok; t += nctas, ++tcount) {{
+                do {{
+{_indent(mma_code, 20)}
+                }} while (false);
             }}
         }} else if (warp == kMmaWarp + 1) {{
             // ================= prefetch warp: the x1 and x2 rows of this CTA's NEXT row tile -> L2 while the producers
@@ -415,12 +628,12 @@ __device__ __forceinline__ void run_group_{gi}(const float* __restrict__ x1, con
 
     ngroups = len(groups)
     dispatch = "\n".join(
-        f"    {'else ' if gi else ''}if (blockIdx.x < cta_end{gi}) run_group_{gi}(x1, x2, W, out, Z, blockIdx.x - cta_begin{gi}, cta_end{gi} - cta_begin{gi}, smem, status);"
+        f"    {'else ' if gi else ''}if (blockIdx.x < cta_end{gi}) run_group_{gi}(x1, x2, W, out, Z, blockIdx.x - cta_begin{gi}, cta_end{gi} - cta_begin{gi}, smem, status, &tmap_x1);"
         for gi in range(ngroups))
     bounds_decl = "\n".join(
         f"    const int cta_begin{gi} = {'0' if gi == 0 else f'cta_end{gi-1}'}, cta_end{gi} = cta_begin{gi} + split.n[{gi}];" for gi in range(ngroups))
     work = [g.work() for g in groups]
-    written = {g.i_out for g in groups}
+    written = {m.i_out for g in groups for m in g.members}
     oo = spec.irreps_out.offsets()
     zero_ranges = [(oo[i], mul * ir.dim) for i, (mul, ir) in enumerate(spec.irreps_out) if i not in written and mul * ir.dim > 0]
     zero_fill = "\n".join(
@@ -441,7 +654,7 @@ constexpr int kEpilogueWarps = 8;        // warpgroups 0 and 1
 constexpr int kProducerWarps = 4;        // warpgroup 2
 constexpr int kMmaWarp = 12;             // first warp of warpgroup 3; the next warp prefetches, the other two only take part in barriers
 constexpr int kThreads = 16 * 32;
-constexpr int kEpilogueRegs = 160, kProducerRegs = 152, kIssueRegs = 40;   // 32 x (8 x 160 + 4 x 152 + 4 x 40) = 65536 = 512 x 128 registers
+constexpr int kEpilogueRegs = 152, kProducerRegs = 152, kIssueRegs = 56;   // 32 x (8 x 152 + 4 x 152 + 4 x 56) = 65536 = 512 x 128 registers
 constexpr int kTmemCols = 512;
 constexpr int kGroups = {ngroups};
 constexpr int kSmemBytes = {smem_max};
@@ -453,13 +666,24 @@ struct CtaSplit {{ int n[kGroups]; }};
 // A thread owns (row, 4 channels) items: D 16-byte loads (element (channel e, component i) at float e D + i), then
 // one 16-byte store per component.  The raw fp32 values are stored: the tensor core reads the top 19 bits of a
 // tf32 operand (truncation; the weights are rounded to nearest in the prologue).  src: x1 + block offset + 32 kc D.
+// One 128 x 32 tile of the tensor map -> a ring stage; the issuing thread arrives for every producer warp, the
+// copy completes the phase through its byte count.  x: first column (a multiple of four floats), y: first row.
+__device__ __forceinline__ void tma_tile_to_stage(void* dst, const CUtensorMap* map, int32_t x, int32_t y, uint64_t* bar) {{
+    const uint32_t b = tc::smem_u32(bar);
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(b), "r"({TILE_BYTES}) : "memory");
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0], %1;" ::"r"(b), "r"(kProducerWarps - 1) : "memory");
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {{%2, %3}}], [%4];"
+                 ::"r"(tc::smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(b)
+                 : "memory");
+}}
+
 template <int D, int NSTAGE>
 __device__ __forceinline__ bool produce_group(const float* __restrict__ src, int64_t z0, int64_t Z, uint8_t* sA,
         uint64_t* bar_full, uint64_t* bar_empty, uint32_t& it, volatile int* abort_flag, int pw, int lane) {{
     static_assert(D < NSTAGE, "the ring must hold one chunk");
     constexpr int ROW = {d1t};
     const int q4 = lane & 7, rsub = lane >> 3;        // 16-byte column piece, row within a group of four rows
-    constexpr int H = D <= 5 ? 4 : 2;        // items per pass and thread (4 D registers each); 8 items per thread and chunk
+    constexpr int H = D <= 3 ? 8 : (D <= 5 ? 4 : 2);        // items per pass and thread (4 D registers each); 8 items per thread and chunk
     constexpr int NPASS = 8 / H;
 #pragma unroll
     for (int pass = 0; pass < NPASS; ++pass) {{
@@ -472,7 +696,7 @@ __device__ __forceinline__ bool produce_group(const float* __restrict__ src, int
             const float4* p = reinterpret_cast<const float4*>(src + z * ROW + q4 * 4 * D);
 #pragma unroll
             for (int m = 0; m < D; ++m) {{
-                const float4 v = __ldg(p + m);
+                const float4 v = __ldcs(p + m);      // streaming: a row tile is read once per group
                 f[h][4 * m] = v.x; f[h][4 * m + 1] = v.y; f[h][4 * m + 2] = v.z; f[h][4 * m + 3] = v.w;
             }}
         }}
@@ -508,7 +732,8 @@ __device__ __forceinline__ bool produce_group(const float* __restrict__ src, int
 {''.join(funcs)}
 
 __global__ void __launch_bounds__(kThreads, 1) uvw_post_kernel(const float* __restrict__ x1, const float* __restrict__ x2,
-        const float* __restrict__ W, float* __restrict__ out, int64_t Z, CtaSplit split, int* status) {{
+        const float* __restrict__ W, float* __restrict__ out, int64_t Z, CtaSplit split, int* status,
+        const __grid_constant__ CUtensorMap tmap_x1) {{
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment: required by the 128-byte swizzle atoms of the MMA operands
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -568,9 +793,13 @@ extern "C" int e3b_uvw_tc_fwd(const float* x1, const float* x2, const float* wei
         }}
         if (n == kGroups) {{ used = 0; for (int g = 0; g < kGroups; ++g) {{ split.n[g] = vals[g]; used += vals[g]; }} }}
     }}
+    CUtensorMap tmap_x1;
+    if (Z > 0x7fffffffLL) return e3b_layout_fail(-1, "uvw_tc_fwd: more than 2^31 - 1 rows");
+    const int enc = tc::encode_tensor_map_2d(&tmap_x1, x1, {d1t}, Z, 32, 128);
+    if (enc != 0) return e3b_layout_fail(-2, "uvw_tc_fwd: cuTensorMapEncodeTiled failed (%d)", enc);
     cudaError_t err = cudaFuncSetAttribute(uvw_post_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (err != cudaSuccess) return e3b_layout_fail(-2, "uvw_tc_fwd: smem attribute: %s", cudaGetErrorString(err));
-    uvw_post_kernel<<<used, kThreads, kSmemBytes, s>>>(x1, x2, weight, out, Z, split, status);
+    uvw_post_kernel<<<used, kThreads, kSmemBytes, s>>>(x1, x2, weight, out, Z, split, status, tmap_x1);
     return e3b_layout_check("uvw_tc_fwd");
 }}
 """

@@ -25,26 +25,29 @@ __device__ __forceinline__ void mbar_init_fence() {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+// One poll.  The time hint lets the hardware park the warp until the phase completes or about `hint_ns` have passed:
+// a parked warp takes no issue slots from the warps that share its scheduler (a plain try_wait returns at once, and
+// a loop around it competes with the single thread that issues the MMAs).
+#ifndef E3B_MBAR_HINT_NS
+#define E3B_MBAR_HINT_NS 1000u
+#endif
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity, uint32_t hint_ns = E3B_MBAR_HINT_NS) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
         : "memory");
     return ok != 0;
 }
-// Bounded wait: gives up after `limit` polls (or as soon as another thread of the block has
-// raised *abort), raises *abort itself and returns false.  No wait in these kernels is unbounded.
+// Bounded wait: gives up after `limit` polls of at most a microsecond each (or as soon as another thread of the
+// block has raised *abort), raises *abort itself and returns false.  No wait in these kernels is unbounded.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort, uint32_t limit = 200000u) {
     for (uint32_t it = 0; it < limit; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((it & 63u) == 63u) {
-            if (*abort) return false;
-            __nanosleep(64);
-        }
+        if (*abort) return false;
     }
     *abort = 1;
     return false;
