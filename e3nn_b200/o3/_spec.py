@@ -166,7 +166,11 @@ class TPSpec:
         return out
 
     def key(self) -> str:
-        """Stable hash of everything a generated kernel depends on."""
+        """Stable hash of everything a generated kernel depends on (computed once: the spec is immutable after
+        construction and the key is looked up on every forward call)."""
+        cached = self.__dict__.get("_key")
+        if cached is not None:
+            return cached
         blob = json.dumps(
             {
                 "in1": str(self.irreps_in1),
@@ -180,7 +184,8 @@ class TPSpec:
             },
             sort_keys=True,
         )
-        return hashlib.sha1(blob.encode()).hexdigest()[:16]
+        self.__dict__["_key"] = hashlib.sha1(blob.encode()).hexdigest()[:16]
+        return self.__dict__["_key"]
 
 
 def normalize_linear_instructions(

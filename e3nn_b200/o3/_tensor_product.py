@@ -402,7 +402,9 @@ class TensorProduct(torch.nn.Module):
         if self.math_mode == "tf32":
             from ._uvw_tc import tc_eligible, uvw_tc_forward
 
-            if tc_eligible(self):
+            if not hasattr(self, "_tc_ok"):
+                self._tc_ok = tc_eligible(self)     # planning the groups costs a fraction of a millisecond: once
+            if self._tc_ok:
                 return uvw_tc_forward(self, x2d, y2d, w, out, accumulate)
             if not getattr(self, "_warned_tc", False):
                 warnings.warn(f"{self}: layout not eligible for the tensor-core kernel, using the fp32 kernel")
