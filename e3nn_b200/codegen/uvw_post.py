@@ -56,7 +56,6 @@ TMEM_COLS = 512
 STAGING_BYTES = 8 * 2048        # output staging tile of 32 rows x 16 floats per epilogue warp
 MAX_ACC_REGS = 96               # accumulator registers of an epilogue thread: sum over members of (width / 2) * (2 l3 + 1)
 MAX_N = 256                     # columns of one MMA instruction (M = 128)
-SLOT_POLICY = "ring"            # "ring": slots handed out round robin; "pingpong": two alternating regions
 
 
 def _f(v: float) -> str:
@@ -228,19 +227,11 @@ def _plan_group(spec: TPSpec, members: List[Member]) -> Optional[Group]:
     nslots = min(8, TMEM_COLS // w)
     pos = 0
     uses = [0] * nslots
-    last_single = -1
     for j in jobs:
         k = -(-j.cols(g.blocks) // w)
         if k > nslots:
             return None
-        if SLOT_POLICY == "pingpong":
-            # two alternating regions: the last slot and everything before it
-            if k == 1 and nslots > 1 and last_single != nslots - 1:
-                pos = nslots - 1
-            else:
-                pos = 0
-            last_single = pos if k == 1 else -1
-        elif pos + k > nslots:
+        if pos + k > nslots:
             pos = 0
         j.slot0, j.nslot = pos, k
         j.use_idx = uses[pos]
@@ -313,51 +304,85 @@ def _indent(text: str, n: int) -> str:
     return "\n".join(pad + line if line and not line.startswith("#pragma") else line for line in text.split("\n"))
 
 
-def _epilogue_job_code(g: Group, j: Job) -> str:
-    """Straight-line epilogue of one job for the thread that owns (row z, half h of every member's channels):
-    t(z) of the job's components, accumulator reads, multiply-adds.  In scope: x2r[] (the x2 row), acc[], lbase
-    (tensor-memory address of this thread's lane, column 0), h."""
-    b = g.blocks[j.block]
-    region_col = j.slot0 * g.slot_cols
-    lines = [f"// block {b.i_in1} (l = {b.l1}, {b.mul1} channels), components {j.comps}, slots [{j.slot0}, {j.slot0 + j.nslot})"]
+def _epilogue_block_code(g: Group, gi: int, bi: int) -> Tuple[str, List[str]]:
+    """Epilogue of all jobs of one input block as a loop over the block's components, for the thread that owns (row z,
+    half h of every member's channels).  The body is the same for every component: t_k(z) = sum_j C[i, j, k] x2[z, j]
+    with the coefficients of component i read from constant memory, then ``acc[w, k] += t_k V_i[w]`` for all k (the
+    accumulator registers depend on (w, k) only).  Unrolling over the components instead (with the zero coefficients
+    left out) is straight-line code of 800 - 2,000 instructions per row tile and thread, more than the instruction
+    cache holds for the two epilogue warps of a scheduler.  Returns (code, constant tables).
+    In scope: x2r[], acc[], lbase (tensor-memory address of this thread's lane, column 0), h, tcount, ok."""
+    b = g.blocks[bi]
+    jobs = [j for j in g.jobs if j.block == bi]
+    consts: List[str] = []
+    body = []
     for pi, p in enumerate(b.paths):
         m = g.members[p.member]
-        c = wigner_3j_numpy(b.l1, p.l2, m.l3) * p.pw
+        c = wigner_3j_numpy(b.l1, p.l2, m.l3) * p.pw              # [d1, d2, d3]
         d2, d3 = 2 * p.l2 + 1, m.d3
-        lines.append(f"{{   // path {p.index}: l={b.l1} (x) l={p.l2} -> l={m.l3}")
-        tn: Dict[Tuple[int, int], str] = {}
-        for i in j.comps:
-            for k in range(d3):
-                terms = [(jj, c[i, jj, k]) for jj in range(d2) if c[i, jj, k] != 0.0]
-                if not terms:
-                    continue
-                expr = " + ".join(f"{_f(v)} * x2r[{p.off2 + jj}]" for jj, v in terms)
-                tn[(i, k)] = f"t{i}_{k}"
-                lines.append(f"    const float t{i}_{k} = {expr};")
-        # a single-component job reads 16 columns per wait (two loads in flight), a job with all components 8 per component
-        step = 8
-        if len(j.comps) == 1:
-            step = 32 if m.half % 32 == 0 else (16 if m.half % 16 == 0 else 8)
-        lines.append(f"    const uint32_t cb = lbase + {region_col + p.coloff} + h * {m.half};")
+        name = f"kC{gi}_{bi}_{pi}"
+        consts.append(f"__constant__ float {name}[{b.d1 * d2 * d3}] = {{{', '.join(_f(v) for v in c.reshape(-1))}}};")
+        step = 32 if m.half % 32 == 0 else (16 if m.half % 16 == 0 else 8)
+        lines = [f"{{   // path {p.index}: l={b.l1} (x) l={p.l2} -> l={m.l3}", f"    float tk[{d3}];"]
+        tk_lines = []
+        for k in range(d3):
+            expr = " + ".join(f"{name}[(i * {d2} + {jj}) * {d3} + {k}] * x2r[{p.off2 + jj}]" for jj in range(d2))
+            tk_lines.append(f"        if (w0 == 0) tk[{k}] = {expr};")
+        lines.append(f"    const uint32_t cb = jb + {p.coloff} + h * {m.half};")
         lines.append("#pragma unroll")
         lines.append(f"    for (int w0 = 0; w0 < {m.half}; w0 += {step}) {{")
-        for ci, i in enumerate(j.comps):
-            for part in range(step // 8):
-                lines.append(f"        uint32_t v{i}_{part}[8];")
-                lines.append(f"        tc::tmem_ld8(cb + {ci * b.ncols + part * 8} + w0, v{i}_{part});")
+        for part in range(step // 8):
+            lines.append(f"        uint32_t v{part}[8];")
+            lines.append(f"        tc::tmem_ld8(cb + w0 + {part * 8}, v{part});")
+        lines.extend(tk_lines)      # the coefficients are formed while the first accumulator loads are in flight
         lines.append("        tc::tmem_ld_wait();")
         for part in range(step // 8):
             lines.append("#pragma unroll")
             lines.append("        for (int c = 0; c < 8; ++c) {")
             for k in range(d3):
-                for i in j.comps:
-                    if (i, k) in tn:
-                        a = f"acc[{m.acc_off} + (w0 + {part * 8} + c) * {d3} + {k}]"
-                        lines.append(f"            {a} = fmaf({tn[(i, k)]}, __uint_as_float(v{i}_{part}[c]), {a});")
+                a = f"acc[{m.acc_off} + (w0 + {part * 8} + c) * {d3} + {k}]"
+                lines.append(f"            {a} = fmaf(tk[{k}], __uint_as_float(v{part}[c]), {a});")
             lines.append("        }")
         lines.append("    }")
         lines.append("}")
-    return "\n".join(lines)
+        body.append("\n".join(lines))
+    body_code = "\n".join(body)
+    head = f"// block {b.i_in1} (l = {b.l1}, {b.mul1} channels)"
+    if len(jobs) == 1:
+        j = jobs[0]
+        code = f"""{head}: one job, slots [{j.slot0}, {j.slot0 + j.nslot})
+{{
+    constexpr int r = {j.slot0};
+    if (!tc::mbar_wait(&bar_reg_full[r], (tcount * {g.uses[j.slot0]}u + {j.use_idx}u) & 1u, abort_flag)) {{ ok = false; break; }}
+    tc::tc_fence_after_sync();
+#pragma unroll 1
+    for (int i = 0; i < {b.d1}; ++i) {{
+        const uint32_t jb = lbase + {j.slot0 * g.slot_cols} + i * {b.ncols};
+{_indent(body_code, 8)}
+    }}
+    tc::tc_fence_before_sync();
+    __syncwarp();
+    if (lane == 0) tc::mbar_arrive(&bar_reg_empty[r]);
+}}"""
+    else:
+        arr = lambda nm, vals: f"__constant__ int {nm}{gi}_{bi}[{len(vals)}] = {{{', '.join(str(v) for v in vals)}}};"
+        consts.append(arr("kESlot", [j.slot0 for j in jobs]))
+        consts.append(arr("kEUses", [g.uses[j.slot0] for j in jobs]))
+        consts.append(arr("kEIdx", [j.use_idx for j in jobs]))
+        code = f"""{head}: one job per component
+#pragma unroll 1
+for (int i = 0; i < {b.d1}; ++i) {{
+    const int r = kESlot{gi}_{bi}[i];
+    if (!tc::mbar_wait(&bar_reg_full[r], (tcount * kEUses{gi}_{bi}[i] + kEIdx{gi}_{bi}[i]) & 1u, abort_flag)) {{ ok = false; break; }}
+    tc::tc_fence_after_sync();
+    const uint32_t jb = lbase + r * {g.slot_cols};
+{_indent(body_code, 4)}
+    tc::tc_fence_before_sync();
+    __syncwarp();
+    if (lane == 0) tc::mbar_arrive(&bar_reg_empty[r]);
+}}
+if (!ok) break;"""
+    return code, consts
 
 
 def emit_module(spec: TPSpec) -> str:
@@ -389,18 +414,12 @@ def emit_module(spec: TPSpec) -> str:
             arr("kPNfull", [g.members[p.member].nfull for b, p in paths]),
         ]))
         nacc = g.nacc()
-        epi_jobs = []
-        for ji, j in enumerate(g.jobs):
-            epi_jobs.append(f"""{{
-    constexpr int r = {j.slot0};
-    if (!tc::mbar_wait(&bar_reg_full[r], (tcount * {g.uses[j.slot0]}u + {j.use_idx}u) & 1u, abort_flag)) {{ ok = false; break; }}
-    tc::tc_fence_after_sync();
-{_indent(_epilogue_job_code(g, j), 4)}
-    tc::tc_fence_before_sync();
-    __syncwarp();
-    if (lane == 0) tc::mbar_arrive(&bar_reg_empty[r]);
-}}""")
-        epi_code = "\n".join(epi_jobs)
+        blocks_code = []
+        for bi in range(len(g.blocks)):
+            code, tables = _epilogue_block_code(g, gi, bi)
+            blocks_code.append(code)
+            consts.append("\n".join(tables))
+        epi_code = "\n".join(blocks_code)
         mma_jobs = []
         for ji, j in enumerate(g.jobs):
             b = g.blocks[j.block]
@@ -537,18 +556,25 @@ __device__ __forceinline__ void run_group_{gi}(const float* __restrict__ x1, con
         float* stg = reinterpret_cast<float*>(sStage + warp * 2048);
         uint32_t tcount = 0u;                   // row tiles of this CTA so far (barrier phases follow from it)
         bool ok = true;
-        for (int64_t t = cta; t < tiles && ok; t += nctas, ++tcount) {{
-            const int64_t z = t * 128 + q * 32 + lane;
-            const bool valid = z < Z;
-            float x2r[{d2t}];
+        float x2r[{d2t}];
+        {{
+            const int64_t z = cta * 128 + q * 32 + lane;
 #pragma unroll
-            for (int j = 0; j < {d2t}; ++j) x2r[j] = valid ? x2[z * {d2t} + j] : 0.0f;
+            for (int j = 0; j < {d2t}; ++j) x2r[j] = (cta < tiles && z < Z) ? x2[z * {d2t} + j] : 0.0f;
+        }}
+        for (int64_t t = cta; t < tiles && ok; t += nctas, ++tcount) {{
             float acc[{nacc}];
 #pragma unroll
             for (int a = 0; a < {nacc}; ++a) acc[a] = 0.0f;
             do {{
 {_indent(epi_code, 16)}
             }} while (false);
+            {{
+                // the x2 row of this CTA's next row tile is requested before the store phase, which hides its latency
+                const int64_t zn = (t + nctas) * 128 + q * 32 + lane;
+#pragma unroll
+                for (int j = 0; j < {d2t}; ++j) x2r[j] = (t + nctas < tiles && zn < Z) ? x2[zn * {d2t} + j] : 0.0f;
+            }}
             if (ok) {{
                 const int64_t zw = t * 128 + q * 32;        // first row of this warp
 {store_code}
