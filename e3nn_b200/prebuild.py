@@ -17,7 +17,7 @@ from .o3._tensor_product import TensorProduct
 
 def _build_tp(tp: TensorProduct) -> str:
     """Every generated module a TensorProduct can use: 'uvu' layout module, tf32 and fp32 tensor-core modules."""
-    from .codegen import tc_gemm, uvw_tc
+    from .codegen import tc_gemm, uvw_post, uvw_tc
 
     paths = []
     if tp._has_uvu:
@@ -25,7 +25,7 @@ def _build_tp(tp: TensorProduct) -> str:
     for n in tp._uuu_ids:
         paths.append(tp._uuu_sub(n)._uvu_module().path)
     if tp._uvw_ids and not tp._has_uvu:
-        if uvw_tc.plan_groups(tp._spec) is not None:
+        if uvw_post.plan_groups(tp._spec) is not None or uvw_tc.plan_groups(tp._spec) is not None:
             paths.append(_lib.uvw_tc_module(tp._spec).path)
         gs = tc_gemm.uvw_gemm_spec(tp._spec)
         if gs is not None:

@@ -27,12 +27,25 @@ def conv_tps():
     ]
 
 
+# layouts that exercise the planner of the post-coupling tensor-core kernel: merged output irreps, slabs of unequal
+# width, blocks whose components are all live at once (several 32-channel chunks), odd-parity irreps, a scalar-only
+# second operand
+UVW_TC_EXTRA_LAYOUTS = [
+    ("64x0e+64x1o+64x2e", "0e+1o+2e", "48x0e+32x1o+16x2e"),
+    ("96x0e+32x1e+32x2e+32x3o", "0e+1o+2e+3o", "64x0e+32x1o+32x2e+16x3o"),
+    ("32x0e+32x1o", "0e+1o", "256x0e+16x1o"),
+    ("64x0e+64x1o+64x2e+64x3o", "0e", "64x0e+64x1o+64x2e+64x3o"),
+]
+
+
 def prebuild():
     from e3nn_b200 import prebuild as pb
 
     for tp in conv_tps():
         tp._uvu_module()
     # layouts of the tensor-core tests
+    for layout in UVW_TC_EXTRA_LAYOUTS:
+        pb._build_tp(o3.FullyConnectedTensorProduct(*layout, math_mode="tf32"))
     for layout in [("32x0e+32x1o+32x2e", "1x0e+1x1o+1x2e", "32x0e+32x1o+32x2e"),
                    ("128x0e+64x1o+32x2e", "0e+1o+2e+3o", "128x0e+64x1o+32x2e")]:
         pb._build_tp(o3.FullyConnectedTensorProduct(*layout, math_mode="tf32x3"))

@@ -352,7 +352,7 @@ TOL_TF32 = 2e-2  # stated bound for the tf32 tensor-core path
 @pytest.mark.parametrize("layout", [
     ("32x0e+32x1o+32x2e", "1x0e+1x1o+1x2e", "32x0e+32x1o+32x2e"),          # benchmark case 1 (10,000-row fully connected product)
     ("128x0e+64x1o+32x2e", "0e+1o+2e+3o", "128x0e+64x1o+32x2e"),          # benchmark case 4 (1,048,576-row fully connected product)
-])
+] + _cases.UVW_TC_EXTRA_LAYOUTS)
 @pytest.mark.parametrize("Z", [1, 300, 5000])
 def test_uvw_tensor_core(layout, Z):
     torch.manual_seed(Z)
