@@ -177,7 +177,7 @@ class Group:
 
 
 def _plan_group(spec: TPSpec, members: List[Member]) -> Optional[Group]:
-    """Blocks, jobs and tensor-memory regions of a group, or None when it does not fit."""
+    """Blocks, jobs and tensor-memory slots of a group, or None when it does not fit."""
     live = spec.live_instructions()
     o1, o2 = spec.irreps_in1.offsets(), spec.irreps_in2.offsets()
     woffs = spec.weight_offsets()
@@ -394,12 +394,11 @@ def emit_module(spec: TPSpec) -> str:
 
     consts, funcs = [], []
     for gi, g in enumerate(groups):
-        nj, nb = len(g.jobs), len(g.blocks)
+        nb = len(g.blocks)
         paths = [(b, p) for b in g.blocks for p in b.paths]
         npth = len(paths)
         arr = lambda name, vals: f"__constant__ int {name}{gi}[{len(vals)}] = {{{', '.join(str(v) for v in vals)}}};"
         consts.append("\n".join([
-            # per job
             # per block (producers)
             arr("kBXoff", [b.off1 for b in g.blocks]),
             arr("kBD1", [b.d1 for b in g.blocks]),
