@@ -121,7 +121,8 @@ def build_layout_module(kind: str, key: str, source: str, force: bool = False, e
     generate_sh_header()
     with _build_lock(f"{kind}_{key}"):
         same = os.path.exists(cu) and open(cu).read() == source
-        if same and os.path.exists(so) and not force and _newer(so, [cu, os.path.join(CSRC, "layout_common.cuh")]):
+        headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith(".cuh")]     # every header a module may include
+        if same and os.path.exists(so) and not force and _newer(so, [cu] + headers):
             return so
         nvcc = nvcc_path()
         if nvcc is None:

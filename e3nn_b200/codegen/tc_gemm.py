@@ -42,6 +42,7 @@ A_TILE = 128 * 128          # one 128 x 32 fp32 sub-tile
 Y_BYTES = 8192
 EPI_BYTES = 4 * 32 * 64 * 4   # 4 epilogue warps x (32 rows x 64 columns) fp32
 PRODUCER_WARPS = 8          # default; GemmSpec.producer_warps selects 8 or 16 per module
+SWAP_DIMS = (3, 5)          # 2l+1 for which the transposed Linear runs with swapped operands (see Group.swap)
 PIECES = 2                  # tf32 pieces the stages have room for (hi, lo); 3 is supported by the code below
 
 
@@ -83,6 +84,10 @@ class Group:
     # and twice the accumulator columns, pays for long contractions (the epilogue reads twice the columns); measured
     # neutral on the Linear groups (N = 64, K = 256-448: 3.05 against 3.07 ms), so only the transposed dense layer uses it
     wide_b: bool = False
+    # Operands swapped in the MMA (rows of the accumulator = output channels, columns = the (z, k) rows of the
+    # produced tile): a warp then stores one component of 32 consecutive channels of ONE row z per instruction
+    # instead of touching 32 / (2l+1) rows.  For 2l+1 > 1 groups of transposed Linears whose width is a multiple of 128.
+    swap: bool = False
 
     def resident_bytes(self) -> int:
         """Bytes of the prepared B operand when all of it stays in shared memory for the life of the CTA:
@@ -244,6 +249,7 @@ def linear_gemm_spec(irreps_in: Irreps, irreps_out: Irreps, instructions, transp
     for g in out:
         g.has_y = False
         g.aligned_out = dst.dim % 4 == 0 and g.out_off % 4 == 0
+        g.swap = transpose and g.dim in SWAP_DIMS and g.n % 128 == 0 and not g.staged_epilogue()
     if any(g.nstage() < 2 for g in out):
         return None
     zero = [(do[i], mul * ir.dim) for i, (mul, ir) in enumerate(dst) if i not in groups and mul * ir.dim > 0]
@@ -635,6 +641,35 @@ for (int q = 0; q < {qn}; ++q) {{{{
                 }}}}
                 __syncwarp();
             }}}}""".replace("{{", "{").replace("}}", "}")
+        elif g.swap:
+            ncol = g.zt * g.dim          # live columns: the (z, k) rows of the produced tile
+            blocks = []
+            for c0 in range(0, ncol, 16):
+                st = []
+                for j in range(min(16, ncol - c0)):
+                    zq, kq = divmod(c0 + j, g.dim)
+                    st.append(f"                    if (z0 + {zq} < Z) orow_n[{zq}ll * {dout} + {kq}] = __uint_as_float(ra[{j}]);")
+                blocks.append("\n".join([
+                    "                {",
+                    f"                    tc::tmem_ld16(tb + {c0}, ra);",
+                    "                    if (nparts == 1) tc::tmem_ld_wait();",
+                    "                    for (int p = 1; p < nparts; ++p) {",
+                    f"                        tc::tmem_ld16(tb + part_off(p) + {c0}, rb);",
+                    "                        tc::tmem_ld_wait();",
+                    "#pragma unroll",
+                    "                        for (int j = 0; j < 16; ++j) ra[j] = __float_as_uint(__uint_as_float(ra[j]) + __uint_as_float(rb[j]));",
+                    "                    }",
+                ] + st + ["                }"]))
+            EPILOGUE = "\n".join([
+                "            // swapped accumulator: lane = output channel n of this 128-channel tile, columns = (z, k) rows of the",
+                "            // produced tile; for a fixed column the warp writes component k of 32 consecutive channels of row z",
+                "            uint32_t ra[16], rb[16];",
+                "            const int64_t z0 = t * ZT;",
+                "            for (int m = 0; m < N / 128; ++m) {",
+                "                const int n = m * 128 + warp * 32 + lane;",
+                f"                float* orow_n = out + z0 * {dout} + OUT_OFF + n * DIM;",
+                "                const uint32_t tb = tbase + m * 128;",
+            ] + blocks + ["            }"])
         else:
             EPILOGUE = f"""            // 16 columns per tcgen05.ld; the next load is in flight while the previous block is stored
             // (a register block is only read after the wait that follows its load)
@@ -692,6 +727,8 @@ __device__ __forceinline__ void run_group_{gi}(const float* __restrict__ x1, con
     constexpr uint32_t RESIDENT_BYTES = {g.resident_bytes()};   // > 0: the whole prepared B stays in shared memory
     constexpr uint32_t IDESC = tc::idesc_tf32_m128(N);
     constexpr uint32_t IDESC_WIDE = tc::idesc_tf32_m128(WIDE ? 2 * N : N);
+    constexpr bool SWAP = {'true' if g.swap else 'false'};      // operands swapped: accumulator rows = output channels, columns = tile rows
+    constexpr uint32_t IDESC_SWAP = tc::idesc_tf32_m128(128);
     // the epilogue sums `nparts` column blocks of width N: the partial accumulators, and in the two-MMA split
     // mode the two halves of each
     const int nsub = (WIDE && pieces == 2) ? 2 : 1;
@@ -785,6 +822,16 @@ __device__ __forceinline__ void run_group_{gi}(const float* __restrict__ x1, con
                 const uint64_t adesc = tc::smem_desc_k_sw128(tc::smem_u32(sS + s * STAGE_BYTES));
                 const uint64_t bdesc = RESIDENT_BYTES > 0 ? bdesc_resident + static_cast<uint64_t>(c) * (({PIECES} * B_HALF) >> 4)
                                                           : adesc + (({PIECES} * A_TILE) >> 4);
+                if constexpr (SWAP) {{
+                    // M = 128 output channels of the weights, N = the 128 rows of the produced tile
+#pragma unroll
+                    for (int m = 0; m < N / 128; ++m) {{
+                        const uint64_t wdesc = bdesc + static_cast<uint64_t>((m * 128 * 128) >> 4);
+                        if (pieces == 1) tc::issue_chunk<1, 128, NACC, B_HALF, A_TILE, ACCW>(d_base + m * 128, wdesc, adesc, IDESC_SWAP, c > 0);
+                        else if (pieces == 2) tc::issue_chunk<2, 128, NACC, B_HALF, A_TILE, ACCW>(d_base + m * 128, wdesc, adesc, IDESC_SWAP, c > 0);
+                        else tc::issue_chunk<3, 128, NACC, B_HALF, A_TILE, ACCW>(d_base + m * 128, wdesc, adesc, IDESC_SWAP, c > 0);
+                    }}
+                }} else
                 if (pieces == 1) tc::issue_chunk<1, N, NACC, A_TILE, B_HALF, ACCW>(d_base, adesc, bdesc, IDESC, c > 0);
                 else if (WIDE && pieces == 2) tc::issue_chunk_wide<N, NACC, A_TILE, B_HALF>(d_base, adesc, bdesc, IDESC, IDESC_WIDE, c > 0);
                 else if (pieces == 2) tc::issue_chunk<2, N, NACC, A_TILE, B_HALF, ACCW>(d_base, adesc, bdesc, IDESC, c > 0);
