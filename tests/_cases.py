@@ -55,6 +55,8 @@ def prebuild():
     pb._build_linear(o3.Linear("64x0e+64x1o+64x2e+64x3o", "256x0e+64x1o+64x2e+64x3o", math_mode="tf32x3"))   # Linear -> Gate
     pb._build_linear(o3.Linear("16x0e+8x1o+4x2e", "8x0e+8x1o+4x2e"))
     pb._build_linear(o3.Linear("64x0e+32x1o+32x2e", "32x0e+64x1o+32x2e"))
+    for mode in ("fp32", "tf32x3", "tf32"):
+        pb._build_linear(o3.Linear("128x0e+128x1o+256x2e+128x3o", "64x0e+64x1o+32x2e+32x3o", math_mode=mode))
     pb._build_tp(o3.ElementwiseTensorProduct("4x0e+3x1o+2x2e+5x1e", "4x0e+3x1o+2x1o+5x2e"))
     pb._build_tp(o3.ElementwiseTensorProduct("5x1o+5x1e", "10x1e", ["0e", "0o"]))
     pb._build_tp(o3.FullTensorProduct("2x0e+3x1o+1x2e", "2x0e+2x1o+1x1e"))

@@ -855,10 +855,16 @@ def test_uvw_tensor_core_split_operands(Z):
         assert rel_err(tp32(x.to(DEV), y.to(DEV)).cpu(), ref) < TOL   # strict fp32 mode: CUDA-core kernel
 
 
-@pytest.mark.parametrize("irreps", [("64x0e+32x1o+32x2e", "32x0e+64x1o+32x2e"), ("128x0e+64x1o+32x2e", "128x0e+64x1o+32x2e")])
-def test_linear_math_modes_forward_and_transpose(irreps):
+@pytest.mark.parametrize("irreps,Z", [
+    (("64x0e+32x1o+32x2e", "32x0e+64x1o+32x2e"), 1000),
+    (("128x0e+64x1o+32x2e", "128x0e+64x1o+32x2e"), 1000),
+    # input blocks 128 and 256 channels wide with 2l+1 = 3 and 5: the transposed contraction runs with swapped operands
+    (("128x0e+128x1o+256x2e+128x3o", "64x0e+64x1o+32x2e+32x3o"), 1000),
+    (("128x0e+128x1o+256x2e+128x3o", "64x0e+64x1o+32x2e+32x3o"), 43),
+    (("128x0e+128x1o+256x2e+128x3o", "64x0e+64x1o+32x2e+32x3o"), 1),
+])
+def test_linear_math_modes_forward_and_transpose(irreps, Z):
     torch.manual_seed(5)
-    Z = 1000
     x = torch.randn(Z, o3.Irreps(irreps[0]).dim)
     ref_lin = o3.Linear(*irreps).to(DEV)
     ref_lin.weight.requires_grad_(False)
