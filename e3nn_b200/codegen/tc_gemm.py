@@ -102,7 +102,7 @@ class Group:
 
     def staged_epilogue(self) -> bool:
         """dim == 1 groups transpose their output through shared memory for fully coalesced stores."""
-        return self.dim == 1 and self.n % 64 == 0 and self.aligned_out
+        return self.dim == 1 and self.n % 64 == 0 and self.aligned_out and not self.swap
 
     def extra_bytes(self) -> int:
         return (Y_BYTES if self.has_y else 0) + (EPI_BYTES if self.staged_epilogue() else 0)
@@ -1030,6 +1030,7 @@ extern "C" int e3b_tc_gemm_fwd_gate(const float* x1, const float* weight, const 
                                     void* scratch, int32_t* status, void* stream) {{
     if (Z == 0) return 0;
     if ({d2} > 0) return e3b_layout_fail(-3, "tc_gemm_fwd_gate: only layouts without a second operand (Linear)");
+    if ({'true' if any(g.swap for g in gs.groups) else 'false'}) return e3b_layout_fail(-3, "tc_gemm_fwd_gate: this module has groups with swapped operands, which have no gate epilogue");
     if (int rc = tc_gemm_check_args(x1, nullptr, weight, out, Z, precision, scratch, status)) return rc;
     if (!gate_table || !gate_const || (n_slots > 0 && !gates) || n_slots < 0 || dout_final <= 0)
         return e3b_layout_fail(-1, "tc_gemm_fwd_gate: bad gate arguments");
