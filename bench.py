@@ -677,6 +677,9 @@ def run_interaction(args, rank, world, device):
     pos_d = pos_host.to(device)
     x_full = torch.empty(n_atoms, 1024, device=device) if world > 1 else x_local
     tp = block.tp
+    if world > 1:
+        # the feature all-gather overlaps the radial layer: that layer's persistent kernel leaves the collective's SMs alone
+        block.overlap_reserved_sms = sharding.OVERLAP_SMS
 
     def forward(p, xs, before_conv=None, phase_mark=None):
         # the block's own forward: global indices into the (replicated) positions and the gathered features,

@@ -10,7 +10,7 @@ import ctypes
 import os
 import threading
 from ctypes import POINTER, c_char_p, c_double, c_float, c_int, c_int32, c_int64, c_void_p
-from typing import Dict, Optional
+from typing import Dict, List, Optional
 
 import torch
 
@@ -345,6 +345,7 @@ class TcGemmModule:
         lib.e3b_tc_gemm_fwd_gate.restype = c_int
         self.key = lib.e3b_layout_key().decode()
         self.scratch_bytes = int(lib.e3b_tc_gemm_scratch_bytes())
+        self.group_work: List[int] = []         # relative cost of a row tile per group (set by tc_gemm_module)
         self._scratch: Dict[str, torch.Tensor] = {}
 
     def check(self, rc: int, what: str) -> None:
@@ -356,9 +357,21 @@ class TcGemmModule:
         # prepared weights live in a per-stream-ordered scratch tensor owned by the caller side (here)
         scratch = torch.empty(max(self.scratch_bytes, 16), dtype=torch.uint8, device=dev)
         poll_status(dev)
+        split = None
+        if _tc_gemm_max_ctas is not None and self.group_work:
+            # CTAs per group in proportion to the groups' work, at least one each, max_ctas in total
+            total, limit = sum(self.group_work), max(int(_tc_gemm_max_ctas), len(self.group_work))
+            n = [max(1, limit * wk // total) for wk in self.group_work]
+            g = len(n) - 1
+            while sum(n) < limit:
+                n[g] += 1
+                g = (g - 1) % len(n)
+            while sum(n) > limit and max(n) > 1:
+                n[n.index(max(n))] -= 1
+            split = (ctypes.c_int * len(n))(*n)
         with torch.cuda.device(dev), nvtx_range("e3b_tc_gemm_fwd " + self.key):
             rc = self.lib.e3b_tc_gemm_fwd(_ptr(x1), _ptr(x2), _ptr(weight), _ptr(out), x1.shape[0], precision,
-                                          _ptr(scratch), None, _ptr(status_word(dev)), stream_ptr())
+                                          _ptr(scratch), split, _ptr(status_word(dev)), stream_ptr())
         self.check(rc, "e3b_tc_gemm_fwd")
         status_after_launch(dev)
         return out
@@ -379,6 +392,22 @@ class TcGemmModule:
 
 
 _tcg_cache: Dict[str, "TcGemmModule"] = {}
+_tc_gemm_max_ctas: Optional[int] = None
+
+
+@contextlib.contextmanager
+def tc_gemm_cta_limit(max_ctas: Optional[int]):
+    """Inside the block the persistent tensor-core contractions launch at most ``max_ctas`` CTAs (one per SM), leaving
+    the other SMs to a kernel that runs at the same time.  These kernels split their row tiles statically over their
+    CTAs and take a whole SM each; when a collective's kernel already holds some SMs, the CTAs that cannot start
+    until it ends hold the whole launch back by its duration, which costs more than giving up those SMs."""
+    global _tc_gemm_max_ctas
+    old = _tc_gemm_max_ctas
+    _tc_gemm_max_ctas = max_ctas
+    try:
+        yield
+    finally:
+        _tc_gemm_max_ctas = old
 
 
 def tc_gemm_module(gemm_spec) -> TcGemmModule:
@@ -394,5 +423,6 @@ def tc_gemm_module(gemm_spec) -> TcGemmModule:
     mod = TcGemmModule(so)
     if mod.key != key:
         raise E3BError(f"layout module {so} was built for another layout ({mod.key} != {key})")
+    mod.group_work = [g.work() for g in gemm_spec.groups]
     _tcg_cache[key] = mod
     return mod

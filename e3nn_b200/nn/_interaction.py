@@ -18,7 +18,7 @@ from typing import Optional, Tuple
 
 import torch
 
-from .. import layouts
+from .. import _lib, layouts
 from ..message_passing import conv_uvu
 from ..o3 import Irreps, Linear
 from ._edge_embed import edge_embed
@@ -110,6 +110,8 @@ class InteractionBlock(torch.nn.Module):
                                     math_mode=radial_math_mode)
         self.lin = Linear(self.tp.irreps_out, self.irreps_out, math_mode=linear_math_mode)
         self.num_basis, self.r_max, self.num_neighbors = num_basis, r_max, num_neighbors
+        # SMs the radial layer leaves free while a feature transfer overlaps it (forward(before_conv=...)); 0: none
+        self.overlap_reserved_sms = 0
 
     def edge_weights(self, edge_vec: torch.Tensor) -> torch.Tensor:
         # the basis sin(k pi r / c) / r is evaluated in fp64 (8 values per edge, negligible cost): in fp32
@@ -137,7 +139,10 @@ class InteractionBlock(torch.nn.Module):
             act = getattr(layer0.act, "__name__", None) if layer0.act is not None else None
             edge_vec, h = edge_embed(pos, edge_src, edge_dst, shift, layer0.weight, self.r_max, layer0._scale(),
                                      layer0.cst * layer0.var_out ** 0.5, act)
-            w = self.fc.layer1(h)
+            # a transfer in flight (before_conv is its wait) runs a kernel of its own: leave it some SMs
+            limit = 148 - self.overlap_reserved_sms if (before_conv is not None and self.overlap_reserved_sms > 0) else None
+            with _lib.tc_gemm_cta_limit(limit):
+                w = self.fc.layer1(h)
         else:
             edge_vec = pos[edge_src] - pos[edge_dst]
             if shift is not None:

@@ -18,14 +18,26 @@ import torch
 import torch.distributed as dist
 
 
+# SMs a collective's kernel may occupy, and the same number the persistent kernel that overlaps it leaves free
+# (``InteractionBlock.overlap_reserved_sms``).  Measured on 4 GPUs (262,144 atoms, radial layer under the feature
+# all-gather): no limit 19.15 ms per step, 16 SMs 18.39 (the gather then ends 0.5 ms after the layer), 24 SMs 17.98,
+# 32 SMs 17.94.
+OVERLAP_SMS = int(os.environ.get("E3NN_B200_OVERLAP_SMS", "24"))      # 0: no limit on either side
+
+
 def init_process_group(backend: str, device: Optional[torch.device] = None, timeout_s: float = 120.0, **kwargs) -> None:
     """``torch.distributed.init_process_group`` with the failure behaviour this package relies on: every collective
     carries a timeout (`timeout_s`), and with NCCL a collective that times out or fails asynchronously (a peer that
     died between steps) is turned into an exception in the waiting rank instead of a hang: the communicator's
     watchdog polls for asynchronous errors and aborts the communicator (``TORCH_NCCL_ASYNC_ERROR_HANDLING``, set
-    here unless the caller chose a value).  Rendezvous settings come from the environment as usual."""
+    here unless the caller chose a value).  NCCL's kernels are limited to ``OVERLAP_SMS`` CTAs (``NCCL_MAX_CTAS``,
+    unless the caller chose a value): the collectives of a step run UNDER compute kernels that own whole SMs, and a
+    collective spread over more SMs than those kernels leave free delays them by its whole duration.  Rendezvous
+    settings come from the environment as usual."""
     if backend == "nccl":
         os.environ.setdefault("TORCH_NCCL_ASYNC_ERROR_HANDLING", "1")
+        if OVERLAP_SMS > 0:
+            os.environ.setdefault("NCCL_MAX_CTAS", str(OVERLAP_SMS))
         if device is not None:
             kwargs.setdefault("device_id", device)
     dist.init_process_group(backend, timeout=datetime.timedelta(seconds=timeout_s), **kwargs)
