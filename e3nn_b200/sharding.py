@@ -44,7 +44,8 @@ def init_process_group(backend: str, device: Optional[torch.device] = None, time
 
 
 def partition_rows_by_edges(rowptr: torch.Tensor, world: int) -> List[int]:
-    """Row boundaries ``b[0]=0 <= ... <= b[world]=N`` with ~E/world edges per part.
+    """Row boundaries ``b[0]=0 <= ... <= b[world]=N`` with ~E/world edges per part (equal row counts when those
+    balance the edges to within 1 %).
 
     ``b[r]`` is the smallest row whose first edge slot is >= r*E/world, the same rule the fused
     kernel uses to split rows over its warp teams."""
@@ -52,6 +53,14 @@ def partition_rows_by_edges(rowptr: torch.Tensor, world: int) -> List[int]:
     rp = rowptr.detach().cpu()
     n = rp.numel() - 1
     e = int(rp[-1])
+    if world > 1 and n % world == 0 and e > 0:
+        # Equal row counts let the feature all-gather run as ONE all_gather_into_tensor instead of a group of
+        # broadcasts of unequal slices; taken when the edge counts then stay within 1 % of the balanced split
+        # (a system of uniform density).
+        rows = n // world
+        most = max(int(rp[(r + 1) * rows]) - int(rp[r * rows]) for r in range(world))
+        if most * world <= 1.01 * e:
+            return [r * rows for r in range(world + 1)]
     targets = torch.tensor([(e * r) // world for r in range(1, world)], dtype=rp.dtype)
     inner = torch.searchsorted(rp[:-1].contiguous(), targets, right=False).tolist() if world > 1 else []
     bounds = [0] + [min(int(v), n) for v in inner] + [n]
