@@ -695,7 +695,7 @@ def run_interaction(args, rank, world, device):
             _, wait = sharding.all_gather_rows(x_local, bounds, out=x_full, async_op=True)
         p = p_in.detach().requires_grad_(True)
         out = forward(p, x_full, wait, phase_mark)
-        loss = (out * G).sum()
+        loss = torch.dot(out.reshape(-1), G.reshape(-1))      # sum(out * G) without materialising the product
         mark("loss")
         loss.backward()
         mark("bwd_embed")
@@ -764,7 +764,7 @@ def run_interaction(args, rank, world, device):
 
         def step32():
             p = pos_d.detach().requires_grad_(True)
-            (block32(p, x_full, src_d, dst_glob, rowptr, shift_d) * G).sum().backward()
+            torch.dot(block32(p, x_full, src_d, dst_glob, rowptr, shift_d).reshape(-1), G.reshape(-1)).backward()
             return p.grad
 
         step32()
@@ -855,7 +855,7 @@ def run_interaction(args, rank, world, device):
                     gather_wait()
 
             p = pos_up.requires_grad_(True)
-            (block(p, xs, s_loc, d_loc, rp_loc, sh_loc, before_conv=wait) * G).sum().backward()
+            torch.dot(block(p, xs, s_loc, d_loc, rp_loc, sh_loc, before_conv=wait).reshape(-1), G.reshape(-1)).backward()
             if world > 1:
                 torch.distributed.all_reduce(p.grad)
             grad_host.copy_(p.grad, non_blocking=True)
