@@ -359,15 +359,7 @@ class TcGemmModule:
         poll_status(dev)
         split = None
         if _tc_gemm_max_ctas is not None and self.group_work:
-            # CTAs per group in proportion to the groups' work, at least one each, max_ctas in total
-            total, limit = sum(self.group_work), max(int(_tc_gemm_max_ctas), len(self.group_work))
-            n = [max(1, limit * wk // total) for wk in self.group_work]
-            g = len(n) - 1
-            while sum(n) < limit:
-                n[g] += 1
-                g = (g - 1) % len(n)
-            while sum(n) > limit and max(n) > 1:
-                n[n.index(max(n))] -= 1
+            n = cta_split(self.group_work, int(_tc_gemm_max_ctas))
             split = (ctypes.c_int * len(n))(*n)
         with torch.cuda.device(dev), nvtx_range("e3b_tc_gemm_fwd " + self.key):
             rc = self.lib.e3b_tc_gemm_fwd(_ptr(x1), _ptr(x2), _ptr(weight), _ptr(out), x1.shape[0], precision,
@@ -393,6 +385,19 @@ class TcGemmModule:
 
 _tcg_cache: Dict[str, "TcGemmModule"] = {}
 _tc_gemm_max_ctas: Optional[int] = None
+
+
+def cta_split(work: List[int], max_ctas: int) -> List[int]:
+    """CTAs per group in proportion to the groups' work: at least one each, ``max(max_ctas, len(work))`` in total."""
+    total, limit = sum(work), max(max_ctas, len(work))
+    n = [max(1, limit * wk // total) for wk in work]
+    g = len(n) - 1
+    while sum(n) < limit:
+        n[g] += 1
+        g = (g - 1) % len(n)
+    while sum(n) > limit and max(n) > 1:
+        n[n.index(max(n))] -= 1
+    return n
 
 
 @contextlib.contextmanager

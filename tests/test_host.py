@@ -255,3 +255,21 @@ def test_tensor_square_layout(golden_meta, name):
     assert np.allclose([i.path_weight for i in sq.instructions], [i[5] for i in m["instructions"]], rtol=1e-14)
     with pytest.raises(ValueError):
         o3.TensorSquare("2x1o", "3x0e", filter_ir_out=["0e"])
+
+
+def test_cta_split_is_proportional_and_bounded():
+    """CTA counts the persistent contraction kernels get when another kernel keeps some SMs (_lib.tc_gemm_cta_limit)."""
+    from e3nn_b200 import _lib
+
+    work = [3000, 1000, 1000, 500, 10]
+    for limit in (148, 124, 5, 3):
+        n = _lib.cta_split(work, limit)
+        assert len(n) == len(work) and min(n) >= 1 and sum(n) == max(limit, len(work))
+    n = _lib.cta_split(work, 124)
+    assert n[0] > n[1] >= n[3] >= n[4] and abs(n[0] - 124 * 3000 / sum(work)) <= 3
+    with _lib.tc_gemm_cta_limit(100):
+        assert _lib._tc_gemm_max_ctas == 100
+        with _lib.tc_gemm_cta_limit(None):
+            assert _lib._tc_gemm_max_ctas is None
+        assert _lib._tc_gemm_max_ctas == 100
+    assert _lib._tc_gemm_max_ctas is None

@@ -87,6 +87,22 @@ def test_partition_edge_cases():
     assert sharding.partition_rows_by_edges(torch.tensor([0]), 4) == [0, 0, 0, 0, 0]
 
 
+def test_partition_prefers_equal_rows_when_edges_balance():
+    # uniform degrees: equal row counts (one all_gather_into_tensor instead of a group of unequal broadcasts)
+    deg = torch.full((64,), 10)
+    deg[::7] += 1                                   # within 1 % of balance per part
+    rowptr = torch.cat([torch.zeros(1, dtype=torch.int64), torch.cumsum(deg, 0)])
+    assert sharding.partition_rows_by_edges(rowptr, 4) == [0, 16, 32, 48, 64]
+    # a skewed graph keeps the split by edges
+    deg = torch.ones(64, dtype=torch.int64)
+    deg[:8] = 100
+    rowptr = torch.cat([torch.zeros(1, dtype=torch.int64), torch.cumsum(deg, 0)])
+    b = sharding.partition_rows_by_edges(rowptr, 4)
+    assert b != [0, 16, 32, 48, 64] and b[0] == 0 and b[-1] == 64 and b == sorted(b)
+    parts = [int(rowptr[b[r + 1]] - rowptr[b[r]]) for r in range(4)]
+    assert max(parts) <= 2 * int(rowptr[-1]) // 4
+
+
 def _timeout_worker(rank, world, port, out_dir):
     """Rank 1 leaves between steps (it never joins the second collective); rank 0's collective must end with an
     error after the process-group timeout instead of waiting for ever."""
