@@ -33,7 +33,8 @@ long long e3b_tc_gemm_scratch_bytes(void);
  * of the reference module (instruction order, each path [u, w] row-major), out [Z, dout] (16-byte
  * aligned).  precision: 1 = plain tf32 operands (one MMA per k-step, ~1e-3 relative), 2 = hi/lo-split
  * operands (three MMAs, ~2e-5 x RMS).  scratch: e3b_tc_gemm_scratch_bytes() bytes, 16-byte aligned.
- * cta_split: NULL, or a host array with the number of CTAs per output group.  status: one device int32
+ * cta_split: NULL, or a host array with the number of CTAs per output group (a caller that overlaps the launch with
+ * a collective passes fewer than one CTA per SM in total, see e3nn_b200/_lib.py: tc_gemm_cta_limit).  status: one device int32
  * zeroed by the caller; 3 = a bounded wait inside the kernel gave up (results invalid).
  */
 int e3b_tc_gemm_fwd(const float* x1, const float* x2, const float* weight, float* out, int64_t Z, int precision,
@@ -53,7 +54,10 @@ int e3b_tc_gemm_fwd_gate(const float* x1, const float* weight, const int32_t* ga
 
 /*
  * 'uvw' tensor product with plain tf32 operands: x1 [Z, d1], x2 [Z, d2], weight [weight_numel] shared,
- * out [Z, dout].  num_ctas: 0 = one per SM.  status as above.
+ * out [Z, dout].  num_ctas: 0 = one per SM.  status as above.  x1 and out 16-byte aligned (row lengths of
+ * "uvwpost" modules are multiples of four floats), Z < 2^31: blocks of scalars of x1 are fetched through a tensor
+ * map that the call encodes on the host (cuTensorMapEncodeTiled, reached through the runtime's entry-point query).
+ * Returns -2 when the driver does not provide that entry point.
  */
 int e3b_uvw_tc_fwd(const float* x1, const float* x2, const float* weight, float* out, int64_t Z, int num_ctas,
                    int32_t* status, void* stream);
