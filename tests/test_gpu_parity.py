@@ -74,7 +74,7 @@ def test_sh_oracle_and_backward(lmax):
             assert torch.all(v.grad == 0)
             continue
         ref.backward(g.double())
-        assert rel_err(v.grad.cpu(), v64.grad) < (2e-5 if lmax <= 8 else 1e-4)
+        assert rel_err(v.grad.cpu(), v64.grad) < 2e-5      # measured: 7.8e-6 at lmax 12
 
 
 def test_sh_batch_shapes_and_module():
@@ -150,7 +150,7 @@ def test_tp_uvu_backward(golden, golden_meta, name):
     out.backward(go.float().to(DEV))
     assert rel_err(a.grad.cpu(), a64.grad) < TOL
     assert rel_err(b.grad.cpu(), b64.grad) < TOL
-    assert rel_err(c.grad.cpu(), c64.grad) < (5e-5 if tp.shared_weights else TOL)  # shared: float atomics over rows
+    assert rel_err(c.grad.cpu(), c64.grad) < TOL   # shared weights: float atomics over rows, measured 1.2e-6
 
 
 def test_tp_cfg1_full_batch():
@@ -300,7 +300,7 @@ def test_conv_random_layouts_forward_backward(idx):
     ref.backward(go)
     out.backward(go.float().to(DEV))
     assert rel_err(wg.grad.cpu(), w64.grad) < TOL
-    assert rel_err(vg.grad.cpu(), v64.grad) < 2e-5
+    assert rel_err(vg.grad.cpu(), v64.grad) < TOL      # measured 4.0e-6
     # node features: the transpose of the gather, accumulated with float atomics (order not fixed)
     assert rel_err(xg.grad.cpu(), x64.grad) < TOL
     # only the node features require a gradient: the weight / vector kernel is skipped
@@ -439,7 +439,7 @@ def test_conv_pipelined_kernel(layout):
     gv, gv_ref = vg.grad.cpu(), v64.grad.clone()
     gv[3] = 0.0      # the zero vector has an unbounded derivative under normalisation
     gv_ref[3] = 0.0
-    assert rel_err(gv, gv_ref) < 3e-5
+    assert rel_err(gv, gv_ref) < TOL       # measured 4.0e-6
     bad = src.clone()
     bad[10] = N + 5
     with pytest.raises(IndexError):
@@ -505,8 +505,9 @@ def test_interaction_block_forward_and_position_gradient(irreps, lmax):
     p2 = pos.clone().to(DEV).requires_grad_(True)
     out2 = fast(p2, node_x.to(DEV), src.to(DEV), dst.to(DEV), rowptr, shift.to(DEV))
     (out2 * G.to(DEV)).sum().backward()
-    assert rel_err(out2.detach().cpu(), ref.detach()) < 1e-4
-    assert rel_err(p2.grad.cpu(), p64.grad) < 1e-4
+    # hi/lo-split tf32 operands (the benchmark's mode): measured 2.1e-5 / 2.2e-5
+    assert rel_err(out2.detach().cpu(), ref.detach()) < 5e-5
+    assert rel_err(p2.grad.cpu(), p64.grad) < 5e-5
 
 
 # ----------------------------------------------------------------------------- self-connection with node attributes
@@ -568,7 +569,7 @@ def test_two_layer_network_forward_and_gradients(mode):
     h64 = orc.gate("16x0e", ["silu"], "32x0e", ["sigmoid"], "16x1o+16x2e", oracle_block(b1, x64))
     ref = oracle_block(b2, h64)
     (ref * G.double()).sum().backward()
-    tol = 3e-5 if mode == "fp32" else 2e-4      # two blocks deep: twice the single-block budget
+    tol = 2e-5 if mode == "fp32" else 2e-4      # two blocks deep: twice the single-block budget (fp32: measured 8.4e-6, 1.4e-5)
     assert rel_err(out.detach().cpu(), ref.detach()) < tol
     assert rel_err(xg.grad.cpu(), x64.grad) < tol
     assert rel_err(p.grad.cpu(), p64.grad) < 2 * tol
@@ -831,7 +832,7 @@ def test_edge_embed_basis_families(basis, cutoff, envelope):
                             cutoff=cutoff, start=start, basis_scale=bscale, envelope=envelope)
     ((h * gh.to(DEV)).sum() + (vec * gv.to(DEV)).sum()).backward()
     assert rel_err(h.detach().cpu(), h64.detach()) < TOL
-    assert rel_err(p.grad.cpu(), p64.grad) < 2e-5
+    assert rel_err(p.grad.cpu(), p64.grad) < TOL      # measured 2.3e-6 over the nine basis / cutoff combinations
 
 
 # ----------------------------------------------------------------------------- tensor-core contractions with split operands
@@ -1157,7 +1158,7 @@ def test_tensor_product_linear_fused(layout, mode, tol):
     assert rel_err(out.detach().cpu(), ref.detach()) < tol
     assert rel_err(xg.grad.cpu(), x64.grad) < tol
     assert rel_err(yg.grad.cpu(), y64.grad) < tol
-    wtol = max(tol, 5e-5)     # weight gradients: float atomics over all rows
+    wtol = tol                # weight gradients: float atomics over all rows, measured 3.6e-6 in the fp32 case
     assert rel_err(tp.weight.grad.cpu(), w64.grad) < wtol
     assert rel_err(lin.weight.grad.cpu(), l64.grad) < wtol
     # the two modules side by side give the same result
