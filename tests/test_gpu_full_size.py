@@ -74,7 +74,7 @@ def test_conv_config3_full_size(layout, nodes, degree):
     assert rel_err(o1[rows.to(DEV)].cpu(), ref) < TOL
 
 
-@pytest.mark.parametrize("mode,tol", [("fp32", TOL), ("tf32x3", 1e-4), ("tf32", 2e-2)])
+@pytest.mark.parametrize("mode,tol", [("fp32", TOL), ("tf32x3", 3e-5), ("tf32", 2e-2)])     # measured 1.2e-6, 7.4e-6, 3.0e-3
 def test_uvw_config4_full_size(mode, tol):
     """1,048,576 rows of the fully connected product of config 4: 256 sampled rows vs the oracle, determinism."""
     Z = 1_048_576
@@ -140,4 +140,4 @@ def test_interaction_config5_full_size():
         [block.fc.layer0.weight.detach().cpu().double(), block.fc.layer1.weight.detach().cpu().double()],
         block.lin.weight.detach().cpu().double(), 8, 5.0, E / n_atoms, [0, 1, 2, 3], chunk=512)
     local = torch.searchsorted(atoms, rows)
-    assert rel_err(out.detach()[rows.to(DEV)].cpu(), ref[local]) < 1e-4
+    assert rel_err(out.detach()[rows.to(DEV)].cpu(), ref[local]) < 3e-5     # hi/lo-split tf32 Linear and radial layer: measured 8.4e-6
