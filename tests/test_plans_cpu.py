@@ -100,3 +100,100 @@ def test_linear_plan_rejects_nothing_it_accepts_in_forward():
     # empty instruction lists and zero-multiplicity irreps build (degenerate) plans
     plan, written = linear_plan(o3.Irreps("0x0e+2x1o"), o3.Irreps("3x1o"), o3.Linear("0x0e+2x1o", "3x1o").instructions)
     assert written == [0] and int(plan[4]) == 1
+
+
+# ----------------------------------------------------------------------------- planner of the post-coupling 'uvw' kernel
+UVW_POST_LAYOUTS = [
+    ("128x0e+64x1o+32x2e", "0e+1o+2e+3o", "128x0e+64x1o+32x2e"),
+    ("32x0e+32x1o+32x2e", "1x0e+1x1o+1x2e", "32x0e+32x1o+32x2e"),
+    ("64x0e+64x1o+64x2e", "0e+1o+2e", "48x0e+32x1o+16x2e"),
+    ("96x0e+32x1e+32x2e+32x3o", "0e+1o+2e+3o", "64x0e+32x1o+32x2e+16x3o"),
+    ("32x0e+32x1o", "0e+1o", "256x0e+16x1o"),
+    ("64x0e+64x1o+64x2e+64x3o", "0e", "64x0e+64x1o+64x2e+64x3o"),
+]
+
+
+def test_uvw_post_plan_covers_every_path_and_fits_the_sm():
+    from e3nn_b200 import o3
+    from e3nn_b200.codegen import uvw_post
+
+    for layout in UVW_POST_LAYOUTS:
+        tp = o3.FullyConnectedTensorProduct(*layout, math_mode="tf32")
+        groups = uvw_post.plan_groups(tp._spec)
+        assert groups is not None, layout
+        covered = {}
+        for g in groups:
+            assert g.smem_bytes() <= uvw_post.SMEM_LIMIT and g.nacc() <= uvw_post.MAX_ACC_REGS
+            assert g.nstage() >= max(b.d1 for b in g.blocks) + 1          # a chunk's component tiles fit the ring together
+            assert g.nslots * g.slot_cols <= uvw_post.TMEM_COLS
+            for b in g.blocks:
+                assert b.ncols <= uvw_post.MAX_N and b.ncols % 16 == 0
+                col = 0
+                for p in b.paths:                                          # the paths of a block lie side by side
+                    m = g.members[p.member]
+                    assert p.coloff == col
+                    col += m.width
+                    covered.setdefault(p.index, []).append((m.col0, m.width))
+                assert col == b.ncols
+            for j in g.jobs:
+                assert 0 <= j.slot0 and j.slot0 + j.nslot <= g.nslots
+                assert j.cols(g.blocks) <= j.nslot * g.slot_cols
+            # every stage the producers emit is consumed by exactly one job, in the producers' order
+            assert sum(len(j.comps) * j.nchunk for j in g.jobs) == g.tiles_per_row_tile()
+        # every live path: all of its output channels, once
+        for n, ins in tp._spec.live_instructions():
+            mul_o = tp._spec.irreps_out[ins.i_out].mul
+            slabs = sorted(covered[n])
+            assert slabs[0][0] == 0 and sum(w for _, w in slabs) == mul_o
+            assert all(a[0] + a[1] == b[0] for a, b in zip(slabs, slabs[1:]))
+
+
+def test_uvw_post_slot_schedule_is_safe():
+    """The issuing thread may overwrite a tensor-memory slot only after the epilogue has read the job that held it,
+    and it learns that from mbarrier phases (one bit): replay the static schedule over several row tiles and check
+    that (a) every job's slots are free of unread accumulators once its waits are done, and (b) the completions of
+    every barrier are observed one by one, in order, before the next job that arrives on that barrier is issued."""
+    from e3nn_b200 import o3
+    from e3nn_b200.codegen import uvw_post
+
+    for layout in UVW_POST_LAYOUTS:
+        tp = o3.FullyConnectedTensorProduct(*layout, math_mode="tf32")
+        for g in uvw_post.plan_groups(tp._spec):
+            holder = [None] * g.nslots              # (tile, job) whose accumulators a slot holds, None once observed as read
+            observed = [0] * g.nslots               # completions of empty[b] the issuing thread has seen
+            produced = [0] * g.nslots               # jobs issued so far whose first slot is b (= arrivals the barrier will get)
+            for tile in range(4):
+                for ji, j in enumerate(g.jobs):
+                    for bar, idx, prev in j.waits:
+                        if prev and tile == 0:
+                            continue                # nothing ran before the first tile
+                        t = tile - 1 if prev else tile
+                        n = t * g.uses[bar] + idx   # the completion this wait is for
+                        assert n == observed[bar], (layout, tile, ji, bar)       # in order, none skipped: parity is enough
+                        assert n < produced[bar]                                    # that job has been issued
+                        observed[bar] += 1
+                        for s in range(g.nslots):   # its slots are free now
+                            if holder[s] is not None and holder[s][2] == (bar, n):
+                                holder[s] = None
+                    for s in range(j.slot0, j.slot0 + j.nslot):
+                        assert holder[s] is None, (layout, tile, ji, s, holder[s])
+                    n_mine = tile * g.uses[j.slot0] + j.use_idx
+                    assert n_mine == produced[j.slot0]                             # the epilogue's phase arithmetic
+                    assert observed[j.slot0] == produced[j.slot0]                  # no unobserved completion on my barrier
+                    produced[j.slot0] += 1
+                    for s in range(j.slot0, j.slot0 + j.nslot):
+                        holder[s] = (tile, ji, (j.slot0, n_mine))
+
+
+def test_transposed_linear_swaps_operands_only_where_it_pays():
+    """Groups of a transposed Linear run with swapped MMA operands when 2l+1 is 3 or 5 and the group is a whole number
+    of 128-channel MMA tiles; forward Linears, scalars and 2l+1 = 7 keep the row order."""
+    from e3nn_b200 import o3
+
+    lin = o3.Linear("128x0e+128x1o+256x2e+128x3o", "64x0e+64x1o+32x2e+32x3o", math_mode="tf32x3")
+    assert [(g.n, g.dim, g.swap) for g in lin._tc_bwd.groups] == [(128, 1, False), (128, 3, True), (256, 5, True), (128, 7, False)]
+    assert not any(g.swap for g in lin._tc_fwd.groups)
+    small = o3.Linear("64x0e+64x1o", "64x0e+64x1o", math_mode="tf32x3")
+    assert not any(g.swap for g in small._tc_bwd.groups)          # 64 channels: half an MMA tile
+    for g in lin._tc_bwd.groups:
+        assert not (g.swap and g.staged_epilogue())
